@@ -1,0 +1,123 @@
+// Per-head RMSNorm of queries and keys, rotary position encoding, and the write of keys and
+// values into the request's pages.
+//
+// qkv[t] = [q heads | k heads | v heads], each head of head_dim values. One warp handles one
+// (token, head): it norms q or k over head_dim in 32-bit (if a norm weight is given), rotates
+// the first rotary_dim dimensions by position * inv_freq (pairs j and j + rotary_dim/2, the
+// non-interleaved form; angles in 32-bit), writes q to q_out[t, head, :] and k, v to
+// kv[0 or 1, page, kv_head, position % page_size, :] with page = block_table[request,
+// position / page_size].
+#include "common.cuh"
+
+namespace {
+
+constexpr int WARPS = 8;
+constexpr int MAX_HEAD_DIM = 512;
+
+template <typename T>
+__global__ void __launch_bounds__(WARPS * 32)
+qk_prep_kernel(const T* __restrict__ qkv, const float* __restrict__ q_weight,
+               const float* __restrict__ k_weight, float eps, const float* __restrict__ inv_freq,
+               int rotary_dim, const int* __restrict__ positions,
+               const int* __restrict__ token_request, T* __restrict__ q_out,
+               T* __restrict__ kv, const int* __restrict__ block_table, int table_width,
+               int page_size, long long kv_half, int tokens, int heads, int kv_heads,
+               int head_dim, int write_kv, int* __restrict__ error_flag) {
+    extern __shared__ float shared[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int slots_per_token = heads + 2 * kv_heads;
+    const long long item = (long long)blockIdx.x * WARPS + warp;
+    if (item >= (long long)tokens * slots_per_token) return;
+    const int t = (int)(item / slots_per_token);
+    const int slot = (int)(item % slots_per_token);
+    float* values = shared + warp * head_dim;
+
+    const T* src = qkv + (size_t)t * slots_per_token * head_dim + (size_t)slot * head_dim;
+    const bool is_q = slot < heads;
+    const bool is_k = !is_q && slot < heads + kv_heads;
+    if (!is_q && !write_kv) return;
+
+    float sum = 0.f;
+    for (int e = lane; e < head_dim; e += 32) {
+        const float v = to_float<T>(src[e]);
+        values[e] = v;
+        sum += v * v;
+    }
+    const int position = positions[t];
+    if (is_q || is_k) {
+        const float* weight = is_q ? q_weight : k_weight;
+        if (weight != nullptr) {
+            sum = warp_sum(sum);
+            const float inv = rsqrtf(sum / (float)head_dim + eps);
+            for (int e = lane; e < head_dim; e += 32) values[e] = values[e] * inv * weight[e];
+        }
+        __syncwarp();
+        if (inv_freq != nullptr) {
+            const int half = rotary_dim / 2;
+            for (int j = lane; j < half; j += 32) {
+                const float angle = (float)position * inv_freq[j];
+                float sine, cosine;
+                sincosf(angle, &sine, &cosine);
+                const float a = values[j], b = values[j + half];
+                values[j] = a * cosine - b * sine;
+                values[j + half] = b * cosine + a * sine;
+            }
+        }
+    }
+    __syncwarp();
+
+    T* dst;
+    if (is_q) {
+        dst = q_out + ((size_t)t * heads + slot) * head_dim;
+    } else {
+        const int kv_head = is_k ? slot - heads : slot - heads - kv_heads;
+        const int r = token_request[t];
+        const int block = position / page_size;
+        const int page = block < table_width ? block_table[(size_t)r * table_width + block] : -1;
+        if (page < 0) {
+            if (lane == 0) atomicExch(error_flag, 2);
+            return;
+        }
+        dst = kv + (is_k ? 0 : kv_half) +
+              (((size_t)page * kv_heads + kv_head) * page_size + position % page_size) * head_dim;
+    }
+    for (int e = lane; e < head_dim; e += 32) dst[e] = from_float<T>(values[e]);
+}
+
+}  // namespace
+
+MLXONE_API int mlxone_qk_prep(const void* qkv, const float* q_weight, const float* k_weight,
+                              float eps, const float* inv_freq, int rotary_dim,
+                              const int* positions, const int* token_request, void* q_out,
+                              void* kv, const int* block_table, int table_width, int page_size,
+                              int pages, int tokens, int heads, int kv_heads, int head_dim,
+                              int write_kv, int dtype, int* error_flag, cudaStream_t stream) {
+    if (tokens == 0) return 0;
+    MLXONE_REQUIRE(tokens > 0 && heads > 0 && kv_heads > 0, "qk_prep: bad sizes");
+    MLXONE_REQUIRE(head_dim >= 2 && head_dim <= MAX_HEAD_DIM,
+                   "qk_prep: head size %d is not in 2..%d", head_dim, MAX_HEAD_DIM);
+    MLXONE_REQUIRE(inv_freq == nullptr ||
+                       (rotary_dim > 0 && rotary_dim % 2 == 0 && rotary_dim <= head_dim),
+                   "qk_prep: rotary size %d must be even and at most the head size %d", rotary_dim,
+                   head_dim);
+    MLXONE_REQUIRE(page_size > 0 && pages > 0 && table_width > 0, "qk_prep: bad page geometry");
+    const long long items = (long long)tokens * (heads + 2 * kv_heads);
+    const int blocks = ceil_div_host(items, WARPS);
+    const size_t shared = (size_t)WARPS * head_dim * sizeof(float);
+    const long long kv_half = (long long)pages * kv_heads * page_size * head_dim;
+    if (dtype == MLXONE_BF16) {
+        using T = __nv_bfloat16;
+        qk_prep_kernel<T><<<blocks, WARPS * 32, shared, stream>>>(
+            (const T*)qkv, q_weight, k_weight, eps, inv_freq, rotary_dim, positions,
+            token_request, (T*)q_out, (T*)kv, block_table, table_width, page_size, kv_half,
+            tokens, heads, kv_heads, head_dim, write_kv, error_flag);
+    } else {
+        using T = float;
+        qk_prep_kernel<T><<<blocks, WARPS * 32, shared, stream>>>(
+            (const T*)qkv, q_weight, k_weight, eps, inv_freq, rotary_dim, positions,
+            token_request, (T*)q_out, (T*)kv, block_table, table_width, page_size, kv_half,
+            tokens, heads, kv_heads, head_dim, write_kv, error_flag);
+    }
+    MLXONE_LAUNCH_CHECK("qk_prep");
+    return 0;
+}

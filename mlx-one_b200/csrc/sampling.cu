@@ -1,0 +1,269 @@
+// Token selection from 32-bit logits: argmax, and temperature sampling with top-k and
+// top-p truncation and a counter-based random number per (seed, step).
+//
+// The truncation rule is the reference's (src/mlx_one/text/sampling.py:56-88): probabilities
+// p = softmax(logits / T); rank by descending p with ties in token order; keep the first
+// top_k; of those keep the shortest prefix whose mass reaches top_p * (kept mass). The kept
+// set is found without sorting: the k-th largest probability and the top-p boundary are
+// located by bisection over the bit patterns of the non-negative floats, and ties at a
+// boundary are admitted in token order. The draw then walks the kept tokens in token order
+// (the reference walks them in rank order; both draw from the same distribution):
+// u = uniform(seed, step) * kept mass, the first kept token whose running mass reaches u.
+//
+// uniform(seed, step) is a splitmix64 hash of seed * 0x9E3779B97F4A7C15 + (step + 1) *
+// 0xBF58476D1CE4E5B9, top 24 bits / 2^24, so a request's draws do not depend on what else is
+// in the batch.
+//
+// Scratch: `probabilities` [rows, vocab] float, written by the kernel (softmax numerators),
+// kept for the caller to inspect.
+#include "common.cuh"
+
+namespace {
+
+constexpr int THREADS = 512;
+
+__device__ __forceinline__ double block_sum_double(double v, double* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int warps = (blockDim.x + 31) >> 5;
+#pragma unroll
+    for (int offset = 16; offset > 0; offset >>= 1) v += __shfl_xor_sync(0xffffffffu, v, offset);
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    if (warp == 0) {
+        double t = lane < warps ? scratch[lane] : 0.0;
+#pragma unroll
+        for (int offset = 16; offset > 0; offset >>= 1)
+            t += __shfl_xor_sync(0xffffffffu, t, offset);
+        if (lane == 0) scratch[32] = t;
+    }
+    __syncthreads();
+    return scratch[32];
+}
+
+__global__ void __launch_bounds__(THREADS)
+argmax_kernel(const float* __restrict__ logits, int vocab, int* __restrict__ out) {
+    __shared__ float best_value[THREADS / 32];
+    __shared__ int best_index[THREADS / 32];
+    const float* row = logits + (size_t)blockIdx.x * vocab;
+    float value = -INFINITY;
+    int index = 0x7fffffff;
+    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+        const float v = row[i];
+        if (v > value || (v == value && i < index)) { value = v; index = i; }
+    }
+    for (int offset = 16; offset > 0; offset >>= 1) {
+        const float other = __shfl_xor_sync(0xffffffffu, value, offset);
+        const int other_index = __shfl_xor_sync(0xffffffffu, index, offset);
+        if (other > value || (other == value && other_index < index)) {
+            value = other; index = other_index;
+        }
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (lane == 0) { best_value[warp] = value; best_index[warp] = index; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < THREADS / 32; ++w)
+            if (best_value[w] > value || (best_value[w] == value && best_index[w] < index)) {
+                value = best_value[w]; index = best_index[w];
+            }
+        out[blockIdx.x] = index == 0x7fffffff ? 0 : index;
+    }
+}
+
+__device__ __forceinline__ float uniform_from(long long seed, int step) {
+    unsigned long long z = (unsigned long long)seed * 0x9E3779B97F4A7C15ull +
+                           (unsigned long long)(step + 1) * 0xBF58476D1CE4E5B9ull;
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+    z = z ^ (z >> 31);
+    return (float)(z >> 40) * (1.0f / 16777216.0f);
+}
+
+// Per row: temperature[r] == 0 -> argmax. top_k[r] <= 0 -> no top-k. top_p[r] >= 1 -> none.
+__global__ void __launch_bounds__(THREADS)
+sample_kernel(const float* __restrict__ logits, int vocab, const float* __restrict__ temperature,
+              const int* __restrict__ top_k, const float* __restrict__ top_p,
+              const long long* __restrict__ seed, const int* __restrict__ step,
+              float* __restrict__ probabilities, int* __restrict__ out) {
+    __shared__ float fscratch[33];
+    __shared__ double dscratch[33];
+    __shared__ int iscratch[33];
+    __shared__ int chosen;
+    __shared__ double carried_mass;
+    __shared__ int carried_ties;
+    const int r = blockIdx.x;
+    const float* row = logits + (size_t)r * vocab;
+    float* p = probabilities + (size_t)r * vocab;
+    const int tid = threadIdx.x;
+
+    // ---- probabilities (numerators of the softmax)
+    float local_max = -INFINITY;
+    for (int i = tid; i < vocab; i += blockDim.x) local_max = fmaxf(local_max, row[i]);
+    const float top = block_max(local_max, fscratch);
+    const float inv_t = 1.0f / temperature[r];
+    for (int i = tid; i < vocab; i += blockDim.x) p[i] = expf((row[i] - top) * inv_t);
+    __syncthreads();
+
+    auto count_ge = [&](unsigned bits) {
+        int c = 0;
+        for (int i = tid; i < vocab; i += blockDim.x) c += __float_as_uint(p[i]) >= bits;
+        // integer block sum through the double path keeps one reduction routine
+        return (long long)(block_sum_double((double)c, dscratch) + 0.5);
+    };
+
+    // ---- top-k: kth = bits of the k-th largest probability, ties_k of its ties are kept
+    unsigned kth = 0u;
+    const int k = top_k[r];
+    if (k > 0 && k < vocab) {
+        for (int bit = 30; bit >= 0; --bit) {
+            const unsigned candidate = kth | (1u << bit);
+            if (count_ge(candidate) >= k) kth = candidate;
+        }
+    }
+    long long above_k = 0;
+    double mass_above_k = 0.0;
+    {
+        int c = 0, e = 0;
+        double m = 0.0;
+        for (int i = tid; i < vocab; i += blockDim.x) {
+            const unsigned b = __float_as_uint(p[i]);
+            if (b > kth) { ++c; m += (double)p[i]; }
+            e += b == kth;
+        }
+        above_k = (long long)(block_sum_double((double)c, dscratch) + 0.5);
+        mass_above_k = block_sum_double(m, dscratch);
+        const long long equal_k = (long long)(block_sum_double((double)e, dscratch) + 0.5);
+        iscratch[0] = 0;
+        __syncthreads();
+        if (tid == 0)
+            iscratch[0] = (int)((k > 0 && k < vocab) ? min((long long)k - above_k, equal_k) : equal_k);
+        __syncthreads();
+    }
+    const int ties_k = iscratch[0];
+    const double kth_value = (double)__uint_as_float(kth);
+    const double kept_mass = mass_above_k + ties_k * kth_value;
+
+    // ---- top-p inside the kept set: boundary value `edge`, ties_edge of its ties are kept
+    unsigned edge = kth;
+    int ties_edge = ties_k;
+    double mass_above_edge = mass_above_k;
+    const float nucleus = top_p[r];
+    if (nucleus < 1.0f) {
+        const double cutoff = (double)nucleus * kept_mass;
+        // mass of kept tokens with probability >= x, for x >= kth
+        auto mass_ge = [&](unsigned bits) {
+            double m = 0.0;
+            for (int i = tid; i < vocab; i += blockDim.x) {
+                const unsigned b = __float_as_uint(p[i]);
+                if (b >= bits && b > kth) m += (double)p[i];
+            }
+            m = block_sum_double(m, dscratch);
+            return bits <= kth ? m + ties_k * kth_value : m;
+        };
+        unsigned found = 0u;
+        for (int bit = 30; bit >= 0; --bit) {
+            const unsigned candidate = found | (1u << bit);
+            const unsigned probe = candidate < kth ? kth : candidate;
+            if (mass_ge(probe) >= cutoff) found = candidate;
+        }
+        edge = found < kth ? kth : found;
+        int e = 0;
+        double m = 0.0;
+        for (int i = tid; i < vocab; i += blockDim.x) {
+            const unsigned b = __float_as_uint(p[i]);
+            if (b > edge) m += (double)p[i];
+            e += b == edge;
+        }
+        mass_above_edge = block_sum_double(m, dscratch);
+        long long available = (long long)(block_sum_double((double)e, dscratch) + 0.5);
+        if (edge == kth) available = ties_k;
+        const double edge_value = (double)__uint_as_float(edge);
+        long long need = 1;
+        if (edge_value > 0.0) need = (long long)ceil((cutoff - mass_above_edge) / edge_value);
+        need = max(1ll, min(need, available));
+        ties_edge = (int)need;
+    }
+    const double edge_value = (double)__uint_as_float(edge);
+    const double total = mass_above_edge + ties_edge * edge_value;
+    const double target = (double)uniform_from(seed[r], step[r]) * total;
+
+    // ---- walk kept tokens in token order until the running mass reaches the target
+    if (tid == 0) { chosen = 0x7fffffff; carried_mass = 0.0; carried_ties = 0; }
+    __syncthreads();
+    int last_kept = -1;
+    for (int base = 0; base < vocab; base += blockDim.x) {
+        const int i = base + tid;
+        unsigned b = 0u;
+        float value = 0.f;
+        if (i < vocab) { value = p[i]; b = __float_as_uint(value); }
+        const int is_tie = (i < vocab && b == edge) ? 1 : 0;
+        // inclusive scan of tie flags over the block
+        int tie_rank = is_tie;
+        const int lane = tid & 31, warp = tid >> 5;
+        for (int offset = 1; offset < 32; offset <<= 1) {
+            const int other = __shfl_up_sync(0xffffffffu, tie_rank, offset);
+            if (lane >= offset) tie_rank += other;
+        }
+        if (lane == 31) iscratch[warp] = tie_rank;
+        __syncthreads();
+        int tie_offset = carried_ties;
+        for (int w = 0; w < warp; ++w) tie_offset += iscratch[w];
+        tie_rank += tie_offset;
+        const bool kept = i < vocab && (b > edge || (is_tie && tie_rank <= ties_edge));
+        double mass = kept ? (double)value : 0.0;
+        double running = mass;
+        for (int offset = 1; offset < 32; offset <<= 1) {
+            const double other = __shfl_up_sync(0xffffffffu, running, offset);
+            if (lane >= offset) running += other;
+        }
+        if (lane == 31) dscratch[warp] = running;
+        __syncthreads();
+        double mass_offset = carried_mass;
+        for (int w = 0; w < warp; ++w) mass_offset += dscratch[w];
+        running += mass_offset;
+        if (kept) {
+            last_kept = i;
+            if (running >= target) atomicMin(&chosen, i);
+        }
+        __syncthreads();
+        if (tid == blockDim.x - 1) { carried_mass = running; carried_ties = tie_rank; }
+        __syncthreads();
+        if (chosen != 0x7fffffff) break;
+    }
+    if (chosen == 0x7fffffff) {
+        // rounding left the running mass just below the target: take the last kept token
+        __syncthreads();
+        if (tid == 0) iscratch[32] = -1;
+        __syncthreads();
+        atomicMax(&iscratch[32], last_kept);
+        __syncthreads();
+        if (tid == 0) out[r] = max(iscratch[32], 0);
+    } else if (tid == 0) {
+        out[r] = chosen;
+    }
+}
+
+}  // namespace
+
+MLXONE_API int mlxone_argmax(const float* logits, int rows, int vocab, int* out,
+                             cudaStream_t stream) {
+    if (rows == 0) return 0;
+    MLXONE_REQUIRE(rows > 0 && vocab > 0, "argmax: bad sizes");
+    argmax_kernel<<<rows, THREADS, 0, stream>>>(logits, vocab, out);
+    MLXONE_LAUNCH_CHECK("argmax");
+    return 0;
+}
+
+MLXONE_API int mlxone_sample(const float* logits, int rows, int vocab, const float* temperature,
+                             const int* top_k, const float* top_p, const long long* seed,
+                             const int* step, float* probabilities, int* out,
+                             cudaStream_t stream) {
+    if (rows == 0) return 0;
+    MLXONE_REQUIRE(rows > 0 && vocab > 0, "sample: bad sizes");
+    MLXONE_REQUIRE(probabilities != nullptr, "sample: scratch for probabilities is missing");
+    sample_kernel<<<rows, THREADS, 0, stream>>>(logits, vocab, temperature, top_k, top_p, seed,
+                                               step, probabilities, out);
+    MLXONE_LAUNCH_CHECK("sample");
+    return 0;
+}

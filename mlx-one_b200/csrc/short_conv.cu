@@ -1,0 +1,115 @@
+// Gated short convolution over a ragged batch, with per-request state in slots.
+//
+// bcx[t, 0:H] = B, bcx[t, H:2H] = C, bcx[t, 2H:3H] = x.  g = round(B * x).
+// y[t, d] = bias[d] + sum_k kernel[d, k] * g_at(position(t) - (taps-1) + k), where g_at reads
+// this step's rows for positions inside the request's portion, the request's state for the
+// taps-1 positions before it, and zero before position 0.  out[t, d] = C * y.
+// State row s of a request holds g at position history - (taps-1) + s.
+//
+// g is rounded to the storage type before it is used, so that a value taken from this
+// step's rows equals the value that a later step reads from the state.
+#include "common.cuh"
+
+namespace {
+
+template <typename T>
+__global__ void short_conv_kernel(const T* __restrict__ bcx, const float* __restrict__ kernel,
+                                  const float* __restrict__ bias, const T* __restrict__ state,
+                                  const int* __restrict__ slots,
+                                  const int* __restrict__ token_request,
+                                  const int* __restrict__ request_start,
+                                  const int* __restrict__ history, T* __restrict__ out,
+                                  int tokens, int hidden, int taps) {
+    const int d = blockIdx.y * blockDim.x + threadIdx.x;
+    const int t = blockIdx.x;
+    if (d >= hidden) return;
+    const int r = token_request[t];
+    const int first = request_start[r];
+    const int index = t - first;                      // place inside the portion
+    const int position = history[r] + index;
+    const size_t row = (size_t)3 * hidden;
+    float y = bias ? bias[d] : 0.f;
+    for (int k = 0; k < taps; ++k) {
+        const int back = taps - 1 - k;                // how many positions before t
+        float g = 0.f;
+        if (index - back >= 0) {
+            const T* src = bcx + (size_t)(t - back) * row;
+            g = round_to<T>(to_float<T>(src[d]) * to_float<T>(src[2 * hidden + d]));
+        } else if (position - back >= 0) {
+            const int s = taps - 1 + (index - back);  // state row, 0 .. taps-2
+            g = to_float<T>(state[((size_t)slots[r] * (taps - 1) + s) * hidden + d]);
+        }
+        y = fmaf(kernel[(size_t)d * taps + k], g, y);
+    }
+    out[(size_t)t * hidden + d] = from_float<T>(to_float<T>(bcx[(size_t)t * row + hidden + d]) * y);
+}
+
+// New state after the step: row s holds g at position (history + n) - (taps-1) + s.
+template <typename T>
+__global__ void short_conv_state_kernel(const T* __restrict__ bcx, T* __restrict__ state,
+                                        const int* __restrict__ slots,
+                                        const int* __restrict__ request_start,
+                                        const int* __restrict__ history, int hidden, int taps) {
+    const int d = blockIdx.x * blockDim.x + threadIdx.x;
+    const int r = blockIdx.y;
+    if (d >= hidden) return;
+    const int first = request_start[r];
+    const int n = request_start[r + 1] - first;
+    if (n <= 0) return;
+    const int before = history[r];
+    T* rows = state + (size_t)slots[r] * (taps - 1) * hidden;
+    constexpr int MAX_ROWS = 16;
+    float kept[MAX_ROWS];
+    for (int s = 0; s < taps - 1; ++s) {
+        const int index = n - (taps - 1) + s;          // place inside the portion, may be < 0
+        float g = 0.f;
+        if (index >= 0) {
+            const T* src = bcx + (size_t)(first + index) * 3 * hidden;
+            g = round_to<T>(to_float<T>(src[d]) * to_float<T>(src[2 * hidden + d]));
+        } else if (before + index >= 0) {
+            g = to_float<T>(rows[(size_t)(taps - 1 + index) * hidden + d]);
+        }
+        kept[s] = g;
+    }
+    for (int s = 0; s < taps - 1; ++s) rows[(size_t)s * hidden + d] = from_float<T>(kept[s]);
+}
+
+}  // namespace
+
+MLXONE_API int mlxone_short_conv(const void* bcx, const float* kernel, const float* bias,
+                                 void* state, const int* slots, const int* token_request,
+                                 const int* request_start, const int* history, void* out,
+                                 int tokens, int requests, int hidden, int taps, int write_state,
+                                 int dtype, cudaStream_t stream) {
+    if (tokens == 0) return 0;
+    MLXONE_REQUIRE(tokens > 0 && requests > 0 && hidden > 0, "short_conv: bad sizes");
+    MLXONE_REQUIRE(taps >= 1 && taps <= 17, "short_conv: kernel width %d is not in 1..17", taps);
+    const int threads = 128;
+    const dim3 grid(tokens, ceil_div_host(hidden, threads));
+    const dim3 state_grid(ceil_div_host(hidden, threads), requests);
+    MLXONE_REQUIRE(requests <= 65535, "short_conv: at most 65535 requests a step");
+    if (dtype == MLXONE_BF16) {
+        using T = __nv_bfloat16;
+        short_conv_kernel<T><<<grid, threads, 0, stream>>>(
+            (const T*)bcx, kernel, bias, (const T*)state, slots, token_request, request_start,
+            history, (T*)out, tokens, hidden, taps);
+        MLXONE_LAUNCH_CHECK("short_conv");
+        if (write_state && taps > 1) {
+            short_conv_state_kernel<T><<<state_grid, threads, 0, stream>>>(
+                (const T*)bcx, (T*)state, slots, request_start, history, hidden, taps);
+            MLXONE_LAUNCH_CHECK("short_conv_state");
+        }
+    } else {
+        using T = float;
+        short_conv_kernel<T><<<grid, threads, 0, stream>>>(
+            (const T*)bcx, kernel, bias, (const T*)state, slots, token_request, request_start,
+            history, (T*)out, tokens, hidden, taps);
+        MLXONE_LAUNCH_CHECK("short_conv");
+        if (write_state && taps > 1) {
+            short_conv_state_kernel<T><<<state_grid, threads, 0, stream>>>(
+                (const T*)bcx, (T*)state, slots, request_start, history, hidden, taps);
+            MLXONE_LAUNCH_CHECK("short_conv_state");
+        }
+    }
+    return 0;
+}

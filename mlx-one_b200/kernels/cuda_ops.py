@@ -1,0 +1,240 @@
+"""The kernel set of the engine: thin Python wrappers around the C launchers.
+
+Each method allocates its output with torch, checks dtypes and shapes, and passes raw
+pointers and the current CUDA stream to the library. There is no fallback: constructing
+``CudaOps`` fails if the library cannot be built or loaded or no CUDA device is present.
+
+Matrix products in bfloat16 go through ``torch.matmul`` (cuBLAS), as the reference uses its
+library's matrix product (nn.Linear, src/mlx_one/models/language/lfm2/reference_math.py:33-34);
+in float32 they go through this library's own FMA kernel, which never uses a
+reduced-precision mode.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from typing import Any
+
+import torch
+
+from .build import KernelBuildError, library_path
+
+_F32, _BF16 = 0, 1
+_c_int, _c_float, _c_void_p, _c_ll = ctypes.c_int, ctypes.c_float, ctypes.c_void_p, ctypes.c_longlong
+
+
+class KernelError(RuntimeError):
+    """A kernel launcher refused its arguments or a kernel reported a fault."""
+
+
+def _dtype_code(dtype: torch.dtype) -> int:
+    if dtype == torch.float32:
+        return _F32
+    if dtype == torch.bfloat16:
+        return _BF16
+    raise KernelError(f"kernels exist for float32 and bfloat16, not {dtype}")
+
+
+def _ptr(tensor: torch.Tensor | None) -> int | None:
+    return None if tensor is None else tensor.data_ptr()
+
+
+class CudaOps:
+    name = "cuda"
+
+    def __init__(self, device: torch.device | str = "cuda:0", verbose: bool = True) -> None:
+        self.device = torch.device(device)
+        if self.device.type != "cuda" or not torch.cuda.is_available():
+            raise KernelBuildError("the engine needs a CUDA device (sm_100a); it has no CPU path")
+        try:
+            self.lib = ctypes.CDLL(str(library_path(verbose=verbose)))
+        except OSError as exc:
+            raise KernelBuildError(f"cannot load the CUDA extension: {exc}") from exc
+        self.lib.mlxone_last_error.restype = ctypes.c_char_p
+        if self.lib.mlxone_abi_version() != 1:
+            raise KernelBuildError("the CUDA extension is of another version; rebuild it")
+        self.error_flag = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.launches = 0
+        self._sample_scratch: torch.Tensor | None = None
+
+    # ------------------------------------------------------------------ plumbing
+
+    def _call(self, name: str, *args: Any) -> None:
+        stream = torch.cuda.current_stream(self.device).cuda_stream
+        code = getattr(self.lib, name)(*args, _c_void_p(stream))
+        if code != 0:
+            raise KernelError(self.lib.mlxone_last_error().decode())
+        self.launches += 1
+
+    def _need(self, tensor: torch.Tensor, dtype: torch.dtype, what: str) -> None:
+        if tensor.dtype != dtype or not tensor.is_contiguous() or tensor.device != self.device:
+            raise KernelError(f"{what} must be a contiguous {dtype} tensor on {self.device}, got "
+                              f"{tensor.dtype} {tuple(tensor.shape)} on {tensor.device}")
+
+    def check_errors(self) -> None:
+        """Reads the device error flag (synchronises) and raises if a kernel set it."""
+        code = int(self.error_flag.item())
+        if code:
+            self.error_flag.zero_()
+            what = {1: "a token id outside the vocabulary",
+                    2: "a key written to a position that has no page",
+                    3: "a key read from a position that has no page"}.get(code, f"code {code}")
+            raise KernelError(f"a kernel reported {what}")
+
+    # ------------------------------------------------------------------ size checks
+
+    def check_attention_sizes(self, heads: int, kv_heads: int, head_dim: int) -> None:
+        if heads % kv_heads:
+            raise KernelError(f"{heads} query heads cannot share {kv_heads} key heads")
+        if not 2 <= head_dim <= 512:
+            raise KernelError(f"head size {head_dim} is outside 2..512")
+
+    # ------------------------------------------------------------------ ops
+
+    def embedding(self, ids: torch.Tensor, table: torch.Tensor) -> torch.Tensor:
+        self._need(ids, torch.int32, "token ids")
+        out = torch.empty((ids.numel(), table.shape[1]), dtype=torch.float32, device=self.device)
+        self._call("mlxone_embedding", _c_void_p(_ptr(ids)), _c_void_p(_ptr(table)),
+                   _c_void_p(_ptr(out)), _c_int(ids.numel()), _c_int(table.shape[1]),
+                   _c_int(table.shape[0]), _c_int(_dtype_code(table.dtype)),
+                   _c_void_p(_ptr(self.error_flag)))
+        return out
+
+    def add_rmsnorm(self, residual, delta, weight, eps, dtype):
+        self._need(residual, torch.float32, "residual")
+        self._need(weight, torch.float32, "norm weight")
+        if delta is not None:
+            self._need(delta, dtype, "delta")
+            if delta.shape != residual.shape:
+                raise KernelError("delta and residual differ in shape")
+        rows, hidden = residual.shape
+        if weight.numel() != hidden:
+            raise KernelError(f"norm weight has {weight.numel()} entries, rows have {hidden}")
+        out = torch.empty((rows, hidden), dtype=dtype, device=self.device)
+        self._call("mlxone_add_rmsnorm", _c_void_p(_ptr(residual)), _c_void_p(_ptr(delta)),
+                   _c_void_p(_ptr(weight)), _c_void_p(_ptr(out)), _c_int(rows), _c_int(hidden),
+                   _c_float(eps), _c_int(_dtype_code(dtype)))
+        return out
+
+    def gather_rows(self, residual, delta, rows):
+        self._need(residual, torch.float32, "residual")
+        self._need(rows, torch.int32, "rows")
+        count, hidden = rows.numel(), residual.shape[1]
+        picked = torch.empty((count, hidden), dtype=torch.float32, device=self.device)
+        picked_delta = None
+        code = _F32
+        if delta is not None:
+            picked_delta = torch.empty((count, hidden), dtype=delta.dtype, device=self.device)
+            code = _dtype_code(delta.dtype)
+        self._call("mlxone_gather_rows", _c_void_p(_ptr(residual)), _c_void_p(_ptr(delta)),
+                   _c_void_p(_ptr(rows)), _c_void_p(_ptr(picked)), _c_void_p(_ptr(picked_delta)),
+                   _c_int(count), _c_int(hidden), _c_int(residual.shape[0]), _c_int(code))
+        return picked, picked_delta
+
+    def linear(self, a, w, bias=None, out_dtype=None):
+        """a[M, K] @ w[N, K]^T (+ bias[N], float32). ``out_dtype``: a's dtype, or float32."""
+        if a.dtype != w.dtype:
+            raise KernelError(f"matrix product of {a.dtype} with {w.dtype}")
+        out_dtype = out_dtype or a.dtype
+        m, k = a.shape
+        n = w.shape[0]
+        if w.shape[1] != k:
+            raise KernelError(f"matrix product of [{m}, {k}] with [{n}, {w.shape[1]}]^T")
+        if a.dtype == torch.float32:
+            self._need(a, torch.float32, "a")
+            self._need(w, torch.float32, "w")
+            out = torch.empty((m, n), dtype=torch.float32, device=self.device)
+            self._call("mlxone_gemm_f32", _c_void_p(_ptr(a)), _c_int(k), _c_void_p(_ptr(w)),
+                       _c_int(k), _c_void_p(_ptr(bias)), _c_void_p(_ptr(out)), _c_int(n),
+                       _c_int(m), _c_int(n), _c_int(k))
+            return out
+        if out_dtype == torch.float32:
+            out = torch.mm(a, w.t(), out_dtype=torch.float32)
+        else:
+            out = torch.mm(a, w.t())
+        if bias is not None:
+            self._call("mlxone_add_bias", _c_void_p(_ptr(out)), _c_void_p(_ptr(bias)), _c_int(m),
+                       _c_int(n), _c_int(_dtype_code(out.dtype)))
+        return out
+
+    def swiglu(self, gate_up):
+        rows, twice = gate_up.shape
+        out = torch.empty((rows, twice // 2), dtype=gate_up.dtype, device=self.device)
+        self._call("mlxone_swiglu", _c_void_p(_ptr(gate_up)), _c_void_p(_ptr(out)), _c_int(rows),
+                   _c_int(twice // 2), _c_int(_dtype_code(gate_up.dtype)))
+        return out
+
+    def short_conv(self, bcx, *, kernel, bias, taps, ctx, view, write):
+        tokens, triple = bcx.shape
+        hidden = triple // 3
+        self._need(bcx, view.state.dtype, "bcx")
+        self._need(kernel, torch.float32, "conv kernel")
+        out = torch.empty((tokens, hidden), dtype=bcx.dtype, device=self.device)
+        self._call("mlxone_short_conv", _c_void_p(_ptr(bcx)), _c_void_p(_ptr(kernel)),
+                   _c_void_p(_ptr(bias)), _c_void_p(_ptr(view.state)), _c_void_p(_ptr(view.slots)),
+                   _c_void_p(_ptr(ctx.token_request)), _c_void_p(_ptr(ctx.request_start)),
+                   _c_void_p(_ptr(ctx.history)), _c_void_p(_ptr(out)), _c_int(tokens),
+                   _c_int(ctx.requests), _c_int(hidden), _c_int(taps), _c_int(1 if write else 0),
+                   _c_int(_dtype_code(bcx.dtype)))
+        return out
+
+    def qk_norm_rope_store(self, qkv, *, heads, kv_heads, head_dim, q_weight, k_weight, eps,
+                           rotary, ctx, view, write):
+        tokens = qkv.shape[0]
+        self._need(qkv, view.kv.dtype, "qkv")
+        if qkv.shape[1] != (heads + 2 * kv_heads) * head_dim:
+            raise KernelError("qkv width does not match the head counts")
+        inv_freq, rotary_dim = (None, 0) if rotary is None else rotary
+        q = torch.empty((tokens, heads, head_dim), dtype=qkv.dtype, device=self.device)
+        pages = view.kv.shape[1]
+        self._call("mlxone_qk_prep", _c_void_p(_ptr(qkv)), _c_void_p(_ptr(q_weight)),
+                   _c_void_p(_ptr(k_weight)), _c_float(0.0 if eps is None else eps),
+                   _c_void_p(_ptr(inv_freq)), _c_int(rotary_dim), _c_void_p(_ptr(ctx.positions)),
+                   _c_void_p(_ptr(ctx.token_request)), _c_void_p(_ptr(q)),
+                   _c_void_p(_ptr(view.kv)), _c_void_p(_ptr(view.block_table)),
+                   _c_int(view.block_table.shape[1]), _c_int(view.page_size), _c_int(pages),
+                   _c_int(tokens), _c_int(heads), _c_int(kv_heads), _c_int(head_dim),
+                   _c_int(1 if write else 0), _c_int(_dtype_code(qkv.dtype)),
+                   _c_void_p(_ptr(self.error_flag)))
+        return q
+
+    def paged_attention(self, q, *, heads, kv_heads, head_dim, scale, window, ctx, view):
+        tokens = q.shape[0]
+        out = torch.empty((tokens, heads * head_dim), dtype=q.dtype, device=self.device)
+        self._call("mlxone_attention_generic", _c_void_p(_ptr(q)), _c_void_p(_ptr(view.kv)),
+                   _c_void_p(_ptr(view.block_table)), _c_int(view.block_table.shape[1]),
+                   _c_int(view.page_size), _c_int(view.kv.shape[1]),
+                   _c_void_p(_ptr(ctx.positions)), _c_void_p(_ptr(ctx.token_request)),
+                   _c_void_p(_ptr(out)), _c_int(tokens), _c_int(heads), _c_int(kv_heads),
+                   _c_int(head_dim), _c_float(scale), _c_int(window or 0),
+                   _c_int(_dtype_code(q.dtype)), _c_void_p(_ptr(self.error_flag)))
+        return out
+
+    def argmax(self, logits):
+        self._need(logits, torch.float32, "logits")
+        out = torch.empty((logits.shape[0],), dtype=torch.int32, device=self.device)
+        self._call("mlxone_argmax", _c_void_p(_ptr(logits)), _c_int(logits.shape[0]),
+                   _c_int(logits.shape[1]), _c_void_p(_ptr(out)))
+        return out
+
+    def sample(self, logits, temperature, top_k, top_p, seed, step):
+        """Per row: temperature (float32, > 0), top_k (int32, <= 0 = off), top_p (float32,
+        >= 1 = off), seed (int64), step (int32). Returns (tokens int32, probabilities)."""
+        self._need(logits, torch.float32, "logits")
+        rows, vocab = logits.shape
+        for tensor, dtype, what in ((temperature, torch.float32, "temperature"),
+                                    (top_k, torch.int32, "top_k"), (top_p, torch.float32, "top_p"),
+                                    (seed, torch.int64, "seed"), (step, torch.int32, "step")):
+            self._need(tensor, dtype, what)
+            if tensor.numel() != rows:
+                raise KernelError(f"{what} must have one entry per row")
+        scratch = self._sample_scratch
+        if scratch is None or scratch.numel() < rows * vocab:
+            scratch = torch.empty(rows * vocab, dtype=torch.float32, device=self.device)
+            self._sample_scratch = scratch
+        out = torch.empty((rows,), dtype=torch.int32, device=self.device)
+        self._call("mlxone_sample", _c_void_p(_ptr(logits)), _c_int(rows), _c_int(vocab),
+                   _c_void_p(_ptr(temperature)), _c_void_p(_ptr(top_k)), _c_void_p(_ptr(top_p)),
+                   _c_void_p(_ptr(seed)), _c_void_p(_ptr(step)), _c_void_p(_ptr(scratch)),
+                   _c_void_p(_ptr(out)))
+        return out, scratch[: rows * vocab].view(rows, vocab)

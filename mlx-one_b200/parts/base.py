@@ -1,0 +1,172 @@
+"""Interfaces of the parts and of what they are given at run time."""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Any, Mapping
+
+import torch
+
+from .spec import PartSpec, TensorSpec
+
+
+# ----------------------------------------------------------------------- cache needs
+
+
+@dataclass(frozen=True)
+class PagedKeyValues:
+    """A mixer that keeps a key and a value vector per token and per key head. Layers
+    whose need is equal share pages and a block table. ``window``: only the last
+    ``window`` positions are ever read again, so earlier pages may be given back."""
+
+    kv_heads: int
+    head_dim: int
+    window: int | None = None
+
+
+@dataclass(frozen=True)
+class FixedState:
+    """A mixer with per-request state of fixed size (``shape`` per cache entry), kept in
+    a slot. The slot is zero when a request gets it."""
+
+    shape: tuple[int, ...]
+    dtype: str = "compute"          # "compute" = the engine's dtype, or "float32"
+
+
+# ----------------------------------------------------------------------- run time
+
+
+@dataclass
+class Runtime:
+    """What a part needs besides its tensors: compute dtype, device and kernels."""
+
+    dtype: torch.dtype
+    device: torch.device
+    ops: Any
+
+
+@dataclass
+class PagedView:
+    """One cache entry of a paged group as a step sees it. ``kv`` is
+    [2, pages, kv_heads, page_size, head_dim]; ``block_table`` is int32 [requests, width]
+    with -1 where a page was given back."""
+
+    kv: torch.Tensor
+    block_table: torch.Tensor
+    page_size: int
+    need: PagedKeyValues
+
+
+@dataclass
+class StateView:
+    """One cache entry of a fixed-state group: ``state`` is [slots, *shape] and
+    ``slots`` int32 [requests] names each request's slot."""
+
+    state: torch.Tensor
+    slots: torch.Tensor
+    need: FixedState
+
+
+@dataclass
+class StepContext:
+    """The ragged batch of one step. All tensors are int32 on the device.
+
+    ``token_ids``/``positions``/``token_request`` have one entry per token; tokens of a
+    request are consecutive and in order. ``request_start`` [requests + 1] are offsets
+    into the tokens; ``history`` [requests] is each request's token count before this
+    step (the position of its first token here)."""
+
+    tokens: int
+    requests: int
+    token_ids: torch.Tensor
+    positions: torch.Tensor
+    token_request: torch.Tensor
+    request_start: torch.Tensor
+    history: torch.Tensor
+    max_portion: int                  # most tokens any request brings (host)
+    max_context: int                  # largest history + portion (host)
+    views: Mapping[int, Any] = field(default_factory=dict)   # cache entry -> view
+    host: Mapping[str, Any] = field(default_factory=dict)    # host copies for tests/toys
+
+
+# ----------------------------------------------------------------------- part bases
+
+
+class Part:
+    """Common construction: checks that the given tensors match ``tensors(spec)``."""
+
+    def __init__(self, spec: PartSpec, tensors: Mapping[str, torch.Tensor],
+                 runtime: Runtime) -> None:
+        self.spec = spec
+        self.runtime = runtime
+        self.ops = runtime.ops
+        expected = self.tensors(spec)
+        for name, want in expected.items():
+            if name not in tensors:
+                raise KeyError(f"{type(self).__name__}: tensor {name!r} was not given")
+            if tuple(tensors[name].shape) != tuple(want.shape):
+                raise ValueError(f"{type(self).__name__}: {name} has shape "
+                                 f"{tuple(tensors[name].shape)}, expected {want.shape}")
+
+    @classmethod
+    def tensors(cls, spec: PartSpec) -> dict[str, TensorSpec]:
+        return {}
+
+    def matrix(self, tensor: torch.Tensor) -> torch.Tensor:
+        """A matrix operand in the compute dtype."""
+        return tensor.to(self.runtime.dtype).contiguous()
+
+    def vector(self, tensor: torch.Tensor) -> torch.Tensor:
+        """A small per-channel vector, read by kernels in 32-bit (exact from bfloat16)."""
+        return tensor.to(torch.float32).contiguous()
+
+
+class Mixer(Part):
+    @classmethod
+    def cache_need(cls, spec: PartSpec):
+        """``PagedKeyValues``, ``FixedState`` or None."""
+        return None
+
+    def forward(self, x: torch.Tensor, ctx: StepContext, cache: Any, write: bool):
+        """x: normed input [tokens, hidden] in the compute dtype. Returns the mixer's
+        output [tokens, hidden] in the compute dtype (the block adds it to the
+        residual). ``write``: append this step's tokens to ``cache``."""
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class Norm(Part):
+    def forward(self, residual: torch.Tensor, delta: torch.Tensor | None) -> torch.Tensor:
+        """Adds ``delta`` (compute dtype, or None) into the 32-bit ``residual`` in place
+        and returns the normed residual in the compute dtype."""
+        raise NotImplementedError
+
+
+class PositionEncoding(Part):
+    def rotary_table(self) -> tuple[torch.Tensor, int] | None:
+        """(inverse frequencies [rotary_dim / 2] float32, rotary_dim) for encodings that
+        rotate queries and keys by position * frequency; None for no rotation."""
+        return None
+
+
+class Block(Part):
+    """Arranges a layer's parts. Gets the built parts by role."""
+
+    def __init__(self, spec, tensors, runtime, *, mixer, mixer_norm, feed_forward,
+                 feed_forward_norm) -> None:
+        super().__init__(spec, tensors, runtime)
+        self.mixer = mixer
+        self.mixer_norm = mixer_norm
+        self.feed_forward = feed_forward
+        self.feed_forward_norm = feed_forward_norm
+
+    def forward(self, residual: torch.Tensor, delta: torch.Tensor | None, ctx: StepContext,
+                cache: Any, write: bool) -> torch.Tensor | None:
+        """``residual`` is the 32-bit stream [tokens, hidden], updated in place; ``delta``
+        is an output of the previous block that is still to be added (or None). Returns
+        this block's pending output in the same way."""
+        raise NotImplementedError

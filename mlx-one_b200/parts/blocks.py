@@ -1,0 +1,19 @@
+"""Arrangements of a layer's parts."""
+
+from __future__ import annotations
+
+from .base import Block
+from .registry import BLOCKS
+
+
+@BLOCKS.register("prenorm")
+class PreNormBlock(Block):
+    """h = x + mixer(norm(x)); out = h + feed_forward(norm(h)). Each residual add is fused
+    with the norm that follows it, so the block returns its last output unadded.
+    Reference: src/mlx_one/models/language/lfm2/reference_math.py:160-179."""
+
+    def forward(self, residual, delta, ctx, cache, write):
+        normed = self.mixer_norm.forward(residual, delta)
+        mixed = self.mixer.forward(normed, ctx, cache, write)
+        normed = self.feed_forward_norm.forward(residual, mixed)
+        return self.feed_forward.forward(normed, ctx)

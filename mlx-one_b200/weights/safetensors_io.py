@@ -1,0 +1,131 @@
+"""Reading and writing safetensors files without a framework around them.
+
+Format: 8 bytes little-endian header length, a JSON header that maps each tensor name to
+{"dtype", "shape", "data_offsets"}, then the raw little-endian data. Files are mapped,
+not read, so a tensor costs host memory only while it is copied to the device.
+"""
+
+from __future__ import annotations
+
+import json
+import mmap
+import struct
+import warnings
+from pathlib import Path
+from typing import Iterator, Mapping
+
+import torch
+
+_DTYPES = {
+    "F64": torch.float64, "F32": torch.float32, "F16": torch.float16, "BF16": torch.bfloat16,
+    "I64": torch.int64, "I32": torch.int32, "I16": torch.int16, "I8": torch.int8,
+    "U8": torch.uint8, "BOOL": torch.bool,
+}
+_NAMES = {value: key for key, value in _DTYPES.items()}
+
+
+class SafetensorsError(ValueError):
+    """The file is not a well-formed safetensors file."""
+
+
+class SafetensorsFile:
+    """A mapped safetensors file. ``entries`` maps names to (dtype, shape)."""
+
+    def __init__(self, path: str | Path) -> None:
+        self.path = Path(path)
+        self._file = open(self.path, "rb")
+        size = self.path.stat().st_size
+        if size < 8:
+            raise SafetensorsError(f"{self.path}: too short to be a safetensors file")
+        (length,) = struct.unpack("<Q", self._file.read(8))
+        if length <= 0 or 8 + length > size:
+            raise SafetensorsError(f"{self.path}: header length {length} exceeds the file")
+        try:
+            header = json.loads(self._file.read(length))
+        except ValueError as exc:
+            raise SafetensorsError(f"{self.path}: header is not JSON: {exc}") from exc
+        self.metadata = header.pop("__metadata__", {})
+        self._data_start = 8 + length
+        self._map = mmap.mmap(self._file.fileno(), 0, access=mmap.ACCESS_READ)
+        self._header = header
+        self.entries: dict[str, tuple[torch.dtype, tuple[int, ...]]] = {}
+        for name, info in header.items():
+            if info["dtype"] not in _DTYPES:
+                raise SafetensorsError(f"{self.path}: {name} has unsupported dtype {info['dtype']}")
+            dtype, shape = _DTYPES[info["dtype"]], tuple(int(v) for v in info["shape"])
+            begin, end = info["data_offsets"]
+            count = 1
+            for extent in shape:
+                count *= extent
+            if end - begin != count * dtype.itemsize or self._data_start + end > size:
+                raise SafetensorsError(f"{self.path}: {name} has inconsistent offsets")
+            self.entries[name] = (dtype, shape)
+
+    def tensor(self, name: str) -> torch.Tensor:
+        """A host tensor that views the mapped file (copy it before the file closes)."""
+        dtype, shape = self.entries[name]
+        begin, end = self._header[name]["data_offsets"]
+        if end == begin:
+            return torch.empty(shape, dtype=dtype)
+        view = memoryview(self._map)[self._data_start + begin:self._data_start + end]
+        with warnings.catch_warnings():
+            warnings.simplefilter("ignore", UserWarning)     # the map is read-only; so is its use
+            return torch.frombuffer(view, dtype=dtype).reshape(shape)
+
+    def close(self) -> None:
+        try:
+            self._map.close()
+        except BufferError:
+            pass        # a tensor still views the map; the map goes with it
+        self._file.close()
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc) -> None:
+        self.close()
+
+
+def checkpoint_files(model_dir: str | Path) -> list[Path]:
+    """The safetensors files of a model folder: ``model.safetensors``, or the shards that
+    ``model.safetensors.index.json`` names (src/mlx_one/text/loading.py:538-610)."""
+    root = Path(model_dir)
+    index = root / "model.safetensors.index.json"
+    if index.is_file():
+        names = sorted(set(json.loads(index.read_text())["weight_map"].values()))
+        files = [root / name for name in names]
+    elif (root / "model.safetensors").is_file():
+        files = [root / "model.safetensors"]
+    else:
+        files = sorted(root.glob("*.safetensors"))
+    if not files:
+        raise FileNotFoundError(f"no safetensors file in {root}")
+    for path in files:
+        if not path.is_file():
+            raise FileNotFoundError(f"{path} is named by the index but does not exist")
+    return files
+
+
+def write_safetensors(path: str | Path, tensors: Mapping[str, torch.Tensor],
+                      metadata: Mapping[str, str] | None = None) -> None:
+    header: dict[str, object] = {}
+    if metadata:
+        header["__metadata__"] = dict(metadata)
+    offset = 0
+    order = sorted(tensors)
+    for name in order:
+        tensor = tensors[name]
+        if tensor.dtype not in _NAMES:
+            raise SafetensorsError(f"{name}: dtype {tensor.dtype} cannot be stored")
+        size = tensor.numel() * tensor.element_size()
+        header[name] = {"dtype": _NAMES[tensor.dtype], "shape": list(tensor.shape),
+                        "data_offsets": [offset, offset + size]}
+        offset += size
+    blob = json.dumps(header, separators=(",", ":")).encode()
+    blob += b" " * (-(8 + len(blob)) % 8)
+    with open(path, "wb") as out:
+        out.write(struct.pack("<Q", len(blob)))
+        out.write(blob)
+        for name in order:
+            tensor = tensors[name].detach().cpu().contiguous()
+            out.write(tensor.view(torch.uint8).numpy().tobytes() if tensor.numel() else b"")
