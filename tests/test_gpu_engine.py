@@ -1,0 +1,109 @@
+"""The engine on the GPU against the plain implementation: whole requests, the last tokens
+one by one, portions of changing size, and mixed batches with pages used again."""
+
+import pytest
+import torch
+
+from plain_lfm2 import PlainModel
+from tiny_models import CONFIGS, assert_close, cut, make_model_dir, prompts, replay
+
+pytestmark = pytest.mark.gpu
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+@pytest.fixture(scope="module")
+def folders(tmp_path_factory):
+    root = tmp_path_factory.mktemp("models")
+    return {name: make_model_dir(name, root) for name in CONFIGS}
+
+
+@pytest.fixture(scope="module")
+def plain(folders):
+    return {name: PlainModel(folder) for name, folder in folders.items()}
+
+
+def engine(folder, dtype, page_size, capacity, max_requests=8):
+    from mlx_one_b200.cache import CacheManager
+    from mlx_one_b200.engine.loading import load_model
+    from mlx_one_b200.engine.runner import Runner
+
+    loaded = load_model(folder, dtype, "cuda:0")
+    cache = CacheManager(loaded.model.cache_needs, page_size=page_size, capacity_tokens=capacity,
+                         max_requests=max_requests, dtype=dtype, device="cuda:0")
+    return Runner(loaded.model, cache), cache
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", list(CONFIGS))
+def test_whole_requests(folders, plain, name, dtype):
+    config, _, page = CONFIGS[name]
+    runner, cache = engine(folders[name], dtype, page, 256)
+    for i, tokens in enumerate(prompts(config["vocab_size"], (7, 13, 21, 100, 1))):
+        got = replay(runner, cache, [([(i, tokens)], [i])])[i]
+        assert_close(got, plain[name].logits(tokens), dtype, f"{name} whole request {i}")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", list(CONFIGS))
+def test_last_tokens_one_by_one(folders, plain, name, dtype):
+    config, _, page = CONFIGS[name]
+    runner, cache = engine(folders[name], dtype, page, 256)
+    (tokens,) = prompts(config["vocab_size"], (97,), seed=3)
+    steps = [([("r", tokens[:65])], [])] + [([("r", [t])], []) for t in tokens[65:]]
+    got = replay(runner, cache, steps)["r"]
+    assert_close(got, plain[name].logits(tokens), dtype, f"{name} decode")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", list(CONFIGS))
+def test_portions_of_changing_size(folders, plain, name, dtype):
+    config, _, page = CONFIGS[name]
+    runner, cache = engine(folders[name], dtype, page, 256)
+    (tokens,) = prompts(config["vocab_size"], (131,), seed=4)
+    for sizes in ((7, 2, 13, 3, 2, 5), (2,), (33, 1, 31)):
+        steps = [([("r", part)], []) for part in cut(tokens, sizes)]
+        steps[-1] = (steps[-1][0], ["r"])
+        got = replay(runner, cache, steps)["r"]
+        assert_close(got, plain[name].logits(tokens), dtype, f"{name} portions {sizes}")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", list(CONFIGS))
+def test_mixed_batches_with_page_reuse(folders, plain, name, dtype):
+    """Up to four live requests, portions of some beside decoded tokens of others, in a pool
+    so small that pages of finished requests are handed to later ones."""
+    config, _, page = CONFIGS[name]
+    lengths = (40, 64, 23, 50, 17, 61, 9, 33)
+    requests = dict(enumerate(prompts(config["vocab_size"], lengths, seed=5)))
+    capacity = 4 * 64
+    runner, cache = engine(folders[name], dtype, page, capacity, max_requests=4)
+    waiting = list(requests)
+    live: dict[int, int] = {}          # id -> tokens fed
+    steps, turn = [], 0
+    while waiting or live:
+        while waiting and len(live) < 4:
+            live[waiting.pop(0)] = 0
+        entries, end = [], []
+        for slot, request_id in enumerate(list(live)):
+            tokens, fed = requests[request_id], live[request_id]
+            prompt_part = len(tokens) - 8          # the last 8 tokens come one at a time
+            if fed < prompt_part:
+                size = min((5, 2, 11, 3)[(turn + slot) % 4], prompt_part - fed)
+            else:
+                size = 1
+            if (turn + slot) % 5 == 4 and fed > 0:
+                continue                            # left out of this step, goes on later
+            entries.append((request_id, tokens[fed:fed + size]))
+            live[request_id] = fed + size
+            if live[request_id] == len(tokens):
+                end.append(request_id)
+                del live[request_id]
+        if entries:
+            steps.append((entries, end))
+        turn += 1
+    got = replay(runner, cache, steps)
+    assert cache.stats().pages_low_water[0] < cache.stats().pages_total[0] // 2
+    for request_id, tokens in requests.items():
+        assert_close(got[request_id], plain[name].logits(tokens), dtype,
+                     f"{name} mixed request {request_id}")
+    assert not cache.requests()

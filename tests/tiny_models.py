@@ -1,0 +1,107 @@
+"""Tiny LFM2 configurations for the tests, and helpers that replay requests.
+
+The configurations differ in every size and option: layer order and first layer kind, hidden
+size, head count, key-head groups (2 per key head, all on one key head, 3 per key head), head
+size (16, 32, 48), feed-forward rule (given width, auto-adjusted), vocabulary (a power of two
+and not), rope theta, convolution width (3, 4, 2) and bias, tied and separate head, norm eps,
+and a sliding window in one of them.
+"""
+
+from __future__ import annotations
+
+import tempfile
+from pathlib import Path
+
+import torch
+
+TINY_A = dict(
+    model_type="lfm2", num_hidden_layers=4,
+    layer_types=["conv", "full_attention", "conv", "full_attention"],
+    hidden_size=64, num_attention_heads=4, num_key_value_heads=2,
+    block_auto_adjust_ff_dim=False, block_ff_dim=192, vocab_size=512, rope_theta=10000.0,
+    conv_L_cache=3, conv_bias=False, tie_embedding=True, norm_eps=1e-5)
+
+TINY_B = dict(
+    model_type="lfm2", num_hidden_layers=6,
+    layer_types=["full_attention", "conv", "conv", "full_attention", "conv", "full_attention"],
+    hidden_size=96, num_attention_heads=3, num_key_value_heads=1,
+    block_auto_adjust_ff_dim=True, block_ff_dim=384, block_multiple_of=64,
+    block_ffn_dim_multiplier=1.0, vocab_size=1000, rope_theta=1000000.0,
+    conv_L_cache=4, conv_bias=True, tie_embedding=False, norm_eps=1e-6)
+
+TINY_C = dict(
+    model_type="lfm2", num_hidden_layers=5,
+    layer_types=["conv", "sliding_attention", "full_attention", "sliding_attention", "conv"],
+    hidden_size=288, num_attention_heads=6, num_key_value_heads=2,
+    block_auto_adjust_ff_dim=True, block_ff_dim=500, block_multiple_of=20,
+    block_ffn_dim_multiplier=1.3, vocab_size=777, rope_theta=50000.0, sliding_window=19,
+    conv_L_cache=2, conv_bias=False, tie_embedding=True, norm_eps=3e-6)
+
+CONFIGS = {"A": (TINY_A, 0, 4), "B": (TINY_B, 1, 8), "C": (TINY_C, 2, 16)}   # config, seed, page
+
+# (atol, rtol) on logits: |engine - plain| <= atol + rtol * |plain|, as the reference gates
+# its own parity runs (src/mlx_one/inference_baseline.py:30).
+TOLERANCE = {torch.float32: (1e-4, 1e-4), torch.bfloat16: (5e-2, 1e-2)}
+
+
+def make_model_dir(name: str, root: Path | None = None, dtype=torch.bfloat16) -> Path:
+    """Writes the tiny model ``name`` into a fresh temporary folder (never into the repo)."""
+    from mlx_one_b200.weights import write_random_model
+
+    config, seed, _ = CONFIGS[name]
+    folder = Path(tempfile.mkdtemp(prefix=f"tiny_{name}_", dir=root))
+    return write_random_model(folder, config, seed, dtype)
+
+
+def prompts(vocab: int, lengths, seed: int = 0):
+    generator = torch.Generator().manual_seed(seed)
+    return [torch.randint(0, vocab, (n,), generator=generator).tolist() for n in lengths]
+
+
+def assert_close(got: torch.Tensor, want: torch.Tensor, dtype, what: str = "") -> None:
+    atol, rtol = TOLERANCE[dtype]
+    got, want = got.float().cpu(), want.float().cpu()
+    excess = (got - want).abs() - (atol + rtol * want.abs())
+    worst = excess.max().item()
+    if not worst <= 0:
+        index = int(excess.argmax())
+        row = index // got.shape[-1] if got.dim() > 1 else 0
+        raise AssertionError(
+            f"{what}: logits differ by {(got - want).abs().max().item():.3e} "
+            f"(allowed {atol} + {rtol}*|ref|), first at row {row}; "
+            f"rows over tolerance: {torch.nonzero((excess > 0).any(dim=-1)).flatten().tolist()[:8]}")
+
+
+def replay(runner, cache, steps):
+    """Runs ``steps`` = list of (entries, end) with entries = [(id, tokens)], asking for
+    logits everywhere. Returns {id: float32 logits [all its tokens, vocab]} on the host."""
+    from mlx_one_b200.engine.runner import StepEntry
+
+    collected: dict = {}
+    for entries, end in steps:
+        batch = []
+        for request_id, tokens in entries:
+            if request_id not in cache:
+                cache.open(request_id)
+            batch.append(StepEntry(request_id, tokens, range(len(tokens))))
+        logits = runner.step(batch)
+        at = 0
+        for request_id, tokens in entries:
+            collected.setdefault(request_id, []).append(logits[at:at + len(tokens)].float().cpu())
+            at += len(tokens)
+        for request_id in end:
+            cache.close(request_id)
+        cache.check()
+    runner.ops.check_errors()
+    return {key: torch.cat(parts) for key, parts in collected.items()}
+
+
+def cut(tokens, sizes):
+    """Cuts ``tokens`` into portions of the given sizes, cycling; the rest in one piece."""
+    out, at, i = [], 0, 0
+    while at < len(tokens):
+        size = sizes[i % len(sizes)]
+        out.append(tokens[at:at + size])
+        at += size
+        i += 1
+    return out
