@@ -7,3 +7,10 @@ Every forward kernel is hand-written CUDA for sm_100a.
 """
 
 __version__ = "0.1.0"
+
+from .engine import BatchingConfig, CacheConfig, Engine, load_model
+from .sampling import GenerationChunk, GenerationResult, TextGenerationOptions
+from .weights import write_random_model
+
+__all__ = ["BatchingConfig", "CacheConfig", "Engine", "load_model", "GenerationChunk",
+           "GenerationResult", "TextGenerationOptions", "write_random_model"]

@@ -41,11 +41,11 @@ __device__ __forceinline__ double block_sum_double(double v, double* scratch) {
     return scratch[32];
 }
 
-__global__ void __launch_bounds__(THREADS)
-argmax_kernel(const float* __restrict__ logits, int vocab, int* __restrict__ out) {
+// Index of the largest value of a row, the lowest index among equals. All threads of the
+// block call it; thread 0 gets the result.
+__device__ __forceinline__ int block_argmax(const float* __restrict__ row, int vocab) {
     __shared__ float best_value[THREADS / 32];
     __shared__ int best_index[THREADS / 32];
-    const float* row = logits + (size_t)blockIdx.x * vocab;
     float value = -INFINITY;
     int index = 0x7fffffff;
     for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
@@ -67,8 +67,14 @@ argmax_kernel(const float* __restrict__ logits, int vocab, int* __restrict__ out
             if (best_value[w] > value || (best_value[w] == value && best_index[w] < index)) {
                 value = best_value[w]; index = best_index[w];
             }
-        out[blockIdx.x] = index == 0x7fffffff ? 0 : index;
     }
+    return index == 0x7fffffff ? 0 : index;
+}
+
+__global__ void __launch_bounds__(THREADS)
+argmax_kernel(const float* __restrict__ logits, int vocab, int* __restrict__ out) {
+    const int index = block_argmax(logits + (size_t)blockIdx.x * vocab, vocab);
+    if (threadIdx.x == 0) out[blockIdx.x] = index;
 }
 
 __device__ __forceinline__ float uniform_from(long long seed, int step) {
@@ -80,7 +86,7 @@ __device__ __forceinline__ float uniform_from(long long seed, int step) {
     return (float)(z >> 40) * (1.0f / 16777216.0f);
 }
 
-// Per row: temperature[r] == 0 -> argmax. top_k[r] <= 0 -> no top-k. top_p[r] >= 1 -> none.
+// Per row: temperature[r] <= 0 -> argmax. top_k[r] <= 0 -> no top-k. top_p[r] >= 1 -> none.
 __global__ void __launch_bounds__(THREADS)
 sample_kernel(const float* __restrict__ logits, int vocab, const float* __restrict__ temperature,
               const int* __restrict__ top_k, const float* __restrict__ top_p,
@@ -96,6 +102,11 @@ sample_kernel(const float* __restrict__ logits, int vocab, const float* __restri
     const float* row = logits + (size_t)r * vocab;
     float* p = probabilities + (size_t)r * vocab;
     const int tid = threadIdx.x;
+    if (!(temperature[r] > 0.f)) {          // greedy row in a mixed batch
+        const int index = block_argmax(row, vocab);
+        if (tid == 0) out[r] = index;
+        return;
+    }
 
     // ---- probabilities (numerators of the softmax)
     float local_max = -INFINITY;

@@ -1,0 +1,347 @@
+"""The Python entry point: ``Engine`` with generate / stream / submit, in the manner of the
+reference's ``Engine`` (src/mlx_one/engine/public.py:61-485) and text API
+(src/mlx_one/text/generation.py:209-263).
+
+Differences that the GPU design brings: requests are batched continuously by one scheduler
+and run through one step function, the caller's thread drives the loop (no actor thread),
+and there are entry points that take and return token ids, because a model with random
+weights has no tokenizer.
+"""
+
+from __future__ import annotations
+
+import time
+from dataclasses import dataclass
+from pathlib import Path
+from typing import Any, Iterator, Sequence
+
+import torch
+
+from ..cache.manager import CacheManager
+from ..sampling.options import GenerationChunk, GenerationResult, TextGenerationOptions
+from ..sampling.sampler import Sampler
+from .loading import LoadedModel, load_model
+from .runner import Runner, StepEntry
+from .scheduler import BatchingConfig, Phase, Request, Scheduler
+
+
+@dataclass(frozen=True)
+class CacheConfig:
+    """``block_size_tokens``: tokens per page (the reference's name,
+    src/mlx_one/engine/cache_specs.py:174-204). The pool's size is ``capacity_tokens`` if
+    given, else what ``memory_budget_bytes`` buys, else 64 * 1024 tokens."""
+
+    block_size_tokens: int = 16
+    capacity_tokens: int | None = None
+    memory_budget_bytes: int | None = None
+    max_requests: int | None = None
+
+    def __post_init__(self) -> None:
+        if self.block_size_tokens not in (1, 2, 4, 8, 16, 32, 64, 128):
+            raise ValueError("cache block size must be a power of two up to 128")
+        for name in ("capacity_tokens", "memory_budget_bytes", "max_requests"):
+            value = getattr(self, name)
+            if value is not None and value < 1:
+                raise ValueError(f"{name} must be positive")
+
+
+class EngineRequestHandle:
+    """A submitted request. ``result()`` drives the engine until the request is done."""
+
+    def __init__(self, engine: "Engine", request: Request, prompt_text: str) -> None:
+        self._engine = engine
+        self.request = request
+        self.prompt_text = prompt_text
+        self.submitted_at = time.perf_counter()
+        self.first_token_at: float | None = None
+        self.finished_at: float | None = None
+
+    def done(self) -> bool:
+        return self.request.phase is Phase.FINISHED
+
+    def cancel(self) -> None:
+        self._engine._scheduler.cancel(self.request)
+
+    def result(self) -> GenerationResult:
+        while not self.done():
+            self._engine.step()
+        return self._engine._result(self)
+
+
+class Engine:
+    def __init__(self, model: str | Path | LoadedModel, *, cache_config: CacheConfig | None = None,
+                 batching_config: BatchingConfig | None = None,
+                 execution_dtype: str | None = None, device: str = "cuda:0",
+                 ops: Any = None) -> None:
+        """``model``: a model folder (config.json + safetensors) or a loaded model.
+        ``execution_dtype``: "bfloat16" (default) or "float32" (everything in true 32-bit)."""
+        self._loaded = model if isinstance(model, LoadedModel) else load_model(
+            model, execution_dtype or "bfloat16", device, ops)
+        built = self._loaded.model
+        self.cache_config = cache_config or CacheConfig()
+        self.batching_config = batching_config or BatchingConfig()
+        capacity = self.cache_config.capacity_tokens
+        if capacity is None and self.cache_config.memory_budget_bytes is not None:
+            capacity = max(self.cache_config.memory_budget_bytes // self._bytes_per_token(), 1)
+        if capacity is None:
+            capacity = 64 * 1024
+        max_requests = self.cache_config.max_requests or max(self.batching_config.max_sequences, 1)
+        self._cache = CacheManager(
+            built.cache_needs, page_size=self.cache_config.block_size_tokens,
+            capacity_tokens=capacity, max_requests=max_requests, dtype=built.runtime.dtype,
+            device=built.runtime.device,
+            max_step_tokens=self.batching_config.max_scheduled_tokens)
+        self._runner = Runner(built, self._cache)
+        self._scheduler = Scheduler(self.batching_config, self._cache)
+        self._sampler = Sampler(built.ops, built.runtime.device)
+        self._handles: dict[Any, EngineRequestHandle] = {}
+        self._tokenizer = self._load_tokenizer()
+        self._stats = {"steps": 0, "tokens_run": 0, "tokens_sampled": 0}
+        self._pinned = None
+
+    # ------------------------------------------------------------------ set-up
+
+    def _bytes_per_token(self) -> int:
+        from ..parts.base import PagedKeyValues
+
+        size = torch.empty((), dtype=self._loaded.model.runtime.dtype).element_size()
+        total = sum(2 * need.kv_heads * need.head_dim * size
+                    for need in self._loaded.model.cache_needs.values()
+                    if isinstance(need, PagedKeyValues))
+        return max(total, 1)
+
+    def _load_tokenizer(self):
+        path = self._loaded.path / "tokenizer.json" if self._loaded.path else None
+        if path is None or not path.is_file():
+            return None
+        from tokenizers import Tokenizer
+
+        return Tokenizer.from_file(str(path))
+
+    @property
+    def model(self):
+        return self._loaded.model
+
+    @property
+    def cache(self) -> CacheManager:
+        return self._cache
+
+    # ------------------------------------------------------------------ text <-> ids
+
+    def encode(self, prompt: str) -> list[int]:
+        """Prompt text -> token ids, with a BOS token in front if the tokenizer did not put
+        one there (the reference's rule for LFM2, src/mlx_one/text/prompts.py:6-17)."""
+        if self._tokenizer is None:
+            raise ValueError("this model folder has no tokenizer.json; pass token ids "
+                             "(generate_ids) instead of text")
+        ids = list(self._tokenizer.encode(prompt).ids)
+        bos = self._loaded.spec.bos_token_id
+        if bos is not None and (not ids or ids[0] != bos):
+            ids.insert(0, bos)
+        return ids
+
+    def decode(self, ids: Sequence[int]) -> str:
+        if self._tokenizer is None:
+            return ""
+        return self._tokenizer.decode(list(ids))
+
+    # ------------------------------------------------------------------ requests
+
+    def _options(self, options, kwargs) -> TextGenerationOptions:
+        if options is not None and kwargs:
+            raise ValueError("pass options or option keywords, not both")
+        return options if options is not None else TextGenerationOptions(**kwargs)
+
+    def submit_ids(self, prompt_ids: Sequence[int], options: TextGenerationOptions | None = None,
+                   *, prompt_text: str = "", **option_kwargs) -> EngineRequestHandle:
+        options = self._options(options, option_kwargs)
+        prompt = tuple(int(t) for t in prompt_ids)
+        limit = self._loaded.spec.max_positions
+        if len(prompt) >= limit:
+            raise ValueError(f"prompt of {len(prompt)} tokens reaches the model's {limit} positions")
+        if len(prompt) + options.max_tokens > limit:
+            options = TextGenerationOptions(**{**options.__dict__,
+                                               "max_tokens": limit - len(prompt)})
+        request = Request(self._scheduler.new_id(), prompt, options,
+                          eos_token_ids=self._loaded.spec.eos_token_ids)
+        self._scheduler.submit(request)
+        handle = EngineRequestHandle(self, request, prompt_text)
+        self._handles[request.request_id] = handle
+        return handle
+
+    def submit(self, prompt: str, options: TextGenerationOptions | None = None,
+               **option_kwargs) -> EngineRequestHandle:
+        return self.submit_ids(self.encode(prompt), self._options(options, option_kwargs),
+                               prompt_text=prompt)
+
+    # ------------------------------------------------------------------ the loop
+
+    def step(self) -> list[Request]:
+        """One scheduler turn: plan, run the batch, sample, commit. Returns the requests
+        that got a token or finished."""
+        planned = self._scheduler.plan()
+        if not planned:
+            return []
+        entries = [StepEntry(item.request.request_id, item.tokens,
+                             (len(item.tokens) - 1,) if item.samples else ())
+                   for item in planned]
+        logits = self._runner.step(entries)
+        sampled: list[int] = []
+        drawing = [item.request for item in planned if item.samples]
+        if drawing:
+            tokens = self._sampler.select(logits, [r.options for r in drawing],
+                                          [len(r.output) for r in drawing])
+            sampled = self._to_host(tokens)
+        touched = self._scheduler.commit(planned, sampled)
+        now = time.perf_counter()
+        for request in touched:
+            handle = self._handles.get(request.request_id)
+            if handle is None:
+                continue
+            if handle.first_token_at is None:
+                handle.first_token_at = now
+            if request.phase is Phase.FINISHED:
+                handle.finished_at = now
+        self._stats["steps"] += 1
+        self._stats["tokens_run"] += sum(len(item.tokens) for item in planned)
+        self._stats["tokens_sampled"] += len(sampled)
+        return touched
+
+    def _to_host(self, tokens: torch.Tensor) -> list[int]:
+        if tokens.device.type != "cuda":
+            return tokens.tolist()
+        if self._pinned is None or self._pinned.numel() < tokens.numel():
+            self._pinned = torch.empty(max(tokens.numel(), 256), dtype=torch.int32,
+                                       pin_memory=True)
+        view = self._pinned[:tokens.numel()]
+        view.copy_(tokens, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        return view.tolist()
+
+    def run(self) -> None:
+        """Drives the loop until no request is waiting or running."""
+        while self._scheduler.has_work():
+            self.step()
+
+    # ------------------------------------------------------------------ results
+
+    def _result(self, handle: EngineRequestHandle) -> GenerationResult:
+        request = handle.request
+        self._handles.pop(request.request_id, None)
+        finished = handle.finished_at or time.perf_counter()
+        first = handle.first_token_at or finished
+        count = len(request.output)
+        timings = {"total_s": finished - handle.submitted_at,
+                   "time_to_first_token_s": first - handle.submitted_at}
+        if count > 1 and finished > first:
+            # decoding speed leaves out the prompt and the first token, as the reference does
+            timings["decode_tokens_per_s"] = (count - 1) / (finished - first)
+        reason = request.finish_reason or "length"
+        text = self._apply_stop(self.decode(request.output), request.options.stop)[0]
+        return GenerationResult(
+            prompt=handle.prompt_text, text=text, prompt_tokens=len(request.prompt),
+            generation_tokens=count, finish_reason="stop" if reason == "cancelled" else reason,
+            model=str(self._loaded.path), timings=timings, token_ids=tuple(request.output))
+
+    @staticmethod
+    def _apply_stop(text: str, stop: Sequence[str]) -> tuple[str, bool]:
+        cut = min((text.find(s) for s in stop if s in text), default=-1)
+        return (text, False) if cut < 0 else (text[:cut], True)
+
+    def generate_ids(self, prompt_ids: Sequence[int], options: TextGenerationOptions | None = None,
+                     **option_kwargs) -> GenerationResult:
+        return self.submit_ids(prompt_ids, self._options(options, option_kwargs)).result()
+
+    def generate_batch_ids(self, prompts: Sequence[Sequence[int]],
+                           options: TextGenerationOptions | Sequence[TextGenerationOptions]
+                           | None = None) -> list[GenerationResult]:
+        """Submits all prompts (waiting for queue room as needed) and runs them together."""
+        many = list(options) if isinstance(options, (list, tuple)) else [options] * len(prompts)
+        handles = []
+        for prompt, option in zip(prompts, many):
+            while len(self._scheduler.waiting) >= self.batching_config.queue_size:
+                self.step()
+            handles.append(self.submit_ids(prompt, option))
+        self.run()
+        return [handle.result() for handle in handles]
+
+    def generate(self, prompt: str, options: TextGenerationOptions | None = None,
+                 **option_kwargs) -> GenerationResult:
+        return self.submit(prompt, self._options(options, option_kwargs)).result()
+
+    def stream_ids(self, prompt_ids: Sequence[int], options: TextGenerationOptions | None = None,
+                   **option_kwargs) -> Iterator[GenerationChunk]:
+        handle = self.submit_ids(prompt_ids, self._options(options, option_kwargs))
+        yield from self._stream(handle)
+
+    def stream(self, prompt: str, options: TextGenerationOptions | None = None,
+               **option_kwargs) -> Iterator[GenerationChunk]:
+        handle = self.submit(prompt, self._options(options, option_kwargs))
+        yield from self._stream(handle)
+
+    def _stream(self, handle: EngineRequestHandle) -> Iterator[GenerationChunk]:
+        request, sent, text_sent = handle.request, 0, ""
+        stop = request.options.stop
+        while True:
+            if not handle.done():
+                self.step()
+            while sent < len(request.output):
+                sent += 1
+                piece = ""
+                if self._tokenizer is not None:
+                    text, matched = self._apply_stop(self.decode(request.output[:sent]), stop)
+                    # hold back text that may still turn into a stop string
+                    safe = text if matched or handle.done() else self._hold_back(text, stop)
+                    piece, text_sent = safe[len(text_sent):], max(safe, text_sent, key=len)
+                    if matched:
+                        self._scheduler.finish(request, "stop")
+                        yield GenerationChunk(request.output[sent - 1], piece, sent, "stop")
+                        self._handles.pop(request.request_id, None)
+                        return
+                yield GenerationChunk(request.output[sent - 1], piece, sent)
+            if handle.done():
+                reason = request.finish_reason or "length"
+                yield GenerationChunk(None, "", sent, "stop" if reason == "cancelled" else reason,
+                                      request.terminal_token_id)
+                self._handles.pop(request.request_id, None)
+                return
+
+    @staticmethod
+    def _hold_back(text: str, stop: Sequence[str]) -> str:
+        keep = 0
+        for s in stop:
+            for size in range(min(len(s) - 1, len(text)), 0, -1):
+                if text.endswith(s[:size]):
+                    keep = max(keep, size)
+                    break
+        return text[:len(text) - keep] if keep else text
+
+    # ------------------------------------------------------------------ introspection
+
+    def runtime_stats(self) -> dict[str, Any]:
+        cache = self._cache.stats()
+        return {**self._stats, "waiting": len(self._scheduler.waiting),
+                "running": len(self._scheduler.running), "pages_total": cache.pages_total,
+                "pages_free": cache.pages_free, "pages_low_water": cache.pages_low_water,
+                "slots_free": cache.slots_free, "kernel_launches": self.model.ops.launches}
+
+    def capabilities(self) -> dict[str, Any]:
+        return {"architecture": self._loaded.spec.architecture,
+                "dtype": str(self.model.runtime.dtype).replace("torch.", ""),
+                "mixed_prefill_decode": True, "paged_cache": True,
+                "page_size": self.cache_config.block_size_tokens,
+                "capacity_tokens": self._cache.capacity_tokens,
+                "max_sequences": self.batching_config.max_sequences,
+                "sampling": ["greedy", "temperature", "top_k", "top_p", "seed"]}
+
+    def close(self) -> None:
+        for request in list(self._scheduler.running) + list(self._scheduler.waiting):
+            self._scheduler.cancel(request)
+        self._scheduler.plan()
+        self._cache.close_all()
+
+    def __enter__(self) -> "Engine":
+        return self
+
+    def __exit__(self, *exc) -> None:
+        self.close()

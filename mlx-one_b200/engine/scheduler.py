@@ -1,0 +1,210 @@
+"""The scheduler above the step function: admits requests, cuts prompts into portions under
+a token budget, decodes, finishes and frees. Host-only; it never touches a tensor.
+
+Decisions:
+
+* Admission is by reservation of a request's whole future (prompt + max_tokens), as in the
+  reference (src/mlx_one/text/generation.py:114-123, src/mlx_one/engine/cache_manager.py:
+  283-341). A request that could never fit is rejected when it is submitted; one that does
+  not fit now waits. So pages cannot run out in the middle of a request, and nothing is ever
+  preempted or recomputed. The waiting queue is served oldest first, but a request that does
+  not fit now does not block a younger one that does.
+* A step holds every running decode (one token each), then prompt portions of the running
+  requests, oldest first, each at most ``prefill_chunk_size`` tokens, all prompt tokens
+  together at most ``max_prefill_tokens``, everything together at most
+  ``max_scheduled_tokens``. The reference's BatchScheduler chooses under the same three
+  limits (src/mlx_one/engine/batching.py:81-117) but runs decodes and prompts as separate
+  forwards; here they are one batch. If decodes alone exceed the budget they take turns.
+"""
+
+from __future__ import annotations
+
+import enum
+import itertools
+from collections import deque
+from dataclasses import dataclass, field
+from typing import Any, Sequence
+
+from ..cache.errors import CacheCapacityError
+from ..cache.manager import CacheManager
+from ..sampling.options import TextGenerationOptions
+
+
+@dataclass(frozen=True)
+class BatchingConfig:
+    """Names and defaults of the reference's BatchingConfig (src/mlx_one/engine/batching.py:
+    24-46), for the options that this scheduler has."""
+
+    max_sequences: int = 1
+    queue_size: int = 8
+    prefill_chunk_size: int = 512
+    max_scheduled_tokens: int = 2048
+    max_prefill_tokens: int = 1024
+
+    def __post_init__(self) -> None:
+        for name in ("max_sequences", "queue_size", "prefill_chunk_size",
+                     "max_scheduled_tokens", "max_prefill_tokens"):
+            value = getattr(self, name)
+            if isinstance(value, bool) or not isinstance(value, int) or value < 1:
+                raise ValueError(f"{name} must be positive")
+
+
+class QueueFullError(RuntimeError):
+    """More requests are waiting than ``queue_size`` allows."""
+
+
+class Phase(enum.Enum):
+    WAITING = "waiting"
+    PREFILL = "prefill"
+    DECODE = "decode"
+    FINISHED = "finished"
+
+
+@dataclass
+class Request:
+    request_id: Any
+    prompt: tuple[int, ...]
+    options: TextGenerationOptions
+    eos_token_ids: tuple[int, ...] = ()
+    phase: Phase = Phase.WAITING
+    fed: int = 0                                     # prompt tokens already run
+    output: list[int] = field(default_factory=list)
+    next_token: int | None = None                    # sampled, to be fed by the next step
+    finish_reason: str | None = None                 # "stop" | "length" | "cancelled"
+    terminal_token_id: int | None = None
+    cancelled: bool = False
+
+    @property
+    def reserve_tokens(self) -> int:
+        # the last sampled token is never fed back, so it needs no place in the cache
+        return len(self.prompt) + self.options.max_tokens - 1
+
+
+@dataclass
+class Scheduled:
+    """One request's share of a planned step."""
+
+    request: Request
+    tokens: tuple[int, ...]
+    samples: bool                # logits at the last token are wanted and a token is drawn
+
+
+class Scheduler:
+    def __init__(self, config: BatchingConfig, cache: CacheManager) -> None:
+        self.config = config
+        self.cache = cache
+        self.waiting: deque[Request] = deque()
+        self.running: list[Request] = []
+        self._decode_turn = 0
+        self._ids = itertools.count()
+
+    # ------------------------------------------------------------------ requests
+
+    def new_id(self) -> int:
+        return next(self._ids)
+
+    def submit(self, request: Request) -> None:
+        if not request.prompt:
+            raise ValueError("a request needs at least one prompt token")
+        if len(self.waiting) >= self.config.queue_size:
+            raise QueueFullError(f"{len(self.waiting)} requests are already waiting")
+        if not self.cache.fits_ever(request.reserve_tokens):
+            raise CacheCapacityError(
+                f"prompt of {len(request.prompt)} tokens plus {request.options.max_tokens} new "
+                f"tokens can never fit into a cache of {self.cache.capacity_tokens} tokens",
+                retryable=False)
+        request.phase = Phase.WAITING
+        self.waiting.append(request)
+
+    def cancel(self, request: Request) -> None:
+        """Takes effect between steps: the request is finished and freed by the next plan."""
+        request.cancelled = True
+
+    def has_work(self) -> bool:
+        return bool(self.waiting or self.running)
+
+    # ------------------------------------------------------------------ one step
+
+    def _admit(self) -> None:
+        for request in list(self.waiting):
+            if len(self.running) >= self.config.max_sequences:
+                break
+            if request.cancelled:
+                self.waiting.remove(request)
+                self._finish(request, "cancelled", held=False)
+                continue
+            try:
+                self.cache.open(request.request_id, reserve_tokens=request.reserve_tokens)
+            except CacheCapacityError as error:
+                if not error.retryable:
+                    self.waiting.remove(request)
+                    self._finish(request, "cancelled", held=False)
+                continue                     # does not fit now; a younger one may
+            self.waiting.remove(request)
+            request.phase = Phase.PREFILL
+            self.running.append(request)
+
+    def plan(self) -> list[Scheduled]:
+        """Frees cancelled requests, admits waiting ones and chooses the next step."""
+        for request in [r for r in self.running if r.cancelled]:
+            self._finish(request, "cancelled")
+        self._admit()
+        config = self.config
+        budget = config.max_scheduled_tokens
+        step: list[Scheduled] = []
+        decodes = [r for r in self.running if r.phase is Phase.DECODE]
+        if len(decodes) > budget:
+            start = self._decode_turn % len(decodes)
+            decodes = (decodes[start:] + decodes[:start])[:budget]
+            self._decode_turn += budget
+        for request in decodes:
+            step.append(Scheduled(request, (request.next_token,), True))
+        budget -= len(decodes)
+        prefill_budget = min(budget, config.max_prefill_tokens)
+        for request in self.running:
+            if request.phase is not Phase.PREFILL or prefill_budget < 1:
+                continue
+            size = min(len(request.prompt) - request.fed, config.prefill_chunk_size,
+                       prefill_budget)
+            tokens = request.prompt[request.fed:request.fed + size]
+            last = request.fed + size == len(request.prompt)
+            step.append(Scheduled(request, tokens, last))
+            prefill_budget -= size
+        return step
+
+    def commit(self, step: Sequence[Scheduled], sampled: Sequence[int]) -> list[Request]:
+        """Records a finished step: ``sampled`` has one token per entry with ``samples``.
+        Returns the requests that produced a token or finished."""
+        touched, drawn = [], iter(sampled)
+        for item in step:
+            request = item.request
+            if request.phase is Phase.PREFILL:
+                request.fed += len(item.tokens)
+            if not item.samples:
+                continue
+            token = int(next(drawn))
+            request.phase = Phase.DECODE
+            touched.append(request)
+            if token in request.eos_token_ids and not request.options.ignore_eos:
+                request.terminal_token_id = token
+                self._finish(request, "stop")
+                continue
+            request.output.append(token)
+            request.next_token = token
+            if len(request.output) >= request.options.max_tokens:
+                self._finish(request, "length")
+        return touched
+
+    def finish(self, request: Request, reason: str) -> None:
+        """Ends a running request from outside (a stop string matched)."""
+        if request.phase is not Phase.FINISHED:
+            self._finish(request, reason)
+
+    def _finish(self, request: Request, reason: str, held: bool = True) -> None:
+        request.finish_reason = reason
+        request.phase = Phase.FINISHED
+        request.next_token = None
+        if request in self.running:
+            self.running.remove(request)
+        if held and request.request_id in self.cache:
+            self.cache.close(request.request_id)
