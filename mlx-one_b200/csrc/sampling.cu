@@ -257,6 +257,35 @@ sample_kernel(const float* __restrict__ logits, int vocab, const float* __restri
 
 }  // namespace
 
+// After a decode step whose tokens were chosen on the device: the chosen token becomes the
+// request's next input, its position moves on by one, and the token is recorded in
+// record[*counter, r]. Lets decode steps follow one another without the host.
+__global__ void decode_advance_kernel(const int* __restrict__ chosen, int* __restrict__ token_ids,
+                                      int* __restrict__ positions, int* __restrict__ history,
+                                      int* __restrict__ record, int* __restrict__ counter,
+                                      int requests, int max_steps) {
+    const int r = blockIdx.x * blockDim.x + threadIdx.x;
+    const int step = *counter;
+    if (r < requests) {
+        token_ids[r] = chosen[r];
+        positions[r] += 1;
+        history[r] += 1;
+        if (step < max_steps) record[(size_t)step * requests + r] = chosen[r];
+    }
+    __syncthreads();
+    if (blockIdx.x == 0 && threadIdx.x == 0) *counter = step + 1;
+}
+
+MLXONE_API int mlxone_decode_advance(const int* chosen, int* token_ids, int* positions,
+                                     int* history, int* record, int* counter, int requests,
+                                     int max_steps, cudaStream_t stream) {
+    MLXONE_REQUIRE(requests > 0 && requests <= 1024, "decode_advance: 1..1024 requests");
+    decode_advance_kernel<<<1, 1024, 0, stream>>>(chosen, token_ids, positions, history, record,
+                                                 counter, requests, max_steps);
+    MLXONE_LAUNCH_CHECK("decode_advance");
+    return 0;
+}
+
 MLXONE_API int mlxone_argmax(const float* logits, int rows, int vocab, int* out,
                              cudaStream_t stream) {
     if (rows == 0) return 0;

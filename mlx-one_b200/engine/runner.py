@@ -34,6 +34,29 @@ def _align(value: int, to: int = 4) -> int:
     return -(-value // to) * to
 
 
+@dataclass
+class _DecodeGraph:
+    """A captured decode-only step: its own metadata buffer (so that addresses never
+    change), the graph, and the tensors it leaves its results in."""
+
+    meta: torch.Tensor
+    graph: Any = None
+    logits: torch.Tensor | None = None
+    uses: int = 0
+    counter: torch.Tensor | None = None
+    record: torch.Tensor | None = None
+    _record: torch.Tensor | None = None
+
+    def record_buffer(self, like: torch.Tensor) -> torch.Tensor:
+        """A buffer at a fixed address that holds at least as many steps as ``like``."""
+        if self._record is None:
+            self._record = torch.zeros((max(like.shape[0], 4096), like.shape[1]),
+                                       dtype=torch.int32, device=like.device)
+        if like.shape[0] > self._record.shape[0]:
+            raise ValueError(f"at most {self._record.shape[0]} steps in one decode loop")
+        return self._record
+
+
 class Runner:
     def __init__(self, model: Model, cache: CacheManager) -> None:
         self.model = model
@@ -46,6 +69,15 @@ class Runner:
         self._turn = 0
         self.steps = 0
         self.last_shape = (0, 0)
+        self.last_meta_bytes = 0
+        # CUDA graphs of decode-only steps, keyed by (requests, table widths, wanted rows)
+        self.use_graphs = self.device.type == "cuda"
+        self._graphs: dict[tuple, _DecodeGraph] = {}
+        self.graph_replays = 0
+        if self.use_graphs:
+            # library handles must exist before a capture begins
+            warm = torch.zeros((8, 8), dtype=torch.bfloat16, device=self.device)
+            torch.mm(warm, warm)
 
     # ------------------------------------------------------------------ staging
 
@@ -69,6 +101,27 @@ class Runner:
     # ------------------------------------------------------------------ the step
 
     def step(self, entries: Sequence[StepEntry]) -> torch.Tensor | None:
+        return self._step(entries)
+
+    def decode_steps(self, entries: Sequence[StepEntry], steps: int) -> torch.Tensor:
+        """``steps`` greedy decode steps in a row without the host in between: every entry
+        brings its next token; each step's argmax becomes the next step's input on the
+        device. Pages for all steps are taken first. Returns the chosen tokens as int32
+        [steps, requests] on the device (not synchronised)."""
+        if steps < 1 or any(len(e.tokens) != 1 for e in entries):
+            raise ValueError("decode_steps takes one token per request and at least one step")
+        limit = self.model.spec.max_positions
+        for entry in entries:
+            if self.cache.get(entry.request_id).length + steps > limit:
+                raise ValueError(f"request {entry.request_id!r} would pass the model's "
+                                 f"{limit} positions")
+        for entry in entries:
+            self.cache.grow(entry.request_id, steps)
+        entries = [StepEntry(e.request_id, e.tokens, (0,)) for e in entries]
+        record = torch.zeros((steps, len(entries)), dtype=torch.int32, device=self.device)
+        return self._step(entries, loop=(steps, record))
+
+    def _step(self, entries: Sequence[StepEntry], loop=None) -> torch.Tensor | None:
         """Runs the entries as one batch. Returns float32 logits [wanted, vocab] on the
         device in the order of the entries and of their ``want``, or None if nothing is
         wanted. Raises before touching any state if the batch is malformed or pages run
@@ -94,8 +147,9 @@ class Runner:
             if held + len(entry.tokens) > limit:
                 raise ValueError(f"request {entry.request_id!r} would pass the model's "
                                  f"{limit} positions")
-        for entry in entries:
-            self.cache.grow(entry.request_id, len(entry.tokens))
+        if loop is None:
+            for entry in entries:
+                self.cache.grow(entry.request_id, len(entry.tokens))
 
         requests = len(entries)
         tokens = sum(len(e.tokens) for e in entries)
@@ -104,6 +158,10 @@ class Runner:
         paged, states = self.cache.paged, self.cache.states
         widths = [_align(max(max(len(c.tables[g]) for c in caches), 1), 8)
                   for g in range(len(paged))]
+        decode_only = (self.use_graphs or loop is not None) and tokens == requests
+        if decode_only:
+            # few distinct widths, so that few graphs are captured
+            widths = [max(1 << (w - 1).bit_length(), 32) for w in widths]
 
         # one packed int32 buffer: five per-token and per-request lists, block tables, slots
         offsets, cursor = {}, 0
@@ -123,6 +181,7 @@ class Runner:
             region(f"slots{g}", requests)
         host = self._host_buffer(cursor)
         data = host.numpy()
+        self.last_meta_bytes = 4 * cursor
 
         def put(name: str, values) -> None:
             start, size = offsets[name]
@@ -154,6 +213,15 @@ class Runner:
             put(f"slots{g}", [c.slots[g] for c in caches])
 
         device = self._device_buffer
+        captured = None
+        if decode_only:
+            key = (requests, tuple(widths), wanted, loop is not None)
+            captured = self._graphs.get(key)
+            if captured is None:
+                captured = _DecodeGraph(torch.empty(cursor, dtype=torch.int32,
+                                                    device=self.device))
+                self._graphs[key] = captured
+            device = captured.meta
         device[:cursor].copy_(host[:cursor], non_blocking=True)
         if self.device.type == "cuda":
             event = torch.cuda.Event()
@@ -177,12 +245,88 @@ class Runner:
             host={"history": history, "request_start": starts, "positions": positions,
                   "token_request": token_request})
 
-        residual, delta = self.model.forward(ctx)
-        logits = None
-        if wanted:
-            logits = self.model.logits(residual, delta, on_device("rows")[:wanted])
+        def run():
+            residual, delta = self.model.forward(ctx)
+            if not wanted:
+                return None
+            return self.model.logits(residual, delta, on_device("rows")[:wanted])
+
+        if loop is not None:
+            return self._run_loop(captured, run, ctx, entries, *loop)
+        if captured is None:
+            logits = run()
+        else:
+            logits = self._run_captured(captured, run)
         for entry in entries:
             self.cache.advance(entry.request_id, len(entry.tokens))
         self.steps += 1
         self.last_shape = (requests, tokens)
         return logits
+
+    def _run_loop(self, captured, run, ctx, entries, steps, record) -> torch.Tensor:
+        if captured.counter is None:
+            captured.counter = torch.zeros(1, dtype=torch.int32, device=self.device)
+        captured.counter.zero_()
+        captured.record = record
+
+        def one_step():
+            chosen = self.ops.argmax(run())
+            # the graph may outlive this call's record; it always writes to captured.record
+            self.ops.decode_advance(chosen, ctx.token_ids, ctx.positions, ctx.history,
+                                    captured.record_buffer(record), captured.counter)
+
+        done = 0
+        if captured.graph is None or not self.use_graphs:
+            one_step()
+            done = 1
+            captured.uses += 1
+        if done < steps and self.use_graphs and captured.graph is None:
+            graph = torch.cuda.CUDAGraph()
+            try:
+                torch.cuda.current_stream(self.device).synchronize()
+                with torch.cuda.graph(graph):
+                    one_step()
+                captured.graph = graph
+            except Exception as error:
+                import warnings
+
+                warnings.warn(f"CUDA graph capture failed ({error}); decode steps run eagerly")
+                self.use_graphs = False
+                torch.cuda.synchronize(self.device)
+        for _ in range(done, steps):
+            if captured.graph is not None:
+                captured.graph.replay()
+                self.graph_replays += 1
+            else:
+                one_step()
+        out = captured.record_buffer(record)[:steps].clone()
+        for entry in entries:
+            self.cache.advance(entry.request_id, steps)
+        self.steps += steps
+        self.last_shape = (len(entries), len(entries))
+        return out
+
+    def _run_captured(self, captured: _DecodeGraph, run) -> torch.Tensor | None:
+        """Decode-only steps of one shape: the first runs eagerly, the second is captured as
+        a CUDA graph and replayed, later ones replay it. The logits of a replay live in the
+        graph's memory and are overwritten by the next replay of the same shape."""
+        captured.uses += 1
+        if captured.uses == 1 or not self.use_graphs:
+            return run()
+        if captured.graph is None:
+            graph = torch.cuda.CUDAGraph()
+            try:
+                torch.cuda.current_stream(self.device).synchronize()
+                with torch.cuda.graph(graph):
+                    captured.logits = run()
+            except Exception as error:        # capture is an optimisation, never a requirement
+                import warnings
+
+                warnings.warn(f"CUDA graph capture failed ({error}); decode steps run eagerly")
+                self.use_graphs = False
+                torch.cuda.synchronize(self.device)
+                return run()
+            captured.graph = graph
+        captured.graph.replay()
+        self.graph_replays += 1
+        return captured.logits

@@ -217,6 +217,15 @@ class CudaOps:
                    _c_int(logits.shape[1]), _c_void_p(_ptr(out)))
         return out
 
+    def decode_advance(self, chosen, token_ids, positions, history, record, counter):
+        """In place: token_ids = chosen, positions += 1, history += 1,
+        record[counter] = chosen, counter += 1 (all int32 on the device)."""
+        for tensor in (chosen, token_ids, positions, history, record, counter):
+            self._need(tensor, torch.int32, "decode_advance argument")
+        self._call("mlxone_decode_advance", _c_void_p(_ptr(chosen)), _c_void_p(_ptr(token_ids)),
+                   _c_void_p(_ptr(positions)), _c_void_p(_ptr(history)), _c_void_p(_ptr(record)),
+                   _c_void_p(_ptr(counter)), _c_int(chosen.numel()), _c_int(record.shape[0]))
+
     def sample(self, logits, temperature, top_k, top_p, seed, step):
         """Per row: temperature (float32, > 0), top_k (int32, <= 0 = off), top_p (float32,
         >= 1 = off), seed (int64), step (int32). Returns (tokens int32, probabilities)."""

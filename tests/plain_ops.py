@@ -141,6 +141,15 @@ class PlainOps:
     def argmax(self, logits):
         return torch.argmax(logits, dim=-1).to(torch.int32)
 
+    def decode_advance(self, chosen, token_ids, positions, history, record, counter):
+        token_ids.copy_(chosen)
+        positions += 1
+        history += 1
+        step = int(counter)
+        if step < record.shape[0]:
+            record[step] = chosen
+        counter += 1
+
     def sample(self, logits, temperature, top_k, top_p, seed, step):
         """Token-order draw over the reference's kept set, in float64."""
         rows, vocab = logits.shape
