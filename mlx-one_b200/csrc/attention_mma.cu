@@ -1,0 +1,594 @@
+// Paged grouped-query attention on tensor cores (bfloat16): a prefill kernel for portions of
+// any length and a split-key decode kernel for steps in which every request brings one token.
+//
+// Both read keys and values only from the request's pages (this step's own keys were written
+// there before), 64 keys at a time, copied asynchronously into shared memory while the
+// previous 64 are being used. Scores and the softmax statistics are 32-bit; probabilities are
+// rounded to bfloat16 for the second product, whose accumulator is 32-bit again.
+//
+//   prefill: one block = 64 query rows of one (request, query head); 4 warps x 16 rows; all
+//            warps walk the same key tiles (two buffers per block).
+//   decode:  one block = one (request, key head, split of the keys); the rows are the query
+//            heads that share the key head (up to 16 a group); the 4 warps take different
+//            key tiles, each with two buffers of its own, and are merged in shared memory.
+//            With more than one split the block writes (unnormalised output, max, sum) per
+//            row to scratch memory and a second kernel merges the splits.
+//
+// Head sizes: multiples of 16 up to 128. Anything else runs the general kernel.
+#include <cuda_pipeline_primitives.h>
+
+#include "common.cuh"
+
+namespace {
+
+using bf16 = __nv_bfloat16;
+constexpr int KEYS = 64;          // keys per tile
+constexpr int WARPS = 4;
+constexpr float LOG2E = 1.4426950408889634f;
+
+// ------------------------------------------------------------------ small PTX wrappers
+
+__device__ __forceinline__ uint32_t smem_address(const void* p) {
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+__device__ __forceinline__ void copy16(void* dst, const void* src, bool live) {
+    const int bytes = live ? 16 : 0;          // 0 bytes read: the 16 bytes are filled with zero
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(smem_address(dst)),
+                 "l"(src), "r"(bytes));
+}
+__device__ __forceinline__ void copy_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N>
+__device__ __forceinline__ void copy_wait() {
+    asm volatile("cp.async.wait_group %0;\n" ::"n"(N));
+}
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(smem_address(p)));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(smem_address(p)));
+}
+
+// d += a (16x16, row) * b (16x8, col), bfloat16 in, float accumulate
+__device__ __forceinline__ void mma_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0,
+                                          uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "
+        "{%8,%9}, {%0,%1,%2,%3};\n"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&v);
+}
+
+// ------------------------------------------------------------------ tiles in shared memory
+
+// A tile row holds HD bfloat16 plus 16 bytes of padding, which keeps the eight rows that one
+// ldmatrix reads on different banks for every HD that is a multiple of 16.
+template <int HD>
+struct Tile {
+    static constexpr int STRIDE = HD + 8;                 // elements
+    static constexpr int CHUNKS = HD / 8;                 // 16-byte pieces of a row
+};
+
+struct Pages {
+    const bf16* keys;        // [pages, kv_heads, page_size, HD]
+    const bf16* values;
+    const int* table;        // this request's row of the block table
+    int table_width, page_size, kv_heads, kv_head;
+};
+
+// Copies keys first..first+63 of one key head into a K and a V tile; rows outside [lowest,
+// last] or without a page are zero. `lanes` threads take part, this one is `lane`.
+template <int HD>
+__device__ __forceinline__ void load_tile(bf16* k_tile, bf16* v_tile, const Pages& pages, int first,
+                                          int lowest, int last, int lane, int lanes) {
+    using T = Tile<HD>;
+    for (int piece = lane; piece < KEYS * T::CHUNKS; piece += lanes) {
+        const int row = piece / T::CHUNKS, chunk = piece % T::CHUNKS;
+        const int key = first + row;
+        bool live = key >= lowest && key <= last;
+        size_t offset = 0;
+        if (live) {
+            const int block = key / pages.page_size;
+            const int page = block < pages.table_width ? pages.table[block] : -1;
+            live = page >= 0;
+            if (live)
+                offset = (((size_t)page * pages.kv_heads + pages.kv_head) * pages.page_size +
+                          key % pages.page_size) * HD + chunk * 8;
+        }
+        copy16(k_tile + row * T::STRIDE + chunk * 8, pages.keys + offset, live);
+        copy16(v_tile + row * T::STRIDE + chunk * 8, pages.values + offset, live);
+    }
+}
+
+// One warp: 16 query rows (in q_tile, rows row0..row0+15) against one tile of 64 keys.
+// `limit_lo[i]`/`limit_hi[i]` (i = 0: row lane/4, 1: row lane/4 + 8) bound the keys that the row
+// may see. Updates the running max `m`, sum `l` (both in the exp2 domain, scaled) and `o`.
+template <int HD>
+__device__ __forceinline__ void attend_tile(const bf16* q_tile, int row0, const bf16* k_tile,
+                                            const bf16* v_tile, int first, const int (&limit_lo)[2],
+                                            const int (&limit_hi)[2], float scale_log2,
+                                            float (&m)[2], float (&l)[2], float (&o)[HD / 8][4],
+                                            int lane) {
+    using T = Tile<HD>;
+    float s[KEYS / 8][4];
+#pragma unroll
+    for (int j = 0; j < KEYS / 8; ++j)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) s[j][c] = 0.f;
+
+    const int matrix = lane >> 3, r = lane & 7;
+#pragma unroll
+    for (int kk = 0; kk < HD / 16; ++kk) {
+        uint32_t a[4];
+        ldmatrix_x4(a, q_tile + (row0 + r + (matrix & 1) * 8) * T::STRIDE + kk * 16 +
+                           (matrix >> 1) * 8);
+#pragma unroll
+        for (int jj = 0; jj < KEYS / 16; ++jj) {
+            uint32_t b[4];
+            ldmatrix_x4(b, k_tile + (jj * 16 + r + (matrix >> 1) * 8) * T::STRIDE + kk * 16 +
+                               (matrix & 1) * 8);
+            mma_16816(s[2 * jj], a, b[0], b[1]);
+            mma_16816(s[2 * jj + 1], a, b[2], b[3]);
+        }
+    }
+
+    // mask, then the tile's row maxima
+    const int t2 = (lane & 3) * 2;
+    float tile_max[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int j = 0; j < KEYS / 8; ++j)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            const int key = first + j * 8 + t2 + (c & 1);
+            const int i = c >> 1;
+            const bool seen = key >= limit_lo[i] && key <= limit_hi[i];
+            s[j][c] = seen ? s[j][c] * scale_log2 : -INFINITY;
+            tile_max[i] = fmaxf(tile_max[i], s[j][c]);
+        }
+    float correction[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        tile_max[i] = fmaxf(tile_max[i], __shfl_xor_sync(0xffffffffu, tile_max[i], 1));
+        tile_max[i] = fmaxf(tile_max[i], __shfl_xor_sync(0xffffffffu, tile_max[i], 2));
+        const float new_max = fmaxf(m[i], tile_max[i]);
+        correction[i] = new_max == -INFINITY ? 1.f : exp2f(m[i] - new_max);
+        m[i] = new_max;
+    }
+    float tile_sum[2] = {0.f, 0.f};
+#pragma unroll
+    for (int j = 0; j < KEYS / 8; ++j)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            const int i = c >> 1;
+            const float p = m[i] == -INFINITY ? 0.f : exp2f(s[j][c] - m[i]);
+            s[j][c] = p;
+            tile_sum[i] += p;
+        }
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        tile_sum[i] += __shfl_xor_sync(0xffffffffu, tile_sum[i], 1);
+        tile_sum[i] += __shfl_xor_sync(0xffffffffu, tile_sum[i], 2);
+        l[i] = l[i] * correction[i] + tile_sum[i];
+    }
+#pragma unroll
+    for (int n = 0; n < HD / 8; ++n) {
+        o[n][0] *= correction[0]; o[n][1] *= correction[0];
+        o[n][2] *= correction[1]; o[n][3] *= correction[1];
+    }
+
+    // o += p * v
+#pragma unroll
+    for (int kk = 0; kk < KEYS / 16; ++kk) {
+        uint32_t a[4];
+        a[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
+        a[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
+        a[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+        a[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+        for (int nn = 0; nn < HD / 16; ++nn) {
+            uint32_t b[4];
+            ldmatrix_x4_trans(b, v_tile + (kk * 16 + r + (matrix & 1) * 8) * T::STRIDE + nn * 16 +
+                                     (matrix >> 1) * 8);
+            mma_16816(o[2 * nn], a, b[0], b[1]);
+            mma_16816(o[2 * nn + 1], a, b[2], b[3]);
+        }
+    }
+}
+
+// ------------------------------------------------------------------ prefill
+
+constexpr int ROWS = 64;      // query rows per block
+
+template <int HD>
+__global__ void __launch_bounds__(WARPS * 32)
+attention_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kv, long long kv_half,
+                         const int* __restrict__ block_table, int table_width, int page_size,
+                         const int* __restrict__ request_start, const int* __restrict__ history,
+                         bf16* __restrict__ out, int requests, int heads, int kv_heads,
+                         float scale_log2, int window) {
+    using T = Tile<HD>;
+    extern __shared__ __align__(16) unsigned char shared_bytes[];
+    bf16* q_tile = reinterpret_cast<bf16*>(shared_bytes);
+    bf16* k_tiles = q_tile + ROWS * T::STRIDE;
+    bf16* v_tiles = k_tiles + 2 * KEYS * T::STRIDE;
+    __shared__ int found[2];
+
+    // which request and which 64 rows of it this block serves
+    if (threadIdx.x == 0) {
+        int left = blockIdx.x, request = -1, start = 0;
+        for (int r = 0; r < requests; ++r) {
+            const int tiles = (request_start[r + 1] - request_start[r] + ROWS - 1) / ROWS;
+            if (left < tiles) { request = r; start = left * ROWS; break; }
+            left -= tiles;
+        }
+        found[0] = request;
+        found[1] = start;
+    }
+    __syncthreads();
+    const int request = found[0];
+    if (request < 0) return;
+    const int row_start = found[1];
+    const int head = blockIdx.y;
+    const int first_token = request_start[request];
+    const int count = request_start[request + 1] - first_token;
+    const int rows = min(ROWS, count - row_start);
+    const int before = history[request];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    Pages pages{kv, kv + kv_half, block_table + (size_t)request * table_width, table_width,
+                page_size, kv_heads, head / (heads / kv_heads)};
+
+    // the query rows of this block (zero beyond the portion's end)
+    for (int piece = threadIdx.x; piece < ROWS * T::CHUNKS; piece += WARPS * 32) {
+        const int row = piece / T::CHUNKS, chunk = piece % T::CHUNKS;
+        const bool live = row < rows;
+        const bf16* src = q + ((size_t)(first_token + row_start + (live ? row : 0)) * heads + head) *
+                                  HD + chunk * 8;
+        copy16(q_tile + row * T::STRIDE + chunk * 8, src, live);
+    }
+    const int first_position = before + row_start;
+    const int last_position = first_position + rows - 1;
+    const int lowest = window > 0 ? max(first_position - window + 1, 0) : 0;
+    const int tile_first = lowest / KEYS, tile_last = last_position / KEYS;
+
+    load_tile<HD>(k_tiles, v_tiles, pages, tile_first * KEYS, lowest, last_position, threadIdx.x,
+                  WARPS * 32);
+    copy_commit();
+
+    // per-thread rows: lane/4 and lane/4 + 8 of the warp's 16
+    int limit_lo[2], limit_hi[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const int row = warp * 16 + (lane >> 2) + i * 8;
+        const int position = first_position + row;
+        limit_hi[i] = row < rows ? position : -1;
+        limit_lo[i] = window > 0 ? max(position - window + 1, 0) : 0;
+    }
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    float o[HD / 8][4];
+#pragma unroll
+    for (int n = 0; n < HD / 8; ++n)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) o[n][c] = 0.f;
+
+    for (int tile = tile_first; tile <= tile_last; ++tile) {
+        const int buffer = (tile - tile_first) & 1;
+        if (tile < tile_last) {
+            load_tile<HD>(k_tiles + (buffer ^ 1) * KEYS * T::STRIDE,
+                          v_tiles + (buffer ^ 1) * KEYS * T::STRIDE, pages, (tile + 1) * KEYS,
+                          lowest, last_position, threadIdx.x, WARPS * 32);
+            copy_commit();
+            copy_wait<1>();
+        } else {
+            copy_wait<0>();
+        }
+        __syncthreads();
+        // a warp whose rows all lie before this tile's keys has nothing to see in it
+        const int warp_last = first_position + min(warp * 16 + 15, rows - 1);
+        if (warp * 16 < rows && tile * KEYS <= warp_last)
+            attend_tile<HD>(q_tile, warp * 16, k_tiles + buffer * KEYS * T::STRIDE,
+                            v_tiles + buffer * KEYS * T::STRIDE, tile * KEYS, limit_lo, limit_hi,
+                            scale_log2, m, l, o, lane);
+        __syncthreads();
+    }
+
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const int row = warp * 16 + (lane >> 2) + i * 8;
+        if (row >= rows) continue;
+        const float inv = l[i] > 0.f ? 1.f / l[i] : 0.f;
+        bf16* dst = out + ((size_t)(first_token + row_start + row) * heads + head) * HD +
+                    (lane & 3) * 2;
+#pragma unroll
+        for (int n = 0; n < HD / 8; ++n)
+            *reinterpret_cast<__nv_bfloat162*>(dst + n * 8) =
+                __floats2bfloat162_rn(o[n][2 * i] * inv, o[n][2 * i + 1] * inv);
+    }
+}
+
+// ------------------------------------------------------------------ decode (split keys)
+
+// partial results: [token, head, split] -> HD floats of unnormalised output, then max and sum
+template <int HD, int BUFFERS>
+__global__ void __launch_bounds__(WARPS * 32)
+attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kv, long long kv_half,
+                        const int* __restrict__ block_table, int table_width, int page_size,
+                        const int* __restrict__ positions, bf16* __restrict__ out,
+                        float* __restrict__ partial, int heads, int kv_heads, int splits,
+                        float scale_log2, int window) {
+    using T = Tile<HD>;
+    extern __shared__ __align__(16) unsigned char shared_bytes[];
+    bf16* q_tile = reinterpret_cast<bf16*>(shared_bytes);               // 16 rows
+    bf16* tiles = q_tile + 16 * T::STRIDE;                               // per warp: 2 x (K, V)
+    const int group = heads / kv_heads;
+    const int groups_of_16 = (group + 15) / 16;
+    const int kv_head = blockIdx.x / groups_of_16;
+    const int head0 = kv_head * group + (blockIdx.x % groups_of_16) * 16;
+    const int rows = min(16, kv_head * group + group - head0);
+    const int request = blockIdx.y;            // one token per request: token index = request
+    const int split = blockIdx.z;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    const int position = positions[request];
+    const int lowest = window > 0 ? max(position - window + 1, 0) : 0;
+    const int tile_first = lowest / KEYS, tile_count = position / KEYS - tile_first + 1;
+    const int per_split = (tile_count + splits - 1) / splits;
+    const int my_first = tile_first + split * per_split;
+    const int my_last = min(my_first + per_split, tile_first + tile_count) - 1;
+
+    Pages pages{kv, kv + kv_half, block_table + (size_t)request * table_width, table_width,
+                page_size, kv_heads, kv_head};
+
+    for (int piece = threadIdx.x; piece < 16 * T::CHUNKS; piece += WARPS * 32) {
+        const int row = piece / T::CHUNKS, chunk = piece % T::CHUNKS;
+        const bool live = row < rows;
+        const bf16* src = q + ((size_t)request * heads + head0 + (live ? row : 0)) * HD + chunk * 8;
+        copy16(q_tile + row * T::STRIDE + chunk * 8, src, live);
+    }
+    copy_commit();
+
+    bf16* my_tiles = tiles + (size_t)warp * 2 * BUFFERS * KEYS * T::STRIDE;
+    auto k_buffer = [&](int b) { return my_tiles + (size_t)b * 2 * KEYS * T::STRIDE; };
+    auto v_buffer = [&](int b) { return my_tiles + (size_t)(b * 2 + 1) * KEYS * T::STRIDE; };
+
+    int limit_lo[2] = {lowest, lowest}, limit_hi[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) limit_hi[i] = (lane >> 2) + i * 8 < rows ? position : -1;
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    float o[HD / 8][4];
+#pragma unroll
+    for (int n = 0; n < HD / 8; ++n)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) o[n][c] = 0.f;
+
+    // this warp takes tiles my_first + warp, + WARPS, ...
+    int tile = my_first + warp;
+    if (tile <= my_last) load_tile<HD>(k_buffer(0), v_buffer(0), pages, tile * KEYS, lowest, position,
+                                       lane, 32);
+    copy_commit();
+    copy_wait<1>();            // the query rows (the first group) have landed for this thread
+    __syncthreads();           // ... and for every thread
+    for (int b = 0; tile <= my_last; tile += WARPS) {
+        if (BUFFERS == 2 && tile + WARPS <= my_last) {
+            load_tile<HD>(k_buffer(b ^ 1), v_buffer(b ^ 1), pages, (tile + WARPS) * KEYS, lowest,
+                          position, lane, 32);
+            copy_commit();
+            copy_wait<1>();
+        } else {
+            copy_wait<0>();
+        }
+        __syncwarp();
+        attend_tile<HD>(q_tile, 0, k_buffer(b), v_buffer(b), tile * KEYS, limit_lo, limit_hi,
+                        scale_log2, m, l, o, lane);
+        __syncwarp();
+        if (BUFFERS == 2) {
+            b ^= 1;
+        } else if (tile + WARPS <= my_last) {      // one buffer: fetch the next tile now
+            load_tile<HD>(k_buffer(0), v_buffer(0), pages, (tile + WARPS) * KEYS, lowest,
+                          position, lane, 32);
+            copy_commit();
+        }
+    }
+    copy_wait<0>();
+    __syncthreads();           // all warps are done with their tiles: reuse them for merging
+
+    // merge the warps: every warp writes (o, m, l) of its 16 rows, warp 0 combines
+    float* merge = reinterpret_cast<float*>(tiles);            // [WARPS][16][HD + 2]
+    constexpr int ROW_FLOATS = HD + 2;
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const int row = (lane >> 2) + i * 8;
+        float* dst = merge + ((size_t)warp * 16 + row) * ROW_FLOATS;
+#pragma unroll
+        for (int n = 0; n < HD / 8; ++n) {
+            dst[n * 8 + (lane & 3) * 2] = o[n][2 * i];
+            dst[n * 8 + (lane & 3) * 2 + 1] = o[n][2 * i + 1];
+        }
+        if ((lane & 3) == 0) { dst[HD] = m[i]; dst[HD + 1] = l[i]; }
+    }
+    __syncthreads();
+    for (int item = threadIdx.x; item < rows * HD; item += WARPS * 32) {
+        const int row = item / HD, d = item % HD;
+        float top = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < WARPS; ++w)
+            top = fmaxf(top, merge[((size_t)w * 16 + row) * ROW_FLOATS + HD]);
+        float value = 0.f, sum = 0.f;
+#pragma unroll
+        for (int w = 0; w < WARPS; ++w) {
+            const float* src = merge + ((size_t)w * 16 + row) * ROW_FLOATS;
+            const float weight = src[HD] == -INFINITY ? 0.f : exp2f(src[HD] - top);
+            value += src[d] * weight;
+            sum += src[HD + 1] * weight;
+        }
+        const int head = head0 + row;
+        if (splits == 1) {
+            out[((size_t)request * heads + head) * HD + d] =
+                __float2bfloat16_rn(sum > 0.f ? value / sum : 0.f);
+        } else {
+            float* dst = partial + (((size_t)request * heads + head) * splits + split) * ROW_FLOATS;
+            dst[d] = value;
+            if (d == 0) { dst[HD] = top; dst[HD + 1] = sum; }
+        }
+    }
+}
+
+// Merges the splits of one (token, head): one warp each.
+template <int HD>
+__global__ void attention_merge_kernel(const float* __restrict__ partial, bf16* __restrict__ out,
+                                       int items, int splits) {
+    constexpr int ROW_FLOATS = HD + 2;
+    const int item = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (item >= items) return;
+    const float* base = partial + (size_t)item * splits * ROW_FLOATS;
+    float top = -INFINITY;
+    for (int s = 0; s < splits; ++s) top = fmaxf(top, base[(size_t)s * ROW_FLOATS + HD]);
+    float sum = 0.f;
+    float value[(HD + 31) / 32];
+#pragma unroll
+    for (int i = 0; i < (HD + 31) / 32; ++i) value[i] = 0.f;
+    for (int s = 0; s < splits; ++s) {
+        const float* src = base + (size_t)s * ROW_FLOATS;
+        const float weight = src[HD] == -INFINITY ? 0.f : exp2f(src[HD] - top);
+        sum += src[HD + 1] * weight;
+#pragma unroll
+        for (int i = 0; i < (HD + 31) / 32; ++i) {
+            const int d = lane + 32 * i;
+            if (d < HD) value[i] += src[d] * weight;
+        }
+    }
+    const float inv = sum > 0.f ? 1.f / sum : 0.f;
+#pragma unroll
+    for (int i = 0; i < (HD + 31) / 32; ++i) {
+        const int d = lane + 32 * i;
+        if (d < HD) out[(size_t)item * HD + d] = __float2bfloat16_rn(value[i] * inv);
+    }
+}
+
+template <int HD>
+int launch_prefill(const void* q, const void* kv, long long kv_half, const int* block_table,
+                   int table_width, int page_size, const int* request_start, const int* history,
+                   void* out, int tokens, int requests, int heads, int kv_heads, float scale,
+                   int window, cudaStream_t stream) {
+    using T = Tile<HD>;
+    const size_t shared = (size_t)(ROWS + 4 * KEYS) * T::STRIDE * 2;
+    auto kernel = attention_prefill_kernel<HD>;
+    if (shared > 48 * 1024)
+        cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
+    const dim3 grid((tokens + ROWS - 1) / ROWS + requests, heads);
+    kernel<<<grid, WARPS * 32, shared, stream>>>(
+        (const bf16*)q, (const bf16*)kv, kv_half, block_table, table_width, page_size,
+        request_start, history, (bf16*)out, requests, heads, kv_heads, scale * LOG2E, window);
+    return 0;
+}
+
+template <int HD>
+int launch_decode(const void* q, const void* kv, long long kv_half, const int* block_table,
+                  int table_width, int page_size, const int* positions, void* out, float* partial,
+                  int requests, int heads, int kv_heads, int splits, float scale, int window,
+                  cudaStream_t stream) {
+    using T = Tile<HD>;
+    constexpr int BUFFERS = HD <= 64 ? 2 : 1;      // what fits into one block's shared memory
+    const size_t tiles = (size_t)WARPS * 2 * BUFFERS * KEYS * T::STRIDE * 2;
+    const size_t merge = (size_t)WARPS * 16 * (HD + 2) * 4;
+    const size_t shared = (size_t)16 * T::STRIDE * 2 + (tiles > merge ? tiles : merge);
+    auto kernel = attention_decode_kernel<HD, BUFFERS>;
+    if (shared > 48 * 1024)
+        cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
+    const int group = heads / kv_heads;
+    const dim3 grid(kv_heads * ((group + 15) / 16), requests, splits);
+    kernel<<<grid, WARPS * 32, shared, stream>>>(
+        (const bf16*)q, (const bf16*)kv, kv_half, block_table, table_width, page_size, positions,
+        (bf16*)out, partial, heads, kv_heads, splits, scale * LOG2E, window);
+    if (splits > 1) {
+        const int items = requests * heads;
+        attention_merge_kernel<HD><<<(items + 3) / 4, 128, 0, stream>>>(partial, (bf16*)out, items,
+                                                                        splits);
+    }
+    return 0;
+}
+
+}  // namespace
+
+#define MLXONE_HEAD_DIMS(CALL)                                                       \
+    switch (head_dim) {                                                              \
+        case 16: CALL(16); break;                                                    \
+        case 32: CALL(32); break;                                                    \
+        case 48: CALL(48); break;                                                    \
+        case 64: CALL(64); break;                                                    \
+        case 80: CALL(80); break;                                                    \
+        case 96: CALL(96); break;                                                    \
+        case 112: CALL(112); break;                                                  \
+        case 128: CALL(128); break;                                                  \
+        default:                                                                     \
+            mlxone_set_error("attention (tensor cores): head size %d is not a multiple of " \
+                             "16 up to 128", head_dim);                              \
+            return 1;                                                                \
+    }
+
+// 1 if the tensor-core kernels take this shape, else 0 (the caller then uses the general one).
+MLXONE_API int mlxone_attention_mma_supports(int head_dim, int dtype) {
+    return dtype == MLXONE_BF16 && head_dim % 16 == 0 && head_dim >= 16 && head_dim <= 128;
+}
+
+MLXONE_API int mlxone_attention_prefill(const void* q, const void* kv, const int* block_table,
+                                        int table_width, int page_size, int pages,
+                                        const int* request_start, const int* history, void* out,
+                                        int tokens, int requests, int heads, int kv_heads,
+                                        int head_dim, float scale, int window,
+                                        cudaStream_t stream) {
+    if (tokens == 0) return 0;
+    MLXONE_REQUIRE(tokens > 0 && requests > 0 && heads > 0 && kv_heads > 0 &&
+                       heads % kv_heads == 0, "attention_prefill: bad sizes");
+    MLXONE_REQUIRE(heads <= 65535, "attention_prefill: too many heads");
+    MLXONE_REQUIRE(page_size > 0 && pages > 0 && table_width > 0,
+                   "attention_prefill: bad page geometry");
+    const long long kv_half = (long long)pages * kv_heads * page_size * head_dim;
+#define CALL(HD)                                                                              \
+    launch_prefill<HD>(q, kv, kv_half, block_table, table_width, page_size, request_start,    \
+                       history, out, tokens, requests, heads, kv_heads, scale, window, stream)
+    MLXONE_HEAD_DIMS(CALL)
+#undef CALL
+    MLXONE_LAUNCH_CHECK("attention_prefill");
+    return 0;
+}
+
+// Floats of scratch that the decode kernel needs for `splits` > 1.
+MLXONE_API long long mlxone_attention_decode_scratch(int requests, int heads, int head_dim,
+                                                     int splits) {
+    return splits > 1 ? (long long)requests * heads * splits * (head_dim + 2) : 0;
+}
+
+MLXONE_API int mlxone_attention_decode(const void* q, const void* kv, const int* block_table,
+                                       int table_width, int page_size, int pages,
+                                       const int* positions, void* out, float* partial,
+                                       int requests, int heads, int kv_heads, int head_dim,
+                                       int splits, float scale, int window, cudaStream_t stream) {
+    if (requests == 0) return 0;
+    MLXONE_REQUIRE(requests > 0 && heads > 0 && kv_heads > 0 && heads % kv_heads == 0,
+                   "attention_decode: bad sizes");
+    MLXONE_REQUIRE(requests <= 65535 && splits >= 1 && splits <= 65535,
+                   "attention_decode: at most 65535 requests and splits");
+    MLXONE_REQUIRE(splits == 1 || partial != nullptr, "attention_decode: scratch is missing");
+    MLXONE_REQUIRE(page_size > 0 && pages > 0 && table_width > 0,
+                   "attention_decode: bad page geometry");
+    const long long kv_half = (long long)pages * kv_heads * page_size * head_dim;
+#define CALL(HD)                                                                               \
+    launch_decode<HD>(q, kv, kv_half, block_table, table_width, page_size, positions, out,     \
+                      partial, requests, heads, kv_heads, splits, scale, window, stream)
+    MLXONE_HEAD_DIMS(CALL)
+#undef CALL
+    MLXONE_LAUNCH_CHECK("attention_decode");
+    return 0;
+}

@@ -55,6 +55,7 @@ class CudaOps:
             raise KernelBuildError("the CUDA extension is of another version; rebuild it")
         self.error_flag = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.launches = 0
+        self.tensor_core_attention = True
         self._sample_scratch: torch.Tensor | None = None
 
     # ------------------------------------------------------------------ plumbing
@@ -199,16 +200,60 @@ class CudaOps:
         return q
 
     def paged_attention(self, q, *, heads, kv_heads, head_dim, scale, window, ctx, view):
+        """Attention of every token over its request's pages. bfloat16 with a head size that
+        is a multiple of 16 up to 128 runs on tensor cores: the split-key decode kernel when
+        every request brings one token, else the prefill kernel. Everything else (float32,
+        other head sizes) runs the general kernel."""
         tokens = q.shape[0]
         out = torch.empty((tokens, heads * head_dim), dtype=q.dtype, device=self.device)
+        width = view.block_table.shape[1]
+        pages = view.kv.shape[1]
+        code = _dtype_code(q.dtype)
+        if self.tensor_core_attention and self.lib.mlxone_attention_mma_supports(head_dim, code):
+            if ctx.max_portion == 1 and tokens == ctx.requests:
+                splits = self.decode_splits(ctx.requests, heads, kv_heads, width * view.page_size,
+                                            window)
+                partial = None
+                if splits > 1:
+                    partial = torch.empty(ctx.requests * heads * splits * (head_dim + 2),
+                                          dtype=torch.float32, device=self.device)
+                self._call("mlxone_attention_decode", _c_void_p(_ptr(q)), _c_void_p(_ptr(view.kv)),
+                           _c_void_p(_ptr(view.block_table)), _c_int(width),
+                           _c_int(view.page_size), _c_int(pages), _c_void_p(_ptr(ctx.positions)),
+                           _c_void_p(_ptr(out)), _c_void_p(_ptr(partial)), _c_int(ctx.requests),
+                           _c_int(heads), _c_int(kv_heads), _c_int(head_dim), _c_int(splits),
+                           _c_float(scale), _c_int(window or 0))
+                if splits > 1:
+                    self.launches += 1
+            else:
+                self._call("mlxone_attention_prefill", _c_void_p(_ptr(q)),
+                           _c_void_p(_ptr(view.kv)), _c_void_p(_ptr(view.block_table)),
+                           _c_int(width), _c_int(view.page_size), _c_int(pages),
+                           _c_void_p(_ptr(ctx.request_start)), _c_void_p(_ptr(ctx.history)),
+                           _c_void_p(_ptr(out)), _c_int(tokens), _c_int(ctx.requests),
+                           _c_int(heads), _c_int(kv_heads), _c_int(head_dim), _c_float(scale),
+                           _c_int(window or 0))
+            return out
         self._call("mlxone_attention_generic", _c_void_p(_ptr(q)), _c_void_p(_ptr(view.kv)),
-                   _c_void_p(_ptr(view.block_table)), _c_int(view.block_table.shape[1]),
-                   _c_int(view.page_size), _c_int(view.kv.shape[1]),
+                   _c_void_p(_ptr(view.block_table)), _c_int(width),
+                   _c_int(view.page_size), _c_int(pages),
                    _c_void_p(_ptr(ctx.positions)), _c_void_p(_ptr(ctx.token_request)),
                    _c_void_p(_ptr(out)), _c_int(tokens), _c_int(heads), _c_int(kv_heads),
                    _c_int(head_dim), _c_float(scale), _c_int(window or 0),
-                   _c_int(_dtype_code(q.dtype)), _c_void_p(_ptr(self.error_flag)))
+                   _c_int(code), _c_void_p(_ptr(self.error_flag)))
         return out
+
+    @staticmethod
+    def decode_splits(requests: int, heads: int, kv_heads: int, context_bound: int,
+                      window: int | None) -> int:
+        """Into how many parts the decode kernel cuts a request's keys: enough blocks to
+        fill the GPU about twice, but at least four tiles of 64 keys per part."""
+        if window:
+            context_bound = min(context_bound, window + 63)
+        tiles = max(-(-context_bound // 64), 1)
+        groups = kv_heads * (-(-(heads // kv_heads) // 16))
+        wanted = max(2 * 148 // max(requests * groups, 1), 1)
+        return max(min(wanted, -(-tiles // 4)), 1)
 
     def argmax(self, logits):
         self._need(logits, torch.float32, "logits")

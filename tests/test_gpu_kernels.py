@@ -1,0 +1,306 @@
+"""Each CUDA kernel alone against its plain restatement (tests/plain_ops.py), at sizes other
+than the engine's tiny models: head sizes in steps of 16, odd head counts and groups, widths
+and vocabularies that are no power of two."""
+
+import math
+
+import pytest
+import torch
+
+from plain_ops import PlainOps, kept_set, uniform
+from mlx_one_b200.parts.base import FixedState, PagedKeyValues, PagedView, StateView, StepContext
+
+pytestmark = pytest.mark.gpu
+DEVICE = "cuda:0"
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from mlx_one_b200.kernels import default_ops
+    return default_ops(DEVICE)
+
+
+@pytest.fixture(scope="module")
+def plain():
+    return PlainOps()
+
+
+def tolerance(dtype):
+    return dict(atol=2e-5, rtol=2e-5) if dtype == torch.float32 else dict(atol=2e-2, rtol=2e-2)
+
+
+def make_batch(portions, histories, page_size, device, extra_pages=3, seed=0):
+    """A ragged batch and block tables with shuffled pages. Returns (ctx, table, pages)."""
+    generator = torch.Generator().manual_seed(seed)
+    requests = len(portions)
+    blocks = [-(-(h + n) // page_size) for h, n in zip(histories, portions)]
+    pages = sum(blocks) + extra_pages
+    order = torch.randperm(pages, generator=generator).tolist()
+    width = max(blocks) + 2
+    table = torch.full((requests, width), -1, dtype=torch.int32)
+    for r, count in enumerate(blocks):
+        for b in range(count):
+            table[r, b] = order.pop()
+    positions, token_request, starts = [], [], [0]
+    for r, (h, n) in enumerate(zip(histories, portions)):
+        positions += list(range(h, h + n))
+        token_request += [r] * n
+        starts.append(starts[-1] + n)
+    as_int = lambda values: torch.tensor(values, dtype=torch.int32, device=device)
+    ctx = StepContext(tokens=len(positions), requests=requests,
+                      token_ids=as_int([0] * len(positions)), positions=as_int(positions),
+                      token_request=as_int(token_request), request_start=as_int(starts),
+                      history=as_int(histories), max_portion=max(portions),
+                      max_context=max(h + n for h, n in zip(histories, portions)))
+    return ctx, table.to(device), pages
+
+
+def on_cpu(ctx):
+    return StepContext(tokens=ctx.tokens, requests=ctx.requests, token_ids=ctx.token_ids.cpu(),
+                       positions=ctx.positions.cpu(), token_request=ctx.token_request.cpu(),
+                       request_start=ctx.request_start.cpu(), history=ctx.history.cpu(),
+                       max_portion=ctx.max_portion, max_context=ctx.max_context)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("hidden,vocab", [(80, 333), (2048, 1000)])
+def test_embedding_and_norm(ops, plain, dtype, hidden, vocab):
+    torch.manual_seed(0)
+    table = torch.randn(vocab, hidden).to(dtype)
+    ids = torch.randint(0, vocab, (37,), dtype=torch.int32)
+    got = ops.embedding(ids.to(DEVICE), table.to(DEVICE))
+    assert torch.equal(got.cpu(), plain.embedding(ids, table))
+    residual = torch.randn(37, hidden)
+    delta = torch.randn(37, hidden).to(dtype)
+    weight = 1 + 0.1 * torch.randn(hidden)
+    for use_delta in (True, False):
+        res_gpu = residual.clone().to(DEVICE)
+        res_cpu = residual.clone()
+        got = ops.add_rmsnorm(res_gpu, delta.to(DEVICE) if use_delta else None,
+                              weight.to(DEVICE), 1e-5, dtype)
+        want = plain.add_rmsnorm(res_cpu, delta if use_delta else None, weight, 1e-5, dtype)
+        torch.testing.assert_close(res_gpu.cpu(), res_cpu, atol=1e-6, rtol=1e-6)
+        torch.testing.assert_close(got.cpu().float(), want.float(), **tolerance(dtype))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_gather_swiglu_bias(ops, plain, dtype):
+    torch.manual_seed(1)
+    residual, delta = torch.randn(29, 112), torch.randn(29, 112).to(dtype)
+    rows = torch.tensor([3, 28, 0, 3], dtype=torch.int32)
+    picked, picked_delta = ops.gather_rows(residual.to(DEVICE), delta.to(DEVICE), rows.to(DEVICE))
+    assert torch.equal(picked.cpu(), residual[rows.long()])
+    assert torch.equal(picked_delta.cpu(), delta[rows.long()])
+    gate_up = torch.randn(29, 2 * 77).to(dtype)
+    torch.testing.assert_close(ops.swiglu(gate_up.to(DEVICE)).cpu().float(),
+                               plain.swiglu(gate_up).float(), **tolerance(dtype))
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 5, 7), (37, 333, 130), (64, 96, 288), (130, 1000, 96)])
+def test_matrix_product_float32(ops, plain, m, n, k):
+    """True 32-bit: compared with a float64 product at float32 rounding, no tensor-core mode."""
+    torch.manual_seed(2)
+    a, w, bias = torch.randn(m, k), torch.randn(n, k), torch.randn(n)
+    got = ops.linear(a.to(DEVICE), w.to(DEVICE), bias.to(DEVICE)).cpu()
+    want = (a.double() @ w.double().T + bias.double()).float()
+    torch.testing.assert_close(got, want, atol=1e-5 * math.sqrt(k), rtol=1e-6)
+    # a row's result does not depend on which other rows the call has
+    alone = ops.linear(a[:1].contiguous().to(DEVICE), w.to(DEVICE), bias.to(DEVICE)).cpu()
+    assert torch.equal(alone[0], got[0])
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 64, 64), (8, 333, 136), (130, 1000, 96)])
+def test_matrix_product_bfloat16(ops, plain, m, n, k):
+    torch.manual_seed(3)
+    a, w = torch.randn(m, k).bfloat16(), torch.randn(n, k).bfloat16()
+    bias = torch.randn(n)
+    got = ops.linear(a.to(DEVICE), w.to(DEVICE), bias.to(DEVICE)).cpu().float()
+    want = a.float() @ w.float().T + bias
+    torch.testing.assert_close(got, want, atol=0.02 * math.sqrt(k), rtol=2e-2)
+    logits = ops.linear(a.to(DEVICE), w.to(DEVICE), out_dtype=torch.float32).cpu()
+    torch.testing.assert_close(logits, a.float() @ w.float().T, atol=1e-3 * math.sqrt(k), rtol=1e-3)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("hidden,taps,bias", [(48, 3, False), (200, 4, True), (64, 2, True),
+                                              (32, 1, False), (96, 7, False)])
+def test_short_conv(ops, plain, dtype, hidden, taps, bias):
+    """Portions that start at position 0, in the middle, shorter than the kernel is wide."""
+    torch.manual_seed(4)
+    portions, histories = [5, 1, 9, 2, 1], [0, 7, 3, 0, 1]
+    ctx, _, _ = make_batch(portions, histories, 4, DEVICE)
+    slots = torch.tensor([4, 0, 2, 5, 1], dtype=torch.int32)
+    state = torch.randn(6, max(taps - 1, 1), hidden).to(dtype)
+    bcx = torch.randn(ctx.tokens, 3 * hidden).to(dtype)
+    kernel = torch.randn(hidden, taps)
+    conv_bias = torch.randn(hidden) if bias else None
+    need = FixedState((max(taps - 1, 1), hidden))
+    state_gpu = state.clone().to(DEVICE)
+    got = ops.short_conv(bcx.to(DEVICE), kernel=kernel.to(DEVICE),
+                         bias=None if conv_bias is None else conv_bias.to(DEVICE), taps=taps,
+                         ctx=ctx, view=StateView(state_gpu, slots.to(DEVICE), need), write=True)
+    state_cpu = state.clone()
+    want = plain.short_conv(bcx, kernel=kernel, bias=conv_bias, taps=taps, ctx=on_cpu(ctx),
+                            view=StateView(state_cpu, slots, need), write=True)
+    torch.testing.assert_close(got.cpu().float(), want.float(), **tolerance(dtype))
+    if taps > 1:
+        # rows of positions before 0 are never read, so they need not agree
+        for r, (h, n) in enumerate(zip(histories, portions)):
+            valid = [s for s in range(taps - 1) if h + n - (taps - 1) + s >= 0]
+            torch.testing.assert_close(state_gpu.cpu()[slots[r], valid].float(),
+                                       state_cpu[slots[r], valid].float(), **tolerance(dtype))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("heads,kv_heads,head_dim,rotary_dim,norm", [
+    (4, 2, 16, 16, True), (3, 1, 32, 32, True), (6, 3, 48, 24, False), (5, 5, 80, 80, True),
+    (2, 1, 256, 256, True)])
+def test_qk_norm_rope_store(ops, plain, dtype, heads, kv_heads, head_dim, rotary_dim, norm):
+    torch.manual_seed(5)
+    page_size = 8
+    ctx, table, pages = make_batch([6, 1, 11], [0, 100_000, 13], page_size, DEVICE)
+    qkv = torch.randn(ctx.tokens, (heads + 2 * kv_heads) * head_dim).to(dtype)
+    q_weight = (1 + 0.1 * torch.randn(head_dim)) if norm else None
+    k_weight = (1 + 0.1 * torch.randn(head_dim)) if norm else None
+    half = rotary_dim // 2
+    inv_freq = torch.pow(torch.tensor(10000.0), -torch.arange(half, dtype=torch.float32) / half)
+    need = PagedKeyValues(kv_heads, head_dim)
+    kv_gpu = torch.zeros(2, pages, kv_heads, page_size, head_dim, dtype=dtype, device=DEVICE)
+    kv_cpu = torch.zeros(2, pages, kv_heads, page_size, head_dim, dtype=dtype)
+    to = lambda t: None if t is None else t.to(DEVICE)
+    got = ops.qk_norm_rope_store(
+        qkv.to(DEVICE), heads=heads, kv_heads=kv_heads, head_dim=head_dim, q_weight=to(q_weight),
+        k_weight=to(k_weight), eps=1e-5, rotary=(inv_freq.to(DEVICE), rotary_dim), ctx=ctx,
+        view=PagedView(kv_gpu, table, page_size, need), write=True)
+    want = plain.qk_norm_rope_store(
+        qkv, heads=heads, kv_heads=kv_heads, head_dim=head_dim, q_weight=q_weight,
+        k_weight=k_weight, eps=1e-5, rotary=(inv_freq, rotary_dim), ctx=on_cpu(ctx),
+        view=PagedView(kv_cpu, table.cpu(), page_size, need), write=True)
+    # at position 100000 a 32-bit angle is exact to ~1e-2 rad only in its last bits; both sides
+    # compute position * inv_freq in 32-bit, so they agree far better than that
+    torch.testing.assert_close(got.cpu().float(), want.float(), **tolerance(dtype))
+    torch.testing.assert_close(kv_gpu.cpu().float(), kv_cpu.float(), **tolerance(dtype))
+    ops.check_errors()
+
+
+def attention_case(ops, plain, dtype, heads, kv_heads, head_dim, page_size, portions, histories,
+                   window, tensor_cores, seed=6, spike=None):
+    torch.manual_seed(seed)
+    ctx, table, pages = make_batch(portions, histories, page_size, DEVICE, seed=seed)
+    kv = torch.randn(2, pages, kv_heads, page_size, head_dim).to(dtype)
+    q = torch.randn(ctx.tokens, heads, head_dim).to(dtype)
+    if spike is not None:
+        # one far key and the last query are scaled so that this key's score stands out:
+        # an error in finding its page or position would change the output visibly
+        request, key_position = spike
+        page = int(table[request, key_position // page_size])
+        kv[0, page, :, key_position % page_size] *= 4
+        last = int(ctx.request_start[request + 1]) - 1
+        q[last] = kv[0, page, :, key_position % page_size].repeat_interleave(
+            heads // kv_heads, dim=0).float().to(dtype) * 2
+    need = PagedKeyValues(kv_heads, head_dim, window)
+    scale = head_dim ** -0.5
+    ops.tensor_core_attention = tensor_cores
+    try:
+        got = ops.paged_attention(q.to(DEVICE), heads=heads, kv_heads=kv_heads, head_dim=head_dim,
+                                  scale=scale, window=window, ctx=ctx,
+                                  view=PagedView(kv.to(DEVICE), table, page_size, need))
+    finally:
+        ops.tensor_core_attention = True
+    want = plain.paged_attention(q, heads=heads, kv_heads=kv_heads, head_dim=head_dim,
+                                 scale=scale, window=window, ctx=on_cpu(ctx),
+                                 view=PagedView(kv, table.cpu(), page_size, need))
+    ops.check_errors()
+    torch.testing.assert_close(got.cpu().float(), want.float(), **tolerance(dtype))
+
+
+SHAPES = [(4, 2, 16, 4), (3, 1, 32, 8), (6, 2, 48, 16), (8, 8, 64, 16), (32, 8, 64, 16),
+          (5, 5, 80, 32), (4, 1, 128, 64), (2, 2, 96, 1), (34, 2, 112, 16)]
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("heads,kv_heads,head_dim,page_size", SHAPES)
+@pytest.mark.parametrize("window", [None, 37])
+def test_attention_general(ops, plain, dtype, heads, kv_heads, head_dim, page_size, window):
+    attention_case(ops, plain, dtype, heads, kv_heads, head_dim, page_size,
+                   portions=[7, 1, 70, 2], histories=[0, 200, 31, 64], window=window,
+                   tensor_cores=False, spike=(1, 3 if window is None else 180))
+
+
+@pytest.mark.parametrize("heads,kv_heads,head_dim,page_size", SHAPES)
+@pytest.mark.parametrize("window", [None, 37, 64, 1])
+def test_attention_prefill_tensor_cores(ops, plain, heads, kv_heads, head_dim, page_size, window):
+    """Portions beside single tokens; a portion that crosses tiles of 64 rows and 64 keys; a
+    window's edge at 37, exactly at a tile (64) and of one key."""
+    attention_case(ops, plain, torch.bfloat16, heads, kv_heads, head_dim, page_size,
+                   portions=[7, 1, 150, 2, 64], histories=[0, 200, 31, 64, 64], window=window,
+                   tensor_cores=True, spike=(1, 3 if window is None else 200))
+
+
+@pytest.mark.parametrize("heads,kv_heads,head_dim,page_size", SHAPES)
+@pytest.mark.parametrize("window", [None, 37])
+@pytest.mark.parametrize("histories", [[0, 1, 63, 64, 65], [700, 3, 255, 256, 1030]])
+def test_attention_decode_tensor_cores(ops, plain, heads, kv_heads, head_dim, page_size, window,
+                                       histories):
+    """One token per request: contexts at the edges of tiles, split over several blocks."""
+    far = (0, 5) if histories[0] > 100 and window is None else None
+    attention_case(ops, plain, torch.bfloat16, heads, kv_heads, head_dim, page_size,
+                   portions=[1] * 5, histories=histories, window=window, tensor_cores=True,
+                   spike=far)
+
+
+def test_decode_splits_are_used(ops):
+    assert ops.decode_splits(1, 32, 8, 4096, None) > 1
+    assert ops.decode_splits(64, 32, 8, 4096, None) == 1
+    assert ops.decode_splits(1, 32, 8, 4096, 10) == 1
+
+
+def test_argmax_and_sampling(ops, plain):
+    torch.manual_seed(7)
+    vocab, rows = 1000, 6
+    logits = torch.randn(rows, vocab) * 3
+    logits[2, 17] = logits[2, 900] = logits[2].max() + 1     # a tie: the lower index wins
+    assert ops.argmax(logits.to(DEVICE)).cpu().tolist() == torch.argmax(logits, -1).tolist()
+    assert ops.argmax(logits.to(DEVICE)).cpu()[2] == 17
+    temperature = torch.tensor([0.8, 1.0, 0.5, 1.3, 0.0, 0.9])
+    top_k = torch.tensor([0, 50, 5, 0, 0, 1], dtype=torch.int32)
+    top_p = torch.tensor([1.0, 1.0, 0.9, 0.7, 1.0, 1.0])
+    seed = torch.tensor([0, 1, 2, 3, 4, 5], dtype=torch.int64)
+    for step in range(20):
+        steps = torch.full((rows,), step, dtype=torch.int32)
+        got, probabilities = ops.sample(logits.to(DEVICE), temperature.to(DEVICE),
+                                        top_k.to(DEVICE), top_p.to(DEVICE), seed.to(DEVICE),
+                                        steps.to(DEVICE))
+        got = got.cpu().tolist()
+        assert got[4] == int(torch.argmax(logits[4]))           # temperature 0 is greedy
+        assert got[5] == int(torch.argmax(logits[5]))           # top_k = 1 too
+        for r in range(4):
+            p = probabilities[r].cpu()
+            kept = set(kept_set(p, int(top_k[r]), float(top_p[r])).tolist())
+            assert got[r] in kept, (r, step)
+            # the same draw in float64 over the same kept set, in token order
+            weights = torch.zeros(vocab, dtype=torch.float64)
+            index = torch.tensor(sorted(kept))
+            weights[index] = p[index].double()
+            running = torch.cumsum(weights, 0)
+            target = uniform(int(seed[r]), step) * float(weights.sum())
+            want = int(torch.nonzero((running >= target) & (weights > 0))[0])
+            if got[r] != want:        # only a draw within rounding of a boundary may differ
+                edge = float(running[min(got[r], want)])
+                assert abs(edge - target) < 1e-5 * float(weights.sum()), (r, step, got[r], want)
+
+
+def test_sampling_distribution(ops):
+    """Over many steps the drawn tokens follow softmax(logits / T)."""
+    logits = torch.tensor([[2.0, 1.0, 0.0, -1.0, 1.5]])
+    counts = torch.zeros(5)
+    rows = 1
+    for step in range(3000):
+        got, _ = ops.sample(logits.to(DEVICE), torch.tensor([0.7], device=DEVICE),
+                            torch.zeros(rows, dtype=torch.int32, device=DEVICE),
+                            torch.ones(rows, device=DEVICE),
+                            torch.tensor([11], dtype=torch.int64, device=DEVICE),
+                            torch.tensor([step], dtype=torch.int32, device=DEVICE))
+        counts[int(got[0])] += 1
+    want = torch.softmax(logits[0] / 0.7, -1)
+    assert (counts / counts.sum() - want).abs().max() < 0.03
