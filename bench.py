@@ -331,6 +331,8 @@ def main() -> int:
     parser.add_argument("--context", type=int, default=4096)
     parser.add_argument("--layers", type=int, default=LFM2_1_2B["num_hidden_layers"])
     parser.add_argument("--skip-points", action="store_true", help="leave out batch 1 and 64")
+    parser.add_argument("--dependent-launches", type=int, default=1,
+                        help="1: kernels of a decode step may start while the one before ends")
     args = parser.parse_args()
     if args.impl == "reference":
         return reference_arm()
@@ -346,6 +348,7 @@ def main() -> int:
     engine = build_engine(LFM2_1_2B, args.layers, max(largest, args.batch), args.context,
                           warmup + args.steps)
     model, spec = engine.model, engine.model.spec
+    model.ops.set_dependent_launches(bool(args.dependent_launches))
     weight_bytes = model.weight_bytes()
     kv_per_token = engine._bytes_per_token()
     state_bytes = sum(g.storage[:, 0].numel() * g.storage.element_size()

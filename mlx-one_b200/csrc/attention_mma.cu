@@ -22,7 +22,8 @@
 namespace {
 
 using bf16 = __nv_bfloat16;
-constexpr int KEYS = 64;          // keys per tile
+constexpr int PREFILL_KEYS = 64;  // keys per tile of the prefill kernel
+constexpr int DECODE_KEYS = 32;   // and of the decode kernel (smaller: more blocks per SM)
 constexpr int WARPS = 4;
 constexpr float LOG2E = 1.4426950408889634f;
 
@@ -86,9 +87,9 @@ struct Pages {
     int table_width, page_size, kv_heads, kv_head;
 };
 
-// Copies keys first..first+63 of one key head into a K and a V tile; rows outside [lowest,
+// Copies keys first..first+KEYS-1 of one key head into a K and a V tile; rows outside [lowest,
 // last] or without a page are zero. `lanes` threads take part, this one is `lane`.
-template <int HD>
+template <int HD, int KEYS>
 __device__ __forceinline__ void load_tile(bf16* k_tile, bf16* v_tile, const Pages& pages, int first,
                                           int lowest, int last, int lane, int lanes) {
     using T = Tile<HD>;
@@ -110,10 +111,10 @@ __device__ __forceinline__ void load_tile(bf16* k_tile, bf16* v_tile, const Page
     }
 }
 
-// One warp: 16 query rows (in q_tile, rows row0..row0+15) against one tile of 64 keys.
+// One warp: 16 query rows (in q_tile, rows row0..row0+15) against one tile of KEYS keys.
 // `limit_lo[i]`/`limit_hi[i]` (i = 0: row lane/4, 1: row lane/4 + 8) bound the keys that the row
 // may see. Updates the running max `m`, sum `l` (both in the exp2 domain, scaled) and `o`.
-template <int HD>
+template <int HD, int KEYS>
 __device__ __forceinline__ void attend_tile(const bf16* q_tile, int row0, const bf16* k_tile,
                                             const bf16* v_tile, int first, const int (&limit_lo)[2],
                                             const int (&limit_hi)[2], float scale_log2,
@@ -217,6 +218,7 @@ attention_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kv
                          bf16* __restrict__ out, int requests, int heads, int kv_heads,
                          float scale_log2, int window) {
     using T = Tile<HD>;
+    constexpr int KEYS = PREFILL_KEYS;
     extern __shared__ __align__(16) unsigned char shared_bytes[];
     bf16* q_tile = reinterpret_cast<bf16*>(shared_bytes);
     bf16* k_tiles = q_tile + ROWS * T::STRIDE;
@@ -261,7 +263,7 @@ attention_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kv
     const int lowest = window > 0 ? max(first_position - window + 1, 0) : 0;
     const int tile_first = lowest / KEYS, tile_last = last_position / KEYS;
 
-    load_tile<HD>(k_tiles, v_tiles, pages, tile_first * KEYS, lowest, last_position, threadIdx.x,
+    load_tile<HD, KEYS>(k_tiles, v_tiles, pages, tile_first * KEYS, lowest, last_position, threadIdx.x,
                   WARPS * 32);
     copy_commit();
 
@@ -284,7 +286,7 @@ attention_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kv
     for (int tile = tile_first; tile <= tile_last; ++tile) {
         const int buffer = (tile - tile_first) & 1;
         if (tile < tile_last) {
-            load_tile<HD>(k_tiles + (buffer ^ 1) * KEYS * T::STRIDE,
+            load_tile<HD, KEYS>(k_tiles + (buffer ^ 1) * KEYS * T::STRIDE,
                           v_tiles + (buffer ^ 1) * KEYS * T::STRIDE, pages, (tile + 1) * KEYS,
                           lowest, last_position, threadIdx.x, WARPS * 32);
             copy_commit();
@@ -296,7 +298,7 @@ attention_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kv
         // a warp whose rows all lie before this tile's keys has nothing to see in it
         const int warp_last = first_position + min(warp * 16 + 15, rows - 1);
         if (warp * 16 < rows && tile * KEYS <= warp_last)
-            attend_tile<HD>(q_tile, warp * 16, k_tiles + buffer * KEYS * T::STRIDE,
+            attend_tile<HD, KEYS>(q_tile, warp * 16, k_tiles + buffer * KEYS * T::STRIDE,
                             v_tiles + buffer * KEYS * T::STRIDE, tile * KEYS, limit_lo, limit_hi,
                             scale_log2, m, l, o, lane);
         __syncthreads();
@@ -327,9 +329,12 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kv,
                         float* __restrict__ partial, int heads, int kv_heads, int splits,
                         float scale_log2, int window) {
     using T = Tile<HD>;
+    constexpr int KEYS = DECODE_KEYS;
     extern __shared__ __align__(16) unsigned char shared_bytes[];
     bf16* q_tile = reinterpret_cast<bf16*>(shared_bytes);               // 16 rows
     bf16* tiles = q_tile + 16 * T::STRIDE;                               // per warp: 2 x (K, V)
+    griddep_launch();
+    griddep_wait();
     const int group = heads / kv_heads;
     const int groups_of_16 = (group + 15) / 16;
     const int kv_head = blockIdx.x / groups_of_16;
@@ -373,14 +378,14 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kv,
 
     // this warp takes tiles my_first + warp, + WARPS, ...
     int tile = my_first + warp;
-    if (tile <= my_last) load_tile<HD>(k_buffer(0), v_buffer(0), pages, tile * KEYS, lowest, position,
+    if (tile <= my_last) load_tile<HD, KEYS>(k_buffer(0), v_buffer(0), pages, tile * KEYS, lowest, position,
                                        lane, 32);
     copy_commit();
     copy_wait<1>();            // the query rows (the first group) have landed for this thread
     __syncthreads();           // ... and for every thread
     for (int b = 0; tile <= my_last; tile += WARPS) {
         if (BUFFERS == 2 && tile + WARPS <= my_last) {
-            load_tile<HD>(k_buffer(b ^ 1), v_buffer(b ^ 1), pages, (tile + WARPS) * KEYS, lowest,
+            load_tile<HD, KEYS>(k_buffer(b ^ 1), v_buffer(b ^ 1), pages, (tile + WARPS) * KEYS, lowest,
                           position, lane, 32);
             copy_commit();
             copy_wait<1>();
@@ -388,13 +393,13 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kv,
             copy_wait<0>();
         }
         __syncwarp();
-        attend_tile<HD>(q_tile, 0, k_buffer(b), v_buffer(b), tile * KEYS, limit_lo, limit_hi,
+        attend_tile<HD, KEYS>(q_tile, 0, k_buffer(b), v_buffer(b), tile * KEYS, limit_lo, limit_hi,
                         scale_log2, m, l, o, lane);
         __syncwarp();
         if (BUFFERS == 2) {
             b ^= 1;
         } else if (tile + WARPS <= my_last) {      // one buffer: fetch the next tile now
-            load_tile<HD>(k_buffer(0), v_buffer(0), pages, (tile + WARPS) * KEYS, lowest,
+            load_tile<HD, KEYS>(k_buffer(0), v_buffer(0), pages, (tile + WARPS) * KEYS, lowest,
                           position, lane, 32);
             copy_commit();
         }
@@ -448,6 +453,8 @@ template <int HD>
 __global__ void attention_merge_kernel(const float* __restrict__ partial, bf16* __restrict__ out,
                                        int items, int splits) {
     constexpr int ROW_FLOATS = HD + 2;
+    griddep_launch();
+    griddep_wait();
     const int item = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     const int lane = threadIdx.x & 31;
     if (item >= items) return;
@@ -482,7 +489,7 @@ int launch_prefill(const void* q, const void* kv, long long kv_half, const int* 
                    void* out, int tokens, int requests, int heads, int kv_heads, float scale,
                    int window, cudaStream_t stream) {
     using T = Tile<HD>;
-    const size_t shared = (size_t)(ROWS + 4 * KEYS) * T::STRIDE * 2;
+    const size_t shared = (size_t)(ROWS + 4 * PREFILL_KEYS) * T::STRIDE * 2;
     auto kernel = attention_prefill_kernel<HD>;
     if (shared > 48 * 1024)
         cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
@@ -499,8 +506,8 @@ int launch_decode(const void* q, const void* kv, long long kv_half, const int* b
                   int requests, int heads, int kv_heads, int splits, float scale, int window,
                   cudaStream_t stream) {
     using T = Tile<HD>;
-    constexpr int BUFFERS = HD <= 64 ? 2 : 1;      // what fits into one block's shared memory
-    const size_t tiles = (size_t)WARPS * 2 * BUFFERS * KEYS * T::STRIDE * 2;
+    constexpr int BUFFERS = 2;
+    const size_t tiles = (size_t)WARPS * 2 * BUFFERS * DECODE_KEYS * T::STRIDE * 2;
     const size_t merge = (size_t)WARPS * 16 * (HD + 2) * 4;
     const size_t shared = (size_t)16 * T::STRIDE * 2 + (tiles > merge ? tiles : merge);
     auto kernel = attention_decode_kernel<HD, BUFFERS>;
@@ -508,13 +515,13 @@ int launch_decode(const void* q, const void* kv, long long kv_half, const int* b
         cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
     const int group = heads / kv_heads;
     const dim3 grid(kv_heads * ((group + 15) / 16), requests, splits);
-    kernel<<<grid, WARPS * 32, shared, stream>>>(
-        (const bf16*)q, (const bf16*)kv, kv_half, block_table, table_width, page_size, positions,
-        (bf16*)out, partial, heads, kv_heads, splits, scale * LOG2E, window);
+    launch_kernel(kernel, grid, dim3(WARPS * 32), shared, stream, true, (const bf16*)q,
+                  (const bf16*)kv, kv_half, block_table, table_width, page_size, positions,
+                  (bf16*)out, partial, heads, kv_heads, splits, scale * LOG2E, window);
     if (splits > 1) {
         const int items = requests * heads;
-        attention_merge_kernel<HD><<<(items + 3) / 4, 128, 0, stream>>>(partial, (bf16*)out, items,
-                                                                        splits);
+        launch_kernel(attention_merge_kernel<HD>, dim3((items + 3) / 4), dim3(128), 0, stream, true,
+                      (const float*)partial, (bf16*)out, items, splits);
     }
     return 0;
 }

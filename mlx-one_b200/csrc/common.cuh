@@ -102,4 +102,35 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
     return scratch[32];
 }
 
+// ------------------------------------------------------------------ dependent launches
+// A kernel launched with the programmatic-serialization attribute may start while its
+// predecessor in the stream still runs. It must call griddep_wait() before it reads anything
+// the predecessor wrote (what it does before that, such as fetching weights, overlaps with the
+// predecessor's tail). griddep_launch() lets the successor start early in the same way. Both
+// do nothing in a kernel launched the ordinary way.
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void griddep_launch() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+// Whether launches of the decode path ask for programmatic serialization (mlxone_set_pdl).
+bool mlxone_pdl_enabled();
+
+template <typename... KernelArgs, typename... Args>
+static inline cudaError_t launch_kernel(void (*kernel)(KernelArgs...), dim3 grid, dim3 block,
+                                        size_t shared, cudaStream_t stream, bool dependent,
+                                        Args... args) {
+    cudaLaunchConfig_t config = {};
+    config.gridDim = grid;
+    config.blockDim = block;
+    config.dynamicSmemBytes = shared;
+    config.stream = stream;
+    cudaLaunchAttribute attribute[1];
+    attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute[0].val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = attribute;
+    config.numAttrs = dependent && mlxone_pdl_enabled() ? 1 : 0;
+    return cudaLaunchKernelEx(&config, kernel, static_cast<KernelArgs>(args)...);
+}
+
 static inline int ceil_div_host(long long a, long long b) { return (int)((a + b - 1) / b); }

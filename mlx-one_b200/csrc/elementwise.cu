@@ -7,6 +7,8 @@ template <typename T>
 __global__ void embedding_kernel(const int* __restrict__ ids, const T* __restrict__ table,
                                  float* __restrict__ out, int hidden, int vocab,
                                  int* __restrict__ error_flag) {
+    griddep_launch();
+    griddep_wait();
     const int t = blockIdx.x;
     int id = ids[t];
     if (id < 0 || id >= vocab) {
@@ -25,11 +27,11 @@ MLXONE_API int mlxone_embedding(const int* ids, const void* table, float* out, i
     MLXONE_REQUIRE(tokens > 0 && hidden > 0 && vocab > 0, "embedding: bad sizes");
     const int threads = hidden >= 1024 ? 256 : 128;
     if (dtype == MLXONE_BF16)
-        embedding_kernel<__nv_bfloat16><<<tokens, threads, 0, stream>>>(
-            ids, (const __nv_bfloat16*)table, out, hidden, vocab, error_flag);
+        launch_kernel(embedding_kernel<__nv_bfloat16>, dim3(tokens), dim3(threads), 0, stream, true,
+                      ids, (const __nv_bfloat16*)table, out, hidden, vocab, error_flag);
     else
-        embedding_kernel<float><<<tokens, threads, 0, stream>>>(ids, (const float*)table, out,
-                                                               hidden, vocab, error_flag);
+        launch_kernel(embedding_kernel<float>, dim3(tokens), dim3(threads), 0, stream, true, ids,
+                      (const float*)table, out, hidden, vocab, error_flag);
     MLXONE_LAUNCH_CHECK("embedding");
     return 0;
 }
@@ -42,6 +44,8 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const T* __rest
                                    const float* __restrict__ weight, T* __restrict__ out,
                                    int hidden, float eps) {
     __shared__ float scratch[33];
+    griddep_launch();
+    griddep_wait();
     const size_t base = (size_t)blockIdx.x * hidden;
     float sum = 0.f;
     for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
@@ -58,18 +62,111 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const T* __rest
         out[base + c] = from_float<T>(residual[base + c] * inv * weight[c]);
 }
 
+// The same for rows of up to 4 * blockDim.x * PASSES values with hidden % 4 == 0: every value
+// stays in a register between the sum and the scaling, so the row is read once.
+template <typename T> struct Vec4;
+template <> struct Vec4<float> {
+    static __device__ __forceinline__ void load(const float* p, float (&v)[4]) {
+        const float4 x = *reinterpret_cast<const float4*>(p);
+        v[0] = x.x; v[1] = x.y; v[2] = x.z; v[3] = x.w;
+    }
+    static __device__ __forceinline__ void store(float* p, const float (&v)[4]) {
+        *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+    }
+};
+template <> struct Vec4<__nv_bfloat16> {
+    static __device__ __forceinline__ void load(const __nv_bfloat16* p, float (&v)[4]) {
+        const uint2 x = *reinterpret_cast<const uint2*>(p);
+        const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(&x.x);
+        const __nv_bfloat162 hi = *reinterpret_cast<const __nv_bfloat162*>(&x.y);
+        v[0] = __low2float(lo); v[1] = __high2float(lo);
+        v[2] = __low2float(hi); v[3] = __high2float(hi);
+    }
+    static __device__ __forceinline__ void store(__nv_bfloat16* p, const float (&v)[4]) {
+        const __nv_bfloat162 lo = __floats2bfloat162_rn(v[0], v[1]);
+        const __nv_bfloat162 hi = __floats2bfloat162_rn(v[2], v[3]);
+        uint2 x;
+        x.x = *reinterpret_cast<const uint32_t*>(&lo);
+        x.y = *reinterpret_cast<const uint32_t*>(&hi);
+        *reinterpret_cast<uint2*>(p) = x;
+    }
+};
+
+template <typename T, int PASSES>
+__global__ void add_rmsnorm_rows_kernel(float* __restrict__ residual, const T* __restrict__ delta,
+                                        const float* __restrict__ weight, T* __restrict__ out,
+                                        int hidden, float eps) {
+    __shared__ float scratch[33];
+    griddep_launch();
+    griddep_wait();
+    const size_t base = (size_t)blockIdx.x * hidden;
+    float values[PASSES][4];
+    float sum = 0.f;
+#pragma unroll
+    for (int pass = 0; pass < PASSES; ++pass) {
+        const int c = (pass * blockDim.x + threadIdx.x) * 4;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) values[pass][i] = 0.f;
+        if (c < hidden) {
+            Vec4<float>::load(residual + base + c, values[pass]);
+            if (delta != nullptr) {
+                float more[4];
+                Vec4<T>::load(delta + base + c, more);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) values[pass][i] += more[i];
+                Vec4<float>::store(residual + base + c, values[pass]);
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i) sum += values[pass][i] * values[pass][i];
+        }
+    }
+    const float total = block_sum(sum, scratch);
+    const float inv = rsqrtf(total / (float)hidden + eps);
+#pragma unroll
+    for (int pass = 0; pass < PASSES; ++pass) {
+        const int c = (pass * blockDim.x + threadIdx.x) * 4;
+        if (c < hidden) {
+            float scale[4], result[4];
+            Vec4<float>::load(weight + c, scale);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) result[i] = values[pass][i] * inv * scale[i];
+            Vec4<T>::store(out + base + c, result);
+        }
+    }
+}
+
+template <typename T>
+static cudaError_t launch_add_rmsnorm(float* residual, const void* delta, const float* weight,
+                                      void* out, int rows, int hidden, float eps,
+                                      cudaStream_t stream) {
+    const bool aligned = hidden % 4 == 0 && (reinterpret_cast<uintptr_t>(residual) & 15) == 0 &&
+                         (reinterpret_cast<uintptr_t>(weight) & 15) == 0 &&
+                         (reinterpret_cast<uintptr_t>(out) & 7) == 0 &&
+                         (reinterpret_cast<uintptr_t>(delta) & 7) == 0;
+    if (aligned && hidden <= 8192) {
+        const int quads = hidden / 4;
+        const int passes = quads <= 1024 ? 1 : 2;
+        int threads = ((quads + passes - 1) / passes + 31) / 32 * 32;
+        if (passes == 1)
+            return launch_kernel(add_rmsnorm_rows_kernel<T, 1>, dim3(rows), dim3(threads), 0, stream,
+                                 true, residual, (const T*)delta, weight, (T*)out, hidden, eps);
+        return launch_kernel(add_rmsnorm_rows_kernel<T, 2>, dim3(rows), dim3(threads), 0, stream,
+                             true, residual, (const T*)delta, weight, (T*)out, hidden, eps);
+    }
+    const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
+    return launch_kernel(add_rmsnorm_kernel<T>, dim3(rows), dim3(threads), 0, stream, true, residual,
+                         (const T*)delta, weight, (T*)out, hidden, eps);
+}
+
 MLXONE_API int mlxone_add_rmsnorm(float* residual, const void* delta, const float* weight,
                                   void* out, int rows, int hidden, float eps, int dtype,
                                   cudaStream_t stream) {
     if (rows == 0) return 0;
     MLXONE_REQUIRE(rows > 0 && hidden > 0, "add_rmsnorm: bad sizes");
-    const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
     if (dtype == MLXONE_BF16)
-        add_rmsnorm_kernel<__nv_bfloat16><<<rows, threads, 0, stream>>>(
-            residual, (const __nv_bfloat16*)delta, weight, (__nv_bfloat16*)out, hidden, eps);
+        launch_add_rmsnorm<__nv_bfloat16>(residual, delta, weight, out, rows, hidden, eps, stream);
     else
-        add_rmsnorm_kernel<float><<<rows, threads, 0, stream>>>(
-            residual, (const float*)delta, weight, (float*)out, hidden, eps);
+        launch_add_rmsnorm<float>(residual, delta, weight, out, rows, hidden, eps, stream);
     MLXONE_LAUNCH_CHECK("add_rmsnorm");
     return 0;
 }
@@ -80,6 +177,8 @@ template <typename T>
 __global__ void gather_rows_kernel(const float* __restrict__ residual, const T* __restrict__ delta,
                                    const int* __restrict__ rows, float* __restrict__ picked,
                                    T* __restrict__ picked_delta, int hidden, int tokens) {
+    griddep_launch();
+    griddep_wait();
     int src = rows[blockIdx.x];
     src = min(max(src, 0), tokens - 1);
     for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
@@ -95,12 +194,12 @@ MLXONE_API int mlxone_gather_rows(const float* residual, const void* delta, cons
     if (count == 0) return 0;
     MLXONE_REQUIRE(count > 0 && hidden > 0 && tokens > 0, "gather_rows: bad sizes");
     if (dtype == MLXONE_BF16)
-        gather_rows_kernel<__nv_bfloat16><<<count, 256, 0, stream>>>(
-            residual, (const __nv_bfloat16*)delta, rows, picked, (__nv_bfloat16*)picked_delta,
-            hidden, tokens);
+        launch_kernel(gather_rows_kernel<__nv_bfloat16>, dim3(count), dim3(256), 0, stream, true,
+                      residual, (const __nv_bfloat16*)delta, rows, picked,
+                      (__nv_bfloat16*)picked_delta, hidden, tokens);
     else
-        gather_rows_kernel<float><<<count, 256, 0, stream>>>(
-            residual, (const float*)delta, rows, picked, (float*)picked_delta, hidden, tokens);
+        launch_kernel(gather_rows_kernel<float>, dim3(count), dim3(256), 0, stream, true, residual,
+                      (const float*)delta, rows, picked, (float*)picked_delta, hidden, tokens);
     MLXONE_LAUNCH_CHECK("gather_rows");
     return 0;
 }

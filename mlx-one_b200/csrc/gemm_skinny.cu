@@ -1,0 +1,324 @@
+// Matrix products with few rows (decode steps): out[M, N] = a[M, K] * w[N, K]^T, M <= 32,
+// bfloat16 operands, 32-bit accumulation. Such a product takes as long as reading w once
+// takes, so the kernel is built around streaming w without a pause:
+//
+//   * persistent blocks, one per SM; a block owns a contiguous range of 16-row tiles of w (16
+//     outputs for every token) over the whole K, so no two blocks add into the same output
+//     and results do not depend on scheduling;
+//   * the block's warps take the 64-wide slices of K of the current tile in turn; every warp
+//     copies its slices of w asynchronously through a ring of its own in shared memory, and the
+//     ring runs on into the next tile, so the stream never drains inside the kernel;
+//   * slices are multiplied on tensor cores (mma m16n8k16: w is the 16-row operand, eight
+//     tokens the 8-column one); per tile the warps' partial sums are added in shared memory in
+//     a fixed order;
+//   * the copies of the first slices are issued before the kernel waits for its predecessor
+//     (griddep_wait), so weights already stream while the previous kernel finishes;
+//   * the activations are read after that wait: into shared memory once per block when the
+//     block has several tiles and they fit, else from L2 slice by slice, one slice ahead.
+//
+// Within a 32-wide piece of K, thread t of a quad reads elements 8t..8t+7 of both operands
+// with one 16-byte load and feeds them to two mma instructions; the sum over K does not care
+// in which order the products are taken.
+//
+// Epilogues: store bfloat16 (+ bias); SwiGLU (the block also owns the 16 matching rows of the
+// "up" half and writes silu(gate) * up); add into the 32-bit residual stream; store float32.
+#include "common.cuh"
+
+namespace {
+
+using bf16 = __nv_bfloat16;
+constexpr int ROWS = 16;          // rows of w per tile
+constexpr int SLICE = 64;         // K elements per slice
+constexpr int STAGES = 4;         // ring of slices per warp
+constexpr int SLICE_BYTES = ROWS * SLICE * 2;
+constexpr int WARPS = 16;
+
+enum : int { STORE_BF16 = 0, SWIGLU = 1, ADD_RESIDUAL = 2, STORE_F32 = 3 };
+
+__device__ __forceinline__ uint32_t shared_address(const void* p) {
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void copy16(uint32_t dst, const void* src, bool live) {
+    const int bytes = live ? 16 : 0;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(dst), "l"(src), "r"(bytes));
+}
+__device__ __forceinline__ void copy_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N>
+__device__ __forceinline__ void copy_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+
+// A 16-byte load that is served by L2: the activations were written by the kernel before this
+// one, which may still have been running when this block started, so neither the read-only
+// path nor a line left in L1 may be used.
+__device__ __forceinline__ uint4 load_l2(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.cg.v4.u32 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p));
+    return v;
+}
+
+__device__ __forceinline__ void mma_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                          uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "
+        "{%8,%9}, {%0,%1,%2,%3};\n"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// NT: groups of 8 tokens (M <= 8 * NT). RESIDENT: activations live in shared memory.
+// A SwiGLU block splits its warps in two halves: the first on the gate rows, the second on
+// the matching up rows.
+template <int NT, int EPILOGUE, bool RESIDENT>
+__global__ void __launch_bounds__(WARPS * 32)
+skinny_gemm_kernel(const bf16* a, int lda, const bf16* __restrict__ w,
+                   const float* __restrict__ bias, void* out, int ldo, int m, int n, int k,
+                   int up_offset, int tiles) {
+    constexpr int HALVES = EPILOGUE == SWIGLU ? 2 : 1;
+    constexpr int WARPS_K = WARPS / HALVES;
+    constexpr int TOKENS = 8 * NT;
+    extern __shared__ __align__(128) unsigned char shared_bytes[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int half = warp / WARPS_K, wk = warp % WARPS_K;
+    const int g = lane >> 2, t = lane & 3;
+    unsigned char* ring = shared_bytes + (size_t)warp * STAGES * SLICE_BYTES;
+    const uint32_t ring_address = shared_address(ring);
+    float* sums = reinterpret_cast<float*>(shared_bytes + (size_t)WARPS * STAGES * SLICE_BYTES);
+    unsigned char* resident = reinterpret_cast<unsigned char*>(sums + WARPS * ROWS * TOKENS);
+
+    // this block's tiles
+    const int tile_begin = (int)((long long)tiles * blockIdx.x / gridDim.x);
+    const int tile_end = (int)((long long)tiles * (blockIdx.x + 1) / gridDim.x);
+    const int row_limit = half == 0 ? (EPILOGUE == SWIGLU ? up_offset : n) : n;
+    const int slices = (k + SLICE - 1) / SLICE;
+    const int mine = slices > wk ? (slices - wk + WARPS_K - 1) / WARPS_K : 0;   // per tile
+    const int total = mine * (tile_end - tile_begin);     // this warp's slices over all tiles
+
+    // copy slice number `index` of this warp's stream into its ring: 16 rows x 8 pieces of 16 B;
+    // piece c of row r is stored at piece c ^ ((r & 1) << 2), which keeps the 16-byte reads of a
+    // quarter warp on different banks
+    auto fetch = [&](int index) {
+        const int tile = tile_begin + index / mine;
+        const int k0 = (wk + (index % mine) * WARPS_K) * SLICE;
+        const int row0 = tile * ROWS + half * up_offset;
+        const int buffer = index % STAGES;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int piece = lane + 32 * i;
+            const int r = piece >> 3, c = piece & 7;
+            const int kk = k0 + c * 8;
+            const bool live = row0 + r < row_limit && kk < k;
+            const bf16* src = w + (live ? (size_t)(row0 + r) * k + kk : 0);
+            copy16(ring_address + buffer * SLICE_BYTES + r * 128 + ((c ^ ((r & 1) << 2)) << 4), src,
+                   live);
+        }
+    };
+
+#pragma unroll
+    for (int p = 0; p < STAGES - 1; ++p) {
+        if (p < total) fetch(p);
+        copy_commit();
+    }
+    griddep_launch();
+    griddep_wait();            // from here on the predecessor's results may be read
+
+    // resident activations: [token][K] with 16-byte pieces swizzled by the token's parity
+    const int resident_stride = ((k + 63) / 64) * 64 * 2;        // bytes per token
+    if (RESIDENT) {
+        const int pieces = resident_stride / 16;
+        for (int item = threadIdx.x; item < TOKENS * pieces; item += WARPS * 32) {
+            const int token = item / pieces, c = item % pieces;
+            const bool live = token < m && c * 8 < k;
+            copy16(shared_address(resident) + token * resident_stride +
+                       ((c ^ ((token & 1) << 2)) << 4),
+                   a + (live ? (size_t)token * lda + c * 8 : 0), live);
+        }
+        copy_commit();
+        copy_wait<0>();        // also completes the ring's first slices; they are needed at once
+        __syncthreads();
+    }
+
+    // activations of the slice at K offset k0: [piece of 32][token group] -> 16 bytes
+    auto load_tokens = [&](int k0, uint4 (&regs)[2][NT]) {
+#pragma unroll
+        for (int q = 0; q < 2; ++q)
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+                const int token = nt * 8 + g, kk = k0 + q * 32 + t * 8;
+                if (RESIDENT) {
+                    const int c = kk >> 3;
+                    regs[q][nt] = *reinterpret_cast<const uint4*>(
+                        resident + token * resident_stride + ((c ^ ((token & 1) << 2)) << 4));
+                } else {
+                    regs[q][nt] = (token < m && kk < k) ? load_l2(a + (size_t)token * lda + kk)
+                                                        : make_uint4(0u, 0u, 0u, 0u);
+                }
+            }
+    };
+
+    float acc[NT][4];
+    uint4 tokens_now[2][NT], tokens_next[2][NT];
+    if (!RESIDENT && total > 0) load_tokens(wk * SLICE, tokens_now);
+
+    int index = 0;
+    for (int tile = tile_begin; tile < tile_end; ++tile) {
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) acc[nt][c] = 0.f;
+
+        for (int i = 0; i < mine; ++i, ++index) {
+            copy_wait<STAGES - 2>();
+            __syncwarp();
+            if (index + STAGES - 1 < total) fetch(index + STAGES - 1);
+            copy_commit();
+            if (RESIDENT) {
+                load_tokens((wk + i * WARPS_K) * SLICE, tokens_now);
+            } else if (index + 1 < total) {
+                load_tokens((wk + ((index + 1) % mine) * WARPS_K) * SLICE, tokens_next);
+            }
+            const unsigned char* slice = ring + (index % STAGES) * SLICE_BYTES;
+#pragma unroll
+            for (int q = 0; q < 2; ++q) {
+                const int c = q * 4 + t;
+                const uint4 lo = *reinterpret_cast<const uint4*>(
+                    slice + g * 128 + ((c ^ ((g & 1) << 2)) << 4));
+                const uint4 hi = *reinterpret_cast<const uint4*>(
+                    slice + (g + 8) * 128 + ((c ^ ((g & 1) << 2)) << 4));
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt) {
+                    mma_16816(acc[nt], lo.x, hi.x, lo.y, hi.y, tokens_now[q][nt].x,
+                              tokens_now[q][nt].y);
+                    mma_16816(acc[nt], lo.z, hi.z, lo.w, hi.w, tokens_now[q][nt].z,
+                              tokens_now[q][nt].w);
+                }
+            }
+            if (!RESIDENT) {
+#pragma unroll
+                for (int q = 0; q < 2; ++q)
+#pragma unroll
+                    for (int nt = 0; nt < NT; ++nt) tokens_now[q][nt] = tokens_next[q][nt];
+            }
+        }
+
+        // partial sums of this tile: [warp][row 0..15][token]
+        float* mine_sums = sums + (size_t)warp * ROWS * TOKENS;
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+            mine_sums[g * TOKENS + nt * 8 + 2 * t] = acc[nt][0];
+            mine_sums[g * TOKENS + nt * 8 + 2 * t + 1] = acc[nt][1];
+            mine_sums[(g + 8) * TOKENS + nt * 8 + 2 * t] = acc[nt][2];
+            mine_sums[(g + 8) * TOKENS + nt * 8 + 2 * t + 1] = acc[nt][3];
+        }
+        __syncthreads();
+        for (int item = threadIdx.x; item < ROWS * TOKENS; item += WARPS * 32) {
+            const int token = item / ROWS, r = item % ROWS;     // rows fastest: neighbours in memory
+            const int column = tile * ROWS + r;
+            if (token >= m || column >= (EPILOGUE == SWIGLU ? up_offset : n)) continue;
+            float value = 0.f;
+#pragma unroll
+            for (int wi = 0; wi < WARPS_K; ++wi)
+                value += sums[((size_t)wi * ROWS + r) * TOKENS + token];
+            if (bias != nullptr) value += bias[column];
+            if (EPILOGUE == SWIGLU) {
+                float up = 0.f;
+#pragma unroll
+                for (int wi = 0; wi < WARPS_K; ++wi)
+                    up += sums[((size_t)(WARPS_K + wi) * ROWS + r) * TOKENS + token];
+                if (bias != nullptr) up += bias[up_offset + column];
+                reinterpret_cast<bf16*>(out)[(size_t)token * ldo + column] =
+                    __float2bfloat16_rn(value / (1.f + expf(-value)) * up);
+            } else if (EPILOGUE == STORE_BF16) {
+                reinterpret_cast<bf16*>(out)[(size_t)token * ldo + column] =
+                    __float2bfloat16_rn(value);
+            } else if (EPILOGUE == ADD_RESIDUAL) {
+                reinterpret_cast<float*>(out)[(size_t)token * ldo + column] += value;
+            } else {
+                reinterpret_cast<float*>(out)[(size_t)token * ldo + column] = value;
+            }
+        }
+        __syncthreads();       // the sums are free for the next tile
+    }
+    copy_wait<0>();
+}
+
+int g_sm_count = 0;
+
+template <int NT, int EPILOGUE>
+cudaError_t launch(const void* a, int lda, const void* w, const float* bias, void* out, int ldo,
+                   int m, int n, int k, int up_offset, cudaStream_t stream) {
+    if (g_sm_count == 0) {
+        int device = 0;
+        cudaGetDevice(&device);
+        cudaDeviceGetAttribute(&g_sm_count, cudaDevAttrMultiProcessorCount, device);
+        if (g_sm_count <= 0) g_sm_count = 148;
+    }
+    const int tiles = ((EPILOGUE == SWIGLU ? up_offset : n) + ROWS - 1) / ROWS;
+    const int grid = tiles < g_sm_count ? tiles : g_sm_count;
+    const size_t rings = (size_t)WARPS * STAGES * SLICE_BYTES;
+    const size_t sums = (size_t)WARPS * ROWS * 8 * NT * sizeof(float);
+    const size_t resident = (size_t)8 * NT * ((k + 63) / 64) * 64 * 2;
+    // activations in shared memory pay off when a block reuses them for several tiles
+    const bool use_resident = NT <= 2 && tiles >= 2 * grid && rings + sums + resident <= 200 * 1024;
+    const size_t shared = rings + sums + (use_resident ? resident : 0);
+    cudaError_t err;
+    if (use_resident) {
+        auto kernel = skinny_gemm_kernel<NT, EPILOGUE, (NT <= 2)>;
+        err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
+        if (err != cudaSuccess) return err;
+        return launch_kernel(kernel, dim3(grid), dim3(WARPS * 32), shared, stream, true,
+                             (const bf16*)a, lda, (const bf16*)w, bias, out, ldo, m, n, k,
+                             up_offset, tiles);
+    }
+    auto kernel = skinny_gemm_kernel<NT, EPILOGUE, false>;
+    err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
+    if (err != cudaSuccess) return err;
+    return launch_kernel(kernel, dim3(grid), dim3(WARPS * 32), shared, stream, true, (const bf16*)a,
+                         lda, (const bf16*)w, bias, out, ldo, m, n, k, up_offset, tiles);
+}
+
+template <int EPILOGUE>
+cudaError_t launch_for_rows(const void* a, int lda, const void* w, const float* bias, void* out,
+                            int ldo, int m, int n, int k, int up_offset, cudaStream_t stream) {
+    if (m <= 8) return launch<1, EPILOGUE>(a, lda, w, bias, out, ldo, m, n, k, up_offset, stream);
+    if (m <= 16) return launch<2, EPILOGUE>(a, lda, w, bias, out, ldo, m, n, k, up_offset, stream);
+    return launch<4, EPILOGUE>(a, lda, w, bias, out, ldo, m, n, k, up_offset, stream);
+}
+
+}  // namespace
+
+// Most rows (tokens) that the skinny product takes; more go to the library product.
+MLXONE_API int mlxone_gemm_skinny_max_rows() { return 32; }
+
+// epilogue: 0 = out bf16 [m, n]; 1 = SwiGLU, w is [gate rows; up rows] with n = 2 * width, out
+// bf16 [m, width]; 2 = out is the float32 residual [m, n], added in place; 3 = out float32.
+MLXONE_API int mlxone_gemm_skinny(const void* a, int lda, const void* w, const float* bias,
+                                  void* out, int ldo, int m, int n, int k, int epilogue,
+                                  cudaStream_t stream) {
+    if (m == 0 || n == 0) return 0;
+    MLXONE_REQUIRE(m > 0 && m <= 32, "gemm_skinny: %d rows, at most 32", m);
+    MLXONE_REQUIRE(n > 0 && k > 0 && k % 8 == 0 && lda % 8 == 0,
+                   "gemm_skinny: K (%d) and the row stride of a (%d) must be multiples of 8", k, lda);
+    MLXONE_REQUIRE((reinterpret_cast<uintptr_t>(a) & 15) == 0 &&
+                       (reinterpret_cast<uintptr_t>(w) & 15) == 0,
+                   "gemm_skinny: operands must be 16-byte aligned");
+    MLXONE_REQUIRE(epilogue >= 0 && epilogue <= 3, "gemm_skinny: unknown epilogue %d", epilogue);
+    MLXONE_REQUIRE(epilogue != SWIGLU || n % 2 == 0, "gemm_skinny: SwiGLU needs an even n");
+    cudaError_t err;
+    switch (epilogue) {
+        case STORE_BF16:
+            err = launch_for_rows<STORE_BF16>(a, lda, w, bias, out, ldo, m, n, k, 0, stream); break;
+        case SWIGLU:
+            err = launch_for_rows<SWIGLU>(a, lda, w, bias, out, ldo, m, n, k, n / 2, stream); break;
+        case ADD_RESIDUAL:
+            err = launch_for_rows<ADD_RESIDUAL>(a, lda, w, bias, out, ldo, m, n, k, 0, stream); break;
+        default:
+            err = launch_for_rows<STORE_F32>(a, lda, w, bias, out, ldo, m, n, k, 0, stream); break;
+    }
+    if (err != cudaSuccess) {
+        mlxone_set_error("gemm_skinny: launch failed: %s", cudaGetErrorString(err));
+        return 2;
+    }
+    MLXONE_LAUNCH_CHECK("gemm_skinny");
+    return 0;
+}

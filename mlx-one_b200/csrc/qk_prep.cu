@@ -24,6 +24,8 @@ qk_prep_kernel(const T* __restrict__ qkv, const float* __restrict__ q_weight,
                int page_size, long long kv_half, int tokens, int heads, int kv_heads,
                int head_dim, int write_kv, int* __restrict__ error_flag) {
     extern __shared__ float shared[];
+    griddep_launch();
+    griddep_wait();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int slots_per_token = heads + 2 * kv_heads;
     const long long item = (long long)blockIdx.x * WARPS + warp;
@@ -107,14 +109,12 @@ MLXONE_API int mlxone_qk_prep(const void* qkv, const float* q_weight, const floa
     const long long kv_half = (long long)pages * kv_heads * page_size * head_dim;
     if (dtype == MLXONE_BF16) {
         using T = __nv_bfloat16;
-        qk_prep_kernel<T><<<blocks, WARPS * 32, shared, stream>>>(
-            (const T*)qkv, q_weight, k_weight, eps, inv_freq, rotary_dim, positions,
+        launch_kernel(qk_prep_kernel<T>, dim3(blocks), dim3(WARPS * 32), shared, stream, true, (const T*)qkv, q_weight, k_weight, eps, inv_freq, rotary_dim, positions,
             token_request, (T*)q_out, (T*)kv, block_table, table_width, page_size, kv_half,
             tokens, heads, kv_heads, head_dim, write_kv, error_flag);
     } else {
         using T = float;
-        qk_prep_kernel<T><<<blocks, WARPS * 32, shared, stream>>>(
-            (const T*)qkv, q_weight, k_weight, eps, inv_freq, rotary_dim, positions,
+        launch_kernel(qk_prep_kernel<T>, dim3(blocks), dim3(WARPS * 32), shared, stream, true, (const T*)qkv, q_weight, k_weight, eps, inv_freq, rotary_dim, positions,
             token_request, (T*)q_out, (T*)kv, block_table, table_width, page_size, kv_half,
             tokens, heads, kv_heads, head_dim, write_kv, error_flag);
     }

@@ -73,6 +73,8 @@ __device__ __forceinline__ int block_argmax(const float* __restrict__ row, int v
 
 __global__ void __launch_bounds__(THREADS)
 argmax_kernel(const float* __restrict__ logits, int vocab, int* __restrict__ out) {
+    griddep_launch();
+    griddep_wait();
     const int index = block_argmax(logits + (size_t)blockIdx.x * vocab, vocab);
     if (threadIdx.x == 0) out[blockIdx.x] = index;
 }
@@ -264,6 +266,8 @@ __global__ void decode_advance_kernel(const int* __restrict__ chosen, int* __res
                                       int* __restrict__ positions, int* __restrict__ history,
                                       int* __restrict__ record, int* __restrict__ counter,
                                       int requests, int max_steps) {
+    griddep_launch();
+    griddep_wait();
     const int r = blockIdx.x * blockDim.x + threadIdx.x;
     const int step = *counter;
     if (r < requests) {
@@ -280,17 +284,92 @@ MLXONE_API int mlxone_decode_advance(const int* chosen, int* token_ids, int* pos
                                      int* history, int* record, int* counter, int requests,
                                      int max_steps, cudaStream_t stream) {
     MLXONE_REQUIRE(requests > 0 && requests <= 1024, "decode_advance: 1..1024 requests");
-    decode_advance_kernel<<<1, 1024, 0, stream>>>(chosen, token_ids, positions, history, record,
-                                                 counter, requests, max_steps);
+    launch_kernel(decode_advance_kernel, dim3(1), dim3(1024), 0, stream, true, chosen, token_ids,
+                  positions, history, record, counter, requests, max_steps);
     MLXONE_LAUNCH_CHECK("decode_advance");
     return 0;
 }
 
+// Argmax in two stages for wide rows: stage 1 reduces pieces of ARGMAX_PIECE entries to
+// (value, index) pairs in scratch, stage 2 reduces the pairs. Few rows then still fill the GPU.
+constexpr int ARGMAX_PIECE = 2048;
+
+__global__ void __launch_bounds__(256)
+argmax_pieces_kernel(const float* __restrict__ logits, int vocab, int pieces,
+                     float* __restrict__ piece_value, int* __restrict__ piece_index) {
+    __shared__ float best_value[8];
+    __shared__ int best_index[8];
+    griddep_launch();
+    griddep_wait();
+    const float* row = logits + (size_t)blockIdx.y * vocab;
+    const int begin = blockIdx.x * ARGMAX_PIECE, end = min(begin + ARGMAX_PIECE, vocab);
+    float value = -INFINITY;
+    int index = 0x7fffffff;
+    for (int i = begin + threadIdx.x; i < end; i += 256) {
+        const float v = row[i];
+        if (v > value || (v == value && i < index)) { value = v; index = i; }
+    }
+    for (int offset = 16; offset > 0; offset >>= 1) {
+        const float other = __shfl_xor_sync(0xffffffffu, value, offset);
+        const int other_index = __shfl_xor_sync(0xffffffffu, index, offset);
+        if (other > value || (other == value && other_index < index)) {
+            value = other; index = other_index;
+        }
+    }
+    if ((threadIdx.x & 31) == 0) { best_value[threadIdx.x >> 5] = value; best_index[threadIdx.x >> 5] = index; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < 8; ++w)
+            if (best_value[w] > value || (best_value[w] == value && best_index[w] < index)) {
+                value = best_value[w]; index = best_index[w];
+            }
+        piece_value[(size_t)blockIdx.y * pieces + blockIdx.x] = value;
+        piece_index[(size_t)blockIdx.y * pieces + blockIdx.x] = index;
+    }
+}
+
+__global__ void argmax_merge_kernel(const float* __restrict__ piece_value,
+                                    const int* __restrict__ piece_index, int pieces,
+                                    int* __restrict__ out) {
+    griddep_launch();
+    griddep_wait();
+    const int lane = threadIdx.x;
+    float value = -INFINITY;
+    int index = 0x7fffffff;
+    for (int i = lane; i < pieces; i += 32) {
+        const float v = piece_value[(size_t)blockIdx.x * pieces + i];
+        const int at = piece_index[(size_t)blockIdx.x * pieces + i];
+        if (v > value || (v == value && at < index)) { value = v; index = at; }
+    }
+    for (int offset = 16; offset > 0; offset >>= 1) {
+        const float other = __shfl_xor_sync(0xffffffffu, value, offset);
+        const int other_index = __shfl_xor_sync(0xffffffffu, index, offset);
+        if (other > value || (other == value && other_index < index)) {
+            value = other; index = other_index;
+        }
+    }
+    if (lane == 0) out[blockIdx.x] = index == 0x7fffffff ? 0 : index;
+}
+
+// Entries of float/int scratch that mlxone_argmax needs for rows of `vocab` entries (0: none).
+MLXONE_API int mlxone_argmax_scratch(int rows, int vocab) {
+    const int pieces = (vocab + ARGMAX_PIECE - 1) / ARGMAX_PIECE;
+    return pieces > 1 ? rows * pieces : 0;
+}
+
 MLXONE_API int mlxone_argmax(const float* logits, int rows, int vocab, int* out,
-                             cudaStream_t stream) {
+                             float* piece_value, int* piece_index, cudaStream_t stream) {
     if (rows == 0) return 0;
-    MLXONE_REQUIRE(rows > 0 && vocab > 0, "argmax: bad sizes");
-    argmax_kernel<<<rows, THREADS, 0, stream>>>(logits, vocab, out);
+    MLXONE_REQUIRE(rows > 0 && vocab > 0 && rows <= 65535, "argmax: bad sizes");
+    const int pieces = (vocab + ARGMAX_PIECE - 1) / ARGMAX_PIECE;
+    if (pieces == 1 || piece_value == nullptr || piece_index == nullptr) {
+        launch_kernel(argmax_kernel, dim3(rows), dim3(THREADS), 0, stream, true, logits, vocab, out);
+    } else {
+        launch_kernel(argmax_pieces_kernel, dim3(pieces, rows), dim3(256), 0, stream, true, logits,
+                      vocab, pieces, piece_value, piece_index);
+        launch_kernel(argmax_merge_kernel, dim3(rows), dim3(32), 0, stream, true,
+                      (const float*)piece_value, (const int*)piece_index, pieces, out);
+    }
     MLXONE_LAUNCH_CHECK("argmax");
     return 0;
 }

@@ -20,6 +20,8 @@ __global__ void short_conv_kernel(const T* __restrict__ bcx, const float* __rest
                                   const int* __restrict__ request_start,
                                   const int* __restrict__ history, T* __restrict__ out,
                                   int tokens, int hidden, int taps) {
+    griddep_launch();
+    griddep_wait();
     const int d = blockIdx.y * blockDim.x + threadIdx.x;
     const int t = blockIdx.x;
     if (d >= hidden) return;
@@ -50,6 +52,8 @@ __global__ void short_conv_state_kernel(const T* __restrict__ bcx, T* __restrict
                                         const int* __restrict__ slots,
                                         const int* __restrict__ request_start,
                                         const int* __restrict__ history, int hidden, int taps) {
+    griddep_launch();
+    griddep_wait();
     const int d = blockIdx.x * blockDim.x + threadIdx.x;
     const int r = blockIdx.y;
     if (d >= hidden) return;
@@ -90,24 +94,20 @@ MLXONE_API int mlxone_short_conv(const void* bcx, const float* kernel, const flo
     MLXONE_REQUIRE(requests <= 65535, "short_conv: at most 65535 requests a step");
     if (dtype == MLXONE_BF16) {
         using T = __nv_bfloat16;
-        short_conv_kernel<T><<<grid, threads, 0, stream>>>(
-            (const T*)bcx, kernel, bias, (const T*)state, slots, token_request, request_start,
+        launch_kernel(short_conv_kernel<T>, grid, dim3(threads), 0, stream, true, (const T*)bcx, kernel, bias, (const T*)state, slots, token_request, request_start,
             history, (T*)out, tokens, hidden, taps);
         MLXONE_LAUNCH_CHECK("short_conv");
         if (write_state && taps > 1) {
-            short_conv_state_kernel<T><<<state_grid, threads, 0, stream>>>(
-                (const T*)bcx, (T*)state, slots, request_start, history, hidden, taps);
+            launch_kernel(short_conv_state_kernel<T>, state_grid, dim3(threads), 0, stream, true, (const T*)bcx, (T*)state, slots, request_start, history, hidden, taps);
             MLXONE_LAUNCH_CHECK("short_conv_state");
         }
     } else {
         using T = float;
-        short_conv_kernel<T><<<grid, threads, 0, stream>>>(
-            (const T*)bcx, kernel, bias, (const T*)state, slots, token_request, request_start,
+        launch_kernel(short_conv_kernel<T>, grid, dim3(threads), 0, stream, true, (const T*)bcx, kernel, bias, (const T*)state, slots, token_request, request_start,
             history, (T*)out, tokens, hidden, taps);
         MLXONE_LAUNCH_CHECK("short_conv");
         if (write_state && taps > 1) {
-            short_conv_state_kernel<T><<<state_grid, threads, 0, stream>>>(
-                (const T*)bcx, (T*)state, slots, request_start, history, hidden, taps);
+            launch_kernel(short_conv_state_kernel<T>, state_grid, dim3(threads), 0, stream, true, (const T*)bcx, (T*)state, slots, request_start, history, hidden, taps);
             MLXONE_LAUNCH_CHECK("short_conv_state");
         }
     }

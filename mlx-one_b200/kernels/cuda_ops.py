@@ -56,6 +56,8 @@ class CudaOps:
         self.error_flag = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.launches = 0
         self.tensor_core_attention = True
+        self.skinny_products = True
+        self._skinny_rows = self.lib.mlxone_gemm_skinny_max_rows()
         self._sample_scratch: torch.Tensor | None = None
 
     # ------------------------------------------------------------------ plumbing
@@ -71,6 +73,11 @@ class CudaOps:
         if tensor.dtype != dtype or not tensor.is_contiguous() or tensor.device != self.device:
             raise KernelError(f"{what} must be a contiguous {dtype} tensor on {self.device}, got "
                               f"{tensor.dtype} {tuple(tensor.shape)} on {tensor.device}")
+
+    def set_dependent_launches(self, enabled: bool) -> None:
+        """Programmatic dependent launches on the decode path: a kernel may start, and fetch
+        its weights, while the one before it finishes."""
+        self.lib.mlxone_set_pdl(1 if enabled else 0)
 
     def check_errors(self) -> None:
         """Reads the device error flag (synchronises) and raises if a kernel set it."""
@@ -132,15 +139,33 @@ class CudaOps:
                    _c_int(count), _c_int(hidden), _c_int(residual.shape[0]), _c_int(code))
         return picked, picked_delta
 
-    def linear(self, a, w, bias=None, out_dtype=None):
-        """a[M, K] @ w[N, K]^T (+ bias[N], float32). ``out_dtype``: a's dtype, or float32."""
+    # epilogues of the skinny product
+    _STORE, _SWIGLU, _ADD, _STORE_F32 = 0, 1, 2, 3
+
+    def _skinny(self, a, w) -> bool:
+        """Whether a[M, K] @ w[N, K]^T goes to the weight-streaming kernel: bfloat16, few rows,
+        16-byte aligned rows. Everything else goes to the library product."""
+        return (self.skinny_products and a.dtype == torch.bfloat16
+                and 0 < a.shape[0] <= self._skinny_rows and a.shape[1] % 8 == 0
+                and a.stride(0) % 8 == 0 and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+    def _skinny_call(self, a, w, bias, out, ldo, epilogue) -> None:
+        self._call("mlxone_gemm_skinny", _c_void_p(_ptr(a)), _c_int(a.stride(0)),
+                   _c_void_p(_ptr(w)), _c_void_p(_ptr(bias)), _c_void_p(_ptr(out)), _c_int(ldo),
+                   _c_int(a.shape[0]), _c_int(w.shape[0]), _c_int(a.shape[1]), _c_int(epilogue))
+
+    def _check_product(self, a, w) -> None:
         if a.dtype != w.dtype:
             raise KernelError(f"matrix product of {a.dtype} with {w.dtype}")
+        if a.dim() != 2 or w.dim() != 2 or w.shape[1] != a.shape[1]:
+            raise KernelError(f"matrix product of {tuple(a.shape)} with {tuple(w.shape)}^T")
+
+    def linear(self, a, w, bias=None, out_dtype=None):
+        """a[M, K] @ w[N, K]^T (+ bias[N], float32). ``out_dtype``: a's dtype, or float32."""
+        self._check_product(a, w)
         out_dtype = out_dtype or a.dtype
         m, k = a.shape
         n = w.shape[0]
-        if w.shape[1] != k:
-            raise KernelError(f"matrix product of [{m}, {k}] with [{n}, {w.shape[1]}]^T")
         if a.dtype == torch.float32:
             self._need(a, torch.float32, "a")
             self._need(w, torch.float32, "w")
@@ -148,6 +173,11 @@ class CudaOps:
             self._call("mlxone_gemm_f32", _c_void_p(_ptr(a)), _c_int(k), _c_void_p(_ptr(w)),
                        _c_int(k), _c_void_p(_ptr(bias)), _c_void_p(_ptr(out)), _c_int(n),
                        _c_int(m), _c_int(n), _c_int(k))
+            return out
+        if self._skinny(a, w):
+            out = torch.empty((m, n), dtype=out_dtype, device=self.device)
+            self._skinny_call(a, w, bias, out, n,
+                              self._STORE_F32 if out_dtype == torch.float32 else self._STORE)
             return out
         if out_dtype == torch.float32:
             out = torch.mm(a, w.t(), out_dtype=torch.float32)
@@ -157,6 +187,28 @@ class CudaOps:
             self._call("mlxone_add_bias", _c_void_p(_ptr(out)), _c_void_p(_ptr(bias)), _c_int(m),
                        _c_int(n), _c_int(_dtype_code(out.dtype)))
         return out
+
+    def linear_swiglu(self, a, gate_up):
+        """silu(a @ gate^T) * (a @ up^T) with gate_up = [gate rows; up rows]: one kernel for
+        few rows, else a product followed by the gate kernel."""
+        self._check_product(a, gate_up)
+        if self._skinny(a, gate_up):
+            width = gate_up.shape[0] // 2
+            out = torch.empty((a.shape[0], width), dtype=a.dtype, device=self.device)
+            self._skinny_call(a, gate_up, None, out, width, self._SWIGLU)
+            return out
+        return self.swiglu(self.linear(a, gate_up))
+
+    def linear_add(self, a, w, bias, residual):
+        """Adds a @ w^T (+ bias) to the float32 ``residual``. Returns None if it was added in
+        place (few rows: the product's epilogue does it), else the product, which the caller
+        adds with the next norm."""
+        self._check_product(a, w)
+        if self._skinny(a, w):
+            self._need(residual, torch.float32, "residual")
+            self._skinny_call(a, w, bias, residual, residual.shape[1], self._ADD)
+            return None
+        return self.linear(a, w, bias)
 
     def swiglu(self, gate_up):
         rows, twice = gate_up.shape
@@ -211,8 +263,8 @@ class CudaOps:
         code = _dtype_code(q.dtype)
         if self.tensor_core_attention and self.lib.mlxone_attention_mma_supports(head_dim, code):
             if ctx.max_portion == 1 and tokens == ctx.requests:
-                splits = self.decode_splits(ctx.requests, heads, kv_heads, width * view.page_size,
-                                            window)
+                splits = self.decode_splits(ctx.requests, heads, kv_heads, head_dim,
+                                            width * view.page_size, window)
                 partial = None
                 if splits > 1:
                     partial = torch.empty(ctx.requests * heads * splits * (head_dim + 2),
@@ -244,22 +296,30 @@ class CudaOps:
         return out
 
     @staticmethod
-    def decode_splits(requests: int, heads: int, kv_heads: int, context_bound: int,
-                      window: int | None) -> int:
-        """Into how many parts the decode kernel cuts a request's keys: enough blocks to
-        fill the GPU about twice, but at least four tiles of 64 keys per part."""
+    def decode_splits(requests: int, heads: int, kv_heads: int, head_dim: int,
+                      context_bound: int, window: int | None) -> int:
+        """Into how many parts the decode kernel cuts a request's keys: as many blocks as the
+        GPU holds at once (one wave), but at least four tiles of 32 keys per part."""
         if window:
-            context_bound = min(context_bound, window + 63)
-        tiles = max(-(-context_bound // 64), 1)
+            context_bound = min(context_bound, window + 31)
+        tiles = max(-(-context_bound // 32), 1)
+        block_bytes = (16 + 4 * 2 * 2 * 32) * (head_dim + 8) * 2
+        blocks_per_sm = max(1, min(8, 220 * 1024 // block_bytes))
         groups = kv_heads * (-(-(heads // kv_heads) // 16))
-        wanted = max(2 * 148 // max(requests * groups, 1), 1)
-        return max(min(wanted, -(-tiles // 4)), 1)
+        wanted = max(148 * blocks_per_sm // max(requests * groups, 1), 1)
+        return max(min(wanted, tiles // 4), 1)
 
     def argmax(self, logits):
         self._need(logits, torch.float32, "logits")
-        out = torch.empty((logits.shape[0],), dtype=torch.int32, device=self.device)
-        self._call("mlxone_argmax", _c_void_p(_ptr(logits)), _c_int(logits.shape[0]),
-                   _c_int(logits.shape[1]), _c_void_p(_ptr(out)))
+        rows, vocab = logits.shape
+        out = torch.empty((rows,), dtype=torch.int32, device=self.device)
+        scratch = self.lib.mlxone_argmax_scratch(rows, vocab)
+        values = indices = None
+        if scratch:
+            values = torch.empty(scratch, dtype=torch.float32, device=self.device)
+            indices = torch.empty(scratch, dtype=torch.int32, device=self.device)
+        self._call("mlxone_argmax", _c_void_p(_ptr(logits)), _c_int(rows), _c_int(vocab),
+                   _c_void_p(_ptr(out)), _c_void_p(_ptr(values)), _c_void_p(_ptr(indices)))
         return out
 
     def decode_advance(self, chosen, token_ids, positions, history, record, counter):

@@ -122,6 +122,9 @@ class Part:
 
 
 class Mixer(Part):
+    # True: forward takes ``residual=`` and may add its output there itself, returning None
+    fuses_residual = False
+
     @classmethod
     def cache_need(cls, spec: PartSpec):
         """``PagedKeyValues``, ``FixedState`` or None."""
@@ -135,6 +138,8 @@ class Mixer(Part):
 
 
 class FeedForward(Part):
+    fuses_residual = False      # as for mixers
+
     def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         raise NotImplementedError
 

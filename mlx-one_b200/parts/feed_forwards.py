@@ -30,6 +30,10 @@ class SwiGLU(FeedForward):
         self.gate_up = self.matrix(torch.cat([tensors["w1.weight"], tensors["w3.weight"]], dim=0))
         self.down = self.matrix(tensors["w2.weight"])
 
-    def forward(self, x, ctx):
-        gate_up = self.ops.linear(x, self.gate_up)
-        return self.ops.linear(self.ops.swiglu(gate_up), self.down)
+    fuses_residual = True
+
+    def forward(self, x, ctx, residual=None):
+        gated = self.ops.linear_swiglu(x, self.gate_up)
+        if residual is None:
+            return self.ops.linear(gated, self.down)
+        return self.ops.linear_add(gated, self.down, None, residual)

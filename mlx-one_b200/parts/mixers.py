@@ -62,7 +62,9 @@ class Attention(Mixer):
         self.position = POSITIONS.get(position.kind)(position, {}, runtime)
         self.ops.check_attention_sizes(self.heads, self.kv_heads, self.head_dim)
 
-    def forward(self, x, ctx, cache, write):
+    fuses_residual = True
+
+    def forward(self, x, ctx, cache, write, residual=None):
         qkv = self.ops.linear(x, self.qkv)
         q = self.ops.qk_norm_rope_store(
             qkv, heads=self.heads, kv_heads=self.kv_heads, head_dim=self.head_dim,
@@ -71,7 +73,9 @@ class Attention(Mixer):
         mixed = self.ops.paged_attention(
             q, heads=self.heads, kv_heads=self.kv_heads, head_dim=self.head_dim,
             scale=self.scale, window=self.window, ctx=ctx, view=cache)
-        return self.ops.linear(mixed, self.out)
+        if residual is None:
+            return self.ops.linear(mixed, self.out)
+        return self.ops.linear_add(mixed, self.out, None, residual)
 
 
 @MIXERS.register("short_conv")
@@ -113,8 +117,12 @@ class ShortConv(Mixer):
         self.conv_bias = self.vector(tensors["conv_bias"]) if bias else None
         self.out_bias = self.vector(tensors["out_proj.bias"]) if bias else None
 
-    def forward(self, x, ctx, cache, write):
+    fuses_residual = True
+
+    def forward(self, x, ctx, cache, write, residual=None):
         bcx = self.ops.linear(x, self.in_proj, self.in_bias)
         gated = self.ops.short_conv(bcx, kernel=self.kernel, bias=self.conv_bias,
                                     taps=self.taps, ctx=ctx, view=cache, write=write)
-        return self.ops.linear(gated, self.out_proj, self.out_bias)
+        if residual is None:
+            return self.ops.linear(gated, self.out_proj, self.out_bias)
+        return self.ops.linear_add(gated, self.out_proj, self.out_bias, residual)

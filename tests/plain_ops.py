@@ -45,6 +45,12 @@ class PlainOps:
             out = out + bias
         return out.to(out_dtype or a.dtype)
 
+    def linear_swiglu(self, a, gate_up):
+        return self.swiglu(self.linear(a, gate_up))
+
+    def linear_add(self, a, w, bias, residual):
+        return self.linear(a, w, bias)
+
     def swiglu(self, gate_up):
         width = gate_up.shape[1] // 2
         gate, up = gate_up[:, :width].float(), gate_up[:, width:].float()

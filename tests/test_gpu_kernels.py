@@ -121,6 +121,37 @@ def test_matrix_product_bfloat16(ops, plain, m, n, k):
     torch.testing.assert_close(logits, a.float() @ w.float().T, atol=1e-3 * math.sqrt(k), rtol=1e-3)
 
 
+@pytest.mark.parametrize("m", [1, 7, 8, 9, 16, 17, 32])
+@pytest.mark.parametrize("n,k", [(16, 64), (333, 136), (1000, 2048), (96, 8192), (50, 8)])
+def test_skinny_product(ops, m, n, k):
+    """The weight-streaming product for few rows, all four epilogues, against float64."""
+    torch.manual_seed(m * 1000 + n + k)
+    a = torch.randn(m, k).bfloat16()
+    w = (torch.randn(n, k) / math.sqrt(k)).bfloat16()
+    bias = torch.randn(n)
+    want = a.double() @ w.double().T
+    assert ops._skinny(a.to(DEVICE), w.to(DEVICE))
+    before = ops.launches
+    got = ops.linear(a.to(DEVICE), w.to(DEVICE), bias.to(DEVICE))
+    assert ops.launches == before + 1          # one kernel, no library call plus bias kernel
+    torch.testing.assert_close(got.cpu().double(), want + bias.double(), atol=2e-2, rtol=2e-2)
+    logits = ops.linear(a.to(DEVICE), w.to(DEVICE), out_dtype=torch.float32)
+    torch.testing.assert_close(logits.cpu().double(), want, atol=1e-3, rtol=1e-3)
+    residual = torch.randn(m, n)
+    on_gpu = residual.clone().to(DEVICE)
+    assert ops.linear_add(a.to(DEVICE), w.to(DEVICE), bias.to(DEVICE), on_gpu) is None
+    torch.testing.assert_close(on_gpu.cpu().double(), residual.double() + want + bias.double(),
+                               atol=1e-3, rtol=1e-3)
+    if n % 2 == 0:
+        gated = ops.linear_swiglu(a.to(DEVICE), w.to(DEVICE))
+        gate, up = want[:, :n // 2], want[:, n // 2:]
+        torch.testing.assert_close(gated.cpu().double(), gate * torch.sigmoid(gate) * up,
+                                   atol=2e-2, rtol=2e-2)
+    # a token's result does not depend on the other tokens of the call
+    alone = ops.linear(a[:1].contiguous().to(DEVICE), w.to(DEVICE), out_dtype=torch.float32)
+    assert torch.equal(alone[0].cpu(), logits[0].cpu())
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("hidden,taps,bias", [(48, 3, False), (200, 4, True), (64, 2, True),
                                               (32, 1, False), (96, 7, False)])
@@ -250,14 +281,14 @@ def test_attention_decode_tensor_cores(ops, plain, heads, kv_heads, head_dim, pa
 
 
 def test_decode_splits_are_used(ops):
-    assert ops.decode_splits(1, 32, 8, 4096, None) > 1
-    assert ops.decode_splits(64, 32, 8, 4096, None) == 1
-    assert ops.decode_splits(1, 32, 8, 4096, 10) == 1
+    assert ops.decode_splits(1, 32, 8, 64, 4096, None) > 1
+    assert ops.decode_splits(64, 32, 8, 64, 4096, None) == 1
+    assert ops.decode_splits(1, 32, 8, 64, 4096, 10) == 1
 
 
 def test_argmax_and_sampling(ops, plain):
     torch.manual_seed(7)
-    vocab, rows = 1000, 6
+    vocab, rows = 5000, 6
     logits = torch.randn(rows, vocab) * 3
     logits[2, 17] = logits[2, 900] = logits[2].max() + 1     # a tie: the lower index wins
     assert ops.argmax(logits.to(DEVICE)).cpu().tolist() == torch.argmax(logits, -1).tolist()
