@@ -8,11 +8,11 @@
 //
 //   prefill: one block = 64 query rows of one (request, query head); 4 warps x 16 rows; all
 //            warps walk the same key tiles (two buffers per block).
-//   decode:  one block = one (request, key head, split of the keys); the rows are the query
-//            heads that share the key head (up to 16 a group); the 4 warps take different
-//            key tiles, each with two buffers of its own, and are merged in shared memory.
-//            With more than one split the block writes (unnormalised output, max, sum) per
-//            row to scratch memory and a second kernel merges the splits.
+//   decode:  one block = one (request, key head, split of the keys) and up to 8 of the query
+//            heads that share the key head; its 8 warps take different tiles of 32 keys, each
+//            through a buffer of its own, and are merged in shared memory. With more than one
+//            split the block writes (unnormalised output, max, sum) per head to scratch
+//            memory and a second kernel merges the splits.
 //
 // Head sizes: multiples of 16 up to 128. Anything else runs the general kernel.
 #include <cuda_pipeline_primitives.h>
@@ -93,6 +93,7 @@ template <int HD, int KEYS>
 __device__ __forceinline__ void load_tile(bf16* k_tile, bf16* v_tile, const Pages& pages, int first,
                                           int lowest, int last, int lane, int lanes) {
     using T = Tile<HD>;
+#pragma unroll 4
     for (int piece = lane; piece < KEYS * T::CHUNKS; piece += lanes) {
         const int row = piece / T::CHUNKS, chunk = piece % T::CHUNKS;
         const int key = first + row;
@@ -320,9 +321,23 @@ attention_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kv
 
 // ------------------------------------------------------------------ decode (split keys)
 
+__device__ __forceinline__ uint32_t transpose_8x8(uint32_t v) {
+    uint32_t out;
+    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;\n" : "=r"(out) : "r"(v));
+    return out;
+}
+
+constexpr int DECODE_WARPS = 8;
+constexpr int DECODE_HEADS = 8;      // query heads per block (the 8-column operand)
+
+// One block = one (request, key head, group of up to 8 query heads, split of the keys).
+// Keys are the 16-row operand of the first product (scores^T = K q^T), so no tensor-core row
+// is wasted on padding; the probabilities are transposed in registers (movmatrix) and become
+// the 8-column operand of the second product (out^T = V^T p^T). Each of the 8 warps takes
+// tiles of 32 keys in turn through a buffer of its own; the warps are merged in shared memory.
 // partial results: [token, head, split] -> HD floats of unnormalised output, then max and sum
-template <int HD, int BUFFERS>
-__global__ void __launch_bounds__(WARPS * 32)
+template <int HD>
+__global__ void __launch_bounds__(DECODE_WARPS * 32)
 attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kv, long long kv_half,
                         const int* __restrict__ block_table, int table_width, int page_size,
                         const int* __restrict__ positions, bf16* __restrict__ out,
@@ -330,19 +345,19 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kv,
                         float scale_log2, int window) {
     using T = Tile<HD>;
     constexpr int KEYS = DECODE_KEYS;
+    constexpr int ROW_FLOATS = HD + 2;
     extern __shared__ __align__(16) unsigned char shared_bytes[];
-    bf16* q_tile = reinterpret_cast<bf16*>(shared_bytes);               // 16 rows
-    bf16* tiles = q_tile + 16 * T::STRIDE;                               // per warp: 2 x (K, V)
     griddep_launch();
     griddep_wait();
     const int group = heads / kv_heads;
-    const int groups_of_16 = (group + 15) / 16;
-    const int kv_head = blockIdx.x / groups_of_16;
-    const int head0 = kv_head * group + (blockIdx.x % groups_of_16) * 16;
-    const int rows = min(16, kv_head * group + group - head0);
+    const int groups_of_8 = (group + DECODE_HEADS - 1) / DECODE_HEADS;
+    const int kv_head = blockIdx.x / groups_of_8;
+    const int head0 = kv_head * group + (blockIdx.x % groups_of_8) * DECODE_HEADS;
+    const int rows = min(DECODE_HEADS, kv_head * group + group - head0);
     const int request = blockIdx.y;            // one token per request: token index = request
     const int split = blockIdx.z;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
 
     const int position = positions[request];
     const int lowest = window > 0 ? max(position - window + 1, 0) : 0;
@@ -353,85 +368,140 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kv,
 
     Pages pages{kv, kv + kv_half, block_table + (size_t)request * table_width, table_width,
                 page_size, kv_heads, kv_head};
+    bf16* k_tile = reinterpret_cast<bf16*>(shared_bytes) + (size_t)warp * 2 * KEYS * T::STRIDE;
+    bf16* v_tile = k_tile + KEYS * T::STRIDE;
 
-    for (int piece = threadIdx.x; piece < 16 * T::CHUNKS; piece += WARPS * 32) {
-        const int row = piece / T::CHUNKS, chunk = piece % T::CHUNKS;
-        const bool live = row < rows;
-        const bf16* src = q + ((size_t)request * heads + head0 + (live ? row : 0)) * HD + chunk * 8;
-        copy16(q_tile + row * T::STRIDE + chunk * 8, src, live);
-    }
-    copy_commit();
-
-    bf16* my_tiles = tiles + (size_t)warp * 2 * BUFFERS * KEYS * T::STRIDE;
-    auto k_buffer = [&](int b) { return my_tiles + (size_t)b * 2 * KEYS * T::STRIDE; };
-    auto v_buffer = [&](int b) { return my_tiles + (size_t)(b * 2 + 1) * KEYS * T::STRIDE; };
-
-    int limit_lo[2] = {lowest, lowest}, limit_hi[2];
-#pragma unroll
-    for (int i = 0; i < 2; ++i) limit_hi[i] = (lane >> 2) + i * 8 < rows ? position : -1;
-    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
-    float o[HD / 8][4];
-#pragma unroll
-    for (int n = 0; n < HD / 8; ++n)
-#pragma unroll
-        for (int c = 0; c < 4; ++c) o[n][c] = 0.f;
-
-    // this warp takes tiles my_first + warp, + WARPS, ...
     int tile = my_first + warp;
-    if (tile <= my_last) load_tile<HD, KEYS>(k_buffer(0), v_buffer(0), pages, tile * KEYS, lowest, position,
-                                       lane, 32);
+    if (tile <= my_last)
+        load_tile<HD, KEYS>(k_tile, v_tile, pages, tile * KEYS, lowest, position, lane, 32);
     copy_commit();
-    copy_wait<1>();            // the query rows (the first group) have landed for this thread
-    __syncthreads();           // ... and for every thread
-    for (int b = 0; tile <= my_last; tile += WARPS) {
-        if (BUFFERS == 2 && tile + WARPS <= my_last) {
-            load_tile<HD, KEYS>(k_buffer(b ^ 1), v_buffer(b ^ 1), pages, (tile + WARPS) * KEYS, lowest,
-                          position, lane, 32);
-            copy_commit();
-            copy_wait<1>();
-        } else {
-            copy_wait<0>();
+
+    // q^T as the 8-column operand: head g, dims 16 kk + 2t (+1) and + 8
+    uint32_t qb[HD / 16][2];
+    {
+        const bool live = g < rows;
+        const bf16* row = q + ((size_t)request * heads + head0 + (live ? g : 0)) * HD;
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; ++kk) {
+            qb[kk][0] = live ? *reinterpret_cast<const uint32_t*>(row + kk * 16 + 2 * t) : 0u;
+            qb[kk][1] = live ? *reinterpret_cast<const uint32_t*>(row + kk * 16 + 8 + 2 * t) : 0u;
+        }
+    }
+    const bool head_live[2] = {2 * t < rows, 2 * t + 1 < rows};
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};      // per head 2t, 2t + 1
+    float o[HD / 16][4];
+#pragma unroll
+    for (int d = 0; d < HD / 16; ++d)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) o[d][c] = 0.f;
+    const int matrix = lane >> 3, r = lane & 7;
+
+    for (; tile <= my_last; tile += DECODE_WARPS) {
+        copy_wait<0>();
+        __syncwarp();
+        const int first = tile * KEYS;
+        float s[KEYS / 16][4];
+#pragma unroll
+        for (int mt = 0; mt < KEYS / 16; ++mt) {
+#pragma unroll
+            for (int c = 0; c < 4; ++c) s[mt][c] = 0.f;
+#pragma unroll
+            for (int kk = 0; kk < HD / 16; ++kk) {
+                uint32_t a[4];
+                ldmatrix_x4(a, k_tile + (mt * 16 + r + (matrix & 1) * 8) * T::STRIDE + kk * 16 +
+                                   (matrix >> 1) * 8);
+                mma_16816(s[mt], a, qb[kk][0], qb[kk][1]);
+            }
+        }
+        float tile_max[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+        for (int mt = 0; mt < KEYS / 16; ++mt)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const int key = first + mt * 16 + g + (c >> 1) * 8;
+                const bool seen = key >= lowest && key <= position && head_live[c & 1];
+                s[mt][c] = seen ? s[mt][c] * scale_log2 : -INFINITY;
+                tile_max[c & 1] = fmaxf(tile_max[c & 1], s[mt][c]);
+            }
+        float correction[2];
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            tile_max[i] = fmaxf(tile_max[i], __shfl_xor_sync(0xffffffffu, tile_max[i], 4));
+            tile_max[i] = fmaxf(tile_max[i], __shfl_xor_sync(0xffffffffu, tile_max[i], 8));
+            tile_max[i] = fmaxf(tile_max[i], __shfl_xor_sync(0xffffffffu, tile_max[i], 16));
+            const float new_max = fmaxf(m[i], tile_max[i]);
+            correction[i] = new_max == -INFINITY ? 1.f : exp2f(m[i] - new_max);
+            m[i] = new_max;
+            l[i] *= correction[i];        // l is this thread's share; the lanes are added at the end
+        }
+        uint32_t pt[KEYS / 16][2];        // probabilities, transposed: head g, keys 2t (+1)
+#pragma unroll
+        for (int mt = 0; mt < KEYS / 16; ++mt) {
+            float p[4];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                p[c] = m[c & 1] == -INFINITY ? 0.f : exp2f(s[mt][c] - m[c & 1]);
+                l[c & 1] += p[c];
+            }
+            pt[mt][0] = transpose_8x8(pack_bf16(p[0], p[1]));
+            pt[mt][1] = transpose_8x8(pack_bf16(p[2], p[3]));
+        }
+#pragma unroll
+        for (int d = 0; d < HD / 16; ++d) {
+            o[d][0] *= correction[0]; o[d][1] *= correction[1];
+            o[d][2] *= correction[0]; o[d][3] *= correction[1];
+#pragma unroll
+            for (int mt = 0; mt < KEYS / 16; ++mt) {
+                uint32_t a[4];
+                ldmatrix_x4_trans(a, v_tile + (mt * 16 + r + (matrix >> 1) * 8) * T::STRIDE + d * 16 +
+                                         (matrix & 1) * 8);
+                mma_16816(o[d], a, pt[mt][0], pt[mt][1]);
+            }
         }
         __syncwarp();
-        attend_tile<HD, KEYS>(q_tile, 0, k_buffer(b), v_buffer(b), tile * KEYS, limit_lo, limit_hi,
-                        scale_log2, m, l, o, lane);
-        __syncwarp();
-        if (BUFFERS == 2) {
-            b ^= 1;
-        } else if (tile + WARPS <= my_last) {      // one buffer: fetch the next tile now
-            load_tile<HD, KEYS>(k_buffer(0), v_buffer(0), pages, (tile + WARPS) * KEYS, lowest,
-                          position, lane, 32);
+        if (tile + DECODE_WARPS <= my_last) {
+            load_tile<HD, KEYS>(k_tile, v_tile, pages, (tile + DECODE_WARPS) * KEYS, lowest,
+                                position, lane, 32);
             copy_commit();
         }
     }
     copy_wait<0>();
-    __syncthreads();           // all warps are done with their tiles: reuse them for merging
-
-    // merge the warps: every warp writes (o, m, l) of its 16 rows, warp 0 combines
-    float* merge = reinterpret_cast<float*>(tiles);            // [WARPS][16][HD + 2]
-    constexpr int ROW_FLOATS = HD + 2;
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
-        const int row = (lane >> 2) + i * 8;
-        float* dst = merge + ((size_t)warp * 16 + row) * ROW_FLOATS;
+        l[i] += __shfl_xor_sync(0xffffffffu, l[i], 4);
+        l[i] += __shfl_xor_sync(0xffffffffu, l[i], 8);
+        l[i] += __shfl_xor_sync(0xffffffffu, l[i], 16);
+    }
+    __syncthreads();           // all warps are done with their tiles: reuse them for merging
+
+    // merge the warps: every warp writes (o, m, l) of its heads, then all threads combine
+    float* merge = reinterpret_cast<float*>(shared_bytes);      // [warp][head 0..7][HD + 2]
 #pragma unroll
-        for (int n = 0; n < HD / 8; ++n) {
-            dst[n * 8 + (lane & 3) * 2] = o[n][2 * i];
-            dst[n * 8 + (lane & 3) * 2 + 1] = o[n][2 * i + 1];
-        }
-        if ((lane & 3) == 0) { dst[HD] = m[i]; dst[HD + 1] = l[i]; }
+    for (int d = 0; d < HD / 16; ++d) {
+        float* base = merge + (size_t)warp * DECODE_HEADS * ROW_FLOATS;
+        base[(2 * t) * ROW_FLOATS + d * 16 + g] = o[d][0];
+        base[(2 * t + 1) * ROW_FLOATS + d * 16 + g] = o[d][1];
+        base[(2 * t) * ROW_FLOATS + d * 16 + g + 8] = o[d][2];
+        base[(2 * t + 1) * ROW_FLOATS + d * 16 + g + 8] = o[d][3];
+    }
+    if (g == 0) {
+        float* base = merge + (size_t)warp * DECODE_HEADS * ROW_FLOATS;
+        base[(2 * t) * ROW_FLOATS + HD] = m[0];
+        base[(2 * t) * ROW_FLOATS + HD + 1] = l[0];
+        base[(2 * t + 1) * ROW_FLOATS + HD] = m[1];
+        base[(2 * t + 1) * ROW_FLOATS + HD + 1] = l[1];
     }
     __syncthreads();
-    for (int item = threadIdx.x; item < rows * HD; item += WARPS * 32) {
+    for (int item = threadIdx.x; item < rows * HD; item += DECODE_WARPS * 32) {
         const int row = item / HD, d = item % HD;
         float top = -INFINITY;
 #pragma unroll
-        for (int w = 0; w < WARPS; ++w)
-            top = fmaxf(top, merge[((size_t)w * 16 + row) * ROW_FLOATS + HD]);
+        for (int w = 0; w < DECODE_WARPS; ++w)
+            top = fmaxf(top, merge[((size_t)w * DECODE_HEADS + row) * ROW_FLOATS + HD]);
         float value = 0.f, sum = 0.f;
 #pragma unroll
-        for (int w = 0; w < WARPS; ++w) {
-            const float* src = merge + ((size_t)w * 16 + row) * ROW_FLOATS;
+        for (int w = 0; w < DECODE_WARPS; ++w) {
+            const float* src = merge + ((size_t)w * DECODE_HEADS + row) * ROW_FLOATS;
             const float weight = src[HD] == -INFINITY ? 0.f : exp2f(src[HD] - top);
             value += src[d] * weight;
             sum += src[HD + 1] * weight;
@@ -506,16 +576,15 @@ int launch_decode(const void* q, const void* kv, long long kv_half, const int* b
                   int requests, int heads, int kv_heads, int splits, float scale, int window,
                   cudaStream_t stream) {
     using T = Tile<HD>;
-    constexpr int BUFFERS = 2;
-    const size_t tiles = (size_t)WARPS * 2 * BUFFERS * DECODE_KEYS * T::STRIDE * 2;
-    const size_t merge = (size_t)WARPS * 16 * (HD + 2) * 4;
-    const size_t shared = (size_t)16 * T::STRIDE * 2 + (tiles > merge ? tiles : merge);
-    auto kernel = attention_decode_kernel<HD, BUFFERS>;
+    const size_t tiles = (size_t)DECODE_WARPS * 2 * DECODE_KEYS * T::STRIDE * 2;
+    const size_t merge = (size_t)DECODE_WARPS * DECODE_HEADS * (HD + 2) * 4;
+    const size_t shared = tiles > merge ? tiles : merge;
+    auto kernel = attention_decode_kernel<HD>;
     if (shared > 48 * 1024)
         cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
     const int group = heads / kv_heads;
-    const dim3 grid(kv_heads * ((group + 15) / 16), requests, splits);
-    launch_kernel(kernel, grid, dim3(WARPS * 32), shared, stream, true, (const bf16*)q,
+    const dim3 grid(kv_heads * ((group + DECODE_HEADS - 1) / DECODE_HEADS), requests, splits);
+    launch_kernel(kernel, grid, dim3(DECODE_WARPS * 32), shared, stream, true, (const bf16*)q,
                   (const bf16*)kv, kv_half, block_table, table_width, page_size, positions,
                   (bf16*)out, partial, heads, kv_heads, splits, scale * LOG2E, window);
     if (splits > 1) {

@@ -303,9 +303,9 @@ class CudaOps:
         if window:
             context_bound = min(context_bound, window + 31)
         tiles = max(-(-context_bound // 32), 1)
-        block_bytes = (16 + 4 * 2 * 2 * 32) * (head_dim + 8) * 2
+        block_bytes = 8 * 2 * 32 * (head_dim + 8) * 2          # 8 warps, a K and a V tile each
         blocks_per_sm = max(1, min(8, 220 * 1024 // block_bytes))
-        groups = kv_heads * (-(-(heads // kv_heads) // 16))
+        groups = kv_heads * (-(-(heads // kv_heads) // 8))
         wanted = max(148 * blocks_per_sm // max(requests * groups, 1), 1)
         return max(min(wanted, tiles // 4), 1)
 
