@@ -14,7 +14,8 @@ Decisions:
   together at most ``max_prefill_tokens``, everything together at most
   ``max_scheduled_tokens``. The reference's BatchScheduler chooses under the same three
   limits (src/mlx_one/engine/batching.py:81-117) but runs decodes and prompts as separate
-  forwards; here they are one batch. If decodes alone exceed the budget they take turns.
+  forwards; here they are one batch. If decodes alone exceed the budget they take turns, and
+  room for a portion of the oldest prompt is always kept, so prompts cannot starve.
 """
 
 from __future__ import annotations
@@ -96,6 +97,7 @@ class Scheduler:
         self.waiting: deque[Request] = deque()
         self.running: list[Request] = []
         self._decode_turn = 0
+        self._single_turn = 0
         self._ids = itertools.count()
 
     # ------------------------------------------------------------------ requests
@@ -153,10 +155,24 @@ class Scheduler:
         budget = config.max_scheduled_tokens
         step: list[Scheduled] = []
         decodes = [r for r in self.running if r.phase is Phase.DECODE]
-        if len(decodes) > budget:
+        prefills = [r for r in self.running if r.phase is Phase.PREFILL]
+        if decodes and prefills:
+            # decodes must not starve prompts: room is kept for a portion of the oldest one,
+            # as the reference keeps room for the smallest waiting prefill
+            # (src/mlx_one/engine/batching.py:89-95); with a budget of one they alternate
+            oldest = prefills[0]
+            room = min(len(oldest.prompt) - oldest.fed, config.prefill_chunk_size,
+                       config.max_prefill_tokens, max(budget // 2, 1))
+            if budget == 1:
+                self._single_turn += 1
+                room = self._single_turn % 2
+            budget_for_decodes = max(budget - room, 0)
+        else:
+            budget_for_decodes = budget
+        if len(decodes) > budget_for_decodes:
             start = self._decode_turn % len(decodes)
-            decodes = (decodes[start:] + decodes[:start])[:budget]
-            self._decode_turn += budget
+            decodes = (decodes[start:] + decodes[:start])[:budget_for_decodes]
+            self._decode_turn += budget_for_decodes
         for request in decodes:
             step.append(Scheduled(request, (request.next_token,), True))
         budget -= len(decodes)

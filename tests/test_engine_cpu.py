@@ -1,0 +1,130 @@
+"""The engine's bookkeeping on the CPU: the step function, block tables, slots, scheduler and
+entry point run with the plain kernel restatements (tests/plain_ops.py) in the place of the
+CUDA kernels, and are compared with the plain implementation. What these tests can find are
+faults of batching and caching; the kernels themselves are tested on the GPU."""
+
+import pytest
+import torch
+
+from mlx_one_b200 import BatchingConfig, CacheConfig, Engine, TextGenerationOptions
+from mlx_one_b200.cache import CacheManager
+from mlx_one_b200.engine.loading import load_model
+from mlx_one_b200.engine.runner import Runner, StepEntry
+from plain_lfm2 import PlainModel, counter_uniform, sample_token
+from plain_ops import PlainOps, uniform
+from tiny_models import (CONFIGS, assert_close, cut, make_model_dir, mixed_schedule, prompts,
+                         replay)
+
+
+@pytest.fixture(scope="module")
+def models(tmp_path_factory):
+    root = tmp_path_factory.mktemp("models")
+    out = {}
+    for name in CONFIGS:
+        folder = make_model_dir(name, root, dtype=torch.float32)
+        out[name] = (folder, load_model(folder, "float32", "cpu", ops=PlainOps()),
+                     PlainModel(folder))
+    return out
+
+
+def runner_for(loaded, page, capacity, max_requests=8):
+    cache = CacheManager(loaded.model.cache_needs, page_size=page, capacity_tokens=capacity,
+                         max_requests=max_requests, dtype=torch.float32, device="cpu")
+    return Runner(loaded.model, cache), cache
+
+
+@pytest.mark.parametrize("name", list(CONFIGS))
+def test_whole_decode_and_portions(models, name):
+    folder, loaded, plain = models[name]
+    config, _, page = CONFIGS[name]
+    runner, cache = runner_for(loaded, page, 256)
+    (tokens,) = prompts(config["vocab_size"], (70,), seed=2)
+    want = plain.logits(tokens)
+    whole = replay(runner, cache, [([("w", tokens)], ["w"])])["w"]
+    assert_close(whole, want, torch.float32, "whole")
+    steps = [([("d", tokens[:38])], [])] + [([("d", [t])], []) for t in tokens[38:]]
+    assert_close(replay(runner, cache, steps)["d"], want, torch.float32, "decode")
+    cache.close("d")
+    for sizes in ((7, 2, 13, 3, 2, 5), (2,)):
+        steps = [([("p", part)], []) for part in cut(tokens, sizes)]
+        steps[-1] = (steps[-1][0], ["p"])
+        assert_close(replay(runner, cache, steps)["p"], want, torch.float32, f"portions {sizes}")
+
+
+@pytest.mark.parametrize("name", list(CONFIGS))
+def test_mixed_batches_reuse_pages(models, name):
+    folder, loaded, plain = models[name]
+    config, _, page = CONFIGS[name]
+    requests = dict(enumerate(prompts(config["vocab_size"], (40, 64, 23, 50, 17, 61), seed=5)))
+    runner, cache = runner_for(loaded, page, 4 * 64, max_requests=4)
+    got = replay(runner, cache, mixed_schedule(requests))
+    stats = cache.stats()
+    assert stats.pages_low_water[0] < stats.pages_total[0] // 2          # pages were reused
+    for request_id, tokens in requests.items():
+        assert_close(got[request_id], plain.logits(tokens), torch.float32, f"request {request_id}")
+    assert not cache.requests()
+
+
+def test_step_refuses_bad_batches_before_touching_state(models):
+    folder, loaded, plain = models["A"]
+    runner, cache = runner_for(loaded, 4, 32)
+    cache.open("a")
+    cache.open("b")
+    for bad in ([StepEntry("a", [1]), StepEntry("a", [2])], [StepEntry("a", [])],
+                [StepEntry("a", [512])], [StepEntry("a", [1, 2], [2])],
+                [StepEntry("unknown", [1])]):
+        with pytest.raises((ValueError, RuntimeError)):
+            runner.step(bad)
+    from mlx_one_b200.cache import CacheCapacityError
+    runner.step([StepEntry("a", list(range(20)))])
+    with pytest.raises(CacheCapacityError):
+        runner.step([StepEntry("b", list(range(20)))])          # 12 tokens of room are left
+    assert cache.get("b").length == 0 and cache.get("a").length == 20
+    cache.check()
+
+
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_entry_point_greedy_and_seeded_sampling(models, name):
+    folder, loaded, plain = models[name]
+    config, _, page = CONFIGS[name]
+    engine = Engine(loaded, cache_config=CacheConfig(block_size_tokens=page, capacity_tokens=512),
+                    batching_config=BatchingConfig(max_sequences=3, prefill_chunk_size=16,
+                                                   max_scheduled_tokens=24))
+    requests = prompts(config["vocab_size"], (1, 9, 33, 64), seed=8)
+    results = engine.generate_batch_ids(requests, TextGenerationOptions(max_tokens=6))
+    for prompt, result in zip(requests, results):
+        assert list(result.token_ids) == plain.greedy(prompt, 6)
+        assert result.finish_reason == "length" and result.prompt_tokens == len(prompt)
+    # sampled tokens follow the documented draw and do not depend on the batch
+    options = TextGenerationOptions(max_tokens=5, temperature=0.8, top_k=40, top_p=0.95, seed=3)
+    alone = engine.generate_ids(requests[1], options).token_ids
+    together = engine.generate_batch_ids(requests[:3], options)[1].token_ids
+    assert alone == together
+    ids = list(requests[1])
+    for step, token in enumerate(alone):
+        assert uniform(3, step) == counter_uniform(3, step)
+        logits = plain.logits(ids)[-1]
+        kept_draw = PlainOps().sample(logits[None], torch.tensor([0.8]), torch.tensor([40]),
+                                      torch.tensor([0.95]), torch.tensor([3]),
+                                      torch.tensor([step]))[0]
+        assert int(kept_draw[0]) == token
+        ids.append(token)
+    streamed = [c.token_id for c in engine.stream_ids(requests[2], max_tokens=4)]
+    assert streamed[:-1] == plain.greedy(requests[2], 4) and streamed[-1] is None
+    stats = engine.runtime_stats()
+    assert stats["running"] == 0 and stats["pages_free"] == stats["pages_total"]
+    engine.close()
+
+
+def test_end_token_stops_generation(models):
+    folder, loaded, plain = models["A"]
+    prompt = prompts(512, (12,), seed=1)[0]
+    expected = plain.greedy(prompt, 3)
+    import dataclasses
+    spec = dataclasses.replace(loaded.spec, eos_token_ids=(expected[2],))
+    patched = dataclasses.replace(loaded, spec=spec)
+    engine = Engine(patched, cache_config=CacheConfig(block_size_tokens=4, capacity_tokens=128))
+    result = engine.generate_ids(prompt, max_tokens=10)
+    assert result.finish_reason == "stop" and list(result.token_ids) == expected[:expected.index(expected[2])]
+    keep_going = engine.generate_ids(prompt, max_tokens=4, ignore_eos=True)
+    assert keep_going.finish_reason == "length" and len(keep_going.token_ids) == 4

@@ -5,7 +5,8 @@ import pytest
 import torch
 
 from plain_lfm2 import PlainModel
-from tiny_models import CONFIGS, assert_close, cut, make_model_dir, prompts, replay
+from tiny_models import (CONFIGS, assert_close, cut, make_model_dir, mixed_schedule, prompts,
+                         replay)
 
 pytestmark = pytest.mark.gpu
 DTYPES = [torch.float32, torch.bfloat16]
@@ -77,30 +78,7 @@ def test_mixed_batches_with_page_reuse(folders, plain, name, dtype):
     requests = dict(enumerate(prompts(config["vocab_size"], lengths, seed=5)))
     capacity = 4 * 64
     runner, cache = engine(folders[name], dtype, page, capacity, max_requests=4)
-    waiting = list(requests)
-    live: dict[int, int] = {}          # id -> tokens fed
-    steps, turn = [], 0
-    while waiting or live:
-        while waiting and len(live) < 4:
-            live[waiting.pop(0)] = 0
-        entries, end = [], []
-        for slot, request_id in enumerate(list(live)):
-            tokens, fed = requests[request_id], live[request_id]
-            prompt_part = len(tokens) - 8          # the last 8 tokens come one at a time
-            if fed < prompt_part:
-                size = min((5, 2, 11, 3)[(turn + slot) % 4], prompt_part - fed)
-            else:
-                size = 1
-            if (turn + slot) % 5 == 4 and fed > 0:
-                continue                            # left out of this step, goes on later
-            entries.append((request_id, tokens[fed:fed + size]))
-            live[request_id] = fed + size
-            if live[request_id] == len(tokens):
-                end.append(request_id)
-                del live[request_id]
-        if entries:
-            steps.append((entries, end))
-        turn += 1
+    steps = mixed_schedule(requests)
     got = replay(runner, cache, steps)
     assert cache.stats().pages_low_water[0] < cache.stats().pages_total[0] // 2
     for request_id, tokens in requests.items():

@@ -105,3 +105,34 @@ def cut(tokens, sizes):
         at += size
         i += 1
     return out
+
+
+def mixed_schedule(requests, live_limit=4, decode_tail=8):
+    """Steps for a dict id -> tokens: up to ``live_limit`` live requests, prompt portions of
+    changing size (down to two tokens) beside single decoded tokens of others, requests
+    sometimes left out of a step, and every request ended as soon as its tokens are fed."""
+    waiting = list(requests)
+    live: dict = {}
+    steps, turn = [], 0
+    while waiting or live:
+        while waiting and len(live) < live_limit:
+            live[waiting.pop(0)] = 0
+        entries, end = [], []
+        for slot, request_id in enumerate(list(live)):
+            tokens, fed = requests[request_id], live[request_id]
+            prompt_part = max(len(tokens) - decode_tail, 1)
+            if fed < prompt_part:
+                size = min((5, 2, 11, 3)[(turn + slot) % 4], prompt_part - fed)
+            else:
+                size = 1
+            if (turn + slot) % 5 == 4 and fed > 0:
+                continue                            # left out of this step, goes on later
+            entries.append((request_id, tokens[fed:fed + size]))
+            live[request_id] = fed + size
+            if live[request_id] == len(tokens):
+                end.append(request_id)
+                del live[request_id]
+        if entries:
+            steps.append((entries, end))
+        turn += 1
+    return steps
