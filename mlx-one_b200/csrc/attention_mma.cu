@@ -668,3 +668,53 @@ MLXONE_API int mlxone_attention_decode(const void* q, const void* kv, const int*
     MLXONE_LAUNCH_CHECK("attention_decode");
     return 0;
 }
+
+// ------------------------------------------------------------------ no-allocation variant
+#include "attention_decode_static.h"
+
+// The partial results of the key splits for callers that cannot allocate (see the header).
+// In host code this name is only a handle of the symbol, not a device address: the address
+// that kernels may use comes from cudaGetSymbolAddress, per device.
+static __device__ __align__(256) float g_static_scratch[MLXONE_STATIC_SCRATCH_FLOATS];
+
+namespace {
+constexpr int MAX_DEVICES = 64;
+float* g_static_scratch_address[MAX_DEVICES] = {};
+}  // namespace
+
+MLXONE_API long long mlxone_attention_decode_static_capacity() {
+    return MLXONE_STATIC_SCRATCH_FLOATS;
+}
+
+MLXONE_API int mlxone_attention_decode_static(const void* q, const void* kv, const int* block_table,
+                                              int table_width, int page_size, int pages,
+                                              const int* positions, void* out, int requests,
+                                              int heads, int kv_heads, int head_dim, int splits,
+                                              float scale, int window, cudaStream_t stream) {
+    if (requests == 0) return 0;
+    MLXONE_REQUIRE(requests > 0 && heads > 0 && kv_heads > 0 && heads % kv_heads == 0,
+                   "attention_decode_static: bad sizes");
+    MLXONE_REQUIRE(splits >= 1 && splits <= 65535 && requests <= 65535,
+                   "attention_decode_static: at most 65535 requests and splits");
+    const long long needed = mlxone_attention_decode_scratch(requests, heads, head_dim, splits);
+    MLXONE_REQUIRE(needed <= MLXONE_STATIC_SCRATCH_FLOATS,
+                   "attention_decode_static: %d requests x %d heads x %d splits need %lld floats of "
+                   "scratch, the fixed array holds %d; use fewer splits or requests per call",
+                   requests, heads, splits, needed, MLXONE_STATIC_SCRATCH_FLOATS);
+    int device = -1;
+    cudaError_t err = cudaGetDevice(&device);
+    MLXONE_REQUIRE(err == cudaSuccess && device >= 0 && device < MAX_DEVICES,
+                   "attention_decode_static: no current device (%s)", cudaGetErrorString(err));
+    if (g_static_scratch_address[device] == nullptr) {
+        // once per device, with that device current; not inside a stream capture
+        float* address = nullptr;
+        err = cudaGetSymbolAddress(reinterpret_cast<void**>(&address), g_static_scratch);
+        MLXONE_REQUIRE(err == cudaSuccess && address != nullptr,
+                       "attention_decode_static: cannot find the scratch array on device %d: %s",
+                       device, cudaGetErrorString(err));
+        g_static_scratch_address[device] = address;
+    }
+    return mlxone_attention_decode(q, kv, block_table, table_width, page_size, pages, positions,
+                                   out, g_static_scratch_address[device], requests, heads, kv_heads,
+                                   head_dim, splits, scale, window, stream);
+}
