@@ -57,6 +57,8 @@ class CudaOps:
         self.launches = 0
         self.tensor_core_attention = True
         self.skinny_products = True
+        # tcgen05 products (TMA + tensor memory) for more rows than the skinny kernel takes
+        self.tcgen05_products = bool(self.lib.mlxone_gemm_tcgen05_available())
         self._skinny_rows = self.lib.mlxone_gemm_skinny_max_rows()
         self._sample_scratch: torch.Tensor | None = None
 
@@ -86,7 +88,8 @@ class CudaOps:
             self.error_flag.zero_()
             what = {1: "a token id outside the vocabulary",
                     2: "a key written to a position that has no page",
-                    3: "a key read from a position that has no page"}.get(code, f"code {code}")
+                    3: "a key read from a position that has no page",
+                    9: "a wait inside the tcgen05 product that gave up"}.get(code, f"code {code}")
             raise KernelError(f"a kernel reported {what}")
 
     # ------------------------------------------------------------------ size checks
@@ -149,6 +152,23 @@ class CudaOps:
                 and 0 < a.shape[0] <= self._skinny_rows and a.shape[1] % 8 == 0
                 and a.stride(0) % 8 == 0 and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
+    def enable_tcgen05(self, enabled: bool = True) -> bool:
+        """Routes bfloat16 products with more rows than the skinny kernel takes to the
+        tcgen05 kernel (TMA loads, accumulator in tensor memory) instead of the library."""
+        self.tcgen05_products = bool(enabled) and bool(self.lib.mlxone_gemm_tcgen05_available())
+        return self.tcgen05_products
+
+    def _tcgen05(self, a, w) -> bool:
+        return (self.tcgen05_products and a.dtype == torch.bfloat16 and a.shape[0] > 0
+                and a.shape[1] % 8 == 0 and a.stride(0) % 8 == 0 and a.stride(1) == 1
+                and w.is_contiguous() and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+    def _tcgen05_call(self, a, w, bias, out, ldo, epilogue) -> None:
+        self._call("mlxone_gemm_tcgen05", _c_void_p(_ptr(a)), _c_int(a.stride(0)),
+                   _c_void_p(_ptr(w)), _c_void_p(_ptr(bias)), _c_void_p(_ptr(out)), _c_int(ldo),
+                   _c_int(a.shape[0]), _c_int(w.shape[0]), _c_int(a.shape[1]), _c_int(epilogue),
+                   _c_void_p(_ptr(self.error_flag)))
+
     def _skinny_call(self, a, w, bias, out, ldo, epilogue) -> None:
         self._call("mlxone_gemm_skinny", _c_void_p(_ptr(a)), _c_int(a.stride(0)),
                    _c_void_p(_ptr(w)), _c_void_p(_ptr(bias)), _c_void_p(_ptr(out)), _c_int(ldo),
@@ -179,6 +199,11 @@ class CudaOps:
             self._skinny_call(a, w, bias, out, n,
                               self._STORE_F32 if out_dtype == torch.float32 else self._STORE)
             return out
+        if self._tcgen05(a, w):
+            out = torch.empty((m, n), dtype=out_dtype, device=self.device)
+            self._tcgen05_call(a, w, bias, out, n,
+                               self._STORE_F32 if out_dtype == torch.float32 else self._STORE)
+            return out
         if out_dtype == torch.float32:
             out = torch.mm(a, w.t(), out_dtype=torch.float32)
         else:
@@ -197,6 +222,11 @@ class CudaOps:
             out = torch.empty((a.shape[0], width), dtype=a.dtype, device=self.device)
             self._skinny_call(a, gate_up, None, out, width, self._SWIGLU)
             return out
+        if self._tcgen05(a, gate_up):
+            width = gate_up.shape[0] // 2
+            out = torch.empty((a.shape[0], width), dtype=a.dtype, device=self.device)
+            self._tcgen05_call(a, gate_up, None, out, width, self._SWIGLU)
+            return out
         return self.swiglu(self.linear(a, gate_up))
 
     def linear_add(self, a, w, bias, residual):
@@ -207,6 +237,10 @@ class CudaOps:
         if self._skinny(a, w):
             self._need(residual, torch.float32, "residual")
             self._skinny_call(a, w, bias, residual, residual.shape[1], self._ADD)
+            return None
+        if self._tcgen05(a, w):
+            self._need(residual, torch.float32, "residual")
+            self._tcgen05_call(a, w, bias, residual, residual.shape[1], self._ADD)
             return None
         return self.linear(a, w, bias)
 

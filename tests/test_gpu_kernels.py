@@ -111,6 +111,7 @@ def test_matrix_product_float32(ops, plain, m, n, k):
 
 @pytest.mark.parametrize("m,n,k", [(1, 64, 64), (8, 333, 136), (130, 1000, 96)])
 def test_matrix_product_bfloat16(ops, plain, m, n, k):
+    """Whatever kernel the sizes select (skinny, tcgen05 or the library) gives the product."""
     torch.manual_seed(3)
     a, w = torch.randn(m, k).bfloat16(), torch.randn(n, k).bfloat16()
     bias = torch.randn(n)
@@ -150,6 +151,36 @@ def test_skinny_product(ops, m, n, k):
     # a token's result does not depend on the other tokens of the call
     alone = ops.linear(a[:1].contiguous().to(DEVICE), w.to(DEVICE), out_dtype=torch.float32)
     assert torch.equal(alone[0].cpu(), logits[0].cpu())
+
+
+@pytest.mark.parametrize("m", [33, 128, 200, 777])
+@pytest.mark.parametrize("n,k", [(128, 64), (334, 136), (1000, 2048), (2048, 520), (50, 8)])
+def test_tcgen05_product(ops, m, n, k):
+    """The tensor-memory product for many rows: all four epilogues, ragged edges in M, N, K."""
+    assert ops.enable_tcgen05(True)
+    try:
+        torch.manual_seed(m + n + k)
+        a = torch.randn(m, k).bfloat16()
+        w = (torch.randn(n, k) / math.sqrt(k)).bfloat16()
+        bias = torch.randn(n)
+        want = a.double() @ w.double().T
+        assert ops._tcgen05(a.to(DEVICE), w.to(DEVICE)) and not ops._skinny(a.to(DEVICE), w.to(DEVICE))
+        got = ops.linear(a.to(DEVICE), w.to(DEVICE), bias.to(DEVICE))
+        torch.testing.assert_close(got.cpu().double(), want + bias.double(), atol=2e-2, rtol=2e-2)
+        logits = ops.linear(a.to(DEVICE), w.to(DEVICE), out_dtype=torch.float32)
+        torch.testing.assert_close(logits.cpu().double(), want, atol=1e-3, rtol=1e-3)
+        residual = torch.randn(m, n)
+        on_gpu = residual.clone().to(DEVICE)
+        assert ops.linear_add(a.to(DEVICE), w.to(DEVICE), bias.to(DEVICE), on_gpu) is None
+        torch.testing.assert_close(on_gpu.cpu().double(), residual.double() + want + bias.double(),
+                                   atol=1e-3, rtol=1e-3)
+        gated = ops.linear_swiglu(a.to(DEVICE), w.to(DEVICE))
+        gate, up = want[:, :n // 2], want[:, n // 2:]
+        torch.testing.assert_close(gated.cpu().double(), gate * torch.sigmoid(gate) * up,
+                                   atol=2e-2, rtol=2e-2)
+        ops.check_errors()
+    finally:
+        ops.enable_tcgen05(True)
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
