@@ -146,7 +146,7 @@ def build_engine(config, layers, batch, context, steps_ahead):
     model = build_model(spec, tensors, "bfloat16", "cuda:0")
     del tensors
     loaded = LoadedModel(Path("random-lfm2-1.2b"), architecture, typed, spec, model)
-    capacity = batch * (-(-(context + steps_ahead + 64) // 64) * 64) + PREFILL_TOKENS + 64
+    capacity = batch * (-(-(context + steps_ahead + 128) // 64) * 64) + PREFILL_TOKENS + 64
     engine = Engine(loaded,
                     cache_config=CacheConfig(block_size_tokens=PAGE_SIZE, capacity_tokens=capacity,
                                              max_requests=batch + 1),
@@ -277,25 +277,32 @@ def time_e2e(engine, batch, context, warmup, steps, seed):
     from mlx_one_b200 import TextGenerationOptions
 
     vocab = engine.model.spec.vocab_size
-    prompt_length = context - warmup - steps - 1
+    # prompts finish one after the other, so the first request has decoded some tokens when
+    # the last one starts; `slack` keeps every request decoding through the timed steps
+    slack = 2 * batch + 8
+    prompt_length = context - warmup - steps - slack
     prompts = random_prompts(vocab, batch, prompt_length, seed + 1)
-    options = TextGenerationOptions(max_tokens=warmup + steps + 1, ignore_eos=True)
+    options = TextGenerationOptions(max_tokens=warmup + steps + slack, ignore_eos=True)
     handles = [engine.submit_ids(p, options) for p in prompts]
     from mlx_one_b200.engine.scheduler import Phase
     while any(h.request.phase is not Phase.DECODE for h in handles):
         engine.step()
-    for _ in range(warmup - 1):
+    for _ in range(warmup):
         engine.step()
     torch.cuda.synchronize()
+    produced = sum(len(h.request.output) for h in handles)
     began = time.perf_counter()
     for _ in range(steps):
         engine.step()
     torch.cuda.synchronize()
     seconds = time.perf_counter() - began
+    produced = sum(len(h.request.output) for h in handles) - produced
+    meta_bytes = engine._runner.last_meta_bytes
+    assert produced == batch * steps, (produced, batch, steps)
     for handle in handles:
         handle.cancel()
     engine.step()
-    return seconds, engine._runner.last_meta_bytes
+    return seconds, meta_bytes
 
 
 def time_prefill(engine, tokens, warmup, repeats, seed):

@@ -69,11 +69,15 @@ __device__ __forceinline__ void mma_16816(float (&d)[4], uint32_t a0, uint32_t a
 // NT: groups of 8 tokens (M <= 8 * NT). RESIDENT: activations live in shared memory.
 // A SwiGLU block splits its warps in two halves: the first on the gate rows, the second on
 // the matching up rows.
-template <int NT, int EPILOGUE, bool RESIDENT>
+// NORM (needs RESIDENT): the activations are RMSNorm(source) * norm_weight, computed here from the
+// 32-bit rows of `source` while they are brought into shared memory, so the norm needs no
+// kernel and no pass over memory of its own.
+template <int NT, int EPILOGUE, bool RESIDENT, bool NORM>
 __global__ void __launch_bounds__(WARPS * 32)
 skinny_gemm_kernel(const bf16* a, int lda, const bf16* __restrict__ w,
                    const float* __restrict__ bias, void* out, int ldo, int m, int n, int k,
-                   int up_offset, int tiles) {
+                   int up_offset, int tiles, const float* source, int source_ld,
+                   const float* __restrict__ norm_weight, float eps) {
     constexpr int HALVES = EPILOGUE == SWIGLU ? 2 : 1;
     constexpr int WARPS_K = WARPS / HALVES;
     constexpr int TOKENS = 8 * NT;
@@ -124,7 +128,86 @@ skinny_gemm_kernel(const bf16* a, int lda, const bf16* __restrict__ w,
 
     // resident activations: [token][K] with 16-byte pieces swizzled by the token's parity
     const int resident_stride = ((k + 63) / 64) * 64 * 2;        // bytes per token
-    if (RESIDENT) {
+    if (RESIDENT && NORM) {
+        // One warp per token. A lane holds its pieces of the row in registers between the sum
+        // of squares and the scaling, so the row crosses from L2 once; all its loads are in
+        // flight together.
+        constexpr int HELD = 8;                       // pieces of 8 values per lane: K <= 2048
+        const int pieces = resident_stride / 16;
+        for (int token = warp; token < TOKENS; token += WARPS) {
+            unsigned char* row_out = resident + token * resident_stride;
+            const float* row = source + (size_t)token * source_ld;
+            uint4 lo[HELD], hi[HELD];
+            float sum = 0.f;
+            if (token < m) {
+#pragma unroll
+                for (int j = 0; j < HELD; ++j) {
+                    const int c = lane + 32 * j;
+                    if (c * 8 < k) {
+                        lo[j] = load_l2(row + c * 8);
+                        hi[j] = load_l2(row + c * 8 + 4);
+                    } else {
+                        lo[j] = hi[j] = make_uint4(0u, 0u, 0u, 0u);
+                    }
+                }
+#pragma unroll
+                for (int j = 0; j < HELD; ++j) {
+                    const float v[8] = {__uint_as_float(lo[j].x), __uint_as_float(lo[j].y),
+                                        __uint_as_float(lo[j].z), __uint_as_float(lo[j].w),
+                                        __uint_as_float(hi[j].x), __uint_as_float(hi[j].y),
+                                        __uint_as_float(hi[j].z), __uint_as_float(hi[j].w)};
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) sum += v[i] * v[i];
+                }
+                for (int c = lane + 32 * HELD; c * 8 < k; c += 32) {     // longer rows: the rest
+                    const uint4 a0 = load_l2(row + c * 8), a1 = load_l2(row + c * 8 + 4);
+                    const float v[8] = {__uint_as_float(a0.x), __uint_as_float(a0.y),
+                                        __uint_as_float(a0.z), __uint_as_float(a0.w),
+                                        __uint_as_float(a1.x), __uint_as_float(a1.y),
+                                        __uint_as_float(a1.z), __uint_as_float(a1.w)};
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) sum += v[i] * v[i];
+                }
+            }
+            sum = warp_sum(sum);
+            const float inv = rsqrtf(sum / (float)k + eps);
+            auto scaled = [&](const uint4& a0, const uint4& a1, int c) {
+                const float4 w0 = *reinterpret_cast<const float4*>(norm_weight + c * 8);
+                const float4 w1 = *reinterpret_cast<const float4*>(norm_weight + c * 8 + 4);
+                __nv_bfloat162 p0 = __floats2bfloat162_rn(__uint_as_float(a0.x) * inv * w0.x,
+                                                          __uint_as_float(a0.y) * inv * w0.y);
+                __nv_bfloat162 p1 = __floats2bfloat162_rn(__uint_as_float(a0.z) * inv * w0.z,
+                                                          __uint_as_float(a0.w) * inv * w0.w);
+                __nv_bfloat162 p2 = __floats2bfloat162_rn(__uint_as_float(a1.x) * inv * w1.x,
+                                                          __uint_as_float(a1.y) * inv * w1.y);
+                __nv_bfloat162 p3 = __floats2bfloat162_rn(__uint_as_float(a1.z) * inv * w1.z,
+                                                          __uint_as_float(a1.w) * inv * w1.w);
+                uint4 packed;
+                packed.x = *reinterpret_cast<uint32_t*>(&p0);
+                packed.y = *reinterpret_cast<uint32_t*>(&p1);
+                packed.z = *reinterpret_cast<uint32_t*>(&p2);
+                packed.w = *reinterpret_cast<uint32_t*>(&p3);
+                return packed;
+            };
+#pragma unroll
+            for (int j = 0; j < HELD; ++j) {
+                const int c = lane + 32 * j;
+                if (c < pieces) {
+                    const uint4 packed = (token < m && c * 8 < k) ? scaled(lo[j], hi[j], c)
+                                                                  : make_uint4(0u, 0u, 0u, 0u);
+                    *reinterpret_cast<uint4*>(row_out + ((c ^ ((token & 1) << 2)) << 4)) = packed;
+                }
+            }
+            for (int c = lane + 32 * HELD; c < pieces; c += 32) {
+                uint4 packed = make_uint4(0u, 0u, 0u, 0u);
+                if (token < m && c * 8 < k)
+                    packed = scaled(load_l2(row + c * 8), load_l2(row + c * 8 + 4), c);
+                *reinterpret_cast<uint4*>(row_out + ((c ^ ((token & 1) << 2)) << 4)) = packed;
+            }
+        }
+        copy_wait<0>();
+        __syncthreads();
+    } else if (RESIDENT) {
         const int pieces = resident_stride / 16;
         for (int item = threadIdx.x; item < TOKENS * pieces; item += WARPS * 32) {
             const int token = item / pieces, c = item % pieces;
@@ -244,9 +327,17 @@ skinny_gemm_kernel(const bf16* a, int lda, const bf16* __restrict__ w,
 
 int g_sm_count = 0;
 
+struct NormInput {
+    const float* source = nullptr;
+    int ld = 0;
+    const float* weight = nullptr;
+    float eps = 0.f;
+};
+
 template <int NT, int EPILOGUE>
 cudaError_t launch(const void* a, int lda, const void* w, const float* bias, void* out, int ldo,
-                   int m, int n, int k, int up_offset, cudaStream_t stream) {
+                   int m, int n, int k, int up_offset, cudaStream_t stream,
+                   NormInput norm = NormInput()) {
     if (g_sm_count == 0) {
         int device = 0;
         cudaGetDevice(&device);
@@ -259,30 +350,44 @@ cudaError_t launch(const void* a, int lda, const void* w, const float* bias, voi
     const size_t sums = (size_t)WARPS * ROWS * 8 * NT * sizeof(float);
     const size_t resident = (size_t)8 * NT * ((k + 63) / 64) * 64 * 2;
     // activations in shared memory pay off when a block reuses them for several tiles
-    const bool use_resident = NT <= 2 && tiles >= 2 * grid && rings + sums + resident <= 200 * 1024;
+    const bool fits = NT <= 2 && rings + sums + resident <= 200 * 1024;
+    const bool use_resident = fits && (norm.source != nullptr || tiles >= 2 * grid);
     const size_t shared = rings + sums + (use_resident ? resident : 0);
     cudaError_t err;
+    if (norm.source != nullptr) {
+        if (!fits) return cudaErrorInvalidValue;
+        auto kernel = skinny_gemm_kernel<NT, EPILOGUE, (NT <= 2), (NT <= 2)>;
+        err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
+        if (err != cudaSuccess) return err;
+        return launch_kernel(kernel, dim3(grid), dim3(WARPS * 32), shared, stream, true,
+                             (const bf16*)nullptr, 0, (const bf16*)w, bias, out, ldo, m, n, k,
+                             up_offset, tiles, norm.source, norm.ld, norm.weight, norm.eps);
+    }
     if (use_resident) {
-        auto kernel = skinny_gemm_kernel<NT, EPILOGUE, (NT <= 2)>;
+        auto kernel = skinny_gemm_kernel<NT, EPILOGUE, (NT <= 2), false>;
         err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
         if (err != cudaSuccess) return err;
         return launch_kernel(kernel, dim3(grid), dim3(WARPS * 32), shared, stream, true,
                              (const bf16*)a, lda, (const bf16*)w, bias, out, ldo, m, n, k,
-                             up_offset, tiles);
+                             up_offset, tiles, (const float*)nullptr, 0, (const float*)nullptr, 0.f);
     }
-    auto kernel = skinny_gemm_kernel<NT, EPILOGUE, false>;
+    auto kernel = skinny_gemm_kernel<NT, EPILOGUE, false, false>;
     err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
     if (err != cudaSuccess) return err;
     return launch_kernel(kernel, dim3(grid), dim3(WARPS * 32), shared, stream, true, (const bf16*)a,
-                         lda, (const bf16*)w, bias, out, ldo, m, n, k, up_offset, tiles);
+                         lda, (const bf16*)w, bias, out, ldo, m, n, k, up_offset, tiles,
+                         (const float*)nullptr, 0, (const float*)nullptr, 0.f);
 }
 
 template <int EPILOGUE>
 cudaError_t launch_for_rows(const void* a, int lda, const void* w, const float* bias, void* out,
-                            int ldo, int m, int n, int k, int up_offset, cudaStream_t stream) {
-    if (m <= 8) return launch<1, EPILOGUE>(a, lda, w, bias, out, ldo, m, n, k, up_offset, stream);
-    if (m <= 16) return launch<2, EPILOGUE>(a, lda, w, bias, out, ldo, m, n, k, up_offset, stream);
-    return launch<4, EPILOGUE>(a, lda, w, bias, out, ldo, m, n, k, up_offset, stream);
+                            int ldo, int m, int n, int k, int up_offset, cudaStream_t stream,
+                            NormInput norm = NormInput()) {
+    if (m <= 8)
+        return launch<1, EPILOGUE>(a, lda, w, bias, out, ldo, m, n, k, up_offset, stream, norm);
+    if (m <= 16)
+        return launch<2, EPILOGUE>(a, lda, w, bias, out, ldo, m, n, k, up_offset, stream, norm);
+    return launch<4, EPILOGUE>(a, lda, w, bias, out, ldo, m, n, k, up_offset, stream, norm);
 }
 
 }  // namespace
@@ -320,5 +425,51 @@ MLXONE_API int mlxone_gemm_skinny(const void* a, int lda, const void* w, const f
         return 2;
     }
     MLXONE_LAUNCH_CHECK("gemm_skinny");
+    return 0;
+}
+
+// Rows and K up to which mlxone_gemm_skinny_norm applies the norm itself.
+MLXONE_API int mlxone_gemm_skinny_norm_fits(int m, int k) {
+    if (m < 1 || m > 16 || k % 8 != 0) return 0;
+    const size_t rings = (size_t)WARPS * STAGES * SLICE_BYTES;
+    const int nt = m <= 8 ? 1 : 2;
+    const size_t sums = (size_t)WARPS * ROWS * 8 * nt * sizeof(float);
+    const size_t resident = (size_t)8 * nt * ((k + 63) / 64) * 64 * 2;
+    return rings + sums + resident <= 200 * 1024 ? 1 : 0;
+}
+
+// As mlxone_gemm_skinny with a = RMSNorm(source; norm_weight, eps) in bfloat16, the norm applied
+// while the rows are brought in. source: float32 [m, k] with row stride source_ld.
+MLXONE_API int mlxone_gemm_skinny_norm(const float* source, int source_ld,
+                                       const float* norm_weight, float eps, const void* w,
+                                       const float* bias, void* out, int ldo, int m, int n, int k,
+                                       int epilogue, cudaStream_t stream) {
+    if (m == 0 || n == 0) return 0;
+    MLXONE_REQUIRE(mlxone_gemm_skinny_norm_fits(m, k), "gemm_skinny_norm: %d rows of %d do not fit", m, k);
+    MLXONE_REQUIRE(n > 0 && source_ld % 4 == 0 &&
+                       (reinterpret_cast<uintptr_t>(source) & 15) == 0 &&
+                       (reinterpret_cast<uintptr_t>(norm_weight) & 15) == 0 &&
+                       (reinterpret_cast<uintptr_t>(w) & 15) == 0,
+                   "gemm_skinny_norm: operands must be 16-byte aligned");
+    MLXONE_REQUIRE(epilogue >= 0 && epilogue <= 3, "gemm_skinny_norm: unknown epilogue %d", epilogue);
+    MLXONE_REQUIRE(epilogue != SWIGLU || n % 2 == 0, "gemm_skinny_norm: SwiGLU needs an even n");
+    NormInput norm;
+    norm.source = source; norm.ld = source_ld; norm.weight = norm_weight; norm.eps = eps;
+    cudaError_t err;
+    switch (epilogue) {
+        case STORE_BF16:
+            err = launch_for_rows<STORE_BF16>(nullptr, 0, w, bias, out, ldo, m, n, k, 0, stream, norm); break;
+        case SWIGLU:
+            err = launch_for_rows<SWIGLU>(nullptr, 0, w, bias, out, ldo, m, n, k, n / 2, stream, norm); break;
+        case ADD_RESIDUAL:
+            err = launch_for_rows<ADD_RESIDUAL>(nullptr, 0, w, bias, out, ldo, m, n, k, 0, stream, norm); break;
+        default:
+            err = launch_for_rows<STORE_F32>(nullptr, 0, w, bias, out, ldo, m, n, k, 0, stream, norm); break;
+    }
+    if (err != cudaSuccess) {
+        mlxone_set_error("gemm_skinny_norm: launch failed: %s", cudaGetErrorString(err));
+        return 2;
+    }
+    MLXONE_LAUNCH_CHECK("gemm_skinny_norm");
     return 0;
 }

@@ -78,7 +78,65 @@ __global__ void short_conv_state_kernel(const T* __restrict__ bcx, T* __restrict
     for (int s = 0; s < taps - 1; ++s) rows[(size_t)s * hidden + d] = from_float<T>(kept[s]);
 }
 
+// One token per request (decode): output and new state in one pass. A thread owns one channel
+// of one request, so it reads the old state before it writes the new one.
+template <typename T>
+__global__ void short_conv_decode_kernel(const T* __restrict__ bcx, const float* __restrict__ kernel,
+                                         const float* __restrict__ bias, T* __restrict__ state,
+                                         const int* __restrict__ slots,
+                                         const int* __restrict__ history, T* __restrict__ out,
+                                         int hidden, int taps, int write_state) {
+    griddep_launch();
+    griddep_wait();
+    const int d = blockIdx.x * blockDim.x + threadIdx.x;
+    const int r = blockIdx.y;
+    if (d >= hidden) return;
+    const int position = history[r];
+    const T* row = bcx + (size_t)r * 3 * hidden;
+    T* rows = state + (size_t)slots[r] * (taps - 1) * hidden;
+    constexpr int MAX_ROWS = 16;
+    float kept[MAX_ROWS];
+    float y = bias ? bias[d] : 0.f;
+    for (int s = 0; s < taps - 1; ++s) {
+        // state row s holds position - (taps-1) + s; zero before the sequence began
+        const float g = position - (taps - 1) + s >= 0 ? to_float<T>(rows[(size_t)s * hidden + d]) : 0.f;
+        kept[s] = g;
+        y = fmaf(kernel[(size_t)d * taps + s], g, y);
+    }
+    const float g_now = round_to<T>(to_float<T>(row[d]) * to_float<T>(row[2 * hidden + d]));
+    y = fmaf(kernel[(size_t)d * taps + taps - 1], g_now, y);
+    out[(size_t)r * hidden + d] = from_float<T>(to_float<T>(row[hidden + d]) * y);
+    if (write_state) {
+        for (int s = 0; s + 1 < taps - 1; ++s) rows[(size_t)s * hidden + d] = from_float<T>(kept[s + 1]);
+        if (taps > 1) rows[(size_t)(taps - 2) * hidden + d] = from_float<T>(g_now);
+    }
+}
+
 }  // namespace
+
+MLXONE_API int mlxone_short_conv_decode(const void* bcx, const float* kernel, const float* bias,
+                                        void* state, const int* slots, const int* history,
+                                        void* out, int requests, int hidden, int taps,
+                                        int write_state, int dtype, cudaStream_t stream) {
+    if (requests == 0) return 0;
+    MLXONE_REQUIRE(requests > 0 && requests <= 65535 && hidden > 0, "short_conv_decode: bad sizes");
+    MLXONE_REQUIRE(taps >= 1 && taps <= 17, "short_conv: kernel width %d is not in 1..17", taps);
+    const int threads = 128;
+    const dim3 grid(ceil_div_host(hidden, threads), requests);
+    if (dtype == MLXONE_BF16) {
+        using T = __nv_bfloat16;
+        launch_kernel(short_conv_decode_kernel<T>, grid, dim3(threads), 0, stream, true,
+                      (const T*)bcx, kernel, bias, (T*)state, slots, history, (T*)out, hidden, taps,
+                      write_state);
+    } else {
+        using T = float;
+        launch_kernel(short_conv_decode_kernel<T>, grid, dim3(threads), 0, stream, true,
+                      (const T*)bcx, kernel, bias, (T*)state, slots, history, (T*)out, hidden, taps,
+                      write_state);
+    }
+    MLXONE_LAUNCH_CHECK("short_conv_decode");
+    return 0;
+}
 
 MLXONE_API int mlxone_short_conv(const void* bcx, const float* kernel, const float* bias,
                                  void* state, const int* slots, const int* token_request,

@@ -13,6 +13,7 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import Any, Sequence
 
+import numpy as np
 import torch
 
 from ..cache.manager import CacheManager
@@ -130,15 +131,18 @@ class Runner:
             return None
         vocab = self.model.spec.vocab_size
         seen = set()
+        arrays: list[np.ndarray] = []
         for entry in entries:
             if entry.request_id in seen:
                 raise ValueError(f"request {entry.request_id!r} appears twice in one step")
             seen.add(entry.request_id)
             if len(entry.tokens) < 1:
                 raise ValueError(f"request {entry.request_id!r} brings no tokens")
-            for token in entry.tokens:
-                if not 0 <= int(token) < vocab:
-                    raise ValueError(f"token {token} is outside the vocabulary of {vocab}")
+            ids = np.asarray(entry.tokens, dtype=np.int64)
+            if ids.ndim != 1 or ids.min() < 0 or ids.max() >= vocab:
+                raise ValueError(f"request {entry.request_id!r} has a token outside the "
+                                 f"vocabulary of {vocab}")
+            arrays.append(ids)
             for place in entry.want:
                 if not 0 <= int(place) < len(entry.tokens):
                     raise ValueError(f"wanted place {place} is outside the request's tokens")
@@ -187,19 +191,20 @@ class Runner:
             start, size = offsets[name]
             data[start:start + size] = values
 
-        token_ids, positions, token_request, starts, history, rows = [], [], [], [0], [], []
-        for r, (entry, cache) in enumerate(zip(entries, caches)):
-            n = len(entry.tokens)
-            first = len(token_ids)
-            token_ids.extend(int(t) for t in entry.tokens)
-            positions.extend(range(cache.length, cache.length + n))
-            token_request.extend([r] * n)
+        starts, history, rows = [0], [], []
+        ids_at = offsets["token_ids"][0]
+        positions_at = offsets["positions"][0]
+        request_at = offsets["token_request"][0]
+        for r, (entry, cache, ids) in enumerate(zip(entries, caches, arrays)):
+            n = len(ids)
+            first = starts[-1]
+            data[ids_at + first:ids_at + first + n] = ids
+            data[positions_at + first:positions_at + first + n] = np.arange(
+                cache.length, cache.length + n, dtype=np.int32)
+            data[request_at + first:request_at + first + n] = r
             starts.append(first + n)
             history.append(cache.length)
             rows.extend(first + int(place) for place in entry.want)
-        put("token_ids", token_ids)
-        put("positions", positions)
-        put("token_request", token_request)
         put("request_start", starts)
         put("history", history)
         put("rows", rows if rows else [0])
@@ -242,8 +247,7 @@ class Runner:
             max_portion=max(len(e.tokens) for e in entries),
             max_context=max(h + len(e.tokens) for h, e in zip(history, entries)),
             views=views,
-            host={"history": history, "request_start": starts, "positions": positions,
-                  "token_request": token_request})
+            host={"history": history, "request_start": starts})
 
         def run():
             residual, delta = self.model.forward(ctx)

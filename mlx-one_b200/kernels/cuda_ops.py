@@ -17,6 +17,7 @@ from typing import Any
 
 import torch
 
+from ..parts.base import NormedInput
 from .build import KernelBuildError, library_path
 
 _F32, _BF16 = 0, 1
@@ -57,6 +58,11 @@ class CudaOps:
         self.launches = 0
         self.tensor_core_attention = True
         self.skinny_products = True
+        # applying a norm inside the product that consumes it saves a launch but delays the
+        # product's start; with dependent launches the separate norm kernel is hidden behind
+        # the next product's weight prefetch and is faster, so this is off by default
+        self.fused_norms = False
+        self.tcgen05_min_rows = 128
         # tcgen05 products (TMA + tensor memory) for more rows than the skinny kernel takes
         self.tcgen05_products = bool(self.lib.mlxone_gemm_tcgen05_available())
         self._skinny_rows = self.lib.mlxone_gemm_skinny_max_rows()
@@ -159,7 +165,9 @@ class CudaOps:
         return self.tcgen05_products
 
     def _tcgen05(self, a, w) -> bool:
-        return (self.tcgen05_products and a.dtype == torch.bfloat16 and a.shape[0] > 0
+        # its tiles are 128 rows high; with fewer rows the library product does better
+        return (self.tcgen05_products and a.dtype == torch.bfloat16
+                and a.shape[0] >= self.tcgen05_min_rows
                 and a.shape[1] % 8 == 0 and a.stride(0) % 8 == 0 and a.stride(1) == 1
                 and w.is_contiguous() and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
@@ -180,8 +188,32 @@ class CudaOps:
         if a.dim() != 2 or w.dim() != 2 or w.shape[1] != a.shape[1]:
             raise KernelError(f"matrix product of {tuple(a.shape)} with {tuple(w.shape)}^T")
 
+    # ---- norms applied inside the product that consumes them
+
+    def can_fuse_norm(self, residual, dtype) -> bool:
+        """Whether RMSNorm(residual) can be applied by the skinny product while it loads its
+        input (bfloat16, up to 16 rows, the rows fit into shared memory)."""
+        return (self.fused_norms and self.skinny_products and dtype == torch.bfloat16
+                and residual.dtype == torch.float32 and residual.is_contiguous()
+                and bool(self.lib.mlxone_gemm_skinny_norm_fits(residual.shape[0], residual.shape[1])))
+
+    def _normed_call(self, a, w, bias, out, ldo, epilogue) -> None:
+        self._need(w, torch.bfloat16, "w")
+        if w.shape[1] != a.residual.shape[1]:
+            raise KernelError(f"matrix product of {tuple(a.shape)} with {tuple(w.shape)}^T")
+        self._call("mlxone_gemm_skinny_norm", _c_void_p(_ptr(a.residual)),
+                   _c_int(a.residual.stride(0)), _c_void_p(_ptr(a.weight)), _c_float(a.eps),
+                   _c_void_p(_ptr(w)), _c_void_p(_ptr(bias)), _c_void_p(_ptr(out)), _c_int(ldo),
+                   _c_int(a.shape[0]), _c_int(w.shape[0]), _c_int(a.shape[1]), _c_int(epilogue))
+
     def linear(self, a, w, bias=None, out_dtype=None):
         """a[M, K] @ w[N, K]^T (+ bias[N], float32). ``out_dtype``: a's dtype, or float32."""
+        if isinstance(a, NormedInput):
+            out_dtype = out_dtype or a.dtype
+            out = torch.empty((a.shape[0], w.shape[0]), dtype=out_dtype, device=self.device)
+            self._normed_call(a, w, bias, out, w.shape[0],
+                              self._STORE_F32 if out_dtype == torch.float32 else self._STORE)
+            return out
         self._check_product(a, w)
         out_dtype = out_dtype or a.dtype
         m, k = a.shape
@@ -216,6 +248,11 @@ class CudaOps:
     def linear_swiglu(self, a, gate_up):
         """silu(a @ gate^T) * (a @ up^T) with gate_up = [gate rows; up rows]: one kernel for
         few rows, else a product followed by the gate kernel."""
+        if isinstance(a, NormedInput):
+            width = gate_up.shape[0] // 2
+            out = torch.empty((a.shape[0], width), dtype=a.dtype, device=self.device)
+            self._normed_call(a, gate_up, None, out, width, self._SWIGLU)
+            return out
         self._check_product(a, gate_up)
         if self._skinny(a, gate_up):
             width = gate_up.shape[0] // 2
@@ -257,6 +294,14 @@ class CudaOps:
         self._need(bcx, view.state.dtype, "bcx")
         self._need(kernel, torch.float32, "conv kernel")
         out = torch.empty((tokens, hidden), dtype=bcx.dtype, device=self.device)
+        if ctx.max_portion == 1 and tokens == ctx.requests:
+            # decode: output and state update in one kernel
+            self._call("mlxone_short_conv_decode", _c_void_p(_ptr(bcx)), _c_void_p(_ptr(kernel)),
+                       _c_void_p(_ptr(bias)), _c_void_p(_ptr(view.state)),
+                       _c_void_p(_ptr(view.slots)), _c_void_p(_ptr(ctx.history)),
+                       _c_void_p(_ptr(out)), _c_int(tokens), _c_int(hidden), _c_int(taps),
+                       _c_int(1 if write else 0), _c_int(_dtype_code(bcx.dtype)))
+            return out
         self._call("mlxone_short_conv", _c_void_p(_ptr(bcx)), _c_void_p(_ptr(kernel)),
                    _c_void_p(_ptr(bias)), _c_void_p(_ptr(view.state)), _c_void_p(_ptr(view.slots)),
                    _c_void_p(_ptr(ctx.token_request)), _c_void_p(_ptr(ctx.request_start)),

@@ -89,6 +89,21 @@ class StepContext:
     host: Mapping[str, Any] = field(default_factory=dict)    # host copies for tests/toys
 
 
+class NormedInput:
+    """The output of a norm that has not been computed yet: the 32-bit rows, the norm's weight
+    and eps. A kernel set that can apply the norm while it loads its input takes this as the
+    input of ``linear`` / ``linear_swiglu``; ``materialize()`` computes it the ordinary way.
+    Only parts that declare ``accepts_normed_input`` are ever given one."""
+
+    def __init__(self, residual: torch.Tensor, weight: torch.Tensor, eps: float,
+                 dtype: torch.dtype, ops: Any) -> None:
+        self.residual, self.weight, self.eps, self.dtype, self.ops = residual, weight, eps, dtype, ops
+        self.shape = residual.shape
+
+    def materialize(self) -> torch.Tensor:
+        return self.ops.add_rmsnorm(self.residual, None, self.weight, self.eps, self.dtype)
+
+
 # ----------------------------------------------------------------------- part bases
 
 
@@ -124,6 +139,9 @@ class Part:
 class Mixer(Part):
     # True: forward takes ``residual=`` and may add its output there itself, returning None
     fuses_residual = False
+    # True: the input is used only as the input of ops.linear / ops.linear_swiglu, so it may be
+    # a NormedInput (the norm then happens inside that product where the kernels can do it)
+    accepts_normed_input = False
 
     @classmethod
     def cache_need(cls, spec: PartSpec):
@@ -139,15 +157,21 @@ class Mixer(Part):
 
 class FeedForward(Part):
     fuses_residual = False      # as for mixers
+    accepts_normed_input = False
 
     def forward(self, x: torch.Tensor, ctx: StepContext) -> torch.Tensor:
         raise NotImplementedError
 
 
 class Norm(Part):
-    def forward(self, residual: torch.Tensor, delta: torch.Tensor | None) -> torch.Tensor:
+    # True: forward takes ``lazy=`` (see below); a norm that leaves it False is always computed
+    supports_lazy = False
+
+    def forward(self, residual: torch.Tensor, delta: torch.Tensor | None,
+                lazy: bool = False) -> torch.Tensor:
         """Adds ``delta`` (compute dtype, or None) into the 32-bit ``residual`` in place
-        and returns the normed residual in the compute dtype."""
+        and returns the normed residual in the compute dtype. With ``lazy`` a norm may return
+        a ``NormedInput`` instead, for a consumer that ``accepts_normed_input``."""
         raise NotImplementedError
 
 

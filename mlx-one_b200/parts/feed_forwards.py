@@ -31,6 +31,7 @@ class SwiGLU(FeedForward):
         self.down = self.matrix(tensors["w2.weight"])
 
     fuses_residual = True
+    accepts_normed_input = True
 
     def forward(self, x, ctx, residual=None):
         gated = self.ops.linear_swiglu(x, self.gate_up)

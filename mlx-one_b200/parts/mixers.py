@@ -63,6 +63,7 @@ class Attention(Mixer):
         self.ops.check_attention_sizes(self.heads, self.kv_heads, self.head_dim)
 
     fuses_residual = True
+    accepts_normed_input = True
 
     def forward(self, x, ctx, cache, write, residual=None):
         qkv = self.ops.linear(x, self.qkv)
@@ -118,6 +119,7 @@ class ShortConv(Mixer):
         self.out_bias = self.vector(tensors["out_proj.bias"]) if bias else None
 
     fuses_residual = True
+    accepts_normed_input = True
 
     def forward(self, x, ctx, cache, write, residual=None):
         bcx = self.ops.linear(x, self.in_proj, self.in_bias)

@@ -103,7 +103,11 @@ class Model:
     def logits(self, residual, delta, rows: torch.Tensor) -> torch.Tensor:
         """32-bit logits [len(rows), vocab] at the token rows ``rows`` (int32, device)."""
         picked, picked_delta = self.ops.gather_rows(residual, delta, rows)
-        normed = self.final_norm.forward(picked, picked_delta)
+        # the output product may apply the norm itself where the kernels can do that
+        if self.final_norm.supports_lazy:
+            normed = self.final_norm.forward(picked, picked_delta, lazy=True)
+        else:
+            normed = self.final_norm.forward(picked, picked_delta)
         return self.ops.linear(normed, self.head, out_dtype=torch.float32)
 
     def weight_bytes(self) -> int:

@@ -2,7 +2,7 @@
 
 from __future__ import annotations
 
-from .base import Norm
+from .base import Norm, NormedInput
 from .registry import NORMS
 from .spec import TensorSpec
 
@@ -13,6 +13,8 @@ class RMSNorm(Norm):
     with the residual add that precedes it. Parameters: ``size``, ``eps``.
     Reference: nn.RMSNorm at src/mlx_one/models/language/lfm2/reference_math.py:156-157."""
 
+    supports_lazy = True
+
     @classmethod
     def tensors(cls, spec):
         return {"weight": TensorSpec((spec["size"],), "norm")}
@@ -22,5 +24,8 @@ class RMSNorm(Norm):
         self.weight = self.vector(tensors["weight"])
         self.eps = float(spec["eps"])
 
-    def forward(self, residual, delta):
+    def forward(self, residual, delta, lazy=False):
+        can_fuse = getattr(self.ops, "can_fuse_norm", None)
+        if lazy and delta is None and can_fuse is not None and can_fuse(residual, self.runtime.dtype):
+            return NormedInput(residual, self.weight, self.eps, self.runtime.dtype, self.ops)
         return self.ops.add_rmsnorm(residual, delta, self.weight, self.eps, self.runtime.dtype)

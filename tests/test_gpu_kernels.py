@@ -151,6 +151,24 @@ def test_skinny_product(ops, m, n, k):
     # a token's result does not depend on the other tokens of the call
     alone = ops.linear(a[:1].contiguous().to(DEVICE), w.to(DEVICE), out_dtype=torch.float32)
     assert torch.equal(alone[0].cpu(), logits[0].cpu())
+    # the same product with the RMSNorm of 32-bit rows applied while they are loaded
+    from mlx_one_b200.parts import NormedInput
+    rows = torch.randn(m, k).to(DEVICE)
+    ops.fused_norms = True
+    fits = ops.can_fuse_norm(rows, torch.bfloat16)
+    ops.fused_norms = False
+    assert fits or m > 8 or k > 4096
+    if fits:
+        scale = (1 + 0.1 * torch.randn(k)).to(DEVICE)
+        lazy = NormedInput(rows, scale, 1e-5, torch.bfloat16, ops)
+        normed = lazy.materialize()
+        fused = ops.linear(lazy, w.to(DEVICE), out_dtype=torch.float32)
+        apart = ops.linear(normed, w.to(DEVICE), out_dtype=torch.float32)
+        torch.testing.assert_close(fused, apart, atol=2e-2, rtol=2e-2)
+        if n % 2 == 0:
+            torch.testing.assert_close(ops.linear_swiglu(lazy, w.to(DEVICE)).float(),
+                                       ops.linear_swiglu(normed, w.to(DEVICE)).float(),
+                                       atol=2e-2, rtol=2e-2)
 
 
 @pytest.mark.parametrize("m", [33, 128, 200, 777])
@@ -158,6 +176,7 @@ def test_skinny_product(ops, m, n, k):
 def test_tcgen05_product(ops, m, n, k):
     """The tensor-memory product for many rows: all four epilogues, ragged edges in M, N, K."""
     assert ops.enable_tcgen05(True)
+    least, ops.tcgen05_min_rows = ops.tcgen05_min_rows, 1
     try:
         torch.manual_seed(m + n + k)
         a = torch.randn(m, k).bfloat16()
@@ -181,15 +200,18 @@ def test_tcgen05_product(ops, m, n, k):
         ops.check_errors()
     finally:
         ops.enable_tcgen05(True)
+        ops.tcgen05_min_rows = least
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("hidden,taps,bias", [(48, 3, False), (200, 4, True), (64, 2, True),
                                               (32, 1, False), (96, 7, False)])
-def test_short_conv(ops, plain, dtype, hidden, taps, bias):
-    """Portions that start at position 0, in the middle, shorter than the kernel is wide."""
+@pytest.mark.parametrize("decode", [False, True])
+def test_short_conv(ops, plain, dtype, hidden, taps, bias, decode):
+    """Portions that start at position 0, in the middle, shorter than the kernel is wide; and
+    single tokens (the fused decode kernel) at positions 0, 1 and beyond."""
     torch.manual_seed(4)
-    portions, histories = [5, 1, 9, 2, 1], [0, 7, 3, 0, 1]
+    portions, histories = ([1] * 5, [0, 7, 3, 1, 2]) if decode else ([5, 1, 9, 2, 1], [0, 7, 3, 0, 1])
     ctx, _, _ = make_batch(portions, histories, 4, DEVICE)
     slots = torch.tensor([4, 0, 2, 5, 1], dtype=torch.int32)
     state = torch.randn(6, max(taps - 1, 1), hidden).to(dtype)
