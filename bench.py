@@ -328,6 +328,91 @@ def time_prefill(engine, tokens, warmup, repeats, seed):
     return statistics.median(times)
 
 
+def kernel_case(name: str, batch: int, context: int) -> int:
+    """Runs one kernel of the step alone a few times at the benchmark's sizes and prints its
+    time: the case that the ncu summaries under profiles/ were captured on."""
+    import math
+
+    import torch
+
+    from mlx_one_b200.kernels import default_ops
+    from mlx_one_b200.parts.base import PagedKeyValues, PagedView, StepContext
+
+    ops, device = default_ops("cuda:0"), "cuda:0"
+    ops.set_dependent_launches(True)
+    hidden, width, heads, kv_heads, head_dim = 2048, 8192, 32, 8, 64
+    torch.manual_seed(0)
+
+    def weights(n, k, copies):          # several copies, so that no call finds its weights in L2
+        return [(torch.randn(n, k, device=device) / math.sqrt(k)).bfloat16() for _ in range(copies)]
+
+    def batch_context(portions, histories):
+        as_int = lambda v: torch.tensor(v, dtype=torch.int32, device=device)
+        positions, owner, starts = [], [], [0]
+        for r, (h, n) in enumerate(zip(histories, portions)):
+            positions += list(range(h, h + n))
+            owner += [r] * n
+            starts.append(starts[-1] + n)
+        blocks = [-(-(h + n) // PAGE_SIZE) for h, n in zip(histories, portions)]
+        table = torch.full((len(portions), max(blocks)), -1, dtype=torch.int32)
+        at = 0
+        for r, count in enumerate(blocks):
+            table[r, :count] = torch.arange(at, at + count)
+            at += count
+        ctx = StepContext(tokens=len(positions), requests=len(portions),
+                          token_ids=as_int([0] * len(positions)), positions=as_int(positions),
+                          token_request=as_int(owner), request_start=as_int(starts),
+                          history=as_int(histories), max_portion=max(portions),
+                          max_context=max(h + n for h, n in zip(histories, portions)))
+        kv = torch.randn(2, at, kv_heads, PAGE_SIZE, head_dim, device=device).bfloat16()
+        return ctx, PagedView(kv, table.to(device), PAGE_SIZE, PagedKeyValues(kv_heads, head_dim))
+
+    if name == "skinny_swiglu":
+        a = torch.randn(batch, hidden, device=device).bfloat16()
+        w = weights(2 * width, hidden, 4)
+        run = lambda i: ops.linear_swiglu(a, w[i % 4])
+        work = f"{2 * width * hidden * 2 / 1e6:.1f} MB of weights"
+    elif name == "skinny_down":
+        a = torch.randn(batch, width, device=device).bfloat16()
+        w = weights(hidden, width, 8)
+        residual = torch.zeros(batch, hidden, device=device)
+        run = lambda i: ops.linear_add(a, w[i % 8], None, residual)
+        work = f"{hidden * width * 2 / 1e6:.1f} MB of weights"
+    elif name == "decode_attention":
+        ctx, view = batch_context([1] * batch, [context - 1] * batch)
+        q = torch.randn(batch, heads, head_dim, device=device).bfloat16()
+        run = lambda i: ops.paged_attention(q, heads=heads, kv_heads=kv_heads, head_dim=head_dim,
+                                            scale=head_dim ** -0.5, window=None, ctx=ctx, view=view)
+        work = f"{batch * context * 2 * kv_heads * head_dim * 2 / 1e6:.1f} MB of keys and values"
+    elif name == "prefill_attention":
+        ctx, view = batch_context([PREFILL_TOKENS], [0])
+        q = torch.randn(PREFILL_TOKENS, heads, head_dim, device=device).bfloat16()
+        run = lambda i: ops.paged_attention(q, heads=heads, kv_heads=kv_heads, head_dim=head_dim,
+                                            scale=head_dim ** -0.5, window=None, ctx=ctx, view=view)
+        work = f"{4 * heads * head_dim * PREFILL_TOKENS * (PREFILL_TOKENS + 1) // 2 / 1e9:.1f} GFLOP"
+    elif name == "tcgen05_swiglu":
+        a = torch.randn(PREFILL_TOKENS, hidden, device=device).bfloat16()
+        w = weights(2 * width, hidden, 2)
+        run = lambda i: ops.linear_swiglu(a, w[i % 2])
+        work = f"{2 * PREFILL_TOKENS * 2 * width * hidden / 1e9:.1f} GFLOP"
+    else:
+        print(f"unknown kernel case {name!r}")
+        return 2
+    for i in range(3):
+        run(i)
+    torch.cuda.synchronize()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for i in range(8):
+        run(i)
+    stop.record()
+    torch.cuda.synchronize()
+    ops.check_errors()
+    print(json.dumps({"kernel": name, "us": round(start.elapsed_time(stop) * 1e3 / 8, 2),
+                      "work": work, "batch": batch, "context": context}))
+    return 0
+
+
 def main() -> int:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
@@ -338,6 +423,9 @@ def main() -> int:
     parser.add_argument("--context", type=int, default=4096)
     parser.add_argument("--layers", type=int, default=LFM2_1_2B["num_hidden_layers"])
     parser.add_argument("--skip-points", action="store_true", help="leave out batch 1 and 64")
+    parser.add_argument("--kernel", default=None,
+                        help="run one kernel alone instead of the benchmark: skinny_swiglu, "
+                             "skinny_down, decode_attention, prefill_attention, tcgen05_swiglu")
     parser.add_argument("--dependent-launches", type=int, default=1,
                         help="1: kernels of a decode step may start while the one before ends")
     args = parser.parse_args()
@@ -346,6 +434,8 @@ def main() -> int:
     if args.gpus != 1:
         print(f"this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
+    if args.kernel:
+        return kernel_case(args.kernel, args.batch, args.context)
     warmup = max(args.warmup, 3)
 
     import torch

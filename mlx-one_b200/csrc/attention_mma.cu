@@ -85,6 +85,7 @@ struct Pages {
     const bf16* values;
     const int* table;        // this request's row of the block table
     int table_width, page_size, kv_heads, kv_head;
+    int page_shift;          // log2(page_size) if it is a power of two, else -1
 };
 
 // Copies keys first..first+KEYS-1 of one key head into a K and a V tile; rows outside [lowest,
@@ -93,19 +94,21 @@ template <int HD, int KEYS>
 __device__ __forceinline__ void load_tile(bf16* k_tile, bf16* v_tile, const Pages& pages, int first,
                                           int lowest, int last, int lane, int lanes) {
     using T = Tile<HD>;
-#pragma unroll 4
+#pragma unroll 8
     for (int piece = lane; piece < KEYS * T::CHUNKS; piece += lanes) {
         const int row = piece / T::CHUNKS, chunk = piece % T::CHUNKS;
         const int key = first + row;
         bool live = key >= lowest && key <= last;
         size_t offset = 0;
         if (live) {
-            const int block = key / pages.page_size;
+            const int block = pages.page_shift >= 0 ? key >> pages.page_shift : key / pages.page_size;
+            const int within = pages.page_shift >= 0 ? key & (pages.page_size - 1)
+                                                      : key - block * pages.page_size;
             const int page = block < pages.table_width ? pages.table[block] : -1;
             live = page >= 0;
             if (live)
                 offset = (((size_t)page * pages.kv_heads + pages.kv_head) * pages.page_size +
-                          key % pages.page_size) * HD + chunk * 8;
+                          within) * HD + chunk * 8;
         }
         copy16(k_tile + row * T::STRIDE + chunk * 8, pages.keys + offset, live);
         copy16(v_tile + row * T::STRIDE + chunk * 8, pages.values + offset, live);
@@ -249,7 +252,8 @@ attention_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kv
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
     Pages pages{kv, kv + kv_half, block_table + (size_t)request * table_width, table_width,
-                page_size, kv_heads, head / (heads / kv_heads)};
+                page_size, kv_heads, head / (heads / kv_heads),
+                (page_size & (page_size - 1)) == 0 ? 31 - __clz(page_size) : -1};
 
     // the query rows of this block (zero beyond the portion's end)
     for (int piece = threadIdx.x; piece < ROWS * T::CHUNKS; piece += WARPS * 32) {
@@ -367,7 +371,8 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kv,
     const int my_last = min(my_first + per_split, tile_first + tile_count) - 1;
 
     Pages pages{kv, kv + kv_half, block_table + (size_t)request * table_width, table_width,
-                page_size, kv_heads, kv_head};
+                page_size, kv_heads, kv_head,
+                (page_size & (page_size - 1)) == 0 ? 31 - __clz(page_size) : -1};
     bf16* k_tile = reinterpret_cast<bf16*>(shared_bytes) + (size_t)warp * 2 * KEYS * T::STRIDE;
     bf16* v_tile = k_tile + KEYS * T::STRIDE;
 

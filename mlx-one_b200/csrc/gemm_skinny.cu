@@ -98,29 +98,40 @@ skinny_gemm_kernel(const bf16* a, int lda, const bf16* __restrict__ w,
     const int mine = slices > wk ? (slices - wk + WARPS_K - 1) / WARPS_K : 0;   // per tile
     const int total = mine * (tile_end - tile_begin);     // this warp's slices over all tiles
 
-    // copy slice number `index` of this warp's stream into its ring: 16 rows x 8 pieces of 16 B;
+    // Copies the next slice of this warp's stream into its ring: 16 rows x 8 pieces of 16 B;
     // piece c of row r is stored at piece c ^ ((r & 1) << 2), which keeps the 16-byte reads of a
-    // quarter warp on different banks
-    auto fetch = [&](int index) {
-        const int tile = tile_begin + index / mine;
-        const int k0 = (wk + (index % mine) * WARPS_K) * SLICE;
-        const int row0 = tile * ROWS + half * up_offset;
-        const int buffer = index % STAGES;
+    // quarter warp on different banks. What depends only on the lane is worked out once.
+    static_assert((STAGES & (STAGES - 1)) == 0, "the ring size must be a power of two");
+    uint32_t piece_dst[4];
+    int piece_row[4], piece_k[4];
+    size_t piece_src[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int piece = lane + 32 * i;
+        const int r = piece >> 3, c = piece & 7;
+        piece_row[i] = r;
+        piece_k[i] = c * 8;
+        piece_dst[i] = ring_address + r * 128 + ((c ^ ((r & 1) << 2)) << 4);
+        piece_src[i] = (size_t)r * k + c * 8;
+    }
+    int fetch_tile = tile_begin, fetch_slice = 0, fetched = 0;
+    auto fetch = [&]() {
+        const int k0 = (wk + fetch_slice * WARPS_K) * SLICE;
+        const int row0 = fetch_tile * ROWS + half * up_offset;
+        const bf16* base = w + (size_t)row0 * k + k0;
+        const uint32_t buffer = (fetched & (STAGES - 1)) * SLICE_BYTES;
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-            const int piece = lane + 32 * i;
-            const int r = piece >> 3, c = piece & 7;
-            const int kk = k0 + c * 8;
-            const bool live = row0 + r < row_limit && kk < k;
-            const bf16* src = w + (live ? (size_t)(row0 + r) * k + kk : 0);
-            copy16(ring_address + buffer * SLICE_BYTES + r * 128 + ((c ^ ((r & 1) << 2)) << 4), src,
-                   live);
+            const bool live = row0 + piece_row[i] < row_limit && k0 + piece_k[i] < k;
+            copy16(piece_dst[i] + buffer, live ? base + piece_src[i] : w, live);
         }
+        ++fetched;
+        if (++fetch_slice == mine) { fetch_slice = 0; ++fetch_tile; }
     };
 
 #pragma unroll
     for (int p = 0; p < STAGES - 1; ++p) {
-        if (p < total) fetch(p);
+        if (p < total) fetch();
         copy_commit();
     }
     griddep_launch();
@@ -242,6 +253,7 @@ skinny_gemm_kernel(const bf16* a, int lda, const bf16* __restrict__ w,
     float acc[NT][4];
     uint4 tokens_now[2][NT], tokens_next[2][NT];
     if (!RESIDENT && total > 0) load_tokens(wk * SLICE, tokens_now);
+    int next_slice = mine > 1 ? 1 : 0;       // the slice (within a tile) whose tokens are fetched next
 
     int index = 0;
     for (int tile = tile_begin; tile < tile_end; ++tile) {
@@ -253,14 +265,15 @@ skinny_gemm_kernel(const bf16* a, int lda, const bf16* __restrict__ w,
         for (int i = 0; i < mine; ++i, ++index) {
             copy_wait<STAGES - 2>();
             __syncwarp();
-            if (index + STAGES - 1 < total) fetch(index + STAGES - 1);
+            if (fetched < total) fetch();
             copy_commit();
             if (RESIDENT) {
                 load_tokens((wk + i * WARPS_K) * SLICE, tokens_now);
             } else if (index + 1 < total) {
-                load_tokens((wk + ((index + 1) % mine) * WARPS_K) * SLICE, tokens_next);
+                load_tokens((wk + next_slice * WARPS_K) * SLICE, tokens_next);
+                if (++next_slice == mine) next_slice = 0;
             }
-            const unsigned char* slice = ring + (index % STAGES) * SLICE_BYTES;
+            const unsigned char* slice = ring + (index & (STAGES - 1)) * SLICE_BYTES;
 #pragma unroll
             for (int q = 0; q < 2; ++q) {
                 const int c = q * 4 + t;
