@@ -94,6 +94,29 @@ template <int HD, int KEYS>
 __device__ __forceinline__ void load_tile(bf16* k_tile, bf16* v_tile, const Pages& pages, int first,
                                           int lowest, int last, int lane, int lanes) {
     using T = Tile<HD>;
+    if (lanes == 32 && pages.page_shift >= 0) {
+        // One warp, pages of a power of two: lane j looks up the tile's j-th page once and the
+        // warp shares the page numbers by shuffle, so the copy loop has no load in its way.
+        const int per_tile = max(KEYS >> pages.page_shift, 1);
+        const int block = (first >> pages.page_shift) + lane;
+        int my_page = -1;
+        if (lane < per_tile && block < pages.table_width) my_page = pages.table[block];
+        const int inside = first & (pages.page_size - 1);       // 0 unless pages are larger than a tile
+#pragma unroll
+        for (int piece = lane; piece < KEYS * T::CHUNKS; piece += 32) {
+            const int row = piece / T::CHUNKS, chunk = piece % T::CHUNKS;
+            const int key = first + row;
+            const int page = __shfl_sync(0xffffffffu, my_page, (inside + row) >> pages.page_shift);
+            const bool live = key >= lowest && key <= last && page >= 0;
+            const size_t offset =
+                live ? (((size_t)page * pages.kv_heads + pages.kv_head) * pages.page_size +
+                        ((inside + row) & (pages.page_size - 1))) * HD + chunk * 8
+                     : 0;
+            copy16(k_tile + row * T::STRIDE + chunk * 8, pages.keys + offset, live);
+            copy16(v_tile + row * T::STRIDE + chunk * 8, pages.values + offset, live);
+        }
+        return;
+    }
 #pragma unroll 8
     for (int piece = lane; piece < KEYS * T::CHUNKS; piece += lanes) {
         const int row = piece / T::CHUNKS, chunk = piece % T::CHUNKS;

@@ -67,8 +67,6 @@ __device__ __forceinline__ void mma_16816(float (&d)[4], uint32_t a0, uint32_t a
 }
 
 // NT: groups of 8 tokens (M <= 8 * NT). RESIDENT: activations live in shared memory.
-// A SwiGLU block splits its warps in two halves: the first on the gate rows, the second on
-// the matching up rows.
 // NORM (needs RESIDENT): the activations are RMSNorm(source) * norm_weight, computed here from the
 // 32-bit rows of `source` while they are brought into shared memory, so the norm needs no
 // kernel and no pass over memory of its own.
@@ -78,17 +76,25 @@ skinny_gemm_kernel(const bf16* a, int lda, const bf16* __restrict__ w,
                    const float* __restrict__ bias, void* out, int ldo, int m, int n, int k,
                    int up_offset, int tiles, const float* source, int source_ld,
                    const float* __restrict__ norm_weight, float eps) {
+    // A SwiGLU block splits its warps in two halves: the first on 16 gate rows, the second on
+    // the 16 matching up rows (measured faster than tiles of 8 + 8 rows, which balance better
+    // but pay the per-tile reduction twice as often).
     constexpr int HALVES = EPILOGUE == SWIGLU ? 2 : 1;
     constexpr int WARPS_K = WARPS / HALVES;
     constexpr int TOKENS = 8 * NT;
+    // With up to 8 tokens and no room to keep all activations in shared memory, each slice of
+    // activations (8 tokens x 64) travels through the ring beside its slice of w.
+    constexpr bool TOKEN_RING = !RESIDENT && NT == 1;
+    constexpr int SLOT_BYTES = SLICE_BYTES + (TOKEN_RING ? 8 * SLICE * 2 : 0);
     extern __shared__ __align__(128) unsigned char shared_bytes[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int half = warp / WARPS_K, wk = warp % WARPS_K;
     const int g = lane >> 2, t = lane & 3;
-    unsigned char* ring = shared_bytes + (size_t)warp * STAGES * SLICE_BYTES;
+    unsigned char* ring = shared_bytes + (size_t)warp * STAGES * SLOT_BYTES;
     const uint32_t ring_address = shared_address(ring);
-    float* sums = reinterpret_cast<float*>(shared_bytes + (size_t)WARPS * STAGES * SLICE_BYTES);
-    unsigned char* resident = reinterpret_cast<unsigned char*>(sums + WARPS * ROWS * TOKENS);
+    // two sets of partial sums, used in turn, so that one block-wide barrier per tile is enough
+    float* sums_base = reinterpret_cast<float*>(shared_bytes + (size_t)WARPS * STAGES * SLOT_BYTES);
+    unsigned char* resident = reinterpret_cast<unsigned char*>(sums_base + 2 * WARPS * ROWS * TOKENS);
 
     // this block's tiles
     const int tile_begin = (int)((long long)tiles * blockIdx.x / gridDim.x);
@@ -117,9 +123,9 @@ skinny_gemm_kernel(const bf16* a, int lda, const bf16* __restrict__ w,
     int fetch_tile = tile_begin, fetch_slice = 0, fetched = 0;
     auto fetch = [&]() {
         const int k0 = (wk + fetch_slice * WARPS_K) * SLICE;
+        const uint32_t buffer = (fetched & (STAGES - 1)) * SLOT_BYTES;
         const int row0 = fetch_tile * ROWS + half * up_offset;
         const bf16* base = w + (size_t)row0 * k + k0;
-        const uint32_t buffer = (fetched & (STAGES - 1)) * SLICE_BYTES;
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             const bool live = row0 + piece_row[i] < row_limit && k0 + piece_k[i] < k;
@@ -127,6 +133,22 @@ skinny_gemm_kernel(const bf16* a, int lda, const bf16* __restrict__ w,
         }
         ++fetched;
         if (++fetch_slice == mine) { fetch_slice = 0; ++fetch_tile; }
+    };
+    // the activations of the next slice of the stream (TOKEN_RING): 8 tokens x 8 pieces
+    int token_slice = 0, tokens_fetched = 0;
+    auto fetch_tokens = [&]() {
+        const int k0 = (wk + token_slice * WARPS_K) * SLICE;
+        const uint32_t buffer = (tokens_fetched & (STAGES - 1)) * SLOT_BYTES + SLICE_BYTES;
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const int piece = lane + 32 * i;
+            const int token = piece >> 3, c = piece & 7;
+            const bool live = token < m && k0 + c * 8 < k;
+            copy16(ring_address + buffer + token * 128 + ((c ^ ((token & 1) << 2)) << 4),
+                   live ? a + (size_t)token * lda + k0 + c * 8 : a, live);
+        }
+        ++tokens_fetched;
+        if (++token_slice == mine) token_slice = 0;
     };
 
 #pragma unroll
@@ -252,7 +274,18 @@ skinny_gemm_kernel(const bf16* a, int lda, const bf16* __restrict__ w,
 
     float acc[NT][4];
     uint4 tokens_now[2][NT], tokens_next[2][NT];
-    if (!RESIDENT && total > 0) load_tokens(wk * SLICE, tokens_now);
+    if (TOKEN_RING) {
+        // the activations of the slices whose weights are already on their way, then all of it
+        // has to land once; from here on a slice's weights and activations travel together
+#pragma unroll
+        for (int p = 0; p < STAGES - 1; ++p)
+            if (p < total) fetch_tokens();
+        copy_commit();
+        copy_wait<0>();
+        __syncwarp();
+    } else if (!RESIDENT && total > 0) {
+        load_tokens(wk * SLICE, tokens_now);
+    }
     int next_slice = mine > 1 ? 1 : 0;       // the slice (within a tile) whose tokens are fetched next
 
     int index = 0;
@@ -265,15 +298,23 @@ skinny_gemm_kernel(const bf16* a, int lda, const bf16* __restrict__ w,
         for (int i = 0; i < mine; ++i, ++index) {
             copy_wait<STAGES - 2>();
             __syncwarp();
-            if (fetched < total) fetch();
+            if (fetched < total) {
+                fetch();
+                if (TOKEN_RING) fetch_tokens();
+            }
             copy_commit();
+            const unsigned char* slice = ring + (index & (STAGES - 1)) * SLOT_BYTES;
             if (RESIDENT) {
                 load_tokens((wk + i * WARPS_K) * SLICE, tokens_now);
+            } else if (TOKEN_RING) {
+#pragma unroll
+                for (int q = 0; q < 2; ++q)
+                    tokens_now[q][0] = *reinterpret_cast<const uint4*>(
+                        slice + SLICE_BYTES + g * 128 + (((q * 4 + t) ^ ((g & 1) << 2)) << 4));
             } else if (index + 1 < total) {
                 load_tokens((wk + next_slice * WARPS_K) * SLICE, tokens_next);
                 if (++next_slice == mine) next_slice = 0;
             }
-            const unsigned char* slice = ring + (index & (STAGES - 1)) * SLICE_BYTES;
 #pragma unroll
             for (int q = 0; q < 2; ++q) {
                 const int c = q * 4 + t;
@@ -289,7 +330,7 @@ skinny_gemm_kernel(const bf16* a, int lda, const bf16* __restrict__ w,
                               tokens_now[q][nt].w);
                 }
             }
-            if (!RESIDENT) {
+            if (!RESIDENT && !TOKEN_RING) {
 #pragma unroll
                 for (int q = 0; q < 2; ++q)
 #pragma unroll
@@ -298,6 +339,7 @@ skinny_gemm_kernel(const bf16* a, int lda, const bf16* __restrict__ w,
         }
 
         // partial sums of this tile: [warp][row 0..15][token]
+        float* sums = sums_base + (size_t)((tile - tile_begin) & 1) * WARPS * ROWS * TOKENS;
         float* mine_sums = sums + (size_t)warp * ROWS * TOKENS;
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
@@ -333,7 +375,8 @@ skinny_gemm_kernel(const bf16* a, int lda, const bf16* __restrict__ w,
                 reinterpret_cast<float*>(out)[(size_t)token * ldo + column] = value;
             }
         }
-        __syncthreads();       // the sums are free for the next tile
+        // no second barrier: the next tile writes the other set of sums, and the one after it
+        // comes after the next tile's barrier, which every thread reaches only after this loop
     }
     copy_wait<0>();
 }
@@ -360,12 +403,13 @@ cudaError_t launch(const void* a, int lda, const void* w, const float* bias, voi
     const int tiles = ((EPILOGUE == SWIGLU ? up_offset : n) + ROWS - 1) / ROWS;
     const int grid = tiles < g_sm_count ? tiles : g_sm_count;
     const size_t rings = (size_t)WARPS * STAGES * SLICE_BYTES;
-    const size_t sums = (size_t)WARPS * ROWS * 8 * NT * sizeof(float);
+    const size_t sums = (size_t)2 * WARPS * ROWS * 8 * NT * sizeof(float);
     const size_t resident = (size_t)8 * NT * ((k + 63) / 64) * 64 * 2;
     // activations in shared memory pay off when a block reuses them for several tiles
     const bool fits = NT <= 2 && rings + sums + resident <= 200 * 1024;
     const bool use_resident = fits && (norm.source != nullptr || tiles >= 2 * grid);
-    const size_t shared = rings + sums + (use_resident ? resident : 0);
+    const size_t token_ring = !use_resident && NT == 1 ? (size_t)WARPS * STAGES * 8 * SLICE * 2 : 0;
+    const size_t shared = rings + token_ring + sums + (use_resident ? resident : 0);
     cudaError_t err;
     if (norm.source != nullptr) {
         if (!fits) return cudaErrorInvalidValue;
@@ -446,7 +490,7 @@ MLXONE_API int mlxone_gemm_skinny_norm_fits(int m, int k) {
     if (m < 1 || m > 16 || k % 8 != 0) return 0;
     const size_t rings = (size_t)WARPS * STAGES * SLICE_BYTES;
     const int nt = m <= 8 ? 1 : 2;
-    const size_t sums = (size_t)WARPS * ROWS * 8 * nt * sizeof(float);
+    const size_t sums = (size_t)2 * WARPS * ROWS * 8 * nt * sizeof(float);
     const size_t resident = (size_t)8 * nt * ((k + 63) / 64) * 64 * 2;
     return rings + sums + resident <= 200 * 1024 ? 1 : 0;
 }
