@@ -138,11 +138,12 @@ __device__ __forceinline__ void load_tile(bf16* k_tile, bf16* v_tile, const Page
     }
 }
 
-// One warp: 16 query rows (in q_tile, rows row0..row0+15) against one tile of KEYS keys.
+// One warp: 16 query rows (their fragments in `qf`) against one tile of KEYS keys.
 // `limit_lo[i]`/`limit_hi[i]` (i = 0: row lane/4, 1: row lane/4 + 8) bound the keys that the row
-// may see. Updates the running max `m`, sum `l` (both in the exp2 domain, scaled) and `o`.
-template <int HD, int KEYS>
-__device__ __forceinline__ void attend_tile(const bf16* q_tile, int row0, const bf16* k_tile,
+// may see; with MASKED false the caller has checked that every row sees the whole tile.
+// Updates the running max `m` (of score * scale * log2 e), the sum `l` and `o`.
+template <int HD, int KEYS, bool MASKED>
+__device__ __forceinline__ void attend_tile(const uint32_t (&qf)[HD / 16][4], const bf16* k_tile,
                                             const bf16* v_tile, int first, const int (&limit_lo)[2],
                                             const int (&limit_hi)[2], float scale_log2,
                                             float (&m)[2], float (&l)[2], float (&o)[HD / 8][4],
@@ -157,30 +158,28 @@ __device__ __forceinline__ void attend_tile(const bf16* q_tile, int row0, const 
     const int matrix = lane >> 3, r = lane & 7;
 #pragma unroll
     for (int kk = 0; kk < HD / 16; ++kk) {
-        uint32_t a[4];
-        ldmatrix_x4(a, q_tile + (row0 + r + (matrix & 1) * 8) * T::STRIDE + kk * 16 +
-                           (matrix >> 1) * 8);
 #pragma unroll
         for (int jj = 0; jj < KEYS / 16; ++jj) {
             uint32_t b[4];
             ldmatrix_x4(b, k_tile + (jj * 16 + r + (matrix >> 1) * 8) * T::STRIDE + kk * 16 +
                                (matrix & 1) * 8);
-            mma_16816(s[2 * jj], a, b[0], b[1]);
-            mma_16816(s[2 * jj + 1], a, b[2], b[3]);
+            mma_16816(s[2 * jj], qf[kk], b[0], b[1]);
+            mma_16816(s[2 * jj + 1], qf[kk], b[2], b[3]);
         }
     }
 
-    // mask, then the tile's row maxima
+    // the tile's row maxima (of the raw scores; masked ones count as -inf)
     const int t2 = (lane & 3) * 2;
     float tile_max[2] = {-INFINITY, -INFINITY};
 #pragma unroll
     for (int j = 0; j < KEYS / 8; ++j)
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
-            const int key = first + j * 8 + t2 + (c & 1);
             const int i = c >> 1;
-            const bool seen = key >= limit_lo[i] && key <= limit_hi[i];
-            s[j][c] = seen ? s[j][c] * scale_log2 : -INFINITY;
+            if (MASKED) {
+                const int key = first + j * 8 + t2 + (c & 1);
+                if (!(key >= limit_lo[i] && key <= limit_hi[i])) s[j][c] = -INFINITY;
+            }
             tile_max[i] = fmaxf(tile_max[i], s[j][c]);
         }
     float correction[2];
@@ -188,17 +187,18 @@ __device__ __forceinline__ void attend_tile(const bf16* q_tile, int row0, const 
     for (int i = 0; i < 2; ++i) {
         tile_max[i] = fmaxf(tile_max[i], __shfl_xor_sync(0xffffffffu, tile_max[i], 1));
         tile_max[i] = fmaxf(tile_max[i], __shfl_xor_sync(0xffffffffu, tile_max[i], 2));
-        const float new_max = fmaxf(m[i], tile_max[i]);
+        const float new_max = fmaxf(m[i], tile_max[i] * scale_log2);
         correction[i] = new_max == -INFINITY ? 1.f : exp2f(m[i] - new_max);
         m[i] = new_max;
     }
     float tile_sum[2] = {0.f, 0.f};
+    const float shift[2] = {m[0] == -INFINITY ? 0.f : m[0], m[1] == -INFINITY ? 0.f : m[1]};
 #pragma unroll
     for (int j = 0; j < KEYS / 8; ++j)
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
             const int i = c >> 1;
-            const float p = m[i] == -INFINITY ? 0.f : exp2f(s[j][c] - m[i]);
+            const float p = exp2f(fmaf(s[j][c], scale_log2, -shift[i]));   // exp2(-inf) = 0
             s[j][c] = p;
             tile_sum[i] += p;
         }
@@ -254,7 +254,8 @@ attention_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kv
 
     // which request and which 64 rows of it this block serves
     if (threadIdx.x == 0) {
-        int left = blockIdx.x, request = -1, start = 0;
+        // the last blocks of a causal prompt have the most keys to walk: they go first
+        int left = gridDim.x - 1 - blockIdx.x, request = -1, start = 0;
         for (int r = 0; r < requests; ++r) {
             const int tiles = (request_start[r + 1] - request_start[r] + ROWS - 1) / ROWS;
             if (left < tiles) { request = r; start = left * ROWS; break; }
@@ -310,6 +311,13 @@ attention_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kv
     for (int n = 0; n < HD / 8; ++n)
 #pragma unroll
         for (int c = 0; c < 4; ++c) o[n][c] = 0.f;
+    uint32_t qf[HD / 16][4];              // this warp's query rows, loaded once
+    bool have_q = false;
+    // keys that every row of this warp sees in full: from the largest lower limit to the first
+    // row's position (rows beyond the portion's end see nothing, so such a warp always masks)
+    const int warp_first = first_position + warp * 16;
+    const bool warp_whole = warp * 16 + 15 < rows;
+    const int open_lo = window > 0 ? max(warp_first + 15 - window + 1, 0) : 0;
 
     for (int tile = tile_first; tile <= tile_last; ++tile) {
         const int buffer = (tile - tile_first) & 1;
@@ -325,10 +333,26 @@ attention_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kv
         __syncthreads();
         // a warp whose rows all lie before this tile's keys has nothing to see in it
         const int warp_last = first_position + min(warp * 16 + 15, rows - 1);
-        if (warp * 16 < rows && tile * KEYS <= warp_last)
-            attend_tile<HD, KEYS>(q_tile, warp * 16, k_tiles + buffer * KEYS * T::STRIDE,
-                            v_tiles + buffer * KEYS * T::STRIDE, tile * KEYS, limit_lo, limit_hi,
-                            scale_log2, m, l, o, lane);
+        if (warp * 16 < rows && tile * KEYS <= warp_last) {
+            if (!have_q) {
+                const int matrix = lane >> 3, r = lane & 7;
+#pragma unroll
+                for (int kk = 0; kk < HD / 16; ++kk)
+                    ldmatrix_x4(qf[kk], q_tile + (warp * 16 + r + (matrix & 1) * 8) * T::STRIDE +
+                                            kk * 16 + (matrix >> 1) * 8);
+                have_q = true;
+            }
+            const bf16* k_now = k_tiles + buffer * KEYS * T::STRIDE;
+            const bf16* v_now = v_tiles + buffer * KEYS * T::STRIDE;
+            const bool open = warp_whole && tile * KEYS >= open_lo &&
+                              tile * KEYS + KEYS - 1 <= warp_first;
+            if (open)
+                attend_tile<HD, KEYS, false>(qf, k_now, v_now, tile * KEYS, limit_lo, limit_hi,
+                                             scale_log2, m, l, o, lane);
+            else
+                attend_tile<HD, KEYS, true>(qf, k_now, v_now, tile * KEYS, limit_lo, limit_hi,
+                                            scale_log2, m, l, o, lane);
+        }
         __syncthreads();
     }
 

@@ -86,6 +86,120 @@ qk_prep_kernel(const T* __restrict__ qkv, const float* __restrict__ q_weight,
     for (int e = lane; e < head_dim; e += 32) dst[e] = from_float<T>(values[e]);
 }
 
+// bfloat16 with a head size of 32, 64, 128 or 256 that is rotated as a whole (or not at all):
+// a lane keeps HD/32 neighbouring values of the head in registers, its rotation partner sits 16
+// lanes away, and the angles are computed once per token, not once per head. One block per
+// token; its warps take the token's heads in turn.
+template <int HD>
+__global__ void __launch_bounds__(WARPS * 32)
+qk_prep_wide_kernel(const __nv_bfloat16* __restrict__ qkv, const float* __restrict__ q_weight,
+                    const float* __restrict__ k_weight, float eps,
+                    const float* __restrict__ inv_freq, const int* __restrict__ positions,
+                    const int* __restrict__ token_request, __nv_bfloat16* __restrict__ q_out,
+                    __nv_bfloat16* __restrict__ kv, const int* __restrict__ block_table,
+                    int table_width, int page_size, long long kv_half, int heads, int kv_heads,
+                    int write_kv, int* __restrict__ error_flag) {
+    using T = __nv_bfloat16;
+    constexpr int E = HD / 32;
+    griddep_launch();
+    griddep_wait();
+    const int t = blockIdx.x;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int slots = heads + 2 * kv_heads;
+    const int position = positions[t];
+    const int e0 = E * lane;
+    float cosine[E], sine[E], q_scale[E], k_scale[E];
+#pragma unroll
+    for (int i = 0; i < E; ++i) {
+        cosine[i] = 1.f;
+        sine[i] = 0.f;
+        if (inv_freq != nullptr) {
+            const float angle = (float)position * inv_freq[(e0 + i) % (HD / 2)];
+            sincosf(angle, &sine[i], &cosine[i]);
+            if (lane < 16) sine[i] = -sine[i];       // first half: a cos - b sin
+        }
+        q_scale[i] = q_weight ? q_weight[e0 + i] : 1.f;
+        k_scale[i] = k_weight ? k_weight[e0 + i] : 1.f;
+    }
+    // where this token's keys and values go
+    T* page_base = nullptr;
+    if (write_kv) {
+        const int r = token_request[t];
+        const int block = position / page_size;
+        const int page = block < table_width ? block_table[(size_t)r * table_width + block] : -1;
+        if (page < 0) {
+            if (threadIdx.x == 0) atomicExch(error_flag, 2);
+        } else {
+            page_base = kv + ((size_t)page * kv_heads * page_size + position % page_size) * HD;
+        }
+    }
+    const T* row = qkv + (size_t)t * slots * HD;
+    for (int slot = warp; slot < slots; slot += WARPS) {
+        const bool is_q = slot < heads;
+        const bool is_k = !is_q && slot < heads + kv_heads;
+        if (!is_q && page_base == nullptr) continue;
+        float v[E];
+        const T* src = row + (size_t)slot * HD + e0;
+        if (E == 1) {
+            v[0] = __bfloat162float(src[0]);
+        } else {
+#pragma unroll
+            for (int i = 0; i < E; i += 2) {
+                const __nv_bfloat162 pair = *reinterpret_cast<const __nv_bfloat162*>(src + i);
+                v[i] = __low2float(pair);
+                v[i + 1] = __high2float(pair);
+            }
+        }
+        if (is_q || is_k) {
+            const float* scale = is_q ? q_scale : k_scale;
+            if ((is_q ? q_weight : k_weight) != nullptr) {
+                float sum = 0.f;
+#pragma unroll
+                for (int i = 0; i < E; ++i) sum += v[i] * v[i];
+                sum = warp_sum(sum);
+                const float inv = rsqrtf(sum / (float)HD + eps);
+#pragma unroll
+                for (int i = 0; i < E; ++i) v[i] = v[i] * inv * scale[i];
+            }
+            if (inv_freq != nullptr) {
+#pragma unroll
+                for (int i = 0; i < E; ++i) {
+                    const float partner = __shfl_xor_sync(0xffffffffu, v[i], 16);
+                    v[i] = v[i] * cosine[i] + partner * sine[i];
+                }
+            }
+        }
+        T* dst;
+        if (is_q) {
+            dst = q_out + ((size_t)t * heads + slot) * HD + e0;
+        } else {
+            const int kv_head = is_k ? slot - heads : slot - heads - kv_heads;
+            dst = page_base + (is_k ? 0 : kv_half) + (size_t)kv_head * page_size * HD + e0;
+        }
+        if (E == 1) {
+            dst[0] = __float2bfloat16_rn(v[0]);
+        } else {
+#pragma unroll
+            for (int i = 0; i < E; i += 2)
+                *reinterpret_cast<__nv_bfloat162*>(dst + i) = __floats2bfloat162_rn(v[i], v[i + 1]);
+        }
+    }
+}
+
+template <int HD>
+static void launch_qk_prep_wide(const void* qkv, const float* q_weight, const float* k_weight,
+                                float eps, const float* inv_freq, const int* positions,
+                                const int* token_request, void* q_out, void* kv,
+                                const int* block_table, int table_width, int page_size,
+                                long long kv_half, int tokens, int heads, int kv_heads,
+                                int write_kv, int* error_flag, cudaStream_t stream) {
+    using T = __nv_bfloat16;
+    launch_kernel(qk_prep_wide_kernel<HD>, dim3(tokens), dim3(WARPS * 32), 0, stream, true,
+                  (const T*)qkv, q_weight, k_weight, eps, inv_freq, positions, token_request,
+                  (T*)q_out, (T*)kv, block_table, table_width, page_size, kv_half, heads, kv_heads,
+                  write_kv, error_flag);
+}
+
 }  // namespace
 
 MLXONE_API int mlxone_qk_prep(const void* qkv, const float* q_weight, const float* k_weight,
@@ -107,7 +221,19 @@ MLXONE_API int mlxone_qk_prep(const void* qkv, const float* q_weight, const floa
     const int blocks = ceil_div_host(items, WARPS);
     const size_t shared = (size_t)WARPS * head_dim * sizeof(float);
     const long long kv_half = (long long)pages * kv_heads * page_size * head_dim;
-    if (dtype == MLXONE_BF16) {
+    const bool whole = inv_freq == nullptr || rotary_dim == head_dim;
+    if (dtype == MLXONE_BF16 && whole &&
+        (head_dim == 32 || head_dim == 64 || head_dim == 128 || head_dim == 256)) {
+#define WIDE(HD)                                                                                 \
+    launch_qk_prep_wide<HD>(qkv, q_weight, k_weight, eps, inv_freq, positions, token_request,   \
+                            q_out, kv, block_table, table_width, page_size, kv_half, tokens,    \
+                            heads, kv_heads, write_kv, error_flag, stream)
+        if (head_dim == 32) WIDE(32);
+        else if (head_dim == 64) WIDE(64);
+        else if (head_dim == 128) WIDE(128);
+        else WIDE(256);
+#undef WIDE
+    } else if (dtype == MLXONE_BF16) {
         using T = __nv_bfloat16;
         launch_kernel(qk_prep_kernel<T>, dim3(blocks), dim3(WARPS * 32), shared, stream, true, (const T*)qkv, q_weight, k_weight, eps, inv_freq, rotary_dim, positions,
             token_request, (T*)q_out, (T*)kv, block_table, table_width, page_size, kv_half,

@@ -46,6 +46,68 @@ __global__ void short_conv_kernel(const T* __restrict__ bcx, const float* __rest
     out[(size_t)t * hidden + d] = from_float<T>(to_float<T>(bcx[(size_t)t * row + hidden + d]) * y);
 }
 
+// The same for bfloat16 with hidden % 8 == 0: a thread takes 8 neighbouring channels of one token
+// with 16-byte loads.
+__global__ void short_conv_wide_kernel(const __nv_bfloat16* __restrict__ bcx,
+                                       const float* __restrict__ kernel,
+                                       const float* __restrict__ bias,
+                                       const __nv_bfloat16* __restrict__ state,
+                                       const int* __restrict__ slots,
+                                       const int* __restrict__ token_request,
+                                       const int* __restrict__ request_start,
+                                       const int* __restrict__ history,
+                                       __nv_bfloat16* __restrict__ out, int tokens, int hidden,
+                                       int taps) {
+    using T = __nv_bfloat16;
+    griddep_launch();
+    griddep_wait();
+    const int groups = hidden / 8;
+    const long long item = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (item >= (long long)tokens * groups) return;
+    const int t = (int)(item / groups);
+    const int d = (int)(item % groups) * 8;
+    const int r = token_request[t];
+    const int index = t - request_start[r];
+    const int position = history[r] + index;
+    const size_t row = (size_t)3 * hidden;
+    auto unpack = [](const uint4& v, float (&f)[8]) {
+        const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { f[2 * i] = __low2float(p[i]); f[2 * i + 1] = __high2float(p[i]); }
+    };
+    float y[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) y[i] = bias ? bias[d + i] : 0.f;
+    for (int k = 0; k < taps; ++k) {
+        const int back = taps - 1 - k;
+        float g[8];
+        if (index - back >= 0) {
+            const T* src = bcx + (size_t)(t - back) * row;
+            float b[8], x[8];
+            unpack(*reinterpret_cast<const uint4*>(src + d), b);
+            unpack(*reinterpret_cast<const uint4*>(src + 2 * hidden + d), x);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) g[i] = round_to<T>(b[i] * x[i]);
+        } else if (position - back >= 0) {
+            const int s = taps - 1 + (index - back);
+            unpack(*reinterpret_cast<const uint4*>(
+                       state + ((size_t)slots[r] * (taps - 1) + s) * hidden + d), g);
+        } else {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) g[i] = 0.f;
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) y[i] = fmaf(kernel[(size_t)(d + i) * taps + k], g[i], y[i]);
+    }
+    float c[8];
+    unpack(*reinterpret_cast<const uint4*>(bcx + (size_t)t * row + hidden + d), c);
+    uint4 packed;
+    __nv_bfloat162* q = reinterpret_cast<__nv_bfloat162*>(&packed);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) q[i] = __floats2bfloat162_rn(c[2 * i] * y[2 * i], c[2 * i + 1] * y[2 * i + 1]);
+    *reinterpret_cast<uint4*>(out + (size_t)t * hidden + d) = packed;
+}
+
 // New state after the step: row s holds g at position (history + n) - (taps-1) + s.
 template <typename T>
 __global__ void short_conv_state_kernel(const T* __restrict__ bcx, T* __restrict__ state,
@@ -152,6 +214,15 @@ MLXONE_API int mlxone_short_conv(const void* bcx, const float* kernel, const flo
     MLXONE_REQUIRE(requests <= 65535, "short_conv: at most 65535 requests a step");
     if (dtype == MLXONE_BF16) {
         using T = __nv_bfloat16;
+        const bool wide = hidden % 8 == 0 && (reinterpret_cast<uintptr_t>(bcx) & 15) == 0 &&
+                          (reinterpret_cast<uintptr_t>(state) & 15) == 0 &&
+                          (reinterpret_cast<uintptr_t>(out) & 15) == 0;
+        if (wide) {
+            const long long items = (long long)tokens * (hidden / 8);
+            launch_kernel(short_conv_wide_kernel, dim3(ceil_div_host(items, 256)), dim3(256), 0,
+                          stream, true, (const T*)bcx, kernel, bias, (const T*)state, slots,
+                          token_request, request_start, history, (T*)out, tokens, hidden, taps);
+        } else
         launch_kernel(short_conv_kernel<T>, grid, dim3(threads), 0, stream, true, (const T*)bcx, kernel, bias, (const T*)state, slots, token_request, request_start,
             history, (T*)out, tokens, hidden, taps);
         MLXONE_LAUNCH_CHECK("short_conv");

@@ -205,7 +205,7 @@ def test_tcgen05_product(ops, m, n, k):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("hidden,taps,bias", [(48, 3, False), (200, 4, True), (64, 2, True),
-                                              (32, 1, False), (96, 7, False)])
+                                              (32, 1, False), (96, 7, False), (204, 3, True)])
 @pytest.mark.parametrize("decode", [False, True])
 def test_short_conv(ops, plain, dtype, hidden, taps, bias, decode):
     """Portions that start at position 0, in the middle, shorter than the kernel is wide; and
@@ -238,7 +238,7 @@ def test_short_conv(ops, plain, dtype, hidden, taps, bias, decode):
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("heads,kv_heads,head_dim,rotary_dim,norm", [
     (4, 2, 16, 16, True), (3, 1, 32, 32, True), (6, 3, 48, 24, False), (5, 5, 80, 80, True),
-    (2, 1, 256, 256, True)])
+    (2, 1, 256, 256, True), (8, 2, 64, 64, True), (4, 4, 128, 128, False), (3, 3, 64, 32, True)])
 def test_qk_norm_rope_store(ops, plain, dtype, heads, kv_heads, head_dim, rotary_dim, norm):
     torch.manual_seed(5)
     page_size = 8
