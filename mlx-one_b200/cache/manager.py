@@ -56,6 +56,7 @@ class RequestCache:
     """What one request holds."""
 
     request_id: Any
+    index: int = 0                                          # a number of its own among live requests
     length: int = 0                                         # tokens committed
     tables: list[list[int]] = field(default_factory=list)   # per paged group; -1 = given back
     live: list[int] = field(default_factory=list)           # pages held, per paged group
@@ -122,6 +123,7 @@ class CacheManager:
             else:
                 raise TypeError(f"cache entry {entries[0]} has an unknown need {need!r}")
         self._requests: dict[Any, RequestCache] = {}
+        self._indices = IndexPool(max_requests, "request number")
 
     # ------------------------------------------------------------------ sizes
 
@@ -159,7 +161,8 @@ class CacheManager:
             if not self.fits_now(reserve_tokens):
                 raise CacheCapacityError(f"{reserve_tokens} tokens do not fit now",
                                          retryable=True)
-        cache = RequestCache(request_id, reserved_tokens=reserve_tokens)
+        cache = RequestCache(request_id, index=self._indices.take(),
+                             reserved_tokens=reserve_tokens)
         for group in self.paged:
             cache.tables.append([])
             cache.live.append(0)
@@ -242,6 +245,7 @@ class CacheManager:
             group.promised -= cache.promised[index]
         for index, group in enumerate(self.states):
             group.pool.give_back(cache.slots[index])
+        self._indices.give_back(cache.index)
 
     def close_all(self) -> None:
         for request_id in list(self._requests):

@@ -280,6 +280,45 @@ __global__ void decode_advance_kernel(const int* __restrict__ chosen, int* __res
     if (blockIdx.x == 0 && threadIdx.x == 0) *counter = step + 1;
 }
 
+// Token ids that the device chose in an earlier step, kept per request so that a later step can
+// take its input from here instead of from the host: published[index of request] = token.
+__global__ void publish_tokens_kernel(const int* __restrict__ chosen, const int* __restrict__ index,
+                                      int* __restrict__ published, int count, int capacity) {
+    griddep_launch();
+    griddep_wait();
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < count && index[i] >= 0 && index[i] < capacity) published[index[i]] = chosen[i];
+}
+
+// token_ids[t] = published[source[t]] wherever source[t] >= 0 (else the host's id stays).
+__global__ void resolve_tokens_kernel(int* __restrict__ token_ids, const int* __restrict__ source,
+                                      const int* __restrict__ published, int count, int capacity) {
+    griddep_launch();
+    griddep_wait();
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < count && source[i] >= 0 && source[i] < capacity) token_ids[i] = published[source[i]];
+}
+
+MLXONE_API int mlxone_publish_tokens(const int* chosen, const int* index, int* published, int count,
+                                     int capacity, cudaStream_t stream) {
+    if (count == 0) return 0;
+    MLXONE_REQUIRE(count > 0 && capacity > 0, "publish_tokens: bad sizes");
+    launch_kernel(publish_tokens_kernel, dim3((count + 255) / 256), dim3(256), 0, stream, true, chosen,
+                  index, published, count, capacity);
+    MLXONE_LAUNCH_CHECK("publish_tokens");
+    return 0;
+}
+
+MLXONE_API int mlxone_resolve_tokens(int* token_ids, const int* source, const int* published,
+                                     int count, int capacity, cudaStream_t stream) {
+    if (count == 0) return 0;
+    MLXONE_REQUIRE(count > 0 && capacity > 0, "resolve_tokens: bad sizes");
+    launch_kernel(resolve_tokens_kernel, dim3((count + 255) / 256), dim3(256), 0, stream, true,
+                  token_ids, source, published, count, capacity);
+    MLXONE_LAUNCH_CHECK("resolve_tokens");
+    return 0;
+}
+
 MLXONE_API int mlxone_decode_advance(const int* chosen, int* token_ids, int* positions,
                                      int* history, int* record, int* counter, int requests,
                                      int max_steps, cudaStream_t stream) {

@@ -22,7 +22,7 @@ from ..sampling.options import GenerationChunk, GenerationResult, TextGeneration
 from ..sampling.sampler import Sampler
 from .loading import LoadedModel, load_model
 from .runner import Runner, StepEntry
-from .scheduler import BatchingConfig, Phase, Request, Scheduler
+from .scheduler import BatchingConfig, Phase, Request, Scheduled, Scheduler
 
 
 @dataclass(frozen=True)
@@ -43,6 +43,17 @@ class CacheConfig:
             value = getattr(self, name)
             if value is not None and value < 1:
                 raise ValueError(f"{name} must be positive")
+
+
+@dataclass
+class _InFlight:
+    """A launched step whose chosen tokens are on their way to the host."""
+
+    planned: list
+    host: Any
+    event: Any
+    draws: int
+    greedy: bool
 
 
 class EngineRequestHandle:
@@ -96,8 +107,10 @@ class Engine:
         self._sampler = Sampler(built.ops, built.runtime.device)
         self._handles: dict[Any, EngineRequestHandle] = {}
         self._tokenizer = self._load_tokenizer()
-        self._stats = {"steps": 0, "tokens_run": 0, "tokens_sampled": 0}
-        self._pinned = None
+        self._stats = {"steps": 0, "steps_ahead": 0, "tokens_run": 0, "tokens_sampled": 0}
+        self._pinned: list[torch.Tensor | None] = [None, None]
+        self._copy_turn = 0
+        self._inflight: _InFlight | None = None
 
     # ------------------------------------------------------------------ set-up
 
@@ -177,21 +190,82 @@ class Engine:
     # ------------------------------------------------------------------ the loop
 
     def step(self) -> list[Request]:
-        """One scheduler turn: plan, run the batch, sample, commit. Returns the requests
-        that got a token or finished."""
+        """One scheduler turn. Returns the requests that got a token or finished.
+
+        A step is planned, launched, its chosen tokens are copied to pinned host memory, and
+        committed when that copy has landed. While every running request decodes greedily
+        (``pipeline_decode``), the next step is launched before the last one is committed: its
+        input tokens are the ones the device has just chosen, so the host's bookkeeping runs
+        under the GPU's work. A request then learns of its end-of-sequence token one step
+        late; the extra token computed for it is dropped."""
+        previous = self._inflight
+        if previous is not None:
+            ahead = self._launch_ahead(previous)
+            touched = self._finish(previous)
+            self._inflight = ahead
+            return touched
         planned = self._scheduler.plan()
         if not planned:
             return []
-        entries = [StepEntry(item.request.request_id, item.tokens,
-                             (len(item.tokens) - 1,) if item.samples else ())
-                   for item in planned]
-        logits = self._runner.step(entries)
-        sampled: list[int] = []
+        launched = self._launch(planned)
+        if self.batching_config.pipeline_decode and launched.greedy:
+            self._inflight = launched
+            return []
+        return self._finish(launched)
+
+    def _launch(self, planned, entries=None) -> "_InFlight":
+        if entries is None:
+            entries = [StepEntry(item.request.request_id, item.tokens,
+                                 (len(item.tokens) - 1,) if item.samples else ())
+                       for item in planned]
         drawing = [item.request for item in planned if item.samples]
+        greedy = bool(drawing) and all(r.options.temperature == 0 for r in drawing)
+        logits = self._runner.step(entries, greedy=greedy)
+        host = event = None
         if drawing:
-            tokens = self._sampler.select(logits, [r.options for r in drawing],
-                                          [len(r.output) for r in drawing])
-            sampled = self._to_host(tokens)
+            tokens = self._runner.last_greedy if greedy else self._sampler.select(
+                logits, [r.options for r in drawing], [len(r.output) for r in drawing])
+            host, event = self._start_copy(tokens)
+        self._stats["steps"] += 1
+        self._stats["tokens_run"] += sum(len(item.tokens) for item in planned)
+        return _InFlight(list(planned), host, event, len(drawing), greedy)
+
+    def _launch_ahead(self, previous: "_InFlight"):
+        """The step after ``previous``, launched before ``previous`` is committed, or None if
+        it cannot be known yet what that step will be."""
+        scheduler = self._scheduler
+        if not (self.batching_config.pipeline_decode and previous.greedy) or scheduler.waiting:
+            return None
+        drew = {id(item.request) for item in previous.planned if item.samples}
+        running = scheduler.running
+        if any(id(r) not in drew or r.cancelled or r.options.stop for r in running):
+            return None          # a prompt still in portions, decodes taking turns, a cancel
+        going_on = [r for r in running if len(r.output) + 1 < r.options.max_tokens]
+        if not going_on or len(going_on) > self.batching_config.max_scheduled_tokens:
+            return None
+        planned = [Scheduled(r, (0,), True) for r in going_on]
+        entries = [StepEntry(r.request_id, (0,), (0,), from_device=True) for r in going_on]
+        self._stats["steps_ahead"] += 1
+        return self._launch(planned, entries)
+
+    def _finish(self, inflight: "_InFlight") -> list[Request]:
+        sampled: list[int] = []
+        if inflight.host is not None:
+            if inflight.event is not None:
+                inflight.event.synchronize()
+            sampled = inflight.host[:inflight.draws].tolist()
+        planned = inflight.planned
+        if any(item.request.phase is Phase.FINISHED for item in planned):
+            # launched ahead for a request that has ended meanwhile: its token is dropped
+            kept, tokens, drawn = [], [], iter(sampled)
+            for item in planned:
+                token = next(drawn) if item.samples else None
+                if item.request.phase is Phase.FINISHED:
+                    continue
+                kept.append(item)
+                if item.samples:
+                    tokens.append(token)
+            planned, sampled = kept, tokens
         touched = self._scheduler.commit(planned, sampled)
         now = time.perf_counter()
         for request in touched:
@@ -202,25 +276,26 @@ class Engine:
                 handle.first_token_at = now
             if request.phase is Phase.FINISHED:
                 handle.finished_at = now
-        self._stats["steps"] += 1
-        self._stats["tokens_run"] += sum(len(item.tokens) for item in planned)
         self._stats["tokens_sampled"] += len(sampled)
         return touched
 
-    def _to_host(self, tokens: torch.Tensor) -> list[int]:
+    def _start_copy(self, tokens: torch.Tensor):
+        """Starts the copy of the chosen tokens to the host; returns (host buffer, event)."""
         if tokens.device.type != "cuda":
-            return tokens.tolist()
-        if self._pinned is None or self._pinned.numel() < tokens.numel():
-            self._pinned = torch.empty(max(tokens.numel(), 256), dtype=torch.int32,
-                                       pin_memory=True)
-        view = self._pinned[:tokens.numel()]
-        view.copy_(tokens, non_blocking=True)
-        torch.cuda.current_stream().synchronize()
-        return view.tolist()
+            return tokens.clone(), None
+        self._copy_turn ^= 1
+        buffer = self._pinned[self._copy_turn]
+        if buffer is None or buffer.numel() < tokens.numel():
+            buffer = torch.empty(max(tokens.numel(), 256), dtype=torch.int32, pin_memory=True)
+            self._pinned[self._copy_turn] = buffer
+        buffer[:tokens.numel()].copy_(tokens, non_blocking=True)
+        event = torch.cuda.Event()
+        event.record()
+        return buffer, event
 
     def run(self) -> None:
         """Drives the loop until no request is waiting or running."""
-        while self._scheduler.has_work():
+        while self._scheduler.has_work() or self._inflight is not None:
             self.step()
 
     # ------------------------------------------------------------------ results
@@ -335,6 +410,9 @@ class Engine:
                 "sampling": ["greedy", "temperature", "top_k", "top_p", "seed"]}
 
     def close(self) -> None:
+        if self._inflight is not None:
+            self._finish(self._inflight)
+            self._inflight = None
         for request in list(self._scheduler.running) + list(self._scheduler.waiting):
             self._scheduler.cancel(request)
         self._scheduler.plan()

@@ -29,6 +29,9 @@ class StepEntry:
     request_id: Any
     tokens: Sequence[int]
     want: Sequence[int] = field(default_factory=tuple)
+    # the (single) token is the one that an earlier greedy step chose for this request and
+    # published on the device; ``tokens`` then only gives the count
+    from_device: bool = False
 
 
 def _align(value: int, to: int = 4) -> int:
@@ -71,6 +74,9 @@ class Runner:
         self.steps = 0
         self.last_shape = (0, 0)
         self.last_meta_bytes = 0
+        self.last_greedy: torch.Tensor | None = None
+        # tokens chosen on the device, by request number (see StepEntry.from_device)
+        self.published = torch.zeros(cache.max_requests, dtype=torch.int32, device=self.device)
         # CUDA graphs of decode-only steps, keyed by (requests, table widths, wanted rows)
         self.use_graphs = self.device.type == "cuda"
         self._graphs: dict[tuple, _DecodeGraph] = {}
@@ -101,8 +107,11 @@ class Runner:
 
     # ------------------------------------------------------------------ the step
 
-    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor | None:
-        return self._step(entries)
+    def step(self, entries: Sequence[StepEntry], greedy: bool = False) -> torch.Tensor | None:
+        """See ``_step``. With ``greedy`` the argmax of every wanted row is computed in the
+        same launch sequence (inside the CUDA graph of a decode-only step) and left in
+        ``last_greedy`` as int32 [wanted] on the device."""
+        return self._step(entries, greedy=greedy)
 
     def decode_steps(self, entries: Sequence[StepEntry], steps: int) -> torch.Tensor:
         """``steps`` greedy decode steps in a row without the host in between: every entry
@@ -122,7 +131,7 @@ class Runner:
         record = torch.zeros((steps, len(entries)), dtype=torch.int32, device=self.device)
         return self._step(entries, loop=(steps, record))
 
-    def _step(self, entries: Sequence[StepEntry], loop=None) -> torch.Tensor | None:
+    def _step(self, entries: Sequence[StepEntry], loop=None, greedy: bool = False):
         """Runs the entries as one batch. Returns float32 logits [wanted, vocab] on the
         device in the order of the entries and of their ``want``, or None if nothing is
         wanted. Raises before touching any state if the batch is malformed or pages run
@@ -139,6 +148,10 @@ class Runner:
             if len(entry.tokens) < 1:
                 raise ValueError(f"request {entry.request_id!r} brings no tokens")
             ids = np.asarray(entry.tokens, dtype=np.int64)
+            if entry.from_device:
+                if len(ids) != 1:
+                    raise ValueError("a token taken from the device is a single token")
+                ids = np.zeros(1, dtype=np.int64)
             if ids.ndim != 1 or ids.min() < 0 or ids.max() >= vocab:
                 raise ValueError(f"request {entry.request_id!r} has a token outside the "
                                  f"vocabulary of {vocab}")
@@ -179,6 +192,8 @@ class Runner:
         region("request_start", requests + 1)
         region("history", requests)
         region("rows", max(wanted, 1))
+        region("token_source", tokens)            # published token to take, or -1
+        region("want_index", max(wanted, 1))       # request number of each wanted row
         for g in range(len(paged)):
             region(f"table{g}", requests * widths[g])
         for g in range(len(states)):
@@ -191,7 +206,9 @@ class Runner:
             start, size = offsets[name]
             data[start:start + size] = values
 
-        starts, history, rows = [0], [], []
+        starts, history, rows, want_index = [0], [], [], []
+        source_at = offsets["token_source"][0]
+        data[source_at:source_at + tokens] = -1
         ids_at = offsets["token_ids"][0]
         positions_at = offsets["positions"][0]
         request_at = offsets["token_request"][0]
@@ -205,6 +222,10 @@ class Runner:
             starts.append(first + n)
             history.append(cache.length)
             rows.extend(first + int(place) for place in entry.want)
+            want_index.extend([cache.index] * len(entry.want))
+            if entry.from_device:
+                data[source_at + first] = cache.index
+        put("want_index", want_index if want_index else [0])
         put("request_start", starts)
         put("history", history)
         put("rows", rows if rows else [0])
@@ -220,7 +241,8 @@ class Runner:
         device = self._device_buffer
         captured = None
         if decode_only:
-            key = (requests, tuple(widths), wanted, loop is not None)
+            key = (requests, tuple(widths), wanted, loop is not None, greedy,
+                   any(e.from_device for e in entries))
             captured = self._graphs.get(key)
             if captured is None:
                 captured = _DecodeGraph(torch.empty(cursor, dtype=torch.int32,
@@ -249,11 +271,20 @@ class Runner:
             views=views,
             host={"history": history, "request_start": starts})
 
+        device_fed = any(e.from_device for e in entries)
+
         def run():
+            if device_fed:
+                self.ops.resolve_tokens(ctx.token_ids, on_device("token_source"), self.published)
             residual, delta = self.model.forward(ctx)
             if not wanted:
                 return None
-            return self.model.logits(residual, delta, on_device("rows")[:wanted])
+            logits = self.model.logits(residual, delta, on_device("rows")[:wanted])
+            if greedy and loop is None:
+                chosen = self.ops.argmax(logits)
+                self.ops.publish_tokens(chosen, on_device("want_index")[:wanted], self.published)
+                return logits, chosen
+            return logits
 
         if loop is not None:
             return self._run_loop(captured, run, ctx, entries, *loop)
@@ -261,6 +292,9 @@ class Runner:
             logits = run()
         else:
             logits = self._run_captured(captured, run)
+        self.last_greedy = None
+        if isinstance(logits, tuple):
+            logits, self.last_greedy = logits
         for entry in entries:
             self.cache.advance(entry.request_id, len(entry.tokens))
         self.steps += 1

@@ -410,6 +410,17 @@ class CudaOps:
                    _c_void_p(_ptr(positions)), _c_void_p(_ptr(history)), _c_void_p(_ptr(record)),
                    _c_void_p(_ptr(counter)), _c_int(chosen.numel()), _c_int(record.shape[0]))
 
+    def publish_tokens(self, chosen, index, published):
+        """published[index[i]] = chosen[i] (all int32 on the device)."""
+        self._call("mlxone_publish_tokens", _c_void_p(_ptr(chosen)), _c_void_p(_ptr(index)),
+                   _c_void_p(_ptr(published)), _c_int(chosen.numel()), _c_int(published.numel()))
+
+    def resolve_tokens(self, token_ids, source, published):
+        """token_ids[t] = published[source[t]] where source[t] >= 0, in place."""
+        self._call("mlxone_resolve_tokens", _c_void_p(_ptr(token_ids)), _c_void_p(_ptr(source)),
+                   _c_void_p(_ptr(published)), _c_int(token_ids.numel()),
+                   _c_int(published.numel()))
+
     def sample(self, logits, temperature, top_k, top_p, seed, step):
         """Per row: temperature (float32, > 0), top_k (int32, <= 0 = off), top_p (float32,
         >= 1 = off), seed (int64), step (int32). Returns (tokens int32, probabilities)."""

@@ -156,6 +156,13 @@ class PlainOps:
             record[step] = chosen
         counter += 1
 
+    def publish_tokens(self, chosen, index, published):
+        published[index.long()] = chosen
+
+    def resolve_tokens(self, token_ids, source, published):
+        taken = source >= 0
+        token_ids[taken] = published[source[taken].long()]
+
     def sample(self, logits, temperature, top_k, top_p, seed, step):
         """Token-order draw over the reference's kept set, in float64."""
         rows, vocab = logits.shape

@@ -128,3 +128,32 @@ def test_end_token_stops_generation(models):
     assert result.finish_reason == "stop" and list(result.token_ids) == expected[:expected.index(expected[2])]
     keep_going = engine.generate_ids(prompt, max_tokens=4, ignore_eos=True)
     assert keep_going.finish_reason == "length" and len(keep_going.token_ids) == 4
+
+
+@pytest.mark.parametrize("pipeline", [True, False])
+def test_pipelined_decode_gives_the_same_tokens(models, pipeline):
+    """Requests of different lengths, one ending on an end-of-sequence token: launching a step
+    before the last one is committed changes nothing but the number of steps run."""
+    import dataclasses
+    folder, loaded, plain = models["B"]
+    requests = prompts(1000, (5, 9, 20), seed=13)
+    lengths = (12, 3, 7)
+    expected = [plain.greedy(p, n) for p, n in zip(requests, lengths)]
+    eos = expected[0][5]                                  # request 0 stops at its sixth token
+    cut = lambda tokens: tokens[:tokens.index(eos)] if eos in tokens else tokens
+    spec = dataclasses.replace(loaded.spec, eos_token_ids=(eos,))
+    engine = Engine(dataclasses.replace(loaded, spec=spec),
+                    cache_config=CacheConfig(block_size_tokens=8, capacity_tokens=512),
+                    batching_config=BatchingConfig(max_sequences=3, prefill_chunk_size=16,
+                                                   max_scheduled_tokens=32,
+                                                   pipeline_decode=pipeline))
+    handles = [engine.submit_ids(p, max_tokens=n) for p, n in zip(requests, lengths)]
+    engine.run()
+    for handle, want in zip(handles, expected):
+        result = handle.result()
+        assert list(result.token_ids) == cut(want)
+        assert result.finish_reason == ("stop" if eos in want else "length")
+    stats = engine.runtime_stats()
+    assert (stats["steps_ahead"] > 0) == pipeline
+    assert stats["running"] == 0 and stats["pages_free"] == stats["pages_total"]
+    engine.cache.check()
