@@ -85,3 +85,25 @@ def test_mixed_batches_with_page_reuse(folders, plain, name, dtype):
         assert_close(got[request_id], plain[name].logits(tokens), dtype,
                      f"{name} mixed request {request_id}")
     assert not cache.requests()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_mid_size_model_with_long_portions(tmp_path, dtype):
+    """Hidden size 512, head size 64, a feed-forward width that is no multiple of 64, and
+    portions of 300+ tokens: the kernels for large steps (tcgen05 products with fused
+    epilogues, the wide conv and q/k kernels, prefill attention over several tiles) run inside
+    the engine, next to decode steps, against the plain implementation."""
+    from tiny_models import ALL_CONFIGS
+    config, _, page = ALL_CONFIGS["MID"]
+    folder = make_model_dir("MID", tmp_path)
+    model = PlainModel(folder)
+    runner, cache = engine(folder, dtype, page, 2048, max_requests=4)
+    a, b = prompts(config["vocab_size"], (700, 330), seed=31)
+    steps = [([("a", a[:384])], []), ([("a", a[384:690]), ("b", b[:300])], [])]
+    steps += [([("a", [t]), ("b", [u])], []) for t, u in zip(a[690:], b[300:310])]
+    steps += [([("b", b[310:])], ["a", "b"])]
+    got = replay(runner, cache, steps)
+    if dtype == torch.bfloat16:
+        assert runner.ops.tcgen05_products
+    assert_close(got["a"], model.logits(a), dtype, "mid a")
+    assert_close(got["b"], model.logits(b), dtype, "mid b")

@@ -37,7 +37,17 @@ TINY_C = dict(
     block_ffn_dim_multiplier=1.3, vocab_size=777, rope_theta=50000.0, sliding_window=19,
     conv_L_cache=2, conv_bias=False, tie_embedding=True, norm_eps=3e-6)
 
+# a size at which the kernels for large steps (tcgen05 products, wide conv and q/k kernels) run
+MID = dict(
+    model_type="lfm2", num_hidden_layers=5,
+    layer_types=["conv", "full_attention", "conv", "sliding_attention", "full_attention"],
+    hidden_size=512, num_attention_heads=8, num_key_value_heads=2,
+    block_auto_adjust_ff_dim=True, block_ff_dim=2000, block_multiple_of=8,
+    vocab_size=3001, rope_theta=1000000.0, sliding_window=150, conv_L_cache=3, conv_bias=False,
+    tie_embedding=True, norm_eps=1e-5)
+
 CONFIGS = {"A": (TINY_A, 0, 4), "B": (TINY_B, 1, 8), "C": (TINY_C, 2, 16)}   # config, seed, page
+ALL_CONFIGS = {**CONFIGS, "MID": (MID, 3, 16)}
 
 # (atol, rtol) on logits: |engine - plain| <= atol + rtol * |plain|, as the reference gates
 # its own parity runs (src/mlx_one/inference_baseline.py:30).
@@ -48,7 +58,7 @@ def make_model_dir(name: str, root: Path | None = None, dtype=torch.bfloat16) ->
     """Writes the tiny model ``name`` into a fresh temporary folder (never into the repo)."""
     from mlx_one_b200.weights import write_random_model
 
-    config, seed, _ = CONFIGS[name]
+    config, seed, _ = ALL_CONFIGS[name]
     folder = Path(tempfile.mkdtemp(prefix=f"tiny_{name}_", dir=root))
     return write_random_model(folder, config, seed, dtype)
 
