@@ -135,6 +135,60 @@ __global__ void add_rmsnorm_rows_kernel(float* __restrict__ residual, const T* _
     }
 }
 
+// Many rows (prefill): one warp per row, the whole row in registers (hidden <= 128 * VEC * ... ),
+// all of a lane's loads in flight together and no block-wide barrier.
+template <typename T, int VEC>
+__global__ void __launch_bounds__(256)
+add_rmsnorm_warp_kernel(float* __restrict__ residual, const T* __restrict__ delta,
+                        const float* __restrict__ weight, T* __restrict__ out, int rows,
+                        int hidden, float eps) {
+    griddep_launch();
+    griddep_wait();
+    const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (row >= rows) return;
+    const size_t base = (size_t)row * hidden;
+    float values[VEC][4];
+    float sum = 0.f;
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) {
+        const int c = (j * 32 + lane) * 4;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) values[j][i] = 0.f;
+        if (c < hidden) Vec4<float>::load(residual + base + c, values[j]);
+    }
+    if (delta != nullptr) {
+#pragma unroll
+        for (int j = 0; j < VEC; ++j) {
+            const int c = (j * 32 + lane) * 4;
+            if (c < hidden) {
+                float more[4];
+                Vec4<T>::load(delta + base + c, more);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) values[j][i] += more[i];
+                Vec4<float>::store(residual + base + c, values[j]);
+            }
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < VEC; ++j)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) sum += values[j][i] * values[j][i];
+    sum = warp_sum(sum);
+    const float inv = rsqrtf(sum / (float)hidden + eps);
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) {
+        const int c = (j * 32 + lane) * 4;
+        if (c < hidden) {
+            float scale[4], result[4];
+            Vec4<float>::load(weight + c, scale);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) result[i] = values[j][i] * inv * scale[i];
+            Vec4<T>::store(out + base + c, result);
+        }
+    }
+}
+
 template <typename T>
 static cudaError_t launch_add_rmsnorm(float* residual, const void* delta, const float* weight,
                                       void* out, int rows, int hidden, float eps,
@@ -143,6 +197,17 @@ static cudaError_t launch_add_rmsnorm(float* residual, const void* delta, const 
                          (reinterpret_cast<uintptr_t>(weight) & 15) == 0 &&
                          (reinterpret_cast<uintptr_t>(out) & 7) == 0 &&
                          (reinterpret_cast<uintptr_t>(delta) & 7) == 0;
+    if (aligned && rows >= 64 && hidden <= 2048) {
+        const dim3 grid((rows + 7) / 8);
+        if (hidden <= 512)
+            return launch_kernel(add_rmsnorm_warp_kernel<T, 4>, grid, dim3(256), 0, stream, true,
+                                 residual, (const T*)delta, weight, (T*)out, rows, hidden, eps);
+        if (hidden <= 1024)
+            return launch_kernel(add_rmsnorm_warp_kernel<T, 8>, grid, dim3(256), 0, stream, true,
+                                 residual, (const T*)delta, weight, (T*)out, rows, hidden, eps);
+        return launch_kernel(add_rmsnorm_warp_kernel<T, 16>, grid, dim3(256), 0, stream, true,
+                             residual, (const T*)delta, weight, (T*)out, rows, hidden, eps);
+    }
     if (aligned && hidden <= 8192) {
         const int quads = hidden / 4;
         const int passes = quads <= 1024 ? 1 : 2;

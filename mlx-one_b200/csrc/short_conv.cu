@@ -48,6 +48,7 @@ __global__ void short_conv_kernel(const T* __restrict__ bcx, const float* __rest
 
 // The same for bfloat16 with hidden % 8 == 0: a thread takes 8 neighbouring channels of one token
 // with 16-byte loads.
+template <int TAPS>
 __global__ void short_conv_wide_kernel(const __nv_bfloat16* __restrict__ bcx,
                                        const float* __restrict__ kernel,
                                        const float* __restrict__ bias,
@@ -56,9 +57,9 @@ __global__ void short_conv_wide_kernel(const __nv_bfloat16* __restrict__ bcx,
                                        const int* __restrict__ token_request,
                                        const int* __restrict__ request_start,
                                        const int* __restrict__ history,
-                                       __nv_bfloat16* __restrict__ out, int tokens, int hidden,
-                                       int taps) {
+                                       __nv_bfloat16* __restrict__ out, int tokens, int hidden) {
     using T = __nv_bfloat16;
+    constexpr int taps = TAPS;
     griddep_launch();
     griddep_wait();
     const int groups = hidden / 8;
@@ -78,7 +79,19 @@ __global__ void short_conv_wide_kernel(const __nv_bfloat16* __restrict__ bcx,
     float y[8];
 #pragma unroll
     for (int i = 0; i < 8; ++i) y[i] = bias ? bias[d + i] : 0.f;
-    for (int k = 0; k < taps; ++k) {
+    // this thread's 8 * taps kernel weights lie together in memory
+    float weights[8 * TAPS];
+    {
+        const float4* src = reinterpret_cast<const float4*>(kernel + (size_t)d * taps);
+#pragma unroll
+        for (int j = 0; j < 2 * TAPS; ++j) {
+            const float4 v = src[j];
+            weights[4 * j] = v.x; weights[4 * j + 1] = v.y;
+            weights[4 * j + 2] = v.z; weights[4 * j + 3] = v.w;
+        }
+    }
+#pragma unroll
+    for (int k = 0; k < TAPS; ++k) {
         const int back = taps - 1 - k;
         float g[8];
         if (index - back >= 0) {
@@ -97,7 +110,7 @@ __global__ void short_conv_wide_kernel(const __nv_bfloat16* __restrict__ bcx,
             for (int i = 0; i < 8; ++i) g[i] = 0.f;
         }
 #pragma unroll
-        for (int i = 0; i < 8; ++i) y[i] = fmaf(kernel[(size_t)(d + i) * taps + k], g[i], y[i]);
+        for (int i = 0; i < 8; ++i) y[i] = fmaf(weights[i * taps + k], g[i], y[i]);
     }
     float c[8];
     unpack(*reinterpret_cast<const uint4*>(bcx + (size_t)t * row + hidden + d), c);
@@ -214,14 +227,22 @@ MLXONE_API int mlxone_short_conv(const void* bcx, const float* kernel, const flo
     MLXONE_REQUIRE(requests <= 65535, "short_conv: at most 65535 requests a step");
     if (dtype == MLXONE_BF16) {
         using T = __nv_bfloat16;
-        const bool wide = hidden % 8 == 0 && (reinterpret_cast<uintptr_t>(bcx) & 15) == 0 &&
+        const bool wide = hidden % 8 == 0 && taps <= 4 &&
+                          (reinterpret_cast<uintptr_t>(kernel) & 15) == 0 &&
+                          (reinterpret_cast<uintptr_t>(bcx) & 15) == 0 &&
                           (reinterpret_cast<uintptr_t>(state) & 15) == 0 &&
                           (reinterpret_cast<uintptr_t>(out) & 15) == 0;
         if (wide) {
             const long long items = (long long)tokens * (hidden / 8);
-            launch_kernel(short_conv_wide_kernel, dim3(ceil_div_host(items, 256)), dim3(256), 0,
-                          stream, true, (const T*)bcx, kernel, bias, (const T*)state, slots,
-                          token_request, request_start, history, (T*)out, tokens, hidden, taps);
+#define WIDE(TAPS)                                                                              \
+    launch_kernel(short_conv_wide_kernel<TAPS>, dim3(ceil_div_host(items, 256)), dim3(256), 0,  \
+                  stream, true, (const T*)bcx, kernel, bias, (const T*)state, slots,            \
+                  token_request, request_start, history, (T*)out, tokens, hidden)
+            if (taps == 1) WIDE(1);
+            else if (taps == 2) WIDE(2);
+            else if (taps == 3) WIDE(3);
+            else WIDE(4);
+#undef WIDE
         } else
         launch_kernel(short_conv_kernel<T>, grid, dim3(threads), 0, stream, true, (const T*)bcx, kernel, bias, (const T*)state, slots, token_request, request_start,
             history, (T*)out, tokens, hidden, taps);
