@@ -413,6 +413,73 @@ def kernel_case(name: str, batch: int, context: int) -> int:
     return 0
 
 
+def product_fractions(model, batch, peak):
+    """The matrix products of the step alone, as the baseline's targets are stated for them:
+    decode products against HBM bandwidth (bytes of weights / time), prefill products against
+    the bf16 tensor peak. Each distinct product of the model is timed in a CUDA graph of
+    back-to-back calls on several copies of its weights (so that none is found in L2)."""
+    import torch
+
+    ops, device = model.ops, "cuda:0"
+
+    def graph_time(fn, copies, inner):
+        for i in range(min(copies, 3)):
+            fn(i)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for i in range(inner):
+                fn(i % copies)
+        graph.replay()
+        torch.cuda.synchronize()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for _ in range(5):
+            graph.replay()
+        stop.record()
+        torch.cuda.synchronize()
+        return start.elapsed_time(stop) / 1e3 / (5 * inner)
+
+    # (weight, kind, how many times a step runs it); kind picks the epilogue the engine uses
+    seen: dict = {}
+    for block in model.layers:
+        mixer, ffn = block.mixer, block.feed_forward
+        first = getattr(mixer, "qkv", None)
+        first = first if first is not None else mixer.in_proj
+        last = getattr(mixer, "out", None)
+        last = last if last is not None else mixer.out_proj
+        for weight, kind in ((first, "plain"), (last, "add"), (ffn.gate_up, "swiglu"),
+                             (ffn.down, "add")):
+            key = (tuple(weight.shape), kind)
+            seen.setdefault(key, [weight, 0])[1] += 1
+    decode_bytes = decode_seconds = prefill_flops = prefill_seconds = 0.0
+    for (shape, kind), (weight, count) in seen.items():
+        n, k = shape
+        copies = max(2, min(16, int(300e6 // (n * k * 2))))
+        weights = [weight] + [torch.randn_like(weight) * 0.02 for _ in range(copies - 1)]
+        for rows in (batch, PREFILL_TOKENS):
+            a = torch.randn(rows, k, device=device).bfloat16()
+            residual = torch.zeros(rows, n, device=device)
+            if kind == "plain":
+                fn = lambda i: ops.linear(a, weights[i])
+            elif kind == "swiglu":
+                fn = lambda i: ops.linear_swiglu(a, weights[i])
+            else:
+                fn = lambda i: ops.linear_add(a, weights[i], None, residual)
+            seconds = graph_time(fn, copies, copies * (2 if rows == batch else 1))
+            if rows == batch:
+                decode_bytes += count * n * k * 2
+                decode_seconds += count * seconds
+            else:
+                prefill_flops += count * 2.0 * rows * n * k
+                prefill_seconds += count * seconds
+        del weights
+    return {"decode_products_gbs": round(decode_bytes / decode_seconds / 1e9, 1),
+            "decode_products_hbm_frac": round(decode_bytes / decode_seconds / 1e9 / peak["hbm_gbs"], 4),
+            "prefill_products_tflops": round(prefill_flops / prefill_seconds / 1e12, 1),
+            "prefill_products_frac": round(prefill_flops / prefill_seconds / 1e12 / peak["bf16_tflops"], 4)}
+
+
 def main() -> int:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
@@ -470,6 +537,7 @@ def main() -> int:
 
     prefill_seconds = time_prefill(engine, PREFILL_TOKENS, 2, 3, seed=11)
     flops = model_flops(spec, PREFILL_TOKENS)
+    products = None if args.skip_points else product_fractions(model, args.batch, peak)
 
     line = {
         "metric": "decode tok/s at batch 8 (LFM2-1.2B shape, bf16, context 4096)",
@@ -503,6 +571,7 @@ def main() -> int:
                      "unit": "GB/s", "frac": round(achieved / peak["hbm_gbs"], 4),
                      "bytes_per_step": int(step_bytes)},
         "points": points,
+        "products": products,
         "clocks": clocks,
     }
     print(json.dumps(line))
