@@ -63,6 +63,8 @@ class CudaOps:
         # the next product's weight prefetch and is faster, so this is off by default
         self.fused_norms = False
         self.tcgen05_min_rows = 128
+        self.tcgen05_always = False       # tests: take the tcgen05 kernel whenever it can run
+        self._sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
         # tcgen05 products (TMA + tensor memory) for more rows than the skinny kernel takes
         self.tcgen05_products = bool(self.lib.mlxone_gemm_tcgen05_available())
         self._skinny_rows = self.lib.mlxone_gemm_skinny_max_rows()
@@ -164,12 +166,29 @@ class CudaOps:
         self.tcgen05_products = bool(enabled) and bool(self.lib.mlxone_gemm_tcgen05_available())
         return self.tcgen05_products
 
-    def _tcgen05(self, a, w) -> bool:
-        # its tiles are 128 rows high; with fewer rows the library product does better
-        return (self.tcgen05_products and a.dtype == torch.bfloat16
+    def _tcgen05(self, a, w, epilogue=0) -> bool:
+        """Whether a[M, K] @ w[N, K]^T goes to the tcgen05 kernel. It needs 16-byte aligned
+        rows and at least 128 rows (its tiles are 128 x 256 and each persistent block walks
+        whole tiles), and it is chosen where it is at least about as fast as the library:
+        when its tiles fill the SMs evenly; a fused SwiGLU epilogue (which saves a pass over
+        the widest activation) is worth more unevenness; products with a long K and few
+        columns, which the library splits along K, stay with the library."""
+        if not (self.tcgen05_products and a.dtype == torch.bfloat16
                 and a.shape[0] >= self.tcgen05_min_rows
                 and a.shape[1] % 8 == 0 and a.stride(0) % 8 == 0 and a.stride(1) == 1
-                and w.is_contiguous() and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+                and w.is_contiguous() and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0):
+            return False
+        if self.tcgen05_always:
+            return True
+        columns = w.shape[0] // 2 if epilogue == self._SWIGLU else w.shape[0]
+        wide = 128 if epilogue == self._SWIGLU else 256
+        tiles = -(-a.shape[0] // 128) * -(-columns // wide)
+        evenness = tiles / (-(-tiles // self._sm_count) * self._sm_count)
+        if epilogue == self._SWIGLU:
+            return evenness >= 0.6
+        if epilogue == self._ADD and a.shape[1] > 4096:
+            return False
+        return evenness >= 0.85
 
     def _tcgen05_call(self, a, w, bias, out, ldo, epilogue) -> None:
         self._call("mlxone_gemm_tcgen05", _c_void_p(_ptr(a)), _c_int(a.stride(0)),
@@ -231,7 +250,7 @@ class CudaOps:
             self._skinny_call(a, w, bias, out, n,
                               self._STORE_F32 if out_dtype == torch.float32 else self._STORE)
             return out
-        if self._tcgen05(a, w):
+        if self._tcgen05(a, w, self._STORE):
             out = torch.empty((m, n), dtype=out_dtype, device=self.device)
             self._tcgen05_call(a, w, bias, out, n,
                                self._STORE_F32 if out_dtype == torch.float32 else self._STORE)
@@ -259,7 +278,7 @@ class CudaOps:
             out = torch.empty((a.shape[0], width), dtype=a.dtype, device=self.device)
             self._skinny_call(a, gate_up, None, out, width, self._SWIGLU)
             return out
-        if self._tcgen05(a, gate_up):
+        if self._tcgen05(a, gate_up, self._SWIGLU):
             width = gate_up.shape[0] // 2
             out = torch.empty((a.shape[0], width), dtype=a.dtype, device=self.device)
             self._tcgen05_call(a, gate_up, None, out, width, self._SWIGLU)
@@ -275,7 +294,7 @@ class CudaOps:
             self._need(residual, torch.float32, "residual")
             self._skinny_call(a, w, bias, residual, residual.shape[1], self._ADD)
             return None
-        if self._tcgen05(a, w):
+        if self._tcgen05(a, w, self._ADD):
             self._need(residual, torch.float32, "residual")
             self._tcgen05_call(a, w, bias, residual, residual.shape[1], self._ADD)
             return None

@@ -98,11 +98,15 @@ def test_mid_size_model_with_long_portions(tmp_path, dtype):
     folder = make_model_dir("MID", tmp_path)
     model = PlainModel(folder)
     runner, cache = engine(folder, dtype, page, 2048, max_requests=4)
+    runner.ops.tcgen05_always = True       # every product that can, also where the library is faster
     a, b = prompts(config["vocab_size"], (700, 330), seed=31)
     steps = [([("a", a[:384])], []), ([("a", a[384:690]), ("b", b[:300])], [])]
     steps += [([("a", [t]), ("b", [u])], []) for t, u in zip(a[690:], b[300:310])]
     steps += [([("b", b[310:])], ["a", "b"])]
-    got = replay(runner, cache, steps)
+    try:
+        got = replay(runner, cache, steps)
+    finally:
+        runner.ops.tcgen05_always = False
     if dtype == torch.bfloat16:
         assert runner.ops.tcgen05_products
     assert_close(got["a"], model.logits(a), dtype, "mid a")

@@ -177,6 +177,7 @@ def test_tcgen05_product(ops, m, n, k):
     """The tensor-memory product for many rows: all four epilogues, ragged edges in M, N, K."""
     assert ops.enable_tcgen05(True)
     least, ops.tcgen05_min_rows = ops.tcgen05_min_rows, 1
+    ops.tcgen05_always = True
     try:
         torch.manual_seed(m + n + k)
         a = torch.randn(m, k).bfloat16()
@@ -201,6 +202,7 @@ def test_tcgen05_product(ops, m, n, k):
     finally:
         ops.enable_tcgen05(True)
         ops.tcgen05_min_rows = least
+        ops.tcgen05_always = False
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
