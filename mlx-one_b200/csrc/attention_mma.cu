@@ -386,14 +386,18 @@ __device__ __forceinline__ uint32_t transpose_8x8(uint32_t v) {
     return out;
 }
 
-constexpr int DECODE_WARPS = 8;
+constexpr int DECODE_WARPS = 2;
+constexpr int DECODE_STAGES = 3;     // tiles a warp keeps in flight or in use
 constexpr int DECODE_HEADS = 8;      // query heads per block (the 8-column operand)
 
 // One block = one (request, key head, group of up to 8 query heads, split of the keys).
 // Keys are the 16-row operand of the first product (scores^T = K q^T), so no tensor-core row
 // is wasted on padding; the probabilities are transposed in registers (movmatrix) and become
-// the 8-column operand of the second product (out^T = V^T p^T). Each of the 8 warps takes
-// tiles of 32 keys in turn through a buffer of its own; the warps are merged in shared memory.
+// the 8-column operand of the second product (out^T = V^T p^T). Each warp takes tiles of 32
+// keys in turn through a ring of its own, which keeps DECODE_STAGES - 1 tiles on their way while
+// one is multiplied: the step is bound by the latency of memory unless enough is in flight, and
+// small blocks (few warps, many blocks per SM) spread the work evenly. The warps are merged in
+// shared memory.
 // partial results: [token, head, split] -> HD floats of unnormalised output, then max and sum
 template <int HD>
 __global__ void __launch_bounds__(DECODE_WARPS * 32)
@@ -428,13 +432,18 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kv,
     Pages pages{kv, kv + kv_half, block_table + (size_t)request * table_width, table_width,
                 page_size, kv_heads, kv_head,
                 (page_size & (page_size - 1)) == 0 ? 31 - __clz(page_size) : -1};
-    bf16* k_tile = reinterpret_cast<bf16*>(shared_bytes) + (size_t)warp * 2 * KEYS * T::STRIDE;
-    bf16* v_tile = k_tile + KEYS * T::STRIDE;
+    constexpr int STAGE = 2 * KEYS * T::STRIDE;          // elements of a K and a V tile
+    bf16* ring = reinterpret_cast<bf16*>(shared_bytes) + (size_t)warp * DECODE_STAGES * STAGE;
 
     int tile = my_first + warp;
-    if (tile <= my_last)
-        load_tile<HD, KEYS>(k_tile, v_tile, pages, tile * KEYS, lowest, position, lane, 32);
-    copy_commit();
+#pragma unroll
+    for (int ahead = 0; ahead < DECODE_STAGES - 1; ++ahead) {
+        const int coming = tile + ahead * DECODE_WARPS;
+        if (coming <= my_last)
+            load_tile<HD, KEYS>(ring + ahead * STAGE, ring + ahead * STAGE + KEYS * T::STRIDE, pages,
+                                coming * KEYS, lowest, position, lane, 32);
+        copy_commit();
+    }
 
     // q^T as the 8-column operand: head g, dims 16 kk + 2t (+1) and + 8
     uint32_t qb[HD / 16][2];
@@ -456,9 +465,19 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kv,
         for (int c = 0; c < 4; ++c) o[d][c] = 0.f;
     const int matrix = lane >> 3, r = lane & 7;
 
-    for (; tile <= my_last; tile += DECODE_WARPS) {
-        copy_wait<0>();
-        __syncwarp();
+    for (int stage = 0; tile <= my_last; tile += DECODE_WARPS, stage = (stage + 1) % DECODE_STAGES) {
+        copy_wait<DECODE_STAGES - 2>();
+        __syncwarp();            // the tile has landed, and every lane is done with the one before
+        {
+            const int coming = tile + (DECODE_STAGES - 1) * DECODE_WARPS;
+            const int into = (stage + DECODE_STAGES - 1) % DECODE_STAGES;
+            if (coming <= my_last)
+                load_tile<HD, KEYS>(ring + into * STAGE, ring + into * STAGE + KEYS * T::STRIDE,
+                                    pages, coming * KEYS, lowest, position, lane, 32);
+            copy_commit();
+        }
+        const bf16* k_tile = ring + stage * STAGE;
+        const bf16* v_tile = k_tile + KEYS * T::STRIDE;
         const int first = tile * KEYS;
         float s[KEYS / 16][4];
 #pragma unroll
@@ -518,12 +537,6 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kv,
                 mma_16816(o[d], a, pt[mt][0], pt[mt][1]);
             }
         }
-        __syncwarp();
-        if (tile + DECODE_WARPS <= my_last) {
-            load_tile<HD, KEYS>(k_tile, v_tile, pages, (tile + DECODE_WARPS) * KEYS, lowest,
-                                position, lane, 32);
-            copy_commit();
-        }
     }
     copy_wait<0>();
 #pragma unroll
@@ -578,11 +591,14 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kv,
     }
 }
 
-// Merges the splits of one (token, head): one warp each.
+// Merges the splits of one (token, head): one warp each. The lanes take the splits' maxima and
+// sums side by side, and the loads of the weighted sum are independent of one another, so that
+// the kernel costs a few trips to L2 and not one per split.
 template <int HD>
 __global__ void attention_merge_kernel(const float* __restrict__ partial, bf16* __restrict__ out,
                                        int items, int splits) {
     constexpr int ROW_FLOATS = HD + 2;
+    constexpr int MINE = (HD + 31) / 32;
     griddep_launch();
     griddep_wait();
     const int item = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -590,24 +606,36 @@ __global__ void attention_merge_kernel(const float* __restrict__ partial, bf16* 
     if (item >= items) return;
     const float* base = partial + (size_t)item * splits * ROW_FLOATS;
     float top = -INFINITY;
-    for (int s = 0; s < splits; ++s) top = fmaxf(top, base[(size_t)s * ROW_FLOATS + HD]);
+    for (int s = lane; s < splits; s += 32) top = fmaxf(top, base[(size_t)s * ROW_FLOATS + HD]);
+    top = warp_max(top);
     float sum = 0.f;
-    float value[(HD + 31) / 32];
+    float value[MINE];
 #pragma unroll
-    for (int i = 0; i < (HD + 31) / 32; ++i) value[i] = 0.f;
-    for (int s = 0; s < splits; ++s) {
-        const float* src = base + (size_t)s * ROW_FLOATS;
-        const float weight = src[HD] == -INFINITY ? 0.f : fast_exp2(src[HD] - top);
-        sum += src[HD + 1] * weight;
+    for (int i = 0; i < MINE; ++i) value[i] = 0.f;
+    for (int s0 = 0; s0 < splits; s0 += 32) {
+        // lane j holds the weight of split s0 + j
+        float weight = 0.f;
+        if (s0 + lane < splits) {
+            const float* src = base + (size_t)(s0 + lane) * ROW_FLOATS;
+            weight = src[HD] == -INFINITY ? 0.f : fast_exp2(src[HD] - top);
+            sum += src[HD + 1] * weight;
+        }
+        const int count = min(32, splits - s0);
+#pragma unroll 8
+        for (int j = 0; j < count; ++j) {
+            const float w = __shfl_sync(0xffffffffu, weight, j);
+            const float* src = base + (size_t)(s0 + j) * ROW_FLOATS;
 #pragma unroll
-        for (int i = 0; i < (HD + 31) / 32; ++i) {
-            const int d = lane + 32 * i;
-            if (d < HD) value[i] += src[d] * weight;
+            for (int i = 0; i < MINE; ++i) {
+                const int d = lane + 32 * i;
+                if (d < HD) value[i] = fmaf(src[d], w, value[i]);
+            }
         }
     }
+    sum = warp_sum(sum);
     const float inv = sum > 0.f ? 1.f / sum : 0.f;
 #pragma unroll
-    for (int i = 0; i < (HD + 31) / 32; ++i) {
+    for (int i = 0; i < MINE; ++i) {
         const int d = lane + 32 * i;
         if (d < HD) out[(size_t)item * HD + d] = __float2bfloat16_rn(value[i] * inv);
     }
@@ -630,15 +658,19 @@ int launch_prefill(const void* q, const void* kv, long long kv_half, const int* 
     return 0;
 }
 
+size_t decode_shared_bytes(int head_dim) {
+    const size_t tiles = (size_t)DECODE_WARPS * DECODE_STAGES * 2 * DECODE_KEYS * (head_dim + 8) * 2;
+    const size_t merge = (size_t)DECODE_WARPS * DECODE_HEADS * (head_dim + 2) * 4;
+    return tiles > merge ? tiles : merge;
+}
+
 template <int HD>
 int launch_decode(const void* q, const void* kv, long long kv_half, const int* block_table,
                   int table_width, int page_size, const int* positions, void* out, float* partial,
                   int requests, int heads, int kv_heads, int splits, float scale, int window,
                   cudaStream_t stream) {
     using T = Tile<HD>;
-    const size_t tiles = (size_t)DECODE_WARPS * 2 * DECODE_KEYS * T::STRIDE * 2;
-    const size_t merge = (size_t)DECODE_WARPS * DECODE_HEADS * (HD + 2) * 4;
-    const size_t shared = tiles > merge ? tiles : merge;
+    const size_t shared = decode_shared_bytes(HD);
     auto kernel = attention_decode_kernel<HD>;
     if (shared > 48 * 1024)
         cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
@@ -656,6 +688,17 @@ int launch_decode(const void* q, const void* kv, long long kv_half, const int* b
 }
 
 }  // namespace
+
+// How many blocks of the decode kernel an SM holds at once (shared memory and warps), which is
+// what the caller sizes the number of key splits by.
+MLXONE_API int mlxone_attention_decode_resident(int head_dim) {
+    const size_t each = decode_shared_bytes(head_dim) + 1024;
+    int blocks = (int)((227 * 1024) / each);
+    const int by_warps = 64 / DECODE_WARPS;
+    if (blocks > by_warps) blocks = by_warps;
+    if (blocks > 32) blocks = 32;
+    return blocks < 1 ? 1 : blocks;
+}
 
 #define MLXONE_HEAD_DIMS(CALL)                                                       \
     switch (head_dim) {                                                              \

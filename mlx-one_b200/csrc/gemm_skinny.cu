@@ -2,9 +2,11 @@
 // bfloat16 operands, 32-bit accumulation. Such a product takes as long as reading w once
 // takes, so the kernel is built around streaming w without a pause:
 //
-//   * persistent blocks, one per SM; a block owns a contiguous range of 16-row tiles of w (16
-//     outputs for every token) over the whole K, so no two blocks add into the same output
-//     and results do not depend on scheduling;
+//   * persistent blocks, one per SM; a block owns a contiguous range of rows of w (outputs for
+//     every token) over the whole K, so no two blocks add into the same output and results do
+//     not depend on scheduling. The ranges are equal to within one row, whatever n is, so all
+//     SMs stream for the same time; a block walks its range in tiles of 16 rows, the last of
+//     which may be partly masked (masked rows are neither read nor written);
 //   * the block's warps take the 64-wide slices of K of the current tile in turn; every warp
 //     copies its slices of w asynchronously through a ring of its own in shared memory, and the
 //     ring runs on into the next tile, so the stream never drains inside the kernel;
@@ -74,7 +76,7 @@ template <int NT, int EPILOGUE, bool RESIDENT, bool NORM>
 __global__ void __launch_bounds__(WARPS * 32)
 skinny_gemm_kernel(const bf16* a, int lda, const bf16* __restrict__ w,
                    const float* __restrict__ bias, void* out, int ldo, int m, int n, int k,
-                   int up_offset, int tiles, const float* source, int source_ld,
+                   int up_offset, const float* source, int source_ld,
                    const float* __restrict__ norm_weight, float eps) {
     // A SwiGLU block splits its warps in two halves: the first on 16 gate rows, the second on
     // the 16 matching up rows (measured faster than tiles of 8 + 8 rows, which balance better
@@ -96,13 +98,14 @@ skinny_gemm_kernel(const bf16* a, int lda, const bf16* __restrict__ w,
     float* sums_base = reinterpret_cast<float*>(shared_bytes + (size_t)WARPS * STAGES * SLOT_BYTES);
     unsigned char* resident = reinterpret_cast<unsigned char*>(sums_base + 2 * WARPS * ROWS * TOKENS);
 
-    // this block's tiles
-    const int tile_begin = (int)((long long)tiles * blockIdx.x / gridDim.x);
-    const int tile_end = (int)((long long)tiles * (blockIdx.x + 1) / gridDim.x);
-    const int row_limit = half == 0 ? (EPILOGUE == SWIGLU ? up_offset : n) : n;
+    // this block's rows (of the gate half for SwiGLU) and the tiles that cover them
+    const int columns = EPILOGUE == SWIGLU ? up_offset : n;
+    const int row_begin = (int)((long long)columns * blockIdx.x / gridDim.x);
+    const int row_end = (int)((long long)columns * (blockIdx.x + 1) / gridDim.x);
+    const int tile_count = (row_end - row_begin + ROWS - 1) / ROWS;
     const int slices = (k + SLICE - 1) / SLICE;
     const int mine = slices > wk ? (slices - wk + WARPS_K - 1) / WARPS_K : 0;   // per tile
-    const int total = mine * (tile_end - tile_begin);     // this warp's slices over all tiles
+    const int total = mine * tile_count;                  // this warp's slices over all tiles
 
     // Copies the next slice of this warp's stream into its ring: 16 rows x 8 pieces of 16 B;
     // piece c of row r is stored at piece c ^ ((r & 1) << 2), which keeps the 16-byte reads of a
@@ -120,15 +123,15 @@ skinny_gemm_kernel(const bf16* a, int lda, const bf16* __restrict__ w,
         piece_dst[i] = ring_address + r * 128 + ((c ^ ((r & 1) << 2)) << 4);
         piece_src[i] = (size_t)r * k + c * 8;
     }
-    int fetch_tile = tile_begin, fetch_slice = 0, fetched = 0;
+    int fetch_tile = 0, fetch_slice = 0, fetched = 0;
     auto fetch = [&]() {
         const int k0 = (wk + fetch_slice * WARPS_K) * SLICE;
         const uint32_t buffer = (fetched & (STAGES - 1)) * SLOT_BYTES;
-        const int row0 = fetch_tile * ROWS + half * up_offset;
-        const bf16* base = w + (size_t)row0 * k + k0;
+        const int row0 = row_begin + fetch_tile * ROWS;
+        const bf16* base = w + (size_t)(row0 + half * up_offset) * k + k0;
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-            const bool live = row0 + piece_row[i] < row_limit && k0 + piece_k[i] < k;
+            const bool live = row0 + piece_row[i] < row_end && k0 + piece_k[i] < k;
             copy16(piece_dst[i] + buffer, live ? base + piece_src[i] : w, live);
         }
         ++fetched;
@@ -289,7 +292,7 @@ skinny_gemm_kernel(const bf16* a, int lda, const bf16* __restrict__ w,
     int next_slice = mine > 1 ? 1 : 0;       // the slice (within a tile) whose tokens are fetched next
 
     int index = 0;
-    for (int tile = tile_begin; tile < tile_end; ++tile) {
+    for (int tile = 0; tile < tile_count; ++tile) {
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
@@ -339,7 +342,7 @@ skinny_gemm_kernel(const bf16* a, int lda, const bf16* __restrict__ w,
         }
 
         // partial sums of this tile: [warp][row 0..15][token]
-        float* sums = sums_base + (size_t)((tile - tile_begin) & 1) * WARPS * ROWS * TOKENS;
+        float* sums = sums_base + (size_t)(tile & 1) * WARPS * ROWS * TOKENS;
         float* mine_sums = sums + (size_t)warp * ROWS * TOKENS;
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
@@ -351,8 +354,8 @@ skinny_gemm_kernel(const bf16* a, int lda, const bf16* __restrict__ w,
         __syncthreads();
         for (int item = threadIdx.x; item < ROWS * TOKENS; item += WARPS * 32) {
             const int token = item / ROWS, r = item % ROWS;     // rows fastest: neighbours in memory
-            const int column = tile * ROWS + r;
-            if (token >= m || column >= (EPILOGUE == SWIGLU ? up_offset : n)) continue;
+            const int column = row_begin + tile * ROWS + r;
+            if (token >= m || column >= row_end) continue;
             float value = 0.f;
 #pragma unroll
             for (int wi = 0; wi < WARPS_K; ++wi)
@@ -400,14 +403,15 @@ cudaError_t launch(const void* a, int lda, const void* w, const float* bias, voi
         cudaDeviceGetAttribute(&g_sm_count, cudaDevAttrMultiProcessorCount, device);
         if (g_sm_count <= 0) g_sm_count = 148;
     }
-    const int tiles = ((EPILOGUE == SWIGLU ? up_offset : n) + ROWS - 1) / ROWS;
-    const int grid = tiles < g_sm_count ? tiles : g_sm_count;
+    const int columns = EPILOGUE == SWIGLU ? up_offset : n;
+    const int grid = columns < g_sm_count ? columns : g_sm_count;
+    const int tiles_a_block = ((columns + grid - 1) / grid + ROWS - 1) / ROWS;
     const size_t rings = (size_t)WARPS * STAGES * SLICE_BYTES;
     const size_t sums = (size_t)2 * WARPS * ROWS * 8 * NT * sizeof(float);
     const size_t resident = (size_t)8 * NT * ((k + 63) / 64) * 64 * 2;
     // activations in shared memory pay off when a block reuses them for several tiles
     const bool fits = NT <= 2 && rings + sums + resident <= 200 * 1024;
-    const bool use_resident = fits && (norm.source != nullptr || tiles >= 2 * grid);
+    const bool use_resident = fits && (norm.source != nullptr || tiles_a_block >= 2);
     const size_t token_ring = !use_resident && NT == 1 ? (size_t)WARPS * STAGES * 8 * SLICE * 2 : 0;
     const size_t shared = rings + token_ring + sums + (use_resident ? resident : 0);
     cudaError_t err;
@@ -418,7 +422,7 @@ cudaError_t launch(const void* a, int lda, const void* w, const float* bias, voi
         if (err != cudaSuccess) return err;
         return launch_kernel(kernel, dim3(grid), dim3(WARPS * 32), shared, stream, true,
                              (const bf16*)nullptr, 0, (const bf16*)w, bias, out, ldo, m, n, k,
-                             up_offset, tiles, norm.source, norm.ld, norm.weight, norm.eps);
+                             up_offset, norm.source, norm.ld, norm.weight, norm.eps);
     }
     if (use_resident) {
         auto kernel = skinny_gemm_kernel<NT, EPILOGUE, (NT <= 2), false>;
@@ -426,13 +430,13 @@ cudaError_t launch(const void* a, int lda, const void* w, const float* bias, voi
         if (err != cudaSuccess) return err;
         return launch_kernel(kernel, dim3(grid), dim3(WARPS * 32), shared, stream, true,
                              (const bf16*)a, lda, (const bf16*)w, bias, out, ldo, m, n, k,
-                             up_offset, tiles, (const float*)nullptr, 0, (const float*)nullptr, 0.f);
+                             up_offset, (const float*)nullptr, 0, (const float*)nullptr, 0.f);
     }
     auto kernel = skinny_gemm_kernel<NT, EPILOGUE, false, false>;
     err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
     if (err != cudaSuccess) return err;
     return launch_kernel(kernel, dim3(grid), dim3(WARPS * 32), shared, stream, true, (const bf16*)a,
-                         lda, (const bf16*)w, bias, out, ldo, m, n, k, up_offset, tiles,
+                         lda, (const bf16*)w, bias, out, ldo, m, n, k, up_offset,
                          (const float*)nullptr, 0, (const float*)nullptr, 0.f);
 }
 

@@ -393,18 +393,16 @@ class CudaOps:
                    _c_int(code), _c_void_p(_ptr(self.error_flag)))
         return out
 
-    @staticmethod
-    def decode_splits(requests: int, heads: int, kv_heads: int, head_dim: int,
+    def decode_splits(self, requests: int, heads: int, kv_heads: int, head_dim: int,
                       context_bound: int, window: int | None) -> int:
         """Into how many parts the decode kernel cuts a request's keys: as many blocks as the
         GPU holds at once (one wave), but at least four tiles of 32 keys per part."""
         if window:
             context_bound = min(context_bound, window + 31)
         tiles = max(-(-context_bound // 32), 1)
-        block_bytes = 8 * 2 * 32 * (head_dim + 8) * 2          # 8 warps, a K and a V tile each
-        blocks_per_sm = max(1, min(8, 220 * 1024 // block_bytes))
+        blocks_per_sm = self.lib.mlxone_attention_decode_resident(_c_int(head_dim))
         groups = kv_heads * (-(-(heads // kv_heads) // 8))
-        wanted = max(148 * blocks_per_sm // max(requests * groups, 1), 1)
+        wanted = max(self._sm_count * blocks_per_sm // max(requests * groups, 1), 1)
         return max(min(wanted, tiles // 4), 1)
 
     def argmax(self, logits):
