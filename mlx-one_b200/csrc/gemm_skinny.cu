@@ -23,7 +23,10 @@
 // in which order the products are taken.
 //
 // Epilogues: store bfloat16 (+ bias); SwiGLU (the block also owns the 16 matching rows of the
-// "up" half and writes silu(gate) * up); add into the 32-bit residual stream; store float32.
+// "up" half and writes silu(gate) * up); add into the 32-bit residual stream; store float32;
+// gated short convolution of a decode step (w = [B rows; C rows; x rows], the block owns the same
+// channels of all three and applies the convolution's single-token update, so that neither the
+// three projections nor a second kernel touch memory).
 #include "common.cuh"
 
 namespace {
@@ -35,7 +38,18 @@ constexpr int STAGES = 4;         // ring of slices per warp
 constexpr int SLICE_BYTES = ROWS * SLICE * 2;
 constexpr int WARPS = 16;
 
-enum : int { STORE_BF16 = 0, SWIGLU = 1, ADD_RESIDUAL = 2, STORE_F32 = 3 };
+enum : int { STORE_BF16 = 0, SWIGLU = 1, ADD_RESIDUAL = 2, STORE_F32 = 3, GATED_CONV = 4 };
+
+// What the gated-convolution epilogue needs beside the product: one token per request.
+struct ConvUpdate {
+    const float* kernel = nullptr;     // [channels, taps]
+    const float* bias = nullptr;       // [channels] or null
+    bf16* state = nullptr;             // [slots, taps - 1, channels]: the last values of B * x
+    const int* slots = nullptr;        // per request
+    const int* history = nullptr;      // per request: tokens before this one
+    int taps = 1;                      // 1..4
+    int write_state = 0;
+};
 
 __device__ __forceinline__ uint32_t shared_address(const void* p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -77,7 +91,7 @@ __global__ void __launch_bounds__(WARPS * 32)
 skinny_gemm_kernel(const bf16* a, int lda, const bf16* __restrict__ w,
                    const float* __restrict__ bias, void* out, int ldo, int m, int n, int k,
                    int up_offset, const float* source, int source_ld,
-                   const float* __restrict__ norm_weight, float eps) {
+                   const float* __restrict__ norm_weight, float eps, ConvUpdate conv) {
     // A SwiGLU block splits its warps in two halves: the first on 16 gate rows, the second on
     // the 16 matching up rows (measured faster than tiles of 8 + 8 rows, which balance better
     // but pay the per-tile reduction twice as often).
@@ -99,10 +113,12 @@ skinny_gemm_kernel(const bf16* a, int lda, const bf16* __restrict__ w,
     unsigned char* resident = reinterpret_cast<unsigned char*>(sums_base + 2 * WARPS * ROWS * TOKENS);
 
     // this block's rows (of the gate half for SwiGLU) and the tiles that cover them
-    const int columns = EPILOGUE == SWIGLU ? up_offset : n;
+    // (gated convolution: channels; every group of 16 channels is three tiles: B, C, x)
+    constexpr int PARTS = EPILOGUE == GATED_CONV ? 3 : 1;
+    const int columns = EPILOGUE == SWIGLU ? up_offset : n / PARTS;
     const int row_begin = (int)((long long)columns * blockIdx.x / gridDim.x);
     const int row_end = (int)((long long)columns * (blockIdx.x + 1) / gridDim.x);
-    const int tile_count = (row_end - row_begin + ROWS - 1) / ROWS;
+    const int tile_count = PARTS * ((row_end - row_begin + ROWS - 1) / ROWS);
     const int slices = (k + SLICE - 1) / SLICE;
     const int mine = slices > wk ? (slices - wk + WARPS_K - 1) / WARPS_K : 0;   // per tile
     const int total = mine * tile_count;                  // this warp's slices over all tiles
@@ -127,8 +143,9 @@ skinny_gemm_kernel(const bf16* a, int lda, const bf16* __restrict__ w,
     auto fetch = [&]() {
         const int k0 = (wk + fetch_slice * WARPS_K) * SLICE;
         const uint32_t buffer = (fetched & (STAGES - 1)) * SLOT_BYTES;
-        const int row0 = row_begin + fetch_tile * ROWS;
-        const bf16* base = w + (size_t)(row0 + half * up_offset) * k + k0;
+        const int row0 = row_begin + (fetch_tile / PARTS) * ROWS;
+        const bf16* base =
+            w + (size_t)(row0 + half * up_offset + (fetch_tile % PARTS) * columns) * k + k0;
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             const bool live = row0 + piece_row[i] < row_end && k0 + piece_k[i] < k;
@@ -291,6 +308,7 @@ skinny_gemm_kernel(const bf16* a, int lda, const bf16* __restrict__ w,
     }
     int next_slice = mine > 1 ? 1 : 0;       // the slice (within a tile) whose tokens are fetched next
 
+    float held_b = 0.f, held_c = 0.f;        // gated convolution: this thread's B and C
     int index = 0;
     for (int tile = 0; tile < tile_count; ++tile) {
 #pragma unroll
@@ -354,14 +372,49 @@ skinny_gemm_kernel(const bf16* a, int lda, const bf16* __restrict__ w,
         __syncthreads();
         for (int item = threadIdx.x; item < ROWS * TOKENS; item += WARPS * 32) {
             const int token = item / ROWS, r = item % ROWS;     // rows fastest: neighbours in memory
-            const int column = row_begin + tile * ROWS + r;
+            const int column = row_begin + (tile / PARTS) * ROWS + r;
             if (token >= m || column >= row_end) continue;
             float value = 0.f;
 #pragma unroll
             for (int wi = 0; wi < WARPS_K; ++wi)
                 value += sums[((size_t)wi * ROWS + r) * TOKENS + token];
-            if (bias != nullptr) value += bias[column];
-            if (EPILOGUE == SWIGLU) {
+            if (bias != nullptr) value += bias[(tile % PARTS) * columns + column];
+            if (EPILOGUE == GATED_CONV) {
+                // the three projections are rounded as if they had been stored; a block has one
+                // item per thread at most, so B and C wait in registers for x
+                value = __bfloat162float(__float2bfloat16_rn(value));
+                const int part = tile % PARTS;
+                if (part == 0) {
+                    held_b = value;
+                } else if (part == 1) {
+                    held_c = value;
+                } else {
+                    const int position = conv.history[token];
+                    bf16* rows = conv.state + (size_t)conv.slots[token] * (conv.taps - 1) * columns;
+                    const float now = __bfloat162float(__float2bfloat16_rn(held_b * value));
+                    float kept[3] = {0.f, 0.f, 0.f};
+                    float y = conv.bias != nullptr ? conv.bias[column] : 0.f;
+#pragma unroll
+                    for (int s = 0; s < 3; ++s)
+                        if (s < conv.taps - 1) {
+                            // state row s holds position - (taps - 1) + s; zero before the start
+                            kept[s] = position - (conv.taps - 1) + s >= 0
+                                          ? __bfloat162float(rows[(size_t)s * columns + column]) : 0.f;
+                            y = fmaf(conv.kernel[(size_t)column * conv.taps + s], kept[s], y);
+                        }
+                    y = fmaf(conv.kernel[(size_t)column * conv.taps + conv.taps - 1], now, y);
+                    reinterpret_cast<bf16*>(out)[(size_t)token * ldo + column] =
+                        __float2bfloat16_rn(held_c * y);
+                    if (conv.write_state) {
+#pragma unroll
+                        for (int s = 0; s < 2; ++s)
+                            if (s + 1 < conv.taps - 1)
+                                rows[(size_t)s * columns + column] = __float2bfloat16_rn(kept[s + 1]);
+                        if (conv.taps > 1)
+                            rows[(size_t)(conv.taps - 2) * columns + column] = __float2bfloat16_rn(now);
+                    }
+                }
+            } else if (EPILOGUE == SWIGLU) {
                 float up = 0.f;
 #pragma unroll
                 for (int wi = 0; wi < WARPS_K; ++wi)
@@ -396,16 +449,17 @@ struct NormInput {
 template <int NT, int EPILOGUE>
 cudaError_t launch(const void* a, int lda, const void* w, const float* bias, void* out, int ldo,
                    int m, int n, int k, int up_offset, cudaStream_t stream,
-                   NormInput norm = NormInput()) {
+                   NormInput norm = NormInput(), ConvUpdate conv = ConvUpdate()) {
     if (g_sm_count == 0) {
         int device = 0;
         cudaGetDevice(&device);
         cudaDeviceGetAttribute(&g_sm_count, cudaDevAttrMultiProcessorCount, device);
         if (g_sm_count <= 0) g_sm_count = 148;
     }
-    const int columns = EPILOGUE == SWIGLU ? up_offset : n;
+    constexpr int PARTS = EPILOGUE == GATED_CONV ? 3 : 1;
+    const int columns = EPILOGUE == SWIGLU ? up_offset : n / PARTS;
     const int grid = columns < g_sm_count ? columns : g_sm_count;
-    const int tiles_a_block = ((columns + grid - 1) / grid + ROWS - 1) / ROWS;
+    const int tiles_a_block = PARTS * (((columns + grid - 1) / grid + ROWS - 1) / ROWS);
     const size_t rings = (size_t)WARPS * STAGES * SLICE_BYTES;
     const size_t sums = (size_t)2 * WARPS * ROWS * 8 * NT * sizeof(float);
     const size_t resident = (size_t)8 * NT * ((k + 63) / 64) * 64 * 2;
@@ -415,14 +469,15 @@ cudaError_t launch(const void* a, int lda, const void* w, const float* bias, voi
     const size_t token_ring = !use_resident && NT == 1 ? (size_t)WARPS * STAGES * 8 * SLICE * 2 : 0;
     const size_t shared = rings + token_ring + sums + (use_resident ? resident : 0);
     cudaError_t err;
-    if (norm.source != nullptr) {
+    if (EPILOGUE != GATED_CONV && norm.source != nullptr) {
         if (!fits) return cudaErrorInvalidValue;
-        auto kernel = skinny_gemm_kernel<NT, EPILOGUE, (NT <= 2), (NT <= 2)>;
+        constexpr bool WITH_NORM = NT <= 2 && EPILOGUE != GATED_CONV;
+        auto kernel = skinny_gemm_kernel<NT, EPILOGUE, WITH_NORM, WITH_NORM>;
         err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
         if (err != cudaSuccess) return err;
         return launch_kernel(kernel, dim3(grid), dim3(WARPS * 32), shared, stream, true,
                              (const bf16*)nullptr, 0, (const bf16*)w, bias, out, ldo, m, n, k,
-                             up_offset, norm.source, norm.ld, norm.weight, norm.eps);
+                             up_offset, norm.source, norm.ld, norm.weight, norm.eps, conv);
     }
     if (use_resident) {
         auto kernel = skinny_gemm_kernel<NT, EPILOGUE, (NT <= 2), false>;
@@ -430,25 +485,25 @@ cudaError_t launch(const void* a, int lda, const void* w, const float* bias, voi
         if (err != cudaSuccess) return err;
         return launch_kernel(kernel, dim3(grid), dim3(WARPS * 32), shared, stream, true,
                              (const bf16*)a, lda, (const bf16*)w, bias, out, ldo, m, n, k,
-                             up_offset, (const float*)nullptr, 0, (const float*)nullptr, 0.f);
+                             up_offset, (const float*)nullptr, 0, (const float*)nullptr, 0.f, conv);
     }
     auto kernel = skinny_gemm_kernel<NT, EPILOGUE, false, false>;
     err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
     if (err != cudaSuccess) return err;
     return launch_kernel(kernel, dim3(grid), dim3(WARPS * 32), shared, stream, true, (const bf16*)a,
                          lda, (const bf16*)w, bias, out, ldo, m, n, k, up_offset,
-                         (const float*)nullptr, 0, (const float*)nullptr, 0.f);
+                         (const float*)nullptr, 0, (const float*)nullptr, 0.f, conv);
 }
 
 template <int EPILOGUE>
 cudaError_t launch_for_rows(const void* a, int lda, const void* w, const float* bias, void* out,
                             int ldo, int m, int n, int k, int up_offset, cudaStream_t stream,
-                            NormInput norm = NormInput()) {
+                            NormInput norm = NormInput(), ConvUpdate conv = ConvUpdate()) {
     if (m <= 8)
-        return launch<1, EPILOGUE>(a, lda, w, bias, out, ldo, m, n, k, up_offset, stream, norm);
+        return launch<1, EPILOGUE>(a, lda, w, bias, out, ldo, m, n, k, up_offset, stream, norm, conv);
     if (m <= 16)
-        return launch<2, EPILOGUE>(a, lda, w, bias, out, ldo, m, n, k, up_offset, stream, norm);
-    return launch<4, EPILOGUE>(a, lda, w, bias, out, ldo, m, n, k, up_offset, stream, norm);
+        return launch<2, EPILOGUE>(a, lda, w, bias, out, ldo, m, n, k, up_offset, stream, norm, conv);
+    return launch<4, EPILOGUE>(a, lda, w, bias, out, ldo, m, n, k, up_offset, stream, norm, conv);
 }
 
 }  // namespace
@@ -486,6 +541,36 @@ MLXONE_API int mlxone_gemm_skinny(const void* a, int lda, const void* w, const f
         return 2;
     }
     MLXONE_LAUNCH_CHECK("gemm_skinny");
+    return 0;
+}
+
+// The short convolution's decode step in the product's epilogue: a [m, k] (one token per request)
+// times w = [B rows; C rows; x rows] ([3 * channels, k]), then per channel g = B * x, the
+// convolution over the kept values of g and this one, times C; out [m, channels] bfloat16; the
+// state [slots, taps - 1, channels] is shifted when write_state is set. Up to 4 taps.
+MLXONE_API int mlxone_gemm_skinny_conv(const void* a, int lda, const void* w, const float* bias,
+                                       void* out, int m, int channels, int k,
+                                       const float* conv_kernel, const float* conv_bias,
+                                       void* state, const int* slots, const int* history, int taps,
+                                       int write_state, cudaStream_t stream) {
+    if (m == 0 || channels == 0) return 0;
+    MLXONE_REQUIRE(m > 0 && m <= 32, "gemm_skinny_conv: %d rows, at most 32", m);
+    MLXONE_REQUIRE(channels > 0 && k > 0 && k % 8 == 0 && lda % 8 == 0,
+                   "gemm_skinny_conv: K (%d) and the row stride of a (%d) must be multiples of 8", k, lda);
+    MLXONE_REQUIRE((reinterpret_cast<uintptr_t>(a) & 15) == 0 &&
+                       (reinterpret_cast<uintptr_t>(w) & 15) == 0,
+                   "gemm_skinny_conv: operands must be 16-byte aligned");
+    MLXONE_REQUIRE(taps >= 1 && taps <= 4, "gemm_skinny_conv: kernel width %d is not in 1..4", taps);
+    ConvUpdate conv;
+    conv.kernel = conv_kernel; conv.bias = conv_bias; conv.state = static_cast<bf16*>(state);
+    conv.slots = slots; conv.history = history; conv.taps = taps; conv.write_state = write_state;
+    const cudaError_t err = launch_for_rows<GATED_CONV>(a, lda, w, bias, out, channels, m,
+                                                        3 * channels, k, 0, stream, NormInput(), conv);
+    if (err != cudaSuccess) {
+        mlxone_set_error("gemm_skinny_conv: launch failed: %s", cudaGetErrorString(err));
+        return 2;
+    }
+    MLXONE_LAUNCH_CHECK("gemm_skinny_conv");
     return 0;
 }
 

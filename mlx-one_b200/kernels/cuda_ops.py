@@ -329,6 +329,26 @@ class CudaOps:
                    _c_int(_dtype_code(bcx.dtype)))
         return out
 
+    def linear_short_conv(self, a, w, w_bias, *, kernel, bias, taps, ctx, view, write):
+        """short_conv(linear(a, w, w_bias)): for a decode step of few rows one kernel, the
+        convolution's update being the product's epilogue; else the two operations."""
+        if (not isinstance(a, NormedInput) and ctx.max_portion == 1
+                and a.shape[0] == ctx.requests and taps <= 4 and w.shape[0] % 3 == 0
+                and view.state.dtype == torch.bfloat16 and self._skinny(a, w)):
+            self._check_product(a, w)
+            self._need(kernel, torch.float32, "conv kernel")
+            hidden = w.shape[0] // 3
+            out = torch.empty((a.shape[0], hidden), dtype=a.dtype, device=self.device)
+            self._call("mlxone_gemm_skinny_conv", _c_void_p(_ptr(a)), _c_int(a.stride(0)),
+                       _c_void_p(_ptr(w)), _c_void_p(_ptr(w_bias)), _c_void_p(_ptr(out)),
+                       _c_int(a.shape[0]), _c_int(hidden), _c_int(a.shape[1]),
+                       _c_void_p(_ptr(kernel)), _c_void_p(_ptr(bias)), _c_void_p(_ptr(view.state)),
+                       _c_void_p(_ptr(view.slots)), _c_void_p(_ptr(ctx.history)), _c_int(taps),
+                       _c_int(1 if write else 0))
+            return out
+        return self.short_conv(self.linear(a, w, w_bias), kernel=kernel, bias=bias, taps=taps,
+                               ctx=ctx, view=view, write=write)
+
     def qk_norm_rope_store(self, qkv, *, heads, kv_heads, head_dim, q_weight, k_weight, eps,
                            rotary, ctx, view, write):
         tokens = qkv.shape[0]

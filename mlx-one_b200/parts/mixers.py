@@ -122,9 +122,9 @@ class ShortConv(Mixer):
     accepts_normed_input = True
 
     def forward(self, x, ctx, cache, write, residual=None):
-        bcx = self.ops.linear(x, self.in_proj, self.in_bias)
-        gated = self.ops.short_conv(bcx, kernel=self.kernel, bias=self.conv_bias,
-                                    taps=self.taps, ctx=ctx, view=cache, write=write)
+        gated = self.ops.linear_short_conv(x, self.in_proj, self.in_bias, kernel=self.kernel,
+                                           bias=self.conv_bias, taps=self.taps, ctx=ctx,
+                                           view=cache, write=write)
         if residual is None:
             return self.ops.linear(gated, self.out_proj, self.out_bias)
         return self.ops.linear_add(gated, self.out_proj, self.out_bias, residual)

@@ -86,6 +86,10 @@ class PlainOps:
                 view.state[slots[r]][:taps - 1] = padded[n:n + taps - 1].to(view.state.dtype)
         return out.to(dtype)
 
+    def linear_short_conv(self, a, w, w_bias, *, kernel, bias, taps, ctx, view, write):
+        return self.short_conv(self.linear(a, w, w_bias), kernel=kernel, bias=bias, taps=taps,
+                               ctx=ctx, view=view, write=write)
+
     def qk_norm_rope_store(self, qkv, *, heads, kv_heads, head_dim, q_weight, k_weight, eps,
                            rotary, ctx, view, write):
         tokens = qkv.shape[0]

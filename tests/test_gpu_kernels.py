@@ -237,6 +237,48 @@ def test_short_conv(ops, plain, dtype, hidden, taps, bias, decode):
                                        state_cpu[slots[r], valid].float(), **tolerance(dtype))
 
 
+@pytest.mark.parametrize("rows,hidden,k,taps,bias", [
+    (5, 40, 64, 3, True), (1, 2048, 2048, 3, False), (8, 136, 200, 4, False), (3, 24, 72, 1, True),
+    (17, 600, 96, 2, True), (32, 48, 2048, 3, False), (4, 40, 64, 5, True)])
+def test_linear_short_conv(ops, plain, rows, hidden, k, taps, bias):
+    """The product with the convolution's decode update as its epilogue, against the plain
+    convolution of the product that the kernel without that epilogue gives (the same sums in
+    the same order, so B, C and x round alike and what is compared is the epilogue): positions
+    0, 1 and later, slots in any order, more taps than it fuses (5)."""
+    torch.manual_seed(14)
+    dtype = torch.bfloat16
+    histories = [(3 * r) % 7 if r % 3 else r % 2 for r in range(rows)]
+    ctx, _, _ = make_batch([1] * rows, histories, 4, DEVICE)
+    slots = torch.randperm(rows + 2)[:rows].to(torch.int32)
+    state = torch.randn(rows + 2, max(taps - 1, 1), hidden).to(dtype)
+    a = torch.randn(rows, k).to(dtype)
+    w = (torch.randn(3 * hidden, k) / k ** 0.5).to(dtype)
+    w_bias = torch.randn(3 * hidden) if bias else None
+    kernel = torch.randn(hidden, taps)
+    conv_bias = torch.randn(hidden) if bias else None
+    need = FixedState((max(taps - 1, 1), hidden))
+    to = lambda t: None if t is None else t.to(DEVICE)
+    state_gpu = state.clone().to(DEVICE)
+    before = ops.launches
+    got = ops.linear_short_conv(to(a), to(w), to(w_bias), kernel=to(kernel), bias=to(conv_bias),
+                                taps=taps, ctx=ctx, view=StateView(state_gpu, to(slots), need),
+                                write=True)
+    assert ops.launches - before == (1 if taps <= 4 else 2)
+    state_cpu = state.clone()
+    bcx = ops.linear(to(a), to(w), to(w_bias)).cpu()
+    torch.testing.assert_close(bcx.float(), plain.linear(a, w, w_bias).float(), **tolerance(dtype))
+    want = plain.short_conv(bcx, kernel=kernel, bias=conv_bias, taps=taps, ctx=on_cpu(ctx),
+                            view=StateView(state_cpu, slots, need), write=True)
+    torch.testing.assert_close(got.cpu().float(), want.float(), **tolerance(dtype))
+    if taps > 1:
+        for r, h in enumerate(histories):
+            valid = [s for s in range(taps - 1) if h + 1 - (taps - 1) + s >= 0]
+            torch.testing.assert_close(state_gpu.cpu()[slots[r], valid].float(),
+                                       state_cpu[slots[r], valid].float(), **tolerance(dtype))
+    untouched = [s for s in range(rows + 2) if s not in slots.tolist()]
+    assert torch.equal(state_gpu.cpu()[untouched], state[untouched])
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("heads,kv_heads,head_dim,rotary_dim,norm", [
     (4, 2, 16, 16, True), (3, 1, 32, 32, True), (6, 3, 48, 24, False), (5, 5, 80, 80, True),
