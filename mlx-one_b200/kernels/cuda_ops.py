@@ -63,6 +63,7 @@ class CudaOps:
         # the next product's weight prefetch and is faster, so this is off by default
         self.fused_norms = False
         self.tcgen05_min_rows = 128
+        self.tcgen05_attention = True     # prefill attention with tcgen05 where it takes the geometry
         self.tcgen05_always = False       # tests: take the tcgen05 kernel whenever it can run
         self._sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
         # tcgen05 products (TMA + tensor memory) for more rows than the skinny kernel takes
@@ -395,6 +396,16 @@ class CudaOps:
                            _c_float(scale), _c_int(window or 0))
                 if splits > 1:
                     self.launches += 1
+            elif (self.tcgen05_attention and q.dtype == torch.bfloat16
+                  and self.lib.mlxone_attention_tcgen05_supports(
+                      _c_int(head_dim), _c_int(heads), _c_int(kv_heads), _c_int(view.page_size))):
+                self._call("mlxone_attention_prefill_tcgen05", _c_void_p(_ptr(q)),
+                           _c_void_p(_ptr(view.kv)), _c_void_p(_ptr(view.block_table)),
+                           _c_int(width), _c_int(view.page_size), _c_int(pages),
+                           _c_void_p(_ptr(ctx.request_start)), _c_void_p(_ptr(ctx.history)),
+                           _c_void_p(_ptr(out)), _c_int(tokens), _c_int(ctx.requests),
+                           _c_int(heads), _c_int(kv_heads), _c_int(head_dim), _c_float(scale),
+                           _c_int(window or 0), _c_void_p(_ptr(self.error_flag)))
             else:
                 self._call("mlxone_attention_prefill", _c_void_p(_ptr(q)),
                            _c_void_p(_ptr(view.kv)), _c_void_p(_ptr(view.block_table)),

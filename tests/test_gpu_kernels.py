@@ -312,7 +312,7 @@ def test_qk_norm_rope_store(ops, plain, dtype, heads, kv_heads, head_dim, rotary
 
 
 def attention_case(ops, plain, dtype, heads, kv_heads, head_dim, page_size, portions, histories,
-                   window, tensor_cores, seed=6, spike=None):
+                   window, tensor_cores, seed=6, spike=None, tcgen05=False):
     torch.manual_seed(seed)
     ctx, table, pages = make_batch(portions, histories, page_size, DEVICE, seed=seed)
     kv = torch.randn(2, pages, kv_heads, page_size, head_dim).to(dtype)
@@ -329,12 +329,14 @@ def attention_case(ops, plain, dtype, heads, kv_heads, head_dim, page_size, port
     need = PagedKeyValues(kv_heads, head_dim, window)
     scale = head_dim ** -0.5
     ops.tensor_core_attention = tensor_cores
+    ops.tcgen05_attention = tcgen05
     try:
         got = ops.paged_attention(q.to(DEVICE), heads=heads, kv_heads=kv_heads, head_dim=head_dim,
                                   scale=scale, window=window, ctx=ctx,
                                   view=PagedView(kv.to(DEVICE), table, page_size, need))
     finally:
         ops.tensor_core_attention = True
+        ops.tcgen05_attention = True
     want = plain.paged_attention(q, heads=heads, kv_heads=kv_heads, head_dim=head_dim,
                                  scale=scale, window=window, ctx=on_cpu(ctx),
                                  view=PagedView(kv, table.cpu(), page_size, need))
@@ -375,6 +377,22 @@ def test_attention_decode_tensor_cores(ops, plain, heads, kv_heads, head_dim, pa
     attention_case(ops, plain, torch.bfloat16, heads, kv_heads, head_dim, page_size,
                    portions=[1] * 5, histories=histories, window=window, tensor_cores=True,
                    spike=far)
+
+
+@pytest.mark.parametrize("heads,kv_heads,page_size", [
+    (8, 8, 16), (32, 8, 16), (4, 2, 8), (16, 2, 64), (3, 3, 128), (8, 1, 256), (64, 1, 32)])
+@pytest.mark.parametrize("window", [None, 37, 128, 300])
+def test_attention_prefill_tcgen05(ops, plain, heads, kv_heads, page_size, window):
+    """The tcgen05 kernel (head size 64): query heads of a group stacked in one block; portions
+    that end inside a block of rows, cross tiles of 128 keys and start deep in a context; single
+    tokens beside them; windows inside a tile, of exactly a tile and over several."""
+    assert ops.lib.mlxone_attention_tcgen05_supports(64, heads, kv_heads, page_size)
+    before = ops.launches
+    attention_case(ops, plain, torch.bfloat16, heads, kv_heads, 64, page_size,
+                   portions=[7, 1, 300, 2, 128, 33], histories=[0, 200, 500, 64, 128, 1000],
+                   window=window, tensor_cores=True, tcgen05=True,
+                   spike=(2, 5 if window is None else 700))
+    assert ops.launches - before == 1
 
 
 def test_decode_splits_are_used(ops):
