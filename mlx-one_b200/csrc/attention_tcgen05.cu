@@ -3,20 +3,22 @@
 // accumulators in tensor memory, keys and values arrive by TMA (cp.async.bulk.tensor, 128-byte
 // swizzle) straight from the cache's pages, and only the softmax runs on ordinary threads.
 //
-// One block = up to 128 query rows that share a key head: 128 / group tokens of one request times
-// the group's query heads (row = token * group + head), so that a key tile is fetched once for
-// the whole group and short portions waste few rows. It walks the request's keys in tiles of 128.
-// The warps have roles:
-//   warps 0-7  softmax: two threads share query row r (lane r of tensor memory), one for keys
-//              0-63 of a tile and output dimensions 0-31, one for the other halves. Per tile a
-//              thread reads its scores with tcgen05.ld, the two agree on the maximum, it writes
-//              exp2(score - max) as bfloat16 into shared memory in the operand layout of the
-//              second product, and then adds the previous tile's P V (read from tensor memory)
-//              into its 32 output registers, scaled as the running maximum moved;
-//   warp 8     the TMA loads: the query tile once (a 3-D box: head size x group x tokens),
+// One item of work = up to 128 query rows that share a key head: 128 / group tokens of one request
+// times the group's query heads (row = token * group + head), so that a key tile is fetched once
+// for the whole group and short portions waste few rows; the request's keys are walked in tiles
+// of 128. Blocks are persistent, one per SM: a block lists its items once and its rings of
+// buffers run on from one item into the next, so that the first loads and products of an item
+// overlap the end of the one before. The warps have roles:
+//   softmax warps (4 x PARTS): PARTS threads share query row r (lane r of tensor memory), each
+//              for its share of a tile's keys and of the output dimensions. Per tile a thread
+//              reads its scores with tcgen05.ld, the row's threads agree on the maximum, it
+//              writes exp2(score - max) as bfloat16 into shared memory in the operand layout of
+//              the second product, and then adds the previous tile's P V (read from tensor
+//              memory) into its output registers, scaled as the running maximum moved;
+//   copy warp  the TMA loads: the query tile once (a 3-D box: head size x group x tokens),
 //              then per key tile lane b looks up page b and copies its K and V into a ring of
 //              three stages;
-//   warp 9     allocates tensor memory; one thread issues the products: scores of tile j + 1
+//   product warp  allocates tensor memory; one thread issues the products: scores of tile j + 1
 //              are computed while the softmax warps work on tile j (two score buffers), P V
 //              of tile j runs while they work on tile j + 1 (two buffers for it as well).
 // V is used as it lies in the cache ([key, head size], head size contiguous): the second
@@ -40,15 +42,17 @@ constexpr int HD = 64;
 constexpr int ROWS = 128;              // query rows per block
 constexpr int KEYS = 128;              // keys per tile
 constexpr int STAGES = 3;              // ring of key/value tiles
-constexpr int THREADS = 320;            // eight softmax warps, the copy warp, the product warp
-constexpr int COPY_WARP = 8, MMA_WARP = 9;
+constexpr int PARTS = 2;               // threads that share a query row
+constexpr int COPY_WARP = 4 * PARTS, MMA_WARP = 4 * PARTS + 1;
+constexpr int THREADS = (4 * PARTS + 2) * 32;     // softmax warps, the copy warp, the product warp
 constexpr int WAIT_LIMIT = 1 << 24;
 constexpr int ERROR_WAIT = 9;
 constexpr int Q_BYTES = ROWS * HD * 2;
 constexpr int K_BYTES = KEYS * HD * 2;
 constexpr int STAGE_BYTES = 2 * K_BYTES;
 constexpr int P_BYTES = ROWS * KEYS * 2;
-constexpr int SHARED_BYTES = Q_BYTES + STAGES * STAGE_BYTES + 2 * P_BYTES + 1024;
+constexpr int SHARED_BYTES = 2 * Q_BYTES + STAGES * STAGE_BYTES + 2 * P_BYTES + 1024;
+constexpr int MAX_ITEMS = 128;         // (token tile, key head) pairs one block may be given
 constexpr int TMEM_COLUMNS = 512;      // scores 2 x 128, P V 2 x 64: 384, rounded to a power of two
 
 __device__ __forceinline__ uint32_t shared_address(const void* p) {
@@ -126,44 +130,26 @@ __device__ __forceinline__ void mma_bf16(uint32_t d_tmem, uint64_t a_desc, uint6
         ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"((uint32_t)accumulate)
         : "memory");
 }
-// 32 consecutive 32-bit columns of this thread's lane of tensor memory.
-__device__ __forceinline__ void tmem_load_32(uint32_t address, float (&v)[32]) {
-    uint32_t r[32];
+// N consecutive 32-bit columns (16, 32 or 64) of this thread's lane of tensor memory; all loads
+// are in flight before the one wait.
+__device__ __forceinline__ void tmem_issue_16(uint32_t address, uint32_t* r) {
     asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
-        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
         : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
           "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
-          "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]),
-          "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]),
-          "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+          "=r"(r[14]), "=r"(r[15])
         : "r"(address));
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
 }
-// 64 columns: two loads in flight, one wait.
-__device__ __forceinline__ void tmem_load_64(uint32_t address, float (&v)[64]) {
-    uint32_t r[64];
+template <int N>
+__device__ __forceinline__ void tmem_load(uint32_t address, float (&v)[N]) {
+    static_assert(N % 16 == 0, "whole loads of 16 columns");
+    uint32_t r[N];
 #pragma unroll
-    for (int h = 0; h < 2; ++h)
-        asm volatile(
-            "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-            "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
-            "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-            : "=r"(r[h * 32 + 0]), "=r"(r[h * 32 + 1]), "=r"(r[h * 32 + 2]), "=r"(r[h * 32 + 3]),
-              "=r"(r[h * 32 + 4]), "=r"(r[h * 32 + 5]), "=r"(r[h * 32 + 6]), "=r"(r[h * 32 + 7]),
-              "=r"(r[h * 32 + 8]), "=r"(r[h * 32 + 9]), "=r"(r[h * 32 + 10]), "=r"(r[h * 32 + 11]),
-              "=r"(r[h * 32 + 12]), "=r"(r[h * 32 + 13]), "=r"(r[h * 32 + 14]), "=r"(r[h * 32 + 15]),
-              "=r"(r[h * 32 + 16]), "=r"(r[h * 32 + 17]), "=r"(r[h * 32 + 18]), "=r"(r[h * 32 + 19]),
-              "=r"(r[h * 32 + 20]), "=r"(r[h * 32 + 21]), "=r"(r[h * 32 + 22]), "=r"(r[h * 32 + 23]),
-              "=r"(r[h * 32 + 24]), "=r"(r[h * 32 + 25]), "=r"(r[h * 32 + 26]), "=r"(r[h * 32 + 27]),
-              "=r"(r[h * 32 + 28]), "=r"(r[h * 32 + 29]), "=r"(r[h * 32 + 30]), "=r"(r[h * 32 + 31])
-            : "r"(address + h * 32));
+    for (int c = 0; c < N / 16; ++c) tmem_issue_16(address + c * 16, r + c * 16);
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
-    for (int i = 0; i < 64; ++i) v[i] = __uint_as_float(r[i]);
+    for (int i = 0; i < N; ++i) v[i] = __uint_as_float(r[i]);
 }
 __device__ __forceinline__ float fast_exp2(float x) {
     float y;
@@ -194,78 +180,101 @@ __host__ __device__ constexpr uint32_t instruction_descriptor(int m, int n, bool
            ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
 
+// What a block does for one (request, tokens, key head): filled in once, read by every role.
+struct Item {
+    int request;            // -1: nothing to do (the grid is sized by an upper bound)
+    int kv_head;
+    int q_token;            // first token of the tile among all tokens of the step
+    int tokens_here;        // tokens of the tile that belong to the portion
+    int first_position;     // position of the first token in its request
+    int tile_first;         // first key tile
+    int tile_count;
+};
+
 __global__ void __launch_bounds__(THREADS)
 attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q,
                          const __grid_constant__ CUtensorMap map_kv, long long value_rows,
                          const int* __restrict__ block_table, int table_width, int page_size,
                          int box_keys, const int* __restrict__ request_start,
                          const int* __restrict__ history, bf16* __restrict__ out, int requests,
-                         int heads, int kv_heads, float scale_log2, int window,
+                         int heads, int kv_heads, float scale_log2, int window, int token_tiles,
                          int* __restrict__ error_flag) {
     extern __shared__ unsigned char shared_raw[];
-    // q_full; kv_full[s], kv_empty[s]; s_ready[b], p_ready[b], o_ready[b]
-    __shared__ __align__(8) unsigned long long barriers[1 + 2 * STAGES + 6];
+    // q_full[2], q_empty[2]; kv_full[s], kv_empty[s]; s_ready[b], p_ready[b], o_ready[b]
+    __shared__ __align__(8) unsigned long long barriers[4 + 2 * STAGES + 6];
     __shared__ uint32_t tmem_base_slot;
-    __shared__ int found[2];
-    __shared__ float maxima[2 * 2 * ROWS];          // [tile parity][half][row]
+    __shared__ Item items[MAX_ITEMS];
+    __shared__ float maxima[2 * PARTS * ROWS];      // [tile parity][part][row]
+    __shared__ float sums[PARTS * ROWS];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int group = heads / kv_heads;
     const int tile_tokens = ROWS / group;
 
-    // which request and which tokens of it this block serves (the last tiles of a causal
-    // prompt walk the most keys: they go first)
-    if (threadIdx.x == 0) {
-        int left = gridDim.x - 1 - blockIdx.x, request = -1, start = 0;
+    // This block's items among all (token tile, key head) pairs, the token tiles counted from
+    // the end (the last tiles of a causal prompt walk the most keys). They are dealt out in
+    // rounds of gridDim.x, every other round in reverse, so that the block with the heaviest
+    // item of one round gets the lightest of the next and all blocks walk about as many keys.
+    const int all_items = token_tiles * kv_heads;
+    const int rounds = all_items / (int)gridDim.x, rest = all_items % (int)gridDim.x;
+    const int last_place = (rounds & 1) ? (int)gridDim.x - 1 - (int)blockIdx.x : (int)blockIdx.x;
+    const int mine = rounds + (last_place < rest ? 1 : 0);
+    if (mine == 0) return;
+    for (int k = threadIdx.x; k < mine; k += THREADS) {
+        const int index = k * gridDim.x + ((k & 1) ? gridDim.x - 1 - blockIdx.x : blockIdx.x);
+        Item item;
+        item.request = -1;
+        item.kv_head = index % kv_heads;
+        int left = index / kv_heads;
         for (int r = 0; r < requests; ++r) {
-            const int tiles = (request_start[r + 1] - request_start[r] + tile_tokens - 1) / tile_tokens;
-            if (left < tiles) { request = r; start = left * tile_tokens; break; }
+            const int first = request_start[r], count = request_start[r + 1] - first;
+            const int tiles = (count + tile_tokens - 1) / tile_tokens;
+            if (left < tiles) {
+                const int token_start = (tiles - 1 - left) * tile_tokens;
+                item.request = r;
+                item.q_token = first + token_start;
+                item.tokens_here = min(tile_tokens, count - token_start);
+                item.first_position = history[r] + token_start;
+                const int last_position = item.first_position + item.tokens_here - 1;
+                const int lowest = window > 0 ? max(item.first_position - window + 1, 0) : 0;
+                item.tile_first = lowest / KEYS;
+                item.tile_count = last_position / KEYS - item.tile_first + 1;
+                break;
+            }
             left -= tiles;
         }
-        found[0] = request;
-        found[1] = start;
+        items[k] = item;
     }
-    __syncthreads();
-    const int request = found[0];
-    if (request < 0) return;
-    const int token_start = found[1];                 // within the portion
-    const int kv_head = blockIdx.y;
-    const int first_token = request_start[request];
-    const int count = request_start[request + 1] - first_token;
-    const int tokens_here = min(tile_tokens, count - token_start);
-    const int first_position = history[request] + token_start;
-    const int last_position = first_position + tokens_here - 1;
-    const int lowest = window > 0 ? max(first_position - window + 1, 0) : 0;
-    const int tile_first = lowest / KEYS, tile_last = last_position / KEYS;
-    const int tile_count = tile_last - tile_first + 1;
 
     const uint32_t base = (shared_address(shared_raw) + 1023u) & ~1023u;
-    const uint32_t q_tile = base;
-    const uint32_t stages = base + Q_BYTES;
+    const uint32_t q_tiles = base;
+    const uint32_t stages = base + 2 * Q_BYTES;
     const uint32_t p_tiles = stages + STAGES * STAGE_BYTES;
     unsigned char* generic_base = shared_raw + (base - shared_address(shared_raw));
-    auto q_full = [&]() { return shared_address(&barriers[0]); };
-    auto kv_full = [&](int s) { return shared_address(&barriers[1 + s]); };
-    auto kv_empty = [&](int s) { return shared_address(&barriers[1 + STAGES + s]); };
-    auto s_ready = [&](int b) { return shared_address(&barriers[1 + 2 * STAGES + b]); };
-    auto p_ready = [&](int b) { return shared_address(&barriers[1 + 2 * STAGES + 2 + b]); };
-    auto o_ready = [&](int b) { return shared_address(&barriers[1 + 2 * STAGES + 4 + b]); };
+    auto q_full = [&](int b) { return shared_address(&barriers[b]); };
+    auto q_empty = [&](int b) { return shared_address(&barriers[2 + b]); };
+    auto kv_full = [&](int s) { return shared_address(&barriers[4 + s]); };
+    auto kv_empty = [&](int s) { return shared_address(&barriers[4 + STAGES + s]); };
+    auto s_ready = [&](int b) { return shared_address(&barriers[4 + 2 * STAGES + b]); };
+    auto p_ready = [&](int b) { return shared_address(&barriers[4 + 2 * STAGES + 2 + b]); };
+    auto o_ready = [&](int b) { return shared_address(&barriers[4 + 2 * STAGES + 4 + b]); };
 
     if (threadIdx.x == 0) {
-        barrier_init(q_full(), 1);
+        for (int b = 0; b < 2; ++b) {
+            barrier_init(q_full(b), 1);
+            barrier_init(q_empty(b), 1);
+            barrier_init(s_ready(b), 1);
+            barrier_init(p_ready(b), 4 * PARTS);       // the softmax warps
+            barrier_init(o_ready(b), 1);
+        }
         for (int s = 0; s < STAGES; ++s) {
             barrier_init(kv_full(s), 1);
             barrier_init(kv_empty(s), 1);
-        }
-        for (int b = 0; b < 2; ++b) {
-            barrier_init(s_ready(b), 1);
-            barrier_init(p_ready(b), 8);               // the eight softmax warps
-            barrier_init(o_ready(b), 1);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     // stages start as zeros: a page that is skipped must not show what shared memory held
     {
-        uint4* stage_words = reinterpret_cast<uint4*>(generic_base + Q_BYTES);
+        uint4* stage_words = reinterpret_cast<uint4*>(generic_base + 2 * Q_BYTES);
         for (int i = threadIdx.x; i < STAGES * STAGE_BYTES / 16; i += THREADS)
             stage_words[i] = make_uint4(0u, 0u, 0u, 0u);
         fence_async_shared();
@@ -276,71 +285,110 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q,
     fence_after_sync();
     const uint32_t tmem_base = tmem_base_slot;
 
+    // Every role walks the same items and key tiles in the same order and counts them the same
+    // way: `taken` items with work (it picks the query buffer), `t` key tiles (it picks the
+    // stage, the score, P and P V buffers). The rings run on from one item into the next, so an
+    // item's first loads and products overlap the end of the item before it.
     if (warp == COPY_WARP) {
         // Lane b brings box b of every key tile (one page, or a page's part): it looks up the
         // page and issues the two copies itself, so that neither the look-ups nor the copies of
         // a tile wait for one another. Lane 0 announces the bytes first.
-        if (lane == 0) {
-            barrier_expect(q_full(), Q_BYTES);
-            tma_load_3d(q_tile, &map_q, 0, kv_head * group, first_token + token_start, q_full());
-        }
-        const int* table = block_table + (size_t)request * table_width;
         const int boxes = KEYS / box_keys;
         bool ok = true;
-        for (int j = 0; j < tile_count && ok; ++j) {
-            const int s = j % STAGES;
-            // this box's rows in the cache, if some query row may see its keys
-            long long row = -1;
-            const int key = (tile_first + j) * KEYS + lane * box_keys;
-            if (lane < boxes && key <= last_position && key + box_keys - 1 >= lowest) {
-                const int block = key / page_size;
-                const int page = block < table_width ? table[block] : -1;
-                if (page >= 0)
-                    row = ((long long)page * kv_heads + kv_head) * page_size + key % page_size;
-            }
-            const int live = __popc(__ballot_sync(0xffffffffu, row >= 0));
+        int taken = 0, t = 0;
+        for (int n = 0; n < mine && ok; ++n) {
+            const Item item = items[n];
+            if (item.request < 0) continue;
             if (lane == 0) {
-                ok = barrier_wait(kv_empty(s), ((j / STAGES) & 1) ^ 1, error_flag);
-                if (ok) barrier_expect(kv_full(s), (uint32_t)live * 2u * (uint32_t)box_keys * HD * 2u);
+                ok = barrier_wait(q_empty(taken & 1), ((taken >> 1) & 1) ^ 1, error_flag);
+                if (ok) {
+                    barrier_expect(q_full(taken & 1), Q_BYTES);
+                    tma_load_3d(q_tiles + (taken & 1) * Q_BYTES, &map_q, 0, item.kv_head * group,
+                                item.q_token, q_full(taken & 1));
+                }
             }
             ok = __shfl_sync(0xffffffffu, ok, 0);
-            if (ok && row >= 0) {
-                const uint32_t at = stages + s * STAGE_BYTES + (uint32_t)(lane * box_keys) * HD * 2;
-                tma_load_2d(at, &map_kv, 0, (int)row, kv_full(s));
-                tma_load_2d(at + K_BYTES, &map_kv, 0, (int)(row + value_rows), kv_full(s));
+            ++taken;
+            const int* table = block_table + (size_t)item.request * table_width;
+            const int last_position = item.first_position + item.tokens_here - 1;
+            const int lowest = window > 0 ? max(item.first_position - window + 1, 0) : 0;
+            for (int j = 0; j < item.tile_count && ok; ++j, ++t) {
+                const int s = t % STAGES;
+                // this box's rows in the cache, if some query row may see its keys
+                long long row = -1;
+                const int key = (item.tile_first + j) * KEYS + lane * box_keys;
+                if (lane < boxes && key <= last_position && key + box_keys - 1 >= lowest) {
+                    const int block = key / page_size;
+                    const int page = block < table_width ? table[block] : -1;
+                    if (page >= 0)
+                        row = ((long long)page * kv_heads + item.kv_head) * page_size + key % page_size;
+                }
+                const int live = __popc(__ballot_sync(0xffffffffu, row >= 0));
+                if (lane == 0) {
+                    ok = barrier_wait(kv_empty(s), ((t / STAGES) & 1) ^ 1, error_flag);
+                    if (ok) barrier_expect(kv_full(s), (uint32_t)live * 2u * (uint32_t)box_keys * HD * 2u);
+                }
+                ok = __shfl_sync(0xffffffffu, ok, 0);
+                if (ok && row >= 0) {
+                    const uint32_t at = stages + s * STAGE_BYTES + (uint32_t)(lane * box_keys) * HD * 2;
+                    tma_load_2d(at, &map_kv, 0, (int)row, kv_full(s));
+                    tma_load_2d(at + K_BYTES, &map_kv, 0, (int)(row + value_rows), kv_full(s));
+                }
             }
         }
     } else if (warp == MMA_WARP) {
         if (lane == 0) {
             constexpr uint32_t idesc_scores = instruction_descriptor(ROWS, KEYS, false);
             constexpr uint32_t idesc_out = instruction_descriptor(ROWS, HD, true);
-            bool ok = barrier_wait(q_full(), 0, error_flag);
-            const uint64_t q_desc = operand_descriptor(q_tile);
-            auto scores = [&](int j) {
-                const int s = j % STAGES;
-                if (!barrier_wait(kv_full(s), (j / STAGES) & 1, error_flag)) return false;
+            // a place in the walk: item n, its tile j; `taken` and `t` as above
+            struct Place { int n, j, taken, t; };
+            auto settle = [&](Place& place) {          // skips items without work
+                while (place.n < mine && items[place.n].request < 0) ++place.n;
+            };
+            auto step = [&](Place place) {
+                if (place.j + 1 < items[place.n].tile_count) {
+                    ++place.j;
+                } else {
+                    ++place.n; place.j = 0; ++place.taken;
+                    settle(place);
+                }
+                ++place.t;
+                return place;
+            };
+            // scores of the tile at `place` into score buffer t & 1
+            auto scores = [&](const Place& place) {
+                const int tile_count = items[place.n].tile_count;
+                const int qb = place.taken & 1, s = place.t % STAGES;
+                if (place.j == 0 &&
+                    !barrier_wait(q_full(qb), (place.taken >> 1) & 1, error_flag)) return false;
+                if (!barrier_wait(kv_full(s), (place.t / STAGES) & 1, error_flag)) return false;
                 fence_after_sync();
+                const uint64_t q_desc = operand_descriptor(q_tiles + qb * Q_BYTES);
                 const uint64_t k_desc = operand_descriptor(stages + s * STAGE_BYTES);
 #pragma unroll
                 for (int kk = 0; kk < HD / 16; ++kk)
-                    mma_bf16(tmem_base + (j & 1) * KEYS, q_desc + 2 * kk, k_desc + 2 * kk,
+                    mma_bf16(tmem_base + (place.t & 1) * KEYS, q_desc + 2 * kk, k_desc + 2 * kk,
                              idesc_scores, kk > 0);
-                mma_commit(s_ready(j & 1));
+                mma_commit(s_ready(place.t & 1));
+                if (place.j == tile_count - 1) mma_commit(q_empty(qb));   // the query tile is done with
                 return true;
             };
-            if (ok) ok = scores(0);
-            for (int j = 0; j < tile_count && ok; ++j) {
+            Place now{0, 0, 0, 0};
+            settle(now);
+            bool ok = now.n < mine ? scores(now) : false;
+            while (ok && now.n < mine) {
                 // the next tile's scores run while the softmax warps work on this one; their
-                // buffer was read to its end before p_ready of tile j - 1 arrived
-                if (j + 1 < tile_count) {
-                    ok = scores(j + 1);
+                // buffer was read to its end before p_ready of the tile before this one arrived
+                const Place next = step(now);
+                if (next.n < mine) {
+                    ok = scores(next);
                     if (!ok) break;
                 }
-                ok = barrier_wait(p_ready(j & 1), (j >> 1) & 1, error_flag);
+                ok = barrier_wait(p_ready(now.t & 1), (now.t >> 1) & 1, error_flag);
                 if (!ok) break;
                 fence_after_sync();
-                const int s = j % STAGES;
-                const uint32_t p_tile = p_tiles + (j & 1) * P_BYTES;
+                const int s = now.t % STAGES;
+                const uint32_t p_tile = p_tiles + (now.t & 1) * P_BYTES;
                 const uint32_t v_tile = stages + s * STAGE_BYTES + K_BYTES;
 #pragma unroll
                 for (int kk = 0; kk < KEYS / 16; ++kk) {
@@ -349,121 +397,136 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q,
                     const uint64_t p_desc =
                         operand_descriptor(p_tile + (kk / 4) * (ROWS * 128)) + 2 * (kk % 4);
                     const uint64_t v_desc = operand_descriptor(v_tile + kk * 2048);
-                    mma_bf16(tmem_base + 2 * KEYS + (j & 1) * HD, p_desc, v_desc, idesc_out, kk > 0);
+                    mma_bf16(tmem_base + 2 * KEYS + (now.t & 1) * HD, p_desc, v_desc, idesc_out, kk > 0);
                 }
                 mma_commit(kv_empty(s));                 // K and V of this tile are done with
-                mma_commit(o_ready(j & 1));
+                mma_commit(o_ready(now.t & 1));
+                now = next;
             }
         }
     } else {
         // Softmax warps. Row r of the block is lane r of tensor memory, and a warp may only touch
-        // lanes 32 (w % 4) .. + 31; warps w and w + 4 share their rows: the first takes keys
-        // 0-63 of every tile and output dimensions 0-31, the second the other halves. They
-        // agree on the row's maximum through shared memory once per tile; their sums are added
-        // at the end.
-        const int half = warp >> 2;
+        // lanes 32 (w % 4) .. + 31; the PARTS warps w, w + 4, ... share their rows: each takes
+        // KEYS / PARTS keys of every tile and HD / PARTS output dimensions. They agree on the
+        // row's maximum through shared memory once per tile; their sums are added at the end.
+        constexpr int MY_KEYS = KEYS / PARTS, MY_DIMS = HD / PARTS;
+        constexpr int PIECES = MY_KEYS / 8;
+        const int part = warp >> 2;
         const int row = (warp & 3) * 32 + lane;
         const int token = row / group;
-        const bool valid = token < tokens_here;
-        const int position = first_position + token;
-        const int limit_hi = valid ? position : -1;
-        const int limit_lo = window > 0 ? max(position - window + 1, 0) : 0;
-        // keys that every row of the block sees: from the last row's lower limit to the first
-        // row's position; a block with rows beyond the portion's end always masks
-        const bool whole = tokens_here == tile_tokens;
-        const int open_lo = window > 0 ? max(last_position - window + 1, 0) : 0;
         const uint32_t lanes = (uint32_t)((warp & 3) * 32) << 16;
-        // this thread's 128 bytes of P: block `half` of 64 keys, row `row`
-        unsigned char* p_row = generic_base + Q_BYTES + STAGES * STAGE_BYTES + half * (ROWS * 128) +
-                               (row >> 3) * 1024 + (row & 7) * 128;
-        const int pair_barrier = 1 + (warp & 3);           // named barrier of the two warps
-        float m = -INFINITY, l = 0.f, correction = 1.f;
-        float o[HD / 2];
-#pragma unroll
-        for (int d = 0; d < HD / 2; ++d) o[d] = 0.f;
+        // this thread's pieces of P: block (of 64 keys) and first 16-byte piece within its row
+        const int first_piece = (part * MY_KEYS % 64) / 8;
+        unsigned char* p_row = generic_base + 2 * Q_BYTES + STAGES * STAGE_BYTES +
+                               (part * MY_KEYS / 64) * (ROWS * 128) + (row >> 3) * 1024 +
+                               (row & 7) * 128;
+        const int row_barrier = 1 + (warp & 3);            // named barrier of the row's warps
         bool ok = true;
-        auto add_out = [&](int j) {
-            // o = o * (how far the maximum moved when tile j was seen) + P_j V_j
-            if (!barrier_wait(o_ready(j & 1), (j >> 1) & 1, error_flag)) return false;
-            fence_after_sync();
-            float part[32];
-            tmem_load_32(tmem_base + lanes + 2 * KEYS + (j & 1) * HD + half * 32, part);
+        int t = 0;
+        for (int n = 0; n < mine && ok; ++n) {
+            const Item item = items[n];
+            if (item.request < 0) continue;
+            const bool valid = token < item.tokens_here;
+            const int position = item.first_position + token;
+            const int last_position = item.first_position + item.tokens_here - 1;
+            const int limit_hi = valid ? position : -1;
+            const int limit_lo = window > 0 ? max(position - window + 1, 0) : 0;
+            // keys that every row of the block sees: from the last row's lower limit to the
+            // first row's position; a block with rows beyond the portion's end always masks
+            const bool whole = item.tokens_here == tile_tokens;
+            const int open_lo = window > 0 ? max(last_position - window + 1, 0) : 0;
+            float m = -INFINITY, l = 0.f, correction = 1.f;
+            float o[MY_DIMS];
 #pragma unroll
-            for (int i = 0; i < 32; ++i) o[i] = fmaf(o[i], correction, part[i]);
-            return true;
-        };
-        for (int j = 0; j < tile_count && ok; ++j) {
-            const int key0 = (tile_first + j) * KEYS + half * 64;
-            ok = barrier_wait(s_ready(j & 1), (j >> 1) & 1, error_flag);
-            if (!ok) break;
-            fence_after_sync();
-            float v[64];
-            tmem_load_64(tmem_base + lanes + (j & 1) * KEYS + half * 64, v);
-            const bool open = whole && (tile_first + j) * KEYS >= open_lo &&
-                              (tile_first + j) * KEYS + KEYS - 1 <= first_position;
-            if (!open) {
+            for (int d = 0; d < MY_DIMS; ++d) o[d] = 0.f;
+            auto add_out = [&](int tile) {
+                // o = o * (how far the maximum moved when the tile was seen) + its P V
+                if (!barrier_wait(o_ready(tile & 1), (tile >> 1) & 1, error_flag)) return false;
+                fence_after_sync();
+                float piece[MY_DIMS];
+                tmem_load<MY_DIMS>(tmem_base + lanes + 2 * KEYS + (tile & 1) * HD + part * MY_DIMS, piece);
 #pragma unroll
-                for (int i = 0; i < 64; ++i)
-                    if (!(key0 + i >= limit_lo && key0 + i <= limit_hi)) v[i] = -INFINITY;
-            }
-            float tops[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+                for (int i = 0; i < MY_DIMS; ++i) o[i] = fmaf(o[i], correction, piece[i]);
+                return true;
+            };
+            for (int j = 0; j < item.tile_count && ok; ++j, ++t) {
+                const int tile_key = (item.tile_first + j) * KEYS;
+                const int key0 = tile_key + part * MY_KEYS;
+                ok = barrier_wait(s_ready(t & 1), (t >> 1) & 1, error_flag);
+                if (!ok) break;
+                fence_after_sync();
+                float v[MY_KEYS];
+                tmem_load<MY_KEYS>(tmem_base + lanes + (t & 1) * KEYS + part * MY_KEYS, v);
+                const bool open = whole && tile_key >= open_lo &&
+                                  tile_key + KEYS - 1 <= item.first_position;
+                if (!open) {
 #pragma unroll
-            for (int i = 0; i < 64; ++i) tops[i & 3] = fmaxf(tops[i & 3], v[i]);
-            const float mine = fmaxf(fmaxf(tops[0], tops[1]), fmaxf(tops[2], tops[3]));
-            maxima[((j & 1) * 2 + half) * ROWS + row] = mine;
-            asm volatile("bar.sync %0, 64;" ::"r"(pair_barrier) : "memory");
-            const float top = fmaxf(mine, maxima[((j & 1) * 2 + (half ^ 1)) * ROWS + row]);
-            const float new_m = fmaxf(m, top * scale_log2);
-            const float previous = correction;
-            const float moved = new_m == -INFINITY ? 1.f : fast_exp2(m - new_m);
-            const float shift = new_m == -INFINITY ? 0.f : new_m;
-            float sums[4] = {0.f, 0.f, 0.f, 0.f};
-            unsigned char* p_tile_row = p_row + (j & 1) * P_BYTES;
-#pragma unroll
-            for (int chunk = 0; chunk < 8; ++chunk) {
-                float p[8];
-#pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    p[i] = fast_exp2(fmaf(v[chunk * 8 + i], scale_log2, -shift));   // exp2(-inf) = 0
-                    sums[i & 3] += p[i];
+                    for (int i = 0; i < MY_KEYS; ++i)
+                        if (!(key0 + i >= limit_lo && key0 + i <= limit_hi)) v[i] = -INFINITY;
                 }
-                uint4 packed;
-                packed.x = pack_bf16(p[0], p[1]);
-                packed.y = pack_bf16(p[2], p[3]);
-                packed.z = pack_bf16(p[4], p[5]);
-                packed.w = pack_bf16(p[6], p[7]);
-                *reinterpret_cast<uint4*>(p_tile_row + ((chunk ^ (row & 7)) << 4)) = packed;
-            }
-            l = l * moved + (sums[0] + sums[1]) + (sums[2] + sums[3]);
-            m = new_m;
-            // P is written and the scores are read: tell the product warp
-            fence_async_shared();
-            fence_before_sync();
-            __syncwarp();
-            if (lane == 0) barrier_arrive(p_ready(j & 1));
-            // the previous tile's P V, scaled by how far the maximum had moved then
-            correction = previous;
-            if (j > 0) ok = add_out(j - 1);
-            correction = moved;
-        }
-        if (ok && tile_count > 0) ok = add_out(tile_count - 1);
-        // the row's sum: both halves used the same maxima, so their sums add
-        maxima[half * ROWS + row] = l;
-        asm volatile("bar.sync %0, 64;" ::"r"(pair_barrier) : "memory");
-        l += maxima[(half ^ 1) * ROWS + row];
-        if (ok && valid) {
-            const float inv = l > 0.f ? 1.f / l : 0.f;
-            const int head = kv_head * group + row % group;
-            bf16* dst = out + ((size_t)(first_token + token_start + token) * heads + head) * HD +
-                        half * 32;
+                float tops[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-            for (int piece = 0; piece < 4; ++piece) {
-                uint4 packed;
-                packed.x = pack_bf16(o[piece * 8 + 0] * inv, o[piece * 8 + 1] * inv);
-                packed.y = pack_bf16(o[piece * 8 + 2] * inv, o[piece * 8 + 3] * inv);
-                packed.z = pack_bf16(o[piece * 8 + 4] * inv, o[piece * 8 + 5] * inv);
-                packed.w = pack_bf16(o[piece * 8 + 6] * inv, o[piece * 8 + 7] * inv);
-                *reinterpret_cast<uint4*>(dst + piece * 8) = packed;
+                for (int i = 0; i < MY_KEYS; ++i) tops[i & 3] = fmaxf(tops[i & 3], v[i]);
+                float top = fmaxf(fmaxf(tops[0], tops[1]), fmaxf(tops[2], tops[3]));
+                maxima[((t & 1) * PARTS + part) * ROWS + row] = top;
+                asm volatile("bar.sync %0, %1;" ::"r"(row_barrier), "n"(PARTS * 32) : "memory");
+#pragma unroll
+                for (int other = 0; other < PARTS; ++other)
+                    top = fmaxf(top, maxima[((t & 1) * PARTS + other) * ROWS + row]);
+                const float new_m = fmaxf(m, top * scale_log2);
+                const float previous = correction;
+                const float moved = new_m == -INFINITY ? 1.f : fast_exp2(m - new_m);
+                const float shift = new_m == -INFINITY ? 0.f : new_m;
+                float partial[4] = {0.f, 0.f, 0.f, 0.f};
+                unsigned char* p_tile_row = p_row + (t & 1) * P_BYTES;
+#pragma unroll
+                for (int piece = 0; piece < PIECES; ++piece) {
+                    float p[8];
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        p[i] = fast_exp2(fmaf(v[piece * 8 + i], scale_log2, -shift));   // exp2(-inf) = 0
+                        partial[i & 3] += p[i];
+                    }
+                    uint4 packed;
+                    packed.x = pack_bf16(p[0], p[1]);
+                    packed.y = pack_bf16(p[2], p[3]);
+                    packed.z = pack_bf16(p[4], p[5]);
+                    packed.w = pack_bf16(p[6], p[7]);
+                    *reinterpret_cast<uint4*>(p_tile_row + (((first_piece + piece) ^ (row & 7)) << 4)) =
+                        packed;
+                }
+                l = l * moved + (partial[0] + partial[1]) + (partial[2] + partial[3]);
+                m = new_m;
+                // P is written and the scores are read: tell the product warp
+                fence_async_shared();
+                fence_before_sync();
+                __syncwarp();
+                if (lane == 0) barrier_arrive(p_ready(t & 1));
+                // the previous tile's P V, scaled by how far the maximum had moved then
+                correction = previous;
+                if (j > 0) ok = add_out(t - 1);
+                correction = moved;
+            }
+            if (ok) ok = add_out(t - 1);
+            // the row's sum: all parts used the same maxima, so their sums add
+            sums[part * ROWS + row] = l;
+            asm volatile("bar.sync %0, %1;" ::"r"(row_barrier), "n"(PARTS * 32) : "memory");
+            l = 0.f;
+#pragma unroll
+            for (int other = 0; other < PARTS; ++other) l += sums[other * ROWS + row];
+            if (ok && valid) {
+                const float inv = l > 0.f ? 1.f / l : 0.f;
+                const int head = item.kv_head * group + row % group;
+                bf16* dst = out + ((size_t)(item.q_token + token) * heads + head) * HD + part * MY_DIMS;
+#pragma unroll
+                for (int piece = 0; piece < MY_DIMS / 8; ++piece) {
+                    uint4 packed;
+                    packed.x = pack_bf16(o[piece * 8 + 0] * inv, o[piece * 8 + 1] * inv);
+                    packed.y = pack_bf16(o[piece * 8 + 2] * inv, o[piece * 8 + 3] * inv);
+                    packed.z = pack_bf16(o[piece * 8 + 4] * inv, o[piece * 8 + 5] * inv);
+                    packed.w = pack_bf16(o[piece * 8 + 6] * inv, o[piece * 8 + 7] * inv);
+                    *reinterpret_cast<uint4*>(dst + piece * 8) = packed;
+                }
             }
         }
     }
@@ -485,6 +548,7 @@ typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, v
                                 const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                 CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 EncodeTiled g_encode = nullptr;
+int g_sm_count = 0;
 
 bool find_encoder() {
     if (g_encode != nullptr) return true;
@@ -568,11 +632,21 @@ MLXONE_API int mlxone_attention_prefill_tcgen05(const void* q, const void* kv, c
         mlxone_set_error("attention_prefill_tcgen05: %s", cudaGetErrorString(err));
         return 2;
     }
-    const dim3 grid((tokens + tile_tokens - 1) / tile_tokens + requests, kv_heads);
-    attention_tcgen05_kernel<<<grid, THREADS, SHARED_BYTES, stream>>>(
+    // persistent blocks, one per SM; more only if a block would get more items than it can list
+    if (g_sm_count == 0) {
+        int device = 0;
+        cudaGetDevice(&device);
+        cudaDeviceGetAttribute(&g_sm_count, cudaDevAttrMultiProcessorCount, device);
+        if (g_sm_count <= 0) g_sm_count = 148;
+    }
+    const int token_tiles = (tokens + tile_tokens - 1) / tile_tokens + requests;     // an upper bound
+    const long long all_items = (long long)token_tiles * kv_heads;
+    long long blocks = all_items < g_sm_count ? all_items : g_sm_count;
+    if ((all_items + blocks - 1) / blocks > MAX_ITEMS) blocks = (all_items + MAX_ITEMS - 1) / MAX_ITEMS;
+    attention_tcgen05_kernel<<<dim3((unsigned)blocks), THREADS, SHARED_BYTES, stream>>>(
         map_q, map_kv, value_rows, block_table, table_width, page_size, box_keys, request_start,
         history, static_cast<bf16*>(out), requests, heads, kv_heads, scale * 1.4426950408889634f,
-        window, error_flag);
+        window, token_tiles, error_flag);
     MLXONE_LAUNCH_CHECK("attention_prefill_tcgen05");
     return 0;
 }
