@@ -121,6 +121,110 @@ __global__ void short_conv_wide_kernel(const __nv_bfloat16* __restrict__ bcx,
     *reinterpret_cast<uint4*>(out + (size_t)t * hidden + d) = packed;
 }
 
+// Many tokens (prefill): a thread takes 8 neighbouring channels of RUN consecutive tokens. The
+// rows of the run are loaded first (they do not wait for one another), and g of the taps - 1
+// positions before a token stays in registers from token to token, so that a row is read once
+// for the run and not once per tap. A request that begins inside the run starts afresh.
+template <int TAPS, int RUN>
+__global__ void __launch_bounds__(256)
+short_conv_run_kernel(const __nv_bfloat16* __restrict__ bcx, const float* __restrict__ kernel,
+                      const float* __restrict__ bias, const __nv_bfloat16* __restrict__ state,
+                      const int* __restrict__ slots, const int* __restrict__ token_request,
+                      const int* __restrict__ request_start, const int* __restrict__ history,
+                      __nv_bfloat16* __restrict__ out, int tokens, int hidden) {
+    using T = __nv_bfloat16;
+    griddep_launch();
+    griddep_wait();
+    const int groups = hidden / 8;
+    const long long item = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const int t0 = (int)(item / groups) * RUN;
+    if (t0 >= tokens) return;
+    const int d = (int)(item % groups) * 8;
+    const size_t row = (size_t)3 * hidden;
+    auto unpack = [](const uint4& v, float (&f)[8]) {
+        const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { f[2 * i] = __low2float(p[i]); f[2 * i + 1] = __high2float(p[i]); }
+    };
+    uint4 raw_b[RUN], raw_c[RUN], raw_x[RUN];
+#pragma unroll
+    for (int i = 0; i < RUN; ++i) {
+        const int t = min(t0 + i, tokens - 1);
+        const T* src = bcx + (size_t)t * row + d;
+        raw_b[i] = *reinterpret_cast<const uint4*>(src);
+        raw_c[i] = *reinterpret_cast<const uint4*>(src + hidden);
+        raw_x[i] = *reinterpret_cast<const uint4*>(src + 2 * hidden);
+    }
+    // this thread's 8 * taps kernel weights lie together in memory
+    float weights[8 * TAPS], offset[8];
+    {
+        const float4* src = reinterpret_cast<const float4*>(kernel + (size_t)d * TAPS);
+#pragma unroll
+        for (int j = 0; j < 2 * TAPS; ++j) {
+            const float4 v = src[j];
+            weights[4 * j] = v.x; weights[4 * j + 1] = v.y;
+            weights[4 * j + 2] = v.z; weights[4 * j + 3] = v.w;
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) offset[i] = bias ? bias[d + i] : 0.f;
+    }
+    float past[TAPS > 1 ? TAPS - 1 : 1][8];      // g of the positions before the token, oldest first
+    int end = -1;                                 // where the current request's tokens end
+#pragma unroll
+    for (int i = 0; i < RUN; ++i) {
+        const int t = t0 + i;
+        if (t >= tokens) break;
+        if (t >= end) {
+            // the run's first token, or a request begins here: g of the positions before it
+            // comes from this step's rows, from the request's state, or is zero
+            const int r = token_request[t];
+            const int first = request_start[r];
+            end = request_start[r + 1];
+            const int index = t - first, position = history[r] + index;
+#pragma unroll
+            for (int k = 0; k < TAPS - 1; ++k) {
+                const int back = TAPS - 1 - k;
+                if (index - back >= 0) {
+                    const T* src = bcx + (size_t)(t - back) * row + d;
+                    float b[8], x[8];
+                    unpack(*reinterpret_cast<const uint4*>(src), b);
+                    unpack(*reinterpret_cast<const uint4*>(src + 2 * hidden), x);
+#pragma unroll
+                    for (int c = 0; c < 8; ++c) past[k][c] = round_to<T>(b[c] * x[c]);
+                } else if (position - back >= 0) {
+                    const int s = TAPS - 1 + (index - back);
+                    unpack(*reinterpret_cast<const uint4*>(
+                               state + ((size_t)slots[r] * (TAPS - 1) + s) * hidden + d), past[k]);
+                } else {
+#pragma unroll
+                    for (int c = 0; c < 8; ++c) past[k][c] = 0.f;
+                }
+            }
+        }
+        float b[8], gate[8], x[8], y[8];
+        unpack(raw_b[i], b);
+        unpack(raw_c[i], gate);
+        unpack(raw_x[i], x);
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+            const float g = round_to<T>(b[c] * x[c]);
+            float sum = offset[c];
+#pragma unroll
+            for (int k = 0; k < TAPS - 1; ++k) sum = fmaf(weights[c * TAPS + k], past[k][c], sum);
+            y[c] = fmaf(weights[c * TAPS + TAPS - 1], g, sum);
+#pragma unroll
+            for (int k = 0; k + 1 < TAPS - 1; ++k) past[k][c] = past[k + 1][c];
+            if (TAPS > 1) past[TAPS - 2][c] = g;
+        }
+        uint4 packed;
+        __nv_bfloat162* q = reinterpret_cast<__nv_bfloat162*>(&packed);
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+            q[c] = __floats2bfloat162_rn(gate[2 * c] * y[2 * c], gate[2 * c + 1] * y[2 * c + 1]);
+        *reinterpret_cast<uint4*>(out + (size_t)t * hidden + d) = packed;
+    }
+}
+
 // New state after the step: row s holds g at position (history + n) - (taps-1) + s.
 template <typename T>
 __global__ void short_conv_state_kernel(const T* __restrict__ bcx, T* __restrict__ state,
@@ -232,7 +336,19 @@ MLXONE_API int mlxone_short_conv(const void* bcx, const float* kernel, const flo
                           (reinterpret_cast<uintptr_t>(bcx) & 15) == 0 &&
                           (reinterpret_cast<uintptr_t>(state) & 15) == 0 &&
                           (reinterpret_cast<uintptr_t>(out) & 15) == 0;
-        if (wide) {
+        if (wide && tokens >= 256) {
+            constexpr int RUN = 4;
+            const long long items = (long long)ceil_div_host(tokens, RUN) * (hidden / 8);
+#define RUNS(TAPS)                                                                                 \
+    launch_kernel(short_conv_run_kernel<TAPS, RUN>, dim3(ceil_div_host(items, 256)), dim3(256), 0, \
+                  stream, true, (const T*)bcx, kernel, bias, (const T*)state, slots,              \
+                  token_request, request_start, history, (T*)out, tokens, hidden)
+            if (taps == 1) RUNS(1);
+            else if (taps == 2) RUNS(2);
+            else if (taps == 3) RUNS(3);
+            else RUNS(4);
+#undef RUNS
+        } else if (wide) {
             const long long items = (long long)tokens * (hidden / 8);
 #define WIDE(TAPS)                                                                              \
     launch_kernel(short_conv_wide_kernel<TAPS>, dim3(ceil_div_host(items, 256)), dim3(256), 0,  \

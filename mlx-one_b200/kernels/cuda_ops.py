@@ -187,7 +187,7 @@ class CudaOps:
         evenness = tiles / (-(-tiles // self._sm_count) * self._sm_count)
         if epilogue == self._SWIGLU:
             return evenness >= 0.6
-        if epilogue == self._ADD and a.shape[1] > 4096:
+        if a.shape[1] > 4096 and tiles < 2 * self._sm_count:
             return False
         return evenness >= 0.85
 

@@ -208,12 +208,16 @@ def test_tcgen05_product(ops, m, n, k):
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("hidden,taps,bias", [(48, 3, False), (200, 4, True), (64, 2, True),
                                               (32, 1, False), (96, 7, False), (204, 3, True)])
-@pytest.mark.parametrize("decode", [False, True])
+@pytest.mark.parametrize("decode", [False, True, "long"])
 def test_short_conv(ops, plain, dtype, hidden, taps, bias, decode):
-    """Portions that start at position 0, in the middle, shorter than the kernel is wide; and
-    single tokens (the fused decode kernel) at positions 0, 1 and beyond."""
+    """Portions that start at position 0, in the middle, shorter than the kernel is wide; single
+    tokens (the fused decode kernel) at positions 0, 1 and beyond; and so many tokens that the
+    kernel for runs of tokens is taken, with requests that begin inside a run."""
     torch.manual_seed(4)
-    portions, histories = ([1] * 5, [0, 7, 3, 1, 2]) if decode else ([5, 1, 9, 2, 1], [0, 7, 3, 0, 1])
+    if decode == "long":
+        portions, histories = [301, 1, 2, 43, 1], [0, 7, 0, 1, 0]
+    else:
+        portions, histories = ([1] * 5, [0, 7, 3, 1, 2]) if decode else ([5, 1, 9, 2, 1], [0, 7, 3, 0, 1])
     ctx, _, _ = make_batch(portions, histories, 4, DEVICE)
     slots = torch.tensor([4, 0, 2, 5, 1], dtype=torch.int32)
     state = torch.randn(6, max(taps - 1, 1), hidden).to(dtype)
