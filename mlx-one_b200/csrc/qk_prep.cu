@@ -106,8 +106,32 @@ qk_prep_wide_kernel(const __nv_bfloat16* __restrict__ qkv, const float* __restri
     const int t = blockIdx.x;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int slots = heads + 2 * kv_heads;
-    const int position = positions[t];
     const int e0 = E * lane;
+    // AHEAD of the warp's heads at a time: their loads are issued together, the first ones
+    // before anything that waits for the token's position or page
+    constexpr int AHEAD = 6;
+    const T* row = qkv + (size_t)t * slots * HD;
+    float held[AHEAD][E];
+    auto load_heads = [&](int base) {
+#pragma unroll
+        for (int a = 0; a < AHEAD; ++a) {
+            const int slot = base + a * WARPS;
+            if (slot >= slots) continue;
+            const T* src = row + (size_t)slot * HD + e0;
+            if (E == 1) {
+                held[a][0] = __bfloat162float(src[0]);
+            } else {
+#pragma unroll
+                for (int i = 0; i < E; i += 2) {
+                    const __nv_bfloat162 pair = *reinterpret_cast<const __nv_bfloat162*>(src + i);
+                    held[a][i] = __low2float(pair);
+                    held[a][i + 1] = __high2float(pair);
+                }
+            }
+        }
+    };
+    load_heads(warp);
+    const int position = positions[t];
     float cosine[E], sine[E], q_scale[E], k_scale[E];
 #pragma unroll
     for (int i = 0; i < E; ++i) {
@@ -133,55 +157,49 @@ qk_prep_wide_kernel(const __nv_bfloat16* __restrict__ qkv, const float* __restri
             page_base = kv + ((size_t)page * kv_heads * page_size + position % page_size) * HD;
         }
     }
-    const T* row = qkv + (size_t)t * slots * HD;
-    for (int slot = warp; slot < slots; slot += WARPS) {
-        const bool is_q = slot < heads;
-        const bool is_k = !is_q && slot < heads + kv_heads;
-        if (!is_q && page_base == nullptr) continue;
-        float v[E];
-        const T* src = row + (size_t)slot * HD + e0;
-        if (E == 1) {
-            v[0] = __bfloat162float(src[0]);
-        } else {
+    for (int base = warp; base < slots; base += AHEAD * WARPS) {
+        if (base != warp) load_heads(base);
 #pragma unroll
-            for (int i = 0; i < E; i += 2) {
-                const __nv_bfloat162 pair = *reinterpret_cast<const __nv_bfloat162*>(src + i);
-                v[i] = __low2float(pair);
-                v[i + 1] = __high2float(pair);
-            }
-        }
-        if (is_q || is_k) {
-            const float* scale = is_q ? q_scale : k_scale;
-            if ((is_q ? q_weight : k_weight) != nullptr) {
-                float sum = 0.f;
+        for (int a = 0; a < AHEAD; ++a) {
+            const int slot = base + a * WARPS;
+            if (slot >= slots) continue;
+            const bool is_q = slot < heads;
+            const bool is_k = !is_q && slot < heads + kv_heads;
+            if (!is_q && page_base == nullptr) continue;
+            float (&v)[E] = held[a];
+            if (is_q || is_k) {
+                const float* scale = is_q ? q_scale : k_scale;
+                if ((is_q ? q_weight : k_weight) != nullptr) {
+                    float sum = 0.f;
 #pragma unroll
-                for (int i = 0; i < E; ++i) sum += v[i] * v[i];
-                sum = warp_sum(sum);
-                const float inv = rsqrtf(sum / (float)HD + eps);
+                    for (int i = 0; i < E; ++i) sum += v[i] * v[i];
+                    sum = warp_sum(sum);
+                    const float inv = rsqrtf(sum / (float)HD + eps);
 #pragma unroll
-                for (int i = 0; i < E; ++i) v[i] = v[i] * inv * scale[i];
-            }
-            if (inv_freq != nullptr) {
+                    for (int i = 0; i < E; ++i) v[i] = v[i] * inv * scale[i];
+                }
+                if (inv_freq != nullptr) {
 #pragma unroll
-                for (int i = 0; i < E; ++i) {
-                    const float partner = __shfl_xor_sync(0xffffffffu, v[i], 16);
-                    v[i] = v[i] * cosine[i] + partner * sine[i];
+                    for (int i = 0; i < E; ++i) {
+                        const float partner = __shfl_xor_sync(0xffffffffu, v[i], 16);
+                        v[i] = v[i] * cosine[i] + partner * sine[i];
+                    }
                 }
             }
-        }
-        T* dst;
-        if (is_q) {
-            dst = q_out + ((size_t)t * heads + slot) * HD + e0;
-        } else {
-            const int kv_head = is_k ? slot - heads : slot - heads - kv_heads;
-            dst = page_base + (is_k ? 0 : kv_half) + (size_t)kv_head * page_size * HD + e0;
-        }
-        if (E == 1) {
-            dst[0] = __float2bfloat16_rn(v[0]);
-        } else {
+            T* dst;
+            if (is_q) {
+                dst = q_out + ((size_t)t * heads + slot) * HD + e0;
+            } else {
+                const int kv_head = is_k ? slot - heads : slot - heads - kv_heads;
+                dst = page_base + (is_k ? 0 : kv_half) + (size_t)kv_head * page_size * HD + e0;
+            }
+            if (E == 1) {
+                dst[0] = __float2bfloat16_rn(v[0]);
+            } else {
 #pragma unroll
-            for (int i = 0; i < E; i += 2)
-                *reinterpret_cast<__nv_bfloat162*>(dst + i) = __floats2bfloat162_rn(v[i], v[i + 1]);
+                for (int i = 0; i < E; i += 2)
+                    *reinterpret_cast<__nv_bfloat162*>(dst + i) = __floats2bfloat162_rn(v[i], v[i + 1]);
+            }
         }
     }
 }
