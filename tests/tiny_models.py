@@ -2,7 +2,7 @@
 
 The configurations differ in every size and option: layer order and first layer kind, hidden
 size, head count, key-head groups (2 per key head, all on one key head, 3 per key head), head
-size (16, 32, 48), feed-forward rule (given width, auto-adjusted), vocabulary (a power of two
+size (16, 32, 48, 64), feed-forward rule (given width, auto-adjusted), vocabulary (a power of two
 and not), rope theta, convolution width (3, 4, 2) and bias, tied and separate head, norm eps,
 and a sliding window in one of them.
 """
@@ -37,6 +37,15 @@ TINY_C = dict(
     block_ffn_dim_multiplier=1.3, vocab_size=777, rope_theta=50000.0, sliding_window=19,
     conv_L_cache=2, conv_bias=False, tie_embedding=True, norm_eps=3e-6)
 
+# head size 64 with pages of 8 keys: prefill attention takes the tcgen05 kernel (two query heads
+# stacked per key head, a window inside a key tile), everything else stays tiny
+TINY_D = dict(
+    model_type="lfm2", num_hidden_layers=4,
+    layer_types=["full_attention", "conv", "sliding_attention", "full_attention"],
+    hidden_size=128, num_attention_heads=2, num_key_value_heads=1,
+    block_auto_adjust_ff_dim=False, block_ff_dim=136, vocab_size=301, rope_theta=20000.0,
+    sliding_window=40, conv_L_cache=3, conv_bias=True, tie_embedding=False, norm_eps=2e-5)
+
 # a size at which the kernels for large steps (tcgen05 products, wide conv and q/k kernels) run
 MID = dict(
     model_type="lfm2", num_hidden_layers=5,
@@ -46,7 +55,8 @@ MID = dict(
     vocab_size=3001, rope_theta=1000000.0, sliding_window=150, conv_L_cache=3, conv_bias=False,
     tie_embedding=True, norm_eps=1e-5)
 
-CONFIGS = {"A": (TINY_A, 0, 4), "B": (TINY_B, 1, 8), "C": (TINY_C, 2, 16)}   # config, seed, page
+CONFIGS = {"A": (TINY_A, 0, 4), "B": (TINY_B, 1, 8), "C": (TINY_C, 2, 16),
+           "D": (TINY_D, 5, 8)}   # config, seed, page
 ALL_CONFIGS = {**CONFIGS, "MID": (MID, 3, 16)}
 
 # (atol, rtol) on logits: |engine - plain| <= atol + rtol * |plain|, as the reference gates
