@@ -40,7 +40,6 @@ namespace {
 using bf16 = __nv_bfloat16;
 constexpr int HD = 64;
 constexpr int ROWS = 128;              // query rows per block
-constexpr int KEYS = 128;              // keys per tile
 constexpr int STAGES = 3;              // ring of key/value tiles
 constexpr int PARTS = 2;               // threads that share a query row
 constexpr int COPY_WARP = 4 * PARTS, MMA_WARP = 4 * PARTS + 1;
@@ -48,12 +47,23 @@ constexpr int THREADS = (4 * PARTS + 2) * 32;     // softmax warps, the copy war
 constexpr int WAIT_LIMIT = 1 << 24;
 constexpr int ERROR_WAIT = 9;
 constexpr int Q_BYTES = ROWS * HD * 2;
-constexpr int K_BYTES = KEYS * HD * 2;
-constexpr int STAGE_BYTES = 2 * K_BYTES;
-constexpr int P_BYTES = ROWS * KEYS * 2;
-constexpr int SHARED_BYTES = 2 * Q_BYTES + STAGES * STAGE_BYTES + 2 * P_BYTES + 1024;
+
+// Two shapes of the kernel. With 128 keys a tile a block fills an SM (tensor memory: scores
+// 2 x 128 columns, P V 2 x 64); with 64 keys a tile two blocks share an SM, and while one waits
+// for a product or a barrier the other computes: faster when there are items for all of them,
+// slower when there are not, since a block then walks its keys in more, smaller steps.
+template <int KEYS_>
+struct Shape {
+    static constexpr int KEYS = KEYS_;
+    static constexpr int BLOCKS_PER_SM = KEYS == 64 ? 2 : 1;
+    static constexpr int Q_BUFFERS = KEYS == 64 ? 1 : 2;           // query tiles in shared memory
+    static constexpr int K_BYTES = KEYS * HD * 2;
+    static constexpr int STAGE_BYTES = 2 * K_BYTES;
+    static constexpr int P_BYTES = ROWS * KEYS * 2;
+    static constexpr int SHARED_BYTES = Q_BUFFERS * Q_BYTES + STAGES * STAGE_BYTES + 2 * P_BYTES + 1024;
+    static constexpr int TMEM_COLUMNS = KEYS == 64 ? 256 : 512;    // scores 2 x KEYS, P V 2 x 64
+};
 constexpr int MAX_ITEMS = 128;         // (token tile, key head) pairs one block may be given
-constexpr int TMEM_COLUMNS = 512;      // scores 2 x 128, P V 2 x 64: 384, rounded to a power of two
 
 __device__ __forceinline__ uint32_t shared_address(const void* p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -191,7 +201,8 @@ struct Item {
     int tile_count;
 };
 
-__global__ void __launch_bounds__(THREADS)
+template <int KEYS>
+__global__ void __launch_bounds__(THREADS, Shape<KEYS>::BLOCKS_PER_SM)
 attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q,
                          const __grid_constant__ CUtensorMap map_kv, long long value_rows,
                          const int* __restrict__ block_table, int table_width, int page_size,
@@ -199,6 +210,9 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q,
                          const int* __restrict__ history, bf16* __restrict__ out, int requests,
                          int heads, int kv_heads, float scale_log2, int window, int token_tiles,
                          int* __restrict__ error_flag) {
+    using S = Shape<KEYS>;
+    constexpr int Q_BUFFERS = S::Q_BUFFERS, K_BYTES = S::K_BYTES, STAGE_BYTES = S::STAGE_BYTES;
+    constexpr int P_BYTES = S::P_BYTES, TMEM_COLUMNS = S::TMEM_COLUMNS;
     extern __shared__ unsigned char shared_raw[];
     // q_full[2], q_empty[2]; kv_full[s], kv_empty[s]; s_ready[b], p_ready[b], o_ready[b]
     __shared__ __align__(8) unsigned long long barriers[4 + 2 * STAGES + 6];
@@ -247,7 +261,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q,
 
     const uint32_t base = (shared_address(shared_raw) + 1023u) & ~1023u;
     const uint32_t q_tiles = base;
-    const uint32_t stages = base + 2 * Q_BYTES;
+    const uint32_t stages = base + Q_BUFFERS * Q_BYTES;
     const uint32_t p_tiles = stages + STAGES * STAGE_BYTES;
     unsigned char* generic_base = shared_raw + (base - shared_address(shared_raw));
     auto q_full = [&](int b) { return shared_address(&barriers[b]); };
@@ -274,7 +288,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q,
     }
     // stages start as zeros: a page that is skipped must not show what shared memory held
     {
-        uint4* stage_words = reinterpret_cast<uint4*>(generic_base + 2 * Q_BYTES);
+        uint4* stage_words = reinterpret_cast<uint4*>(generic_base + Q_BUFFERS * Q_BYTES);
         for (int i = threadIdx.x; i < STAGES * STAGE_BYTES / 16; i += THREADS)
             stage_words[i] = make_uint4(0u, 0u, 0u, 0u);
         fence_async_shared();
@@ -300,11 +314,12 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q,
             const Item item = items[n];
             if (item.request < 0) continue;
             if (lane == 0) {
-                ok = barrier_wait(q_empty(taken & 1), ((taken >> 1) & 1) ^ 1, error_flag);
+                const int qb = taken % Q_BUFFERS;
+                ok = barrier_wait(q_empty(qb), ((taken / Q_BUFFERS) & 1) ^ 1, error_flag);
                 if (ok) {
-                    barrier_expect(q_full(taken & 1), Q_BYTES);
-                    tma_load_3d(q_tiles + (taken & 1) * Q_BYTES, &map_q, 0, item.kv_head * group,
-                                item.q_token, q_full(taken & 1));
+                    barrier_expect(q_full(qb), Q_BYTES);
+                    tma_load_3d(q_tiles + qb * Q_BYTES, &map_q, 0, item.kv_head * group,
+                                item.q_token, q_full(qb));
                 }
             }
             ok = __shfl_sync(0xffffffffu, ok, 0);
@@ -358,9 +373,9 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q,
             // scores of the tile at `place` into score buffer t & 1
             auto scores = [&](const Place& place) {
                 const int tile_count = items[place.n].tile_count;
-                const int qb = place.taken & 1, s = place.t % STAGES;
+                const int qb = place.taken % Q_BUFFERS, s = place.t % STAGES;
                 if (place.j == 0 &&
-                    !barrier_wait(q_full(qb), (place.taken >> 1) & 1, error_flag)) return false;
+                    !barrier_wait(q_full(qb), (place.taken / Q_BUFFERS) & 1, error_flag)) return false;
                 if (!barrier_wait(kv_full(s), (place.t / STAGES) & 1, error_flag)) return false;
                 fence_after_sync();
                 const uint64_t q_desc = operand_descriptor(q_tiles + qb * Q_BYTES);
@@ -417,7 +432,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q,
         const uint32_t lanes = (uint32_t)((warp & 3) * 32) << 16;
         // this thread's pieces of P: block (of 64 keys) and first 16-byte piece within its row
         const int first_piece = (part * MY_KEYS % 64) / 8;
-        unsigned char* p_row = generic_base + 2 * Q_BYTES + STAGES * STAGE_BYTES +
+        unsigned char* p_row = generic_base + Q_BUFFERS * Q_BYTES + STAGES * STAGE_BYTES +
                                (part * MY_KEYS / 64) * (ROWS * 128) + (row >> 3) * 1024 +
                                (row & 7) * 128;
         const int row_barrier = 1 + (warp & 3);            // named barrier of the row's warps
@@ -566,7 +581,8 @@ bool supported(int head_dim, int heads, int kv_heads, int page_size) {
     const int group = heads / kv_heads;
     if (group > ROWS || ROWS % group != 0) return false;
     if (page_size < 8 || page_size % 8 != 0) return false;
-    return page_size <= KEYS ? KEYS % page_size == 0 : page_size % KEYS == 0;
+    // pages divide a tile of 64 keys (and so one of 128), or are whole tiles
+    return page_size <= 64 ? 64 % page_size == 0 : page_size % 128 == 0;
 }
 
 }  // namespace
@@ -598,9 +614,20 @@ MLXONE_API int mlxone_attention_prefill_tcgen05(const void* q, const void* kv, c
     MLXONE_REQUIRE(table_width > 0 && pages > 0, "attention_prefill_tcgen05: bad page geometry");
     const int group = heads / kv_heads;
     const int tile_tokens = ROWS / group;
-    const int box_keys = page_size < KEYS ? page_size : KEYS;
     const long long value_rows = (long long)pages * kv_heads * page_size;
     MLXONE_REQUIRE(2 * value_rows < (1LL << 31), "attention_prefill_tcgen05: the cache has too many rows");
+    if (g_sm_count == 0) {
+        int device = 0;
+        cudaGetDevice(&device);
+        cudaDeviceGetAttribute(&g_sm_count, cudaDevAttrMultiProcessorCount, device);
+        if (g_sm_count <= 0) g_sm_count = 148;
+    }
+    const int token_tiles = (tokens + tile_tokens - 1) / tile_tokens + requests;     // an upper bound
+    const long long all_items = (long long)token_tiles * kv_heads;
+    // tiles of 64 keys and two blocks an SM when there are items for all of those blocks
+    const bool small_tiles = all_items >= 2LL * g_sm_count;
+    const int keys = small_tiles ? 64 : 128;
+    const int box_keys = page_size < keys ? page_size : keys;
     CUtensorMap map_q, map_kv;
     {
         const cuuint64_t dims[3] = {HD, (cuuint64_t)heads, (cuuint64_t)tokens};
@@ -626,24 +653,19 @@ MLXONE_API int mlxone_attention_prefill_tcgen05(const void* q, const void* kv, c
                                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
         MLXONE_REQUIRE(r == CUDA_SUCCESS, "attention_prefill_tcgen05: cannot encode the cache map (%d)", (int)r);
     }
-    cudaError_t err = cudaFuncSetAttribute(attention_tcgen05_kernel,
-                                           cudaFuncAttributeMaxDynamicSharedMemorySize, SHARED_BYTES);
+    // persistent blocks, as many as the GPU holds at once; more only if a block would get more
+    // items than it can list
+    const long long resident = (long long)g_sm_count * (small_tiles ? 2 : 1);
+    long long blocks = all_items < resident ? all_items : resident;
+    if ((all_items + blocks - 1) / blocks > MAX_ITEMS) blocks = (all_items + MAX_ITEMS - 1) / MAX_ITEMS;
+    const int shared = small_tiles ? Shape<64>::SHARED_BYTES : Shape<128>::SHARED_BYTES;
+    auto kernel = small_tiles ? attention_tcgen05_kernel<64> : attention_tcgen05_kernel<128>;
+    const cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, shared);
     if (err != cudaSuccess) {
         mlxone_set_error("attention_prefill_tcgen05: %s", cudaGetErrorString(err));
         return 2;
     }
-    // persistent blocks, one per SM; more only if a block would get more items than it can list
-    if (g_sm_count == 0) {
-        int device = 0;
-        cudaGetDevice(&device);
-        cudaDeviceGetAttribute(&g_sm_count, cudaDevAttrMultiProcessorCount, device);
-        if (g_sm_count <= 0) g_sm_count = 148;
-    }
-    const int token_tiles = (tokens + tile_tokens - 1) / tile_tokens + requests;     // an upper bound
-    const long long all_items = (long long)token_tiles * kv_heads;
-    long long blocks = all_items < g_sm_count ? all_items : g_sm_count;
-    if ((all_items + blocks - 1) / blocks > MAX_ITEMS) blocks = (all_items + MAX_ITEMS - 1) / MAX_ITEMS;
-    attention_tcgen05_kernel<<<dim3((unsigned)blocks), THREADS, SHARED_BYTES, stream>>>(
+    kernel<<<dim3((unsigned)blocks), THREADS, shared, stream>>>(
         map_q, map_kv, value_rows, block_table, table_width, page_size, box_keys, request_start,
         history, static_cast<bf16*>(out), requests, heads, kv_heads, scale * 1.4426950408889634f,
         window, token_tiles, error_flag);

@@ -399,6 +399,19 @@ def test_attention_prefill_tcgen05(ops, plain, heads, kv_heads, page_size, windo
     assert ops.launches - before == 1
 
 
+@pytest.mark.parametrize("heads,kv_heads,page_size", [(32, 8, 16), (8, 4, 8), (6, 6, 64)])
+@pytest.mark.parametrize("window", [None, 300])
+def test_attention_prefill_tcgen05_many_items(ops, plain, heads, kv_heads, page_size, window):
+    """So many tokens that the kernel takes its shape with tiles of 64 keys and two blocks an
+    SM (at least two items of work for every SM)."""
+    before = ops.launches
+    attention_case(ops, plain, torch.bfloat16, heads, kv_heads, 64, page_size,
+                   portions=[2100, 1, 1900, 2, 37], histories=[0, 200, 300, 64, 1000],
+                   window=window, tensor_cores=True, tcgen05=True,
+                   spike=(2, 5 if window is None else 2000))
+    assert ops.launches - before == 1
+
+
 def test_decode_splits_are_used(ops):
     assert ops.decode_splits(1, 32, 8, 64, 4096, None) > 1
     assert ops.decode_splits(64, 32, 8, 64, 4096, None) == 1
