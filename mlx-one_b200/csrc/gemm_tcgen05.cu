@@ -235,12 +235,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
         }
     } else {
         // epilogue warps 2..5 read the lane quarters 2, 3, 0, 1 (a warp may only touch its own).
-        // A thread gets 32 columns of one row from tensor memory; the warp turns its 32 x 32
-        // piece around in shared memory so that global memory is touched a row at a time.
+        // A thread gets 32 columns of one row from tensor memory and writes them itself.
         const int quarter = warp & 3;
         float* turn = reinterpret_cast<float*>(shared_raw + (tiles - shared_address(shared_raw)) +
                                                STAGES * (A_BYTES + W_BYTES)) + (warp - 2) * 32 * 33;
         const int limit = EPILOGUE == SWIGLU ? up_offset : n;
+        // whether every row of the output starts on a 16-byte boundary
+        const bool whole_rows =
+            (EPILOGUE == STORE_BF16 || EPILOGUE == SWIGLU)
+                ? (ldo % 8 == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0)
+                : (ldo % 4 == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0);
         int round = 0;
         for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++round) {
             const int buffer = round & 1;
@@ -279,6 +283,49 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
                         asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(drained(buffer))
                                      : "memory");
                 }
+                const int row = tile_m + quarter * 32 + lane;
+                const int column0 = tile_n + c0;
+                if (whole_rows && column0 + 32 <= limit) {
+                    // This thread's 32 columns of its own row, 16 bytes at a time: the lanes
+                    // touch 32 rows, but every access fills whole sectors and there are a
+                    // quarter as many of them as with one value per access.
+                    if (row < m) {
+                        const size_t at = (size_t)row * ldo + column0;
+                        if (EPILOGUE == STORE_BF16 || EPILOGUE == SWIGLU) {
+                            uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<bf16*>(out) + at);
+#pragma unroll
+                            for (int piece = 0; piece < 4; ++piece) {
+                                uint4 packed;
+                                __nv_bfloat162* pairs = reinterpret_cast<__nv_bfloat162*>(&packed);
+#pragma unroll
+                                for (int i = 0; i < 4; ++i)
+                                    pairs[i] = __floats2bfloat162_rn(value[piece * 8 + 2 * i],
+                                                                     value[piece * 8 + 2 * i + 1]);
+                                dst[piece] = packed;
+                            }
+                        } else if (EPILOGUE == ADD_RESIDUAL) {
+                            float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(out) + at);
+                            float4 old[8];
+#pragma unroll
+                            for (int piece = 0; piece < 8; ++piece) old[piece] = dst[piece];
+#pragma unroll
+                            for (int piece = 0; piece < 8; ++piece)
+                                dst[piece] = make_float4(old[piece].x + value[piece * 4],
+                                                         old[piece].y + value[piece * 4 + 1],
+                                                         old[piece].z + value[piece * 4 + 2],
+                                                         old[piece].w + value[piece * 4 + 3]);
+                        } else {
+                            float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(out) + at);
+#pragma unroll
+                            for (int piece = 0; piece < 8; ++piece)
+                                dst[piece] = make_float4(value[piece * 4], value[piece * 4 + 1],
+                                                         value[piece * 4 + 2], value[piece * 4 + 3]);
+                        }
+                    }
+                    continue;
+                }
+                // rows that 16-byte accesses cannot take, or the ragged last columns: the warp
+                // turns its 32 x 32 piece around in shared memory and writes a row at a time
                 __syncwarp();
 #pragma unroll
                 for (int i = 0; i < 32; ++i) turn[lane * 33 + i] = value[i];

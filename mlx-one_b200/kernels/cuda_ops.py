@@ -171,9 +171,10 @@ class CudaOps:
         """Whether a[M, K] @ w[N, K]^T goes to the tcgen05 kernel. It needs 16-byte aligned
         rows and at least 128 rows (its tiles are 128 x 256 and each persistent block walks
         whole tiles), and it is chosen where it is at least about as fast as the library:
-        when its tiles fill the SMs evenly; a fused SwiGLU epilogue (which saves a pass over
-        the widest activation) is worth more unevenness; products with a long K and few
-        columns, which the library splits along K, stay with the library."""
+        when its tiles fill the SMs evenly. A fused SwiGLU epilogue (which saves a pass over
+        the widest activation) is worth more unevenness than the residual epilogue (which
+        saves the next norm kernel a read and a write of the stream); a plain product gains
+        nothing from its epilogue and goes to the library unless the tiles fit well."""
         if not (self.tcgen05_products and a.dtype == torch.bfloat16
                 and a.shape[0] >= self.tcgen05_min_rows
                 and a.shape[1] % 8 == 0 and a.stride(0) % 8 == 0 and a.stride(1) == 1
@@ -187,9 +188,11 @@ class CudaOps:
         evenness = tiles / (-(-tiles // self._sm_count) * self._sm_count)
         if epilogue == self._SWIGLU:
             return evenness >= 0.6
-        if a.shape[1] > 4096 and tiles < 2 * self._sm_count:
-            return False
-        return evenness >= 0.85
+        if epilogue == self._ADD:
+            # inside a step a long-K product with one tile a block ran slower than alone
+            # (65 us against 49 us for K = 8192 at 2048 rows); the library's does not
+            return evenness >= 0.85 and (a.shape[1] <= 4096 or tiles >= 2 * self._sm_count)
+        return evenness >= 0.9
 
     def _tcgen05_call(self, a, w, bias, out, ldo, epilogue) -> None:
         self._call("mlxone_gemm_tcgen05", _c_void_p(_ptr(a)), _c_int(a.stride(0)),
