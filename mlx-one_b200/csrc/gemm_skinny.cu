@@ -4,9 +4,9 @@
 //
 //   * persistent blocks, one per SM; a block owns a contiguous range of rows of w (outputs for
 //     every token) over the whole K, so no two blocks add into the same output and results do
-//     not depend on scheduling. The ranges are equal to within one row, whatever n is, so all
-//     SMs stream for the same time; a block walks its range in tiles of 16 rows, the last of
-//     which may be partly masked (masked rows are neither read nor written);
+//     not depend on scheduling. A block walks its range in tiles of 16 rows: whole tiles when
+//     there is at least one for every block, else ranges equal to within one row (so that all
+//     SMs stream), whose last tile is partly masked (masked rows are neither read nor written);
 //   * the block's warps take the 64-wide slices of K of the current tile in turn; every warp
 //     copies its slices of w asynchronously through a ring of its own in shared memory, and the
 //     ring runs on into the next tile, so the stream never drains inside the kernel;
@@ -116,8 +116,16 @@ skinny_gemm_kernel(const bf16* a, int lda, const bf16* __restrict__ w,
     // (gated convolution: channels; every group of 16 channels is three tiles: B, C, x)
     constexpr int PARTS = EPILOGUE == GATED_CONV ? 3 : 1;
     const int columns = EPILOGUE == SWIGLU ? up_offset : n / PARTS;
-    const int row_begin = (int)((long long)columns * blockIdx.x / gridDim.x);
-    const int row_end = (int)((long long)columns * (blockIdx.x + 1) / gridDim.x);
+    // With at least a tile for every block, blocks take whole tiles (some one more than others:
+    // a tile's fixed cost weighs more than the imbalance); with fewer, the rows are spread to
+    // within one row, so that every SM streams.
+    const int whole_tiles = (columns + ROWS - 1) / ROWS;
+    const bool by_tiles = whole_tiles >= (int)gridDim.x;
+    const int row_begin = by_tiles ? ROWS * (int)((long long)whole_tiles * blockIdx.x / gridDim.x)
+                                   : (int)((long long)columns * blockIdx.x / gridDim.x);
+    const int row_end = by_tiles
+        ? min(columns, ROWS * (int)((long long)whole_tiles * (blockIdx.x + 1) / gridDim.x))
+        : (int)((long long)columns * (blockIdx.x + 1) / gridDim.x);
     const int tile_count = PARTS * ((row_end - row_begin + ROWS - 1) / ROWS);
     const int slices = (k + SLICE - 1) / SLICE;
     const int mine = slices > wk ? (slices - wk + WARPS_K - 1) / WARPS_K : 0;   // per tile
@@ -459,7 +467,8 @@ cudaError_t launch(const void* a, int lda, const void* w, const float* bias, voi
     constexpr int PARTS = EPILOGUE == GATED_CONV ? 3 : 1;
     const int columns = EPILOGUE == SWIGLU ? up_offset : n / PARTS;
     const int grid = columns < g_sm_count ? columns : g_sm_count;
-    const int tiles_a_block = PARTS * (((columns + grid - 1) / grid + ROWS - 1) / ROWS);
+    const int whole_tiles = (columns + ROWS - 1) / ROWS;
+    const int tiles_a_block = PARTS * (whole_tiles >= grid ? (whole_tiles + grid - 1) / grid : 1);
     const size_t rings = (size_t)WARPS * STAGES * SLICE_BYTES;
     const size_t sums = (size_t)2 * WARPS * ROWS * 8 * NT * sizeof(float);
     const size_t resident = (size_t)8 * NT * ((k + 63) / 64) * 64 * 2;
