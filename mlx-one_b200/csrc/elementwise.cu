@@ -197,7 +197,9 @@ static cudaError_t launch_add_rmsnorm(float* residual, const void* delta, const 
                          (reinterpret_cast<uintptr_t>(weight) & 15) == 0 &&
                          (reinterpret_cast<uintptr_t>(out) & 7) == 0 &&
                          (reinterpret_cast<uintptr_t>(delta) & 7) == 0;
-    if (aligned && rows >= 64 && hidden <= 2048) {
+    // measured at 2048 columns: a block per row is faster up to about a thousand rows (64 rows:
+    // 1.7 us against 2.6 us), a warp per row beyond (2048 rows: 3.5 us against 5.6 us)
+    if (aligned && rows >= 1536 && hidden <= 2048) {
         const dim3 grid((rows + 7) / 8);
         if (hidden <= 512)
             return launch_kernel(add_rmsnorm_warp_kernel<T, 4>, grid, dim3(256), 0, stream, true,

@@ -63,15 +63,16 @@ def on_cpu(ctx):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("hidden,vocab", [(80, 333), (2048, 1000)])
-def test_embedding_and_norm(ops, plain, dtype, hidden, vocab):
+@pytest.mark.parametrize("hidden,vocab", [(80, 333), (2048, 1000), (1000, 50)])
+@pytest.mark.parametrize("rows", [37, 1600])      # a block per row; a warp per row
+def test_embedding_and_norm(ops, plain, dtype, hidden, vocab, rows):
     torch.manual_seed(0)
     table = torch.randn(vocab, hidden).to(dtype)
-    ids = torch.randint(0, vocab, (37,), dtype=torch.int32)
+    ids = torch.randint(0, vocab, (rows,), dtype=torch.int32)
     got = ops.embedding(ids.to(DEVICE), table.to(DEVICE))
     assert torch.equal(got.cpu(), plain.embedding(ids, table))
-    residual = torch.randn(37, hidden)
-    delta = torch.randn(37, hidden).to(dtype)
+    residual = torch.randn(rows, hidden)
+    delta = torch.randn(rows, hidden).to(dtype)
     weight = 1 + 0.1 * torch.randn(hidden)
     for use_delta in (True, False):
         res_gpu = residual.clone().to(DEVICE)
