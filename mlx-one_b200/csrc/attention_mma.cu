@@ -398,8 +398,12 @@ constexpr int DECODE_HEADS = 8;      // query heads per block (the 8-column oper
 // one is multiplied: the step is bound by the latency of memory unless enough is in flight, and
 // small blocks (few warps, many blocks per SM) spread the work evenly. The warps are merged in
 // shared memory.
-// partial results: [token, head, split] -> HD floats of unnormalised output, then max and sum
-template <int HD>
+// partial results: [token, head, split] -> HD floats of unnormalised output, then max and sum.
+// With CLUSTER the blocks of one (request, key head) form a thread-block cluster (one block per
+// split, at most 8): they leave their partial results in their own shared memory, and after a
+// barrier over the cluster block r merges head r from the others' shared memory (distributed
+// shared memory), so that neither a scratch buffer nor a merge kernel is needed.
+template <int HD, bool CLUSTER>
 __global__ void __launch_bounds__(DECODE_WARPS * 32)
 attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kv, long long kv_half,
                         const int* __restrict__ block_table, int table_width, int page_size,
@@ -583,11 +587,54 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kv,
         if (splits == 1) {
             out[((size_t)request * heads + head) * HD + d] =
                 __float2bfloat16_rn(sum > 0.f ? value / sum : 0.f);
+        } else if (CLUSTER) {
+            float* own = merge + DECODE_WARPS * DECODE_HEADS * ROW_FLOATS + row * ROW_FLOATS;
+            own[d] = value;
+            if (d == 0) { own[HD] = top; own[HD + 1] = sum; }
         } else {
             float* dst = partial + (((size_t)request * heads + head) * splits + split) * ROW_FLOATS;
             dst[d] = value;
             if (d == 0) { dst[HD] = top; dst[HD + 1] = sum; }
         }
+    }
+    if (CLUSTER && splits > 1) {
+        // every block of the cluster has left its partial results; block `split` merges the
+        // heads split, split + splits, ... reading the others' shared memory
+        asm volatile("barrier.cluster.arrive.release.aligned;\n"
+                     "barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+        const uint32_t own_base =
+            smem_address(merge + DECODE_WARPS * DECODE_HEADS * ROW_FLOATS);
+        for (int item = threadIdx.x; item < rows * HD; item += DECODE_WARPS * 32) {
+            const int row = item / HD, d = item % HD;
+            if (row % splits != split) continue;
+            float top = -INFINITY;
+            float tops[8], sums[8], values[8];
+#pragma unroll
+            for (int s = 0; s < 8; ++s) {
+                tops[s] = -INFINITY; sums[s] = 0.f; values[s] = 0.f;
+                if (s < splits) {
+                    uint32_t remote;
+                    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n"
+                                 : "=r"(remote) : "r"(own_base + row * ROW_FLOATS * 4), "r"(s));
+                    asm volatile("ld.shared::cluster.f32 %0, [%1];\n" : "=f"(tops[s]) : "r"(remote + HD * 4));
+                    asm volatile("ld.shared::cluster.f32 %0, [%1];\n" : "=f"(sums[s]) : "r"(remote + (HD + 1) * 4));
+                    asm volatile("ld.shared::cluster.f32 %0, [%1];\n" : "=f"(values[s]) : "r"(remote + d * 4));
+                    top = fmaxf(top, tops[s]);
+                }
+            }
+            float value = 0.f, sum = 0.f;
+#pragma unroll
+            for (int s = 0; s < 8; ++s) {
+                const float weight = tops[s] == -INFINITY ? 0.f : fast_exp2(tops[s] - top);
+                value += values[s] * weight;
+                sum += sums[s] * weight;
+            }
+            out[((size_t)request * heads + head0 + row) * HD + d] =
+                __float2bfloat16_rn(sum > 0.f ? value / sum : 0.f);
+        }
+        // no block may leave while another still reads its shared memory
+        asm volatile("barrier.cluster.arrive.release.aligned;\n"
+                     "barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
     }
 }
 
@@ -671,14 +718,44 @@ int launch_decode(const void* q, const void* kv, long long kv_half, const int* b
                   cudaStream_t stream) {
     using T = Tile<HD>;
     const size_t shared = decode_shared_bytes(HD);
-    auto kernel = attention_decode_kernel<HD>;
-    if (shared > 48 * 1024)
-        cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
     const int group = heads / kv_heads;
     const dim3 grid(kv_heads * ((group + DECODE_HEADS - 1) / DECODE_HEADS), requests, splits);
+    const float scale_log2 = scale * LOG2E;
+    // 2 to 8 splits without a scratch buffer: a cluster of the splits' blocks merges them itself
+    if (splits > 1 && splits <= 8 && partial == nullptr) {
+        auto kernel = attention_decode_kernel<HD, true>;
+        if (shared > 48 * 1024)
+            cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
+        cudaLaunchConfig_t config = {};
+        config.gridDim = grid;
+        config.blockDim = dim3(DECODE_WARPS * 32);
+        config.dynamicSmemBytes = shared;
+        config.stream = stream;
+        cudaLaunchAttribute attributes[2];
+        attributes[0].id = cudaLaunchAttributeClusterDimension;
+        attributes[0].val.clusterDim.x = 1;
+        attributes[0].val.clusterDim.y = 1;
+        attributes[0].val.clusterDim.z = splits;
+        attributes[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attributes[1].val.programmaticStreamSerializationAllowed = 1;
+        config.attrs = attributes;
+        config.numAttrs = mlxone_pdl_enabled() ? 2 : 1;
+        const cudaError_t err = cudaLaunchKernelEx(
+            &config, kernel, (const bf16*)q, (const bf16*)kv, kv_half, block_table, table_width,
+            page_size, positions, (bf16*)out, (float*)nullptr, heads, kv_heads, splits, scale_log2,
+            window);
+        if (err != cudaSuccess) {
+            mlxone_set_error("attention_decode: cluster launch failed: %s", cudaGetErrorString(err));
+            return 2;
+        }
+        return 0;
+    }
+    auto kernel = attention_decode_kernel<HD, false>;
+    if (shared > 48 * 1024)
+        cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
     launch_kernel(kernel, grid, dim3(DECODE_WARPS * 32), shared, stream, true, (const bf16*)q,
                   (const bf16*)kv, kv_half, block_table, table_width, page_size, positions,
-                  (bf16*)out, partial, heads, kv_heads, splits, scale * LOG2E, window);
+                  (bf16*)out, partial, heads, kv_heads, splits, scale_log2, window);
     if (splits > 1) {
         const int items = requests * heads;
         launch_kernel(attention_merge_kernel<HD>, dim3((items + 3) / 4), dim3(128), 0, stream, true,
@@ -759,7 +836,8 @@ MLXONE_API int mlxone_attention_decode(const void* q, const void* kv, const int*
                    "attention_decode: bad sizes");
     MLXONE_REQUIRE(requests <= 65535 && splits >= 1 && splits <= 65535,
                    "attention_decode: at most 65535 requests and splits");
-    MLXONE_REQUIRE(splits == 1 || partial != nullptr, "attention_decode: scratch is missing");
+    MLXONE_REQUIRE(splits <= 8 || partial != nullptr,
+                   "attention_decode: more than 8 splits need a scratch buffer");
     MLXONE_REQUIRE(page_size > 0 && pages > 0 && table_width > 0,
                    "attention_decode: bad page geometry");
     const long long kv_half = (long long)pages * kv_heads * page_size * head_dim;

@@ -64,6 +64,11 @@ class CudaOps:
         self.fused_norms = False
         self.tcgen05_min_rows = 128
         self.tcgen05_attention = True     # prefill attention with tcgen05 where it takes the geometry
+        # decode attention: up to 8 key splits merged by a thread-block cluster through distributed
+        # shared memory instead of a scratch buffer and a merge kernel. Off: alone it is faster
+        # (8 x 4096 keys 16.5 us against 17.9 us), inside the decode step slower (0.728 ms a step
+        # against 0.717 ms)
+        self.cluster_merge = False
         self.tcgen05_always = False       # tests: take the tcgen05 kernel whenever it can run
         self._sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
         # tcgen05 products (TMA + tensor memory) for more rows than the skinny kernel takes
@@ -387,8 +392,10 @@ class CudaOps:
             if ctx.max_portion == 1 and tokens == ctx.requests:
                 splits = self.decode_splits(ctx.requests, heads, kv_heads, head_dim,
                                             width * view.page_size, window)
+                if self.cluster_merge and 8 < splits <= 12 and width * view.page_size <= 8192:
+                    splits = 8          # with more keys a ninth split is worth more than the merge kernel
                 partial = None
-                if splits > 1:
+                if splits > 8 or (splits > 1 and not self.cluster_merge):
                     partial = torch.empty(ctx.requests * heads * splits * (head_dim + 2),
                                           dtype=torch.float32, device=self.device)
                 self._call("mlxone_attention_decode", _c_void_p(_ptr(q)), _c_void_p(_ptr(view.kv)),
@@ -397,8 +404,8 @@ class CudaOps:
                            _c_void_p(_ptr(out)), _c_void_p(_ptr(partial)), _c_int(ctx.requests),
                            _c_int(heads), _c_int(kv_heads), _c_int(head_dim), _c_int(splits),
                            _c_float(scale), _c_int(window or 0))
-                if splits > 1:
-                    self.launches += 1
+                if partial is not None:
+                    self.launches += 1          # the merge kernel
             elif (self.tcgen05_attention and q.dtype == torch.bfloat16
                   and self.lib.mlxone_attention_tcgen05_supports(
                       _c_int(head_dim), _c_int(heads), _c_int(kv_heads), _c_int(view.page_size))):

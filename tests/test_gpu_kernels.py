@@ -375,13 +375,19 @@ def test_attention_prefill_tensor_cores(ops, plain, heads, kv_heads, head_dim, p
 @pytest.mark.parametrize("heads,kv_heads,head_dim,page_size", SHAPES)
 @pytest.mark.parametrize("window", [None, 37])
 @pytest.mark.parametrize("histories", [[0, 1, 63, 64, 65], [700, 3, 255, 256, 1030]])
+@pytest.mark.parametrize("cluster", [False, True])
 def test_attention_decode_tensor_cores(ops, plain, heads, kv_heads, head_dim, page_size, window,
-                                       histories):
-    """One token per request: contexts at the edges of tiles, split over several blocks."""
+                                       histories, cluster):
+    """One token per request: contexts at the edges of tiles, split over several blocks, which
+    are merged by a kernel of its own or, as a thread-block cluster, among themselves."""
     far = (0, 5) if histories[0] > 100 and window is None else None
-    attention_case(ops, plain, torch.bfloat16, heads, kv_heads, head_dim, page_size,
-                   portions=[1] * 5, histories=histories, window=window, tensor_cores=True,
-                   spike=far)
+    ops.cluster_merge = cluster
+    try:
+        attention_case(ops, plain, torch.bfloat16, heads, kv_heads, head_dim, page_size,
+                       portions=[1] * 5, histories=histories, window=window, tensor_cores=True,
+                       spike=far)
+    finally:
+        ops.cluster_merge = False
 
 
 @pytest.mark.parametrize("heads,kv_heads,page_size", [
