@@ -36,6 +36,9 @@ def _dtype_code(dtype: torch.dtype) -> int:
     raise KernelError(f"kernels exist for float32 and bfloat16, not {dtype}")
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def _ptr(tensor: torch.Tensor | None) -> int | None:
     return None if tensor is None else tensor.data_ptr()
 
@@ -75,12 +78,20 @@ class CudaOps:
         self.tcgen05_products = bool(self.lib.mlxone_gemm_tcgen05_available())
         self._skinny_rows = self.lib.mlxone_gemm_skinny_max_rows()
         self._sample_scratch: torch.Tensor | None = None
+        self._device_index = self.device.index if self.device.index is not None else torch.cuda.current_device()
 
     # ------------------------------------------------------------------ plumbing
 
+    def _stream(self) -> int:
+        """The current stream's handle (the capture stream while a graph is captured). torch's
+        raw query costs a fraction of building a Stream object, which a step would pay a
+        hundred times."""
+        if _raw_stream is not None:
+            return _raw_stream(self._device_index)
+        return torch.cuda.current_stream(self.device).cuda_stream
+
     def _call(self, name: str, *args: Any) -> None:
-        stream = torch.cuda.current_stream(self.device).cuda_stream
-        code = getattr(self.lib, name)(*args, _c_void_p(stream))
+        code = getattr(self.lib, name)(*args, _c_void_p(self._stream()))
         if code != 0:
             raise KernelError(self.lib.mlxone_last_error().decode())
         self.launches += 1
