@@ -77,10 +77,15 @@ class Runner:
         self.last_greedy: torch.Tensor | None = None
         # tokens chosen on the device, by request number (see StepEntry.from_device)
         self.published = torch.zeros(cache.max_requests, dtype=torch.int32, device=self.device)
-        # CUDA graphs of decode-only steps, keyed by (requests, table widths, wanted rows)
+        # CUDA graphs of steps, keyed by shape (requests, tokens, table widths, wanted rows, ...)
         self.use_graphs = self.device.type == "cuda"
         self._graphs: dict[tuple, _DecodeGraph] = {}
         self.graph_replays = 0
+        # steps with portions: captured at their third occurrence if they have at most this many
+        # tokens (larger ones keep the GPU busy longer than the host needs to launch them)
+        self.graph_token_limit = 1024
+        self.portion_graphs = 8
+        self._portion_keys: list[tuple] = []
         if self.use_graphs:
             # library handles must exist before a capture begins
             warm = torch.zeros((8, 8), dtype=torch.bfloat16, device=self.device)
@@ -176,7 +181,11 @@ class Runner:
         widths = [_align(max(max(len(c.tables[g]) for c in caches), 1), 8)
                   for g in range(len(paged))]
         decode_only = (self.use_graphs or loop is not None) and tokens == requests
-        if decode_only:
+        # Steps with portions are captured too when their shape comes back and they are small
+        # enough to be bound by the host's launches rather than by the GPU's work.
+        portions = (self.use_graphs and not decode_only and loop is None
+                    and tokens <= self.graph_token_limit)
+        if decode_only or portions:
             # few distinct widths, so that few graphs are captured
             widths = [max(1 << (w - 1).bit_length(), 32) for w in widths]
 
@@ -240,14 +249,16 @@ class Runner:
 
         device = self._device_buffer
         captured = None
-        if decode_only:
-            key = (requests, tuple(widths), wanted, loop is not None, greedy,
+        if decode_only or portions:
+            key = (requests, tokens, tuple(widths), wanted, loop is not None, greedy,
                    any(e.from_device for e in entries))
             captured = self._graphs.get(key)
             if captured is None:
                 captured = _DecodeGraph(torch.empty(cursor, dtype=torch.int32,
                                                     device=self.device))
                 self._graphs[key] = captured
+                if portions:
+                    self._forget_old_portion_graphs(key)
             device = captured.meta
         device[:cursor].copy_(host[:cursor], non_blocking=True)
         if self.device.type == "cuda":
@@ -291,7 +302,7 @@ class Runner:
         if captured is None:
             logits = run()
         else:
-            logits = self._run_captured(captured, run)
+            logits = self._run_captured(captured, run, eager_uses=2 if portions else 1)
         self.last_greedy = None
         if isinstance(logits, tuple):
             logits, self.last_greedy = logits
@@ -344,12 +355,19 @@ class Runner:
         self.last_shape = (len(entries), len(entries))
         return out
 
-    def _run_captured(self, captured: _DecodeGraph, run) -> torch.Tensor | None:
-        """Decode-only steps of one shape: the first runs eagerly, the second is captured as
-        a CUDA graph and replayed, later ones replay it. The logits of a replay live in the
+    def _forget_old_portion_graphs(self, newest: tuple) -> None:
+        """A captured step keeps its activations' memory: of the shapes with portions only the
+        ``portion_graphs`` most recently met are kept."""
+        self._portion_keys = [k for k in self._portion_keys if k != newest] + [newest]
+        while len(self._portion_keys) > self.portion_graphs:
+            self._graphs.pop(self._portion_keys.pop(0), None)
+
+    def _run_captured(self, captured: _DecodeGraph, run, eager_uses: int = 1):
+        """Steps of one shape: the first ``eager_uses`` run eagerly, the next is captured as a
+        CUDA graph and replayed, later ones replay it. The logits of a replay live in the
         graph's memory and are overwritten by the next replay of the same shape."""
         captured.uses += 1
-        if captured.uses == 1 or not self.use_graphs:
+        if captured.uses <= eager_uses or not self.use_graphs:
             return run()
         if captured.graph is None:
             graph = torch.cuda.CUDAGraph()

@@ -88,6 +88,26 @@ def test_mixed_batches_with_page_reuse(folders, plain, name, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["B", "D"])
+def test_steps_of_a_repeated_shape_are_replayed(folders, plain, name, dtype):
+    """Steps with portions whose shape comes back (two requests, 24 + 17 tokens, then a portion
+    beside a decoded token) are captured as graphs at their third occurrence and replayed:
+    different tokens, different pages, different histories, the same shape."""
+    config, _, page = CONFIGS[name]
+    runner, cache = engine(folders[name], dtype, page, 512)
+    requests = dict(enumerate(prompts(config["vocab_size"], [42, 35] * 6, seed=9)))
+    for pair in range(6):
+        a, b = requests[2 * pair], requests[2 * pair + 1]
+        steps = [([(2 * pair, a[:24]), (2 * pair + 1, b[:17])], []),
+                 ([(2 * pair, a[24:41]), (2 * pair + 1, b[17:18])], []),
+                 ([(2 * pair, a[41:]), (2 * pair + 1, b[18:])], [2 * pair, 2 * pair + 1])]
+        got = replay(runner, cache, steps)
+        assert_close(got[2 * pair], plain[name].logits(a), dtype, f"{name} pair {pair} a")
+        assert_close(got[2 * pair + 1], plain[name].logits(b), dtype, f"{name} pair {pair} b")
+    assert runner.use_graphs and runner.graph_replays >= 9        # three shapes, pairs 2 to 5
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 def test_mid_size_model_with_long_portions(tmp_path, dtype):
     """Hidden size 512, head size 64, a feed-forward width that is no multiple of 64, and
     portions of 300+ tokens: the kernels for large steps (tcgen05 products with fused
