@@ -76,6 +76,12 @@ class CudaOps:
         self._sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
         # tcgen05 products (TMA + tensor memory) for more rows than the skinny kernel takes
         self.tcgen05_products = bool(self.lib.mlxone_gemm_tcgen05_available())
+        # 33 to 128 rows: a tcgen05 product with swapped operands (weights as the 128-row operand,
+        # K split over a thread-block cluster). Off: at 64 rows only w2 is faster than the library's
+        # product (12.0 us against 13.3 us; in_proj 10.7 us against 6.9 us, w13 + SwiGLU 21.7 us
+        # against 17.3 us), because a block's start and epilogue (about 8 us) are not hidden
+        self.swapped_products = False
+        self._swapped_rows = self.lib.mlxone_gemm_tcgen05_swapped_max_rows()
         self._skinny_rows = self.lib.mlxone_gemm_skinny_max_rows()
         self._sample_scratch: torch.Tensor | None = None
         self._device_index = self.device.index if self.device.index is not None else torch.cuda.current_device()
@@ -181,6 +187,8 @@ class CudaOps:
         """Routes bfloat16 products with more rows than the skinny kernel takes to the
         tcgen05 kernel (TMA loads, accumulator in tensor memory) instead of the library."""
         self.tcgen05_products = bool(enabled) and bool(self.lib.mlxone_gemm_tcgen05_available())
+        if not self.tcgen05_products:
+            self.swapped_products = False
         return self.tcgen05_products
 
     def _tcgen05(self, a, w, epilogue=0) -> bool:
@@ -212,6 +220,20 @@ class CudaOps:
 
     def _tcgen05_call(self, a, w, bias, out, ldo, epilogue) -> None:
         self._call("mlxone_gemm_tcgen05", _c_void_p(_ptr(a)), _c_int(a.stride(0)),
+                   _c_void_p(_ptr(w)), _c_void_p(_ptr(bias)), _c_void_p(_ptr(out)), _c_int(ldo),
+                   _c_int(a.shape[0]), _c_int(w.shape[0]), _c_int(a.shape[1]), _c_int(epilogue),
+                   _c_void_p(_ptr(self.error_flag)))
+
+    def _swapped(self, a, w) -> bool:
+        """Whether a[M, K] @ w[N, K]^T goes to the tcgen05 product with swapped operands: more
+        rows than the skinny kernel takes, at most 128, 16-byte aligned rows."""
+        return (self.swapped_products and a.dtype == torch.bfloat16
+                and self._skinny_rows < a.shape[0] <= self._swapped_rows
+                and a.shape[1] % 8 == 0 and a.stride(0) % 8 == 0 and a.stride(1) == 1
+                and w.is_contiguous() and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+    def _swapped_call(self, a, w, bias, out, ldo, epilogue) -> None:
+        self._call("mlxone_gemm_tcgen05_swapped", _c_void_p(_ptr(a)), _c_int(a.stride(0)),
                    _c_void_p(_ptr(w)), _c_void_p(_ptr(bias)), _c_void_p(_ptr(out)), _c_int(ldo),
                    _c_int(a.shape[0]), _c_int(w.shape[0]), _c_int(a.shape[1]), _c_int(epilogue),
                    _c_void_p(_ptr(self.error_flag)))
@@ -270,6 +292,11 @@ class CudaOps:
             self._skinny_call(a, w, bias, out, n,
                               self._STORE_F32 if out_dtype == torch.float32 else self._STORE)
             return out
+        if self._swapped(a, w):
+            out = torch.empty((m, n), dtype=out_dtype, device=self.device)
+            self._swapped_call(a, w, bias, out, n,
+                               self._STORE_F32 if out_dtype == torch.float32 else self._STORE)
+            return out
         if self._tcgen05(a, w, self._STORE):
             out = torch.empty((m, n), dtype=out_dtype, device=self.device)
             self._tcgen05_call(a, w, bias, out, n,
@@ -298,6 +325,11 @@ class CudaOps:
             out = torch.empty((a.shape[0], width), dtype=a.dtype, device=self.device)
             self._skinny_call(a, gate_up, None, out, width, self._SWIGLU)
             return out
+        if self._swapped(a, gate_up):
+            width = gate_up.shape[0] // 2
+            out = torch.empty((a.shape[0], width), dtype=a.dtype, device=self.device)
+            self._swapped_call(a, gate_up, None, out, width, self._SWIGLU)
+            return out
         if self._tcgen05(a, gate_up, self._SWIGLU):
             width = gate_up.shape[0] // 2
             out = torch.empty((a.shape[0], width), dtype=a.dtype, device=self.device)
@@ -313,6 +345,10 @@ class CudaOps:
         if self._skinny(a, w):
             self._need(residual, torch.float32, "residual")
             self._skinny_call(a, w, bias, residual, residual.shape[1], self._ADD)
+            return None
+        if self._swapped(a, w):
+            self._need(residual, torch.float32, "residual")
+            self._swapped_call(a, w, bias, residual, residual.shape[1], self._ADD)
             return None
         if self._tcgen05(a, w, self._ADD):
             self._need(residual, torch.float32, "residual")

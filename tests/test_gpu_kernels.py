@@ -206,6 +206,45 @@ def test_tcgen05_product(ops, m, n, k):
         ops.tcgen05_always = False
 
 
+@pytest.mark.parametrize("m", [33, 64, 65, 100, 128])
+@pytest.mark.parametrize("n,k", [(128, 128), (334, 136), (2048, 2048), (2048, 8192), (6144, 520),
+                                 (50, 64), (16384, 2048)])
+def test_tcgen05_swapped_product(ops, m, n, k):
+    """The product for 33 to 128 rows with the weights as the 128-row operand: all four
+    epilogues, ragged edges in M, N and K, clusters of 1 to 8 blocks that split K."""
+    assert ops.enable_tcgen05(True)
+    ops.swapped_products = True
+    try:
+        _swapped_product_case(ops, m, n, k)
+    finally:
+        ops.swapped_products = False
+
+
+def _swapped_product_case(ops, m, n, k):
+    torch.manual_seed(m + n + k)
+    a = torch.randn(m, k).bfloat16()
+    w = (torch.randn(n, k) / math.sqrt(k)).bfloat16()
+    bias = torch.randn(n)
+    want = a.double() @ w.double().T
+    assert ops._swapped(a.to(DEVICE), w.to(DEVICE))
+    got = ops.linear(a.to(DEVICE), w.to(DEVICE), bias.to(DEVICE))
+    torch.testing.assert_close(got.cpu().double(), want + bias.double(), atol=2e-2, rtol=2e-2)
+    logits = ops.linear(a.to(DEVICE), w.to(DEVICE), out_dtype=torch.float32)
+    torch.testing.assert_close(logits.cpu().double(), want, atol=1e-3, rtol=1e-3)
+    again = ops.linear(a.to(DEVICE), w.to(DEVICE), out_dtype=torch.float32)
+    assert torch.equal(logits, again)                      # the same sum whatever the timing
+    residual = torch.randn(m, n)
+    on_gpu = residual.clone().to(DEVICE)
+    assert ops.linear_add(a.to(DEVICE), w.to(DEVICE), bias.to(DEVICE), on_gpu) is None
+    torch.testing.assert_close(on_gpu.cpu().double(), residual.double() + want + bias.double(),
+                               atol=1e-3, rtol=1e-3)
+    gated = ops.linear_swiglu(a.to(DEVICE), w.to(DEVICE))
+    gate, up = want[:, :n // 2], want[:, n // 2:]
+    torch.testing.assert_close(gated.cpu().double(), gate * torch.sigmoid(gate) * up,
+                               atol=2e-2, rtol=2e-2)
+    ops.check_errors()
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("hidden,taps,bias", [(48, 3, False), (200, 4, True), (64, 2, True),
                                               (32, 1, False), (96, 7, False), (204, 3, True)])
