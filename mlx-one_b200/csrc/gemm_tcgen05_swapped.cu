@@ -279,11 +279,16 @@ gemm_swapped_kernel(const __grid_constant__ CUtensorMap map_w,
                 const int token = split + splits * (j0 + 4 * u);
 #pragma unroll
                 for (int s = 0; s < 8; ++s)
-                    if (s < splits && j0 + 4 * u < count)
-                        asm volatile("ld.shared::cluster.v4.f32 {%0,%1,%2,%3}, [%4];\n"
-                                     : "=f"(parts[u][s].x), "=f"(parts[u][s].y),
-                                       "=f"(parts[u][s].z), "=f"(parts[u][s].w)
-                                     : "r"(remote[s] + (uint32_t)(token * ROWS) * 4));
+                    if (s < splits && j0 + 4 * u < count) {
+                        if (s == split)          // this block's own sums: an ordinary load
+                            parts[u][s] = *reinterpret_cast<const float4*>(
+                                partial + (size_t)token * ROWS + 4 * lane);
+                        else
+                            asm volatile("ld.shared::cluster.v4.f32 {%0,%1,%2,%3}, [%4];\n"
+                                         : "=f"(parts[u][s].x), "=f"(parts[u][s].y),
+                                           "=f"(parts[u][s].z), "=f"(parts[u][s].w)
+                                         : "r"(remote[s] + (uint32_t)(token * ROWS) * 4));
+                    }
             }
 #pragma unroll
             for (int u = 0; u < 2; ++u) {
