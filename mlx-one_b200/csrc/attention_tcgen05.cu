@@ -6,9 +6,10 @@
 // One item of work = up to 128 query rows that share a key head: 128 / group tokens of one request
 // times the group's query heads (row = token * group + head), so that a key tile is fetched once
 // for the whole group and short portions waste few rows; the request's keys are walked in tiles
-// of 128. Blocks are persistent, one per SM: a block lists its items once and its rings of
-// buffers run on from one item into the next, so that the first loads and products of an item
-// overlap the end of the one before. The warps have roles:
+// of 128 or of 64 (two shapes of the kernel, see Shape below). Blocks are persistent, as many as
+// the GPU holds at once: a block lists its items once and its rings of buffers run on from one
+// item into the next, so that the first loads and products of an item overlap the end of the
+// one before. The warps have roles:
 //   softmax warps (4 x PARTS): PARTS threads share query row r (lane r of tensor memory), each
 //              for its share of a tile's keys and of the output dimensions. Per tile a thread
 //              reads its scores with tcgen05.ld, the row's threads agree on the maximum, it
