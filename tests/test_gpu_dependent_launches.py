@@ -38,5 +38,5 @@ def test_same_logits_with_dependent_launches(tmp_path, name):
             assert runner.graph_replays >= 10
             results.append(torch.stack(collected))
     finally:
-        ops.set_dependent_launches(False)
+        ops.set_dependent_launches(True)
     assert torch.equal(results[0], results[1])
