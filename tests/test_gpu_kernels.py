@@ -126,7 +126,16 @@ def test_matrix_product_bfloat16(ops, plain, m, n, k):
 @pytest.mark.parametrize("m", [1, 7, 8, 9, 16, 17, 32])
 @pytest.mark.parametrize("n,k", [(16, 64), (333, 136), (1000, 2048), (96, 8192), (50, 8)])
 def test_skinny_product(ops, m, n, k):
-    """The weight-streaming product for few rows, all four epilogues, against float64."""
+    """The weight-streaming product for few rows (up to the 32 that the kernel takes, not only
+    the 8 that the engine sends it), all four epilogues, against float64."""
+    ops.skinny_max_rows = 32
+    try:
+        _skinny_product_case(ops, m, n, k)
+    finally:
+        ops.skinny_max_rows = 8
+
+
+def _skinny_product_case(ops, m, n, k):
     torch.manual_seed(m * 1000 + n + k)
     a = torch.randn(m, k).bfloat16()
     w = (torch.randn(n, k) / math.sqrt(k)).bfloat16()
@@ -289,6 +298,14 @@ def test_linear_short_conv(ops, plain, rows, hidden, k, taps, bias):
     convolution of the product that the kernel without that epilogue gives (the same sums in
     the same order, so B, C and x round alike and what is compared is the epilogue): positions
     0, 1 and later, slots in any order, more taps than it fuses (5)."""
+    ops.skinny_max_rows = 32
+    try:
+        _linear_short_conv_case(ops, plain, rows, hidden, k, taps, bias)
+    finally:
+        ops.skinny_max_rows = 8
+
+
+def _linear_short_conv_case(ops, plain, rows, hidden, k, taps, bias):
     torch.manual_seed(14)
     dtype = torch.bfloat16
     histories = [(3 * r) % 7 if r % 3 else r % 2 for r in range(rows)]
