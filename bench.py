@@ -277,9 +277,10 @@ def time_e2e(engine, batch, context, warmup, steps, seed):
     from mlx_one_b200 import TextGenerationOptions
 
     vocab = engine.model.spec.vocab_size
-    # prompts finish one after the other, so the first request has decoded some tokens when
-    # the last one starts; `slack` keeps every request decoding through the timed steps
-    slack = 2 * batch + 8
+    # prompts finish one after the other (long ones in several portions), so the first request
+    # has decoded some tokens when the last one starts; `slack` keeps every request decoding
+    # through the timed steps
+    slack = batch * (context // PREFILL_TOKENS + 2) + 8
     prompt_length = context - warmup - steps - slack
     prompts = random_prompts(vocab, batch, prompt_length, seed + 1)
     options = TextGenerationOptions(max_tokens=warmup + steps + slack, ignore_eos=True)
