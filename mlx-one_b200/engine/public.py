@@ -19,7 +19,6 @@ import torch
 
 from ..cache.manager import CacheManager
 from ..sampling.options import GenerationChunk, GenerationResult, TextGenerationOptions
-from ..sampling.sampler import Sampler
 from .loading import LoadedModel, load_model
 from .runner import Runner, StepEntry
 from .scheduler import BatchingConfig, Phase, Request, Scheduled, Scheduler
@@ -53,7 +52,7 @@ class _InFlight:
     host: Any
     event: Any
     draws: int
-    greedy: bool
+    chosen_on_device: bool
 
 
 class EngineRequestHandle:
@@ -104,7 +103,6 @@ class Engine:
             max_step_tokens=self.batching_config.max_scheduled_tokens)
         self._runner = Runner(built, self._cache)
         self._scheduler = Scheduler(self.batching_config, self._cache)
-        self._sampler = Sampler(built.ops, built.runtime.device)
         self._handles: dict[Any, EngineRequestHandle] = {}
         self._tokenizer = self._load_tokenizer()
         self._stats = {"steps": 0, "steps_ahead": 0, "tokens_run": 0, "tokens_sampled": 0}
@@ -193,7 +191,7 @@ class Engine:
         """One scheduler turn. Returns the requests that got a token or finished.
 
         A step is planned, launched, its chosen tokens are copied to pinned host memory, and
-        committed when that copy has landed. While every running request decodes greedily
+        committed when that copy has landed. While every running request decodes
         (``pipeline_decode``), the next step is launched before the last one is committed: its
         input tokens are the ones the device has just chosen, so the host's bookkeeping runs
         under the GPU's work. A request then learns of its end-of-sequence token one step
@@ -208,33 +206,38 @@ class Engine:
         if not planned:
             return []
         launched = self._launch(planned)
-        if self.batching_config.pipeline_decode and launched.greedy:
+        if self.batching_config.pipeline_decode and launched.chosen_on_device:
             self._inflight = launched
             return []
         return self._finish(launched)
 
-    def _launch(self, planned, entries=None) -> "_InFlight":
+    def _launch(self, planned, entries=None, ahead: int = 0) -> "_InFlight":
+        """Launches a step; the tokens of the requests that draw one are chosen on the device
+        inside it (argmax, or the sampling kernel with each request's options, seed and count
+        of tokens drawn so far; ``ahead``: tokens drawn but not yet committed)."""
         if entries is None:
             entries = [StepEntry(item.request.request_id, item.tokens,
                                  (len(item.tokens) - 1,) if item.samples else ())
                        for item in planned]
         drawing = [item.request for item in planned if item.samples]
         greedy = bool(drawing) and all(r.options.temperature == 0 for r in drawing)
-        logits = self._runner.step(entries, greedy=greedy)
+        draw = None
+        if drawing and not greedy:
+            draw = [(r.options.temperature, r.options.top_k or 0, r.options.top_p, r.options.seed,
+                     len(r.output) + ahead) for r in drawing]
+        self._runner.step(entries, greedy=greedy, draw=draw)
         host = event = None
         if drawing:
-            tokens = self._runner.last_greedy if greedy else self._sampler.select(
-                logits, [r.options for r in drawing], [len(r.output) for r in drawing])
-            host, event = self._start_copy(tokens)
+            host, event = self._start_copy(self._runner.last_greedy)
         self._stats["steps"] += 1
         self._stats["tokens_run"] += sum(len(item.tokens) for item in planned)
-        return _InFlight(list(planned), host, event, len(drawing), greedy)
+        return _InFlight(list(planned), host, event, len(drawing), bool(drawing))
 
     def _launch_ahead(self, previous: "_InFlight"):
         """The step after ``previous``, launched before ``previous`` is committed, or None if
         it cannot be known yet what that step will be."""
         scheduler = self._scheduler
-        if not (self.batching_config.pipeline_decode and previous.greedy) or scheduler.waiting:
+        if not (self.batching_config.pipeline_decode and previous.chosen_on_device) or scheduler.waiting:
             return None
         drew = {id(item.request) for item in previous.planned if item.samples}
         running = scheduler.running
@@ -246,7 +249,7 @@ class Engine:
         planned = [Scheduled(r, (0,), True) for r in going_on]
         entries = [StepEntry(r.request_id, (0,), (0,), from_device=True) for r in going_on]
         self._stats["steps_ahead"] += 1
-        return self._launch(planned, entries)
+        return self._launch(planned, entries, ahead=1)
 
     def _finish(self, inflight: "_InFlight") -> list[Request]:
         sampled: list[int] = []

@@ -112,11 +112,14 @@ class Runner:
 
     # ------------------------------------------------------------------ the step
 
-    def step(self, entries: Sequence[StepEntry], greedy: bool = False) -> torch.Tensor | None:
-        """See ``_step``. With ``greedy`` the argmax of every wanted row is computed in the
-        same launch sequence (inside the CUDA graph of a decode-only step) and left in
-        ``last_greedy`` as int32 [wanted] on the device."""
-        return self._step(entries, greedy=greedy)
+    def step(self, entries: Sequence[StepEntry], greedy: bool = False,
+             draw: Sequence[tuple] | None = None) -> torch.Tensor | None:
+        """See ``_step``. With ``greedy`` the argmax of every wanted row, with ``draw`` a sampled
+        token, is computed in the same launch sequence (inside the CUDA graph of a captured
+        step), published for steps that take their input from the device, and left in
+        ``last_greedy`` as int32 [wanted] on the device. ``draw`` gives for every wanted row
+        (temperature, top_k, top_p, seed, tokens drawn so far); a temperature of 0 is greedy."""
+        return self._step(entries, greedy=greedy, draw=draw)
 
     def decode_steps(self, entries: Sequence[StepEntry], steps: int) -> torch.Tensor:
         """``steps`` greedy decode steps in a row without the host in between: every entry
@@ -136,7 +139,7 @@ class Runner:
         record = torch.zeros((steps, len(entries)), dtype=torch.int32, device=self.device)
         return self._step(entries, loop=(steps, record))
 
-    def _step(self, entries: Sequence[StepEntry], loop=None, greedy: bool = False):
+    def _step(self, entries: Sequence[StepEntry], loop=None, greedy: bool = False, draw=None):
         """Runs the entries as one batch. Returns float32 logits [wanted, vocab] on the
         device in the order of the entries and of their ``want``, or None if nothing is
         wanted. Raises before touching any state if the batch is malformed or pages run
@@ -207,6 +210,15 @@ class Runner:
             region(f"table{g}", requests * widths[g])
         for g in range(len(states)):
             region(f"slots{g}", requests)
+        if draw is not None:
+            if len(draw) != wanted or not wanted:
+                raise ValueError("draw needs one entry per wanted row")
+            # the sampling kernel's arguments, per wanted row: floats by their bits, the seed
+            # as two 32-bit halves
+            for name in ("draw_temperature", "draw_top_k", "draw_top_p", "draw_step"):
+                region(name, wanted)
+            region("draw_seed", 2 * wanted)
+            self.ops.reserve_sample_scratch(self.cache.max_requests, vocab)
         host = self._host_buffer(cursor)
         data = host.numpy()
         self.last_meta_bytes = 4 * cursor
@@ -234,6 +246,15 @@ class Runner:
             want_index.extend([cache.index] * len(entry.want))
             if entry.from_device:
                 data[source_at + first] = cache.index
+        if draw is not None:
+            def view(name, kind):
+                start, size = offsets[name]
+                return data[start:start + size].view(kind)
+            view("draw_temperature", np.float32)[:] = [d[0] for d in draw]
+            view("draw_top_k", np.int32)[:] = [d[1] or 0 for d in draw]
+            view("draw_top_p", np.float32)[:] = [d[2] for d in draw]
+            view("draw_seed", np.int64)[:] = [d[3] for d in draw]
+            view("draw_step", np.int32)[:] = [d[4] for d in draw]
         put("want_index", want_index if want_index else [0])
         put("request_start", starts)
         put("history", history)
@@ -251,7 +272,7 @@ class Runner:
         captured = None
         if decode_only or portions:
             key = (requests, tokens, tuple(widths), wanted, loop is not None, greedy,
-                   any(e.from_device for e in entries))
+                   draw is not None, any(e.from_device for e in entries))
             captured = self._graphs.get(key)
             if captured is None:
                 captured = _DecodeGraph(torch.empty(cursor, dtype=torch.int32,
@@ -291,8 +312,14 @@ class Runner:
             if not wanted:
                 return None
             logits = self.model.logits(residual, delta, on_device("rows")[:wanted])
-            if greedy and loop is None:
-                chosen = self.ops.argmax(logits)
+            if (greedy or draw is not None) and loop is None:
+                if draw is not None:
+                    chosen, _ = self.ops.sample(
+                        logits, on_device("draw_temperature").view(torch.float32),
+                        on_device("draw_top_k"), on_device("draw_top_p").view(torch.float32),
+                        on_device("draw_seed").view(torch.int64), on_device("draw_step"))
+                else:
+                    chosen = self.ops.argmax(logits)
                 self.ops.publish_tokens(chosen, on_device("want_index")[:wanted], self.published)
                 return logits, chosen
             return logits

@@ -41,8 +41,9 @@ class BatchingConfig:
     prefill_chunk_size: int = 512
     max_scheduled_tokens: int = 2048
     max_prefill_tokens: int = 1024
-    # not in the reference: while all running requests decode greedily, launch the next step
-    # (its input tokens taken on the device) before the last step's tokens are read back
+    # not in the reference: while all running requests decode, launch the next step (its input
+    # tokens taken on the device, where they were chosen) before the last step's tokens are read
+    # back
     pipeline_decode: bool = True
 
     def __post_init__(self) -> None:

@@ -531,6 +531,14 @@ class CudaOps:
                    _c_void_p(_ptr(published)), _c_int(token_ids.numel()),
                    _c_int(published.numel()))
 
+    def reserve_sample_scratch(self, rows: int, vocab: int) -> None:
+        """Makes the sampling kernel's scratch large enough for ``rows`` rows now, so that no
+        call inside a graph capture has to allocate it."""
+        scratch = self._sample_scratch
+        if scratch is None or scratch.numel() < rows * vocab:
+            self._sample_scratch = torch.empty(rows * vocab, dtype=torch.float32,
+                                               device=self.device)
+
     def sample(self, logits, temperature, top_k, top_p, seed, step):
         """Per row: temperature (float32, > 0), top_k (int32, <= 0 = off), top_p (float32,
         >= 1 = off), seed (int64), step (int32). Returns (tokens int32, probabilities)."""

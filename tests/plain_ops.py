@@ -167,12 +167,20 @@ class PlainOps:
         taken = source >= 0
         token_ids[taken] = published[source[taken].long()]
 
+    def reserve_sample_scratch(self, rows, vocab):
+        pass
+
     def sample(self, logits, temperature, top_k, top_p, seed, step):
         """Token-order draw over the reference's kept set, in float64."""
         rows, vocab = logits.shape
         out = torch.empty(rows, dtype=torch.int32)
         probabilities = torch.empty(rows, vocab, dtype=torch.float32)
         for r in range(rows):
+            if float(temperature[r]) <= 0:                   # greedy row
+                out[r] = int(torch.argmax(logits[r]))
+                probabilities[r] = 0
+                probabilities[r, int(out[r])] = 1
+                continue
             scaled = (logits[r] - logits[r].max()) * (1.0 / temperature[r])
             p = torch.exp(scaled.float())
             probabilities[r] = p
