@@ -493,27 +493,55 @@ def test_argmax_and_sampling(ops, plain):
     top_p = torch.tensor([1.0, 1.0, 0.9, 0.7, 1.0, 1.0])
     seed = torch.tensor([0, 1, 2, 3, 4, 5], dtype=torch.int64)
     for step in range(20):
-        steps = torch.full((rows,), step, dtype=torch.int32)
-        got, probabilities = ops.sample(logits.to(DEVICE), temperature.to(DEVICE),
-                                        top_k.to(DEVICE), top_p.to(DEVICE), seed.to(DEVICE),
-                                        steps.to(DEVICE))
-        got = got.cpu().tolist()
+        got = check_draws(ops, logits, temperature, top_k, top_p, seed, step, range(4))
         assert got[4] == int(torch.argmax(logits[4]))           # temperature 0 is greedy
         assert got[5] == int(torch.argmax(logits[5]))           # top_k = 1 too
-        for r in range(4):
-            p = probabilities[r].cpu()
-            kept = set(kept_set(p, int(top_k[r]), float(top_p[r])).tolist())
-            assert got[r] in kept, (r, step)
-            # the same draw in float64 over the same kept set, in token order
-            weights = torch.zeros(vocab, dtype=torch.float64)
-            index = torch.tensor(sorted(kept))
-            weights[index] = p[index].double()
-            running = torch.cumsum(weights, 0)
-            target = uniform(int(seed[r]), step) * float(weights.sum())
-            want = int(torch.nonzero((running >= target) & (weights > 0))[0])
-            if got[r] != want:        # only a draw within rounding of a boundary may differ
-                edge = float(running[min(got[r], want)])
-                assert abs(edge - target) < 1e-5 * float(weights.sum()), (r, step, got[r], want)
+
+
+def check_draws(ops, logits, temperature, top_k, top_p, seed, step, sampled_rows):
+    """One call of the sampling kernel; every sampled row's token lies in the kept set that the
+    reference's rule gives for the kernel's own probabilities, and is the token that the same
+    draw in float64, in token order, gives."""
+    rows, vocab = logits.shape
+    steps = torch.full((rows,), step, dtype=torch.int32)
+    got, probabilities = ops.sample(logits.to(DEVICE), temperature.to(DEVICE),
+                                    top_k.to(DEVICE), top_p.to(DEVICE), seed.to(DEVICE),
+                                    steps.to(DEVICE))
+    got = got.cpu().tolist()
+    for r in sampled_rows:
+        p = probabilities[r].cpu()
+        want_p = torch.exp((logits[r] - logits[r].max()) * (1.0 / temperature[r]))
+        assert torch.allclose(p, want_p, rtol=1e-5, atol=1e-30)
+        kept = set(kept_set(p, int(top_k[r]), float(top_p[r])).tolist())
+        assert got[r] in kept, (r, step)
+        weights = torch.zeros(vocab, dtype=torch.float64)
+        index = torch.tensor(sorted(kept))
+        weights[index] = p[index].double()
+        running = torch.cumsum(weights, 0)
+        target = uniform(int(seed[r]), step) * float(weights.sum())
+        want = int(torch.nonzero((running >= target) & (weights > 0))[0])
+        if got[r] != want:        # only a draw within rounding of a boundary may differ
+            edge = float(running[min(got[r], want)])
+            assert abs(edge - target) < 1e-5 * float(weights.sum()), (r, step, got[r], want)
+    return got
+
+
+@pytest.mark.parametrize("vocab", [301, 70001])
+def test_sampling_among_equal_probabilities(ops, vocab):
+    """Logits on a coarse grid, so that the k-th largest probability and the top-p boundary are
+    shared by many tokens, and a row in which all tokens are equal: ties enter in token order."""
+    torch.manual_seed(vocab)
+    rows = 8
+    logits = torch.round(torch.randn(rows, vocab) * 2) * 0.5
+    logits[6] = 1.25                                     # all equal
+    logits[7] = -40.0
+    logits[7, 5::97] = 3.0                               # a few equal tokens far above the rest
+    temperature = torch.tensor([0.7, 1.0, 0.6, 1.2, 0.9, 1.0, 1.0, 0.5])
+    top_k = torch.tensor([0, 40, 7, 0, 200, 3, 11, 0], dtype=torch.int32)
+    top_p = torch.tensor([1.0, 1.0, 0.9, 0.6, 0.5, 0.95, 0.5, 0.8])
+    seed = torch.arange(rows, dtype=torch.int64) + 100
+    for step in range(12):
+        check_draws(ops, logits, temperature, top_k, top_p, seed, step, range(rows))
 
 
 def test_sampling_distribution(ops):
