@@ -131,3 +131,22 @@ def test_mid_size_model_with_long_portions(tmp_path, dtype):
         assert runner.ops.tcgen05_products
     assert_close(got["a"], model.logits(a), dtype, "mid a")
     assert_close(got["b"], model.logits(b), dtype, "mid b")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_a_prompt_of_thousands_of_tokens(folders, plain, dtype):
+    """5000 tokens of the head-size-64 model in portions of up to 2048 tokens and a decoded tail:
+    attention over hundreds of pages and dozens of key tiles, the window long past its first
+    pages, and the pages that the window left given back while the request lives."""
+    config, _, page = CONFIGS["D"]
+    (tokens,) = prompts(config["vocab_size"], (5000,), seed=77)
+    runner, cache = engine(folders["D"], dtype, page, 5056, max_requests=2)
+    sizes = [2048, 1300, 1024, 600] + [1] * 28
+    assert sum(sizes) == len(tokens)
+    steps, at = [], 0
+    for size in sizes:
+        steps.append(([("long", tokens[at:at + size])], []))
+        at += size
+    steps[-1] = (steps[-1][0], ["long"])
+    got = replay(runner, cache, steps)["long"]
+    assert_close(got, plain["D"].logits(tokens), dtype, "long prompt")
