@@ -396,6 +396,16 @@ def kernel_case(name: str, batch: int, context: int) -> int:
         w = weights(2 * width, hidden, 2)
         run = lambda i: ops.linear_swiglu(a, w[i % 2])
         work = f"{2 * PREFILL_TOKENS * 2 * width * hidden / 1e9:.1f} GFLOP"
+    elif name == "sampling":
+        vocab = LFM2_1_2B["vocab_size"]
+        logits = [torch.randn(batch, vocab, device=device) * 3 for _ in range(4)]
+        temperature = torch.full((batch,), 0.8, device=device)
+        top_k = torch.full((batch,), 40, dtype=torch.int32, device=device)
+        top_p = torch.full((batch,), 0.9, device=device)
+        seed = torch.arange(batch, dtype=torch.int64, device=device)
+        steps = torch.zeros(batch, dtype=torch.int32, device=device)
+        run = lambda i: ops.sample(logits[i % 4], temperature, top_k, top_p, seed, steps)
+        work = f"{batch} rows of {vocab} logits, temperature 0.8, top-k 40, top-p 0.9"
     else:
         print(f"unknown kernel case {name!r}")
         return 2
@@ -493,7 +503,8 @@ def main() -> int:
     parser.add_argument("--skip-points", action="store_true", help="leave out batch 1 and 64")
     parser.add_argument("--kernel", default=None,
                         help="run one kernel alone instead of the benchmark: skinny_swiglu, "
-                             "skinny_down, decode_attention, prefill_attention, tcgen05_swiglu")
+                             "skinny_down, decode_attention, prefill_attention, tcgen05_swiglu, "
+                             "sampling")
     parser.add_argument("--dependent-launches", type=int, default=1,
                         help="1: kernels of a decode step may start while the one before ends")
     args = parser.parse_args()
