@@ -11,6 +11,10 @@
 // (the reference walks them in rank order; both draw from the same distribution), with
 // u = uniform(seed, step).
 //
+// A row is shared by the blocks of a thread-block cluster (eight, four, two or one, by the number
+// of rows); each block counts its stretch of the row and adds its counts to every block's
+// histogram through distributed shared memory.
+//
 // uniform(seed, step) is a splitmix64 hash of seed * 0x9E3779B97F4A7C15 + (step + 1) *
 // 0xBF58476D1CE4E5B9, top 24 bits / 2^24, so a request's draws do not depend on what else is
 // in the batch.
@@ -111,33 +115,71 @@ __device__ __forceinline__ void visit_row(const float* row, int n, F&& f) {
     if (i < n) f(i, row[i]);
 }
 
-// Counts and masses of a run of entries of one bucket, added to the shared histogram when the
-// bucket changes: equal neighbours then cost one atomic, not one each.
+// Counts and masses of a run of entries of one bucket, handed to `flush(digit, count, mass)`
+// when the bucket changes: equal neighbours then cost one update of the histogram, not one each.
 struct BucketRun {
     unsigned digit = 0xffffffffu, count = 0u;
     unsigned long long mass = 0ull;
-    // A 64-bit sum in shared memory as two 32-bit atomics: the low word's wrap-around is seen in
-    // the value it held before, and carried into the high word. Exact in any order.
-    __device__ __forceinline__ void flush(unsigned* count_of, unsigned long long* mass_of) {
-        if (count) {
-            atomicAdd(&count_of[digit], count);
-            unsigned* words = reinterpret_cast<unsigned*>(mass_of + digit);
-            const unsigned low = (unsigned)mass, high = (unsigned)(mass >> 32);
-            const unsigned before = atomicAdd(&words[0], low);
-            const unsigned carry = before + low < before ? 1u : 0u;
-            if (high + carry) atomicAdd(&words[1], high + carry);
-        }
-    }
-    __device__ __forceinline__ void add(unsigned d, float value, unsigned* count_of,
-                                        unsigned long long* mass_of) {
+    template <typename Flush>
+    __device__ __forceinline__ void add(unsigned d, float value, Flush&& flush) {
         if (d != digit) {
-            flush(count_of, mass_of);
+            if (count) flush(digit, count, mass);
             digit = d; count = 0u; mass = 0ull;
         }
         ++count;
         mass += fixed_mass(value);
     }
+    template <typename Flush>
+    __device__ __forceinline__ void finish(Flush&& flush) {
+        if (count) flush(digit, count, mass);
+        count = 0u;
+    }
 };
+
+// A 64-bit sum in this block's shared memory as two 32-bit atomics: the low word's wrap-around
+// is seen in the value it held before, and carried into the high word. Exact in any order.
+__device__ __forceinline__ void add_wide(unsigned long long* sum, unsigned long long value) {
+    unsigned* words = reinterpret_cast<unsigned*>(sum);
+    const unsigned low = (unsigned)value, high = (unsigned)(value >> 32);
+    const unsigned before = atomicAdd(&words[0], low);
+    const unsigned carry = before + low < before ? 1u : 0u;
+    if (high + carry) atomicAdd(&words[1], high + carry);
+}
+
+// ---- the blocks of one row form a thread-block cluster and reach one another's shared memory
+__device__ __forceinline__ unsigned cluster_rank() {
+    unsigned rank;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;\n" : "=r"(rank));
+    return rank;
+}
+// A barrier over all threads of the cluster; what they wrote before it (also into other blocks'
+// shared memory) is visible after it.
+__device__ __forceinline__ void cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n"
+                 "barrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+}
+// The address, in the cluster's shared window, of block `rank`'s copy of a shared variable.
+__device__ __forceinline__ unsigned in_block(const void* local, unsigned rank) {
+    const unsigned address = (unsigned)__cvta_generic_to_shared(local);
+    unsigned mapped;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(mapped) : "r"(address), "r"(rank));
+    return mapped;
+}
+__device__ __forceinline__ void remote_add(unsigned address, unsigned value) {
+    asm volatile("red.shared::cluster.add.u32 [%0], %1;\n" :: "r"(address), "r"(value) : "memory");
+}
+__device__ __forceinline__ void remote_add(unsigned address, unsigned long long value) {
+    asm volatile("red.shared::cluster.add.u64 [%0], %1;\n" :: "r"(address), "l"(value) : "memory");
+}
+__device__ __forceinline__ void remote_store(unsigned address, unsigned long long value) {
+    asm volatile("st.shared::cluster.u64 [%0], %1;\n" :: "r"(address), "l"(value) : "memory");
+}
+__device__ __forceinline__ void remote_store(unsigned address, float value) {
+    asm volatile("st.shared::cluster.f32 [%0], %1;\n" :: "r"(address), "f"(value) : "memory");
+}
+__device__ __forceinline__ void remote_store(unsigned address, int value) {
+    asm volatile("st.shared::cluster.s32 [%0], %1;\n" :: "r"(address), "r"(value) : "memory");
+}
 
 // Exclusive prefix sum over the block, in thread order; *total gets the sum. scratch: 33 entries.
 __device__ __forceinline__ unsigned long long block_scan_exclusive(unsigned long long v,
@@ -209,77 +251,149 @@ __device__ __forceinline__ void find_bucket(const T* hist, int buckets, unsigned
 }
 
 // Per row: temperature[r] <= 0 -> argmax. top_k[r] <= 0 -> no top-k. top_p[r] >= 1 -> none.
+// CLUSTER blocks share a row: block `rank` owns a stretch of consecutive tokens. Every block
+// holds the whole histograms (each adds what it counted to every block's copy), so all blocks
+// take the same decisions without asking one another.
+constexpr int SAMPLE_SHARED_BYTES = TOP_BUCKETS * (2 * 8 + 2 * 4);
+
+template <int CLUSTER>
 __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_kernel(const float* __restrict__ logits, int vocab, const float* __restrict__ temperature,
               const int* __restrict__ top_k, const float* __restrict__ top_p,
               const long long* __restrict__ seed, const int* __restrict__ step,
               float* probabilities, int* __restrict__ out) {
-    __shared__ unsigned top_count[TOP_BUCKETS];              // first digit, all entries
-    __shared__ unsigned long long top_mass[TOP_BUCKETS];
-    __shared__ unsigned count_of[LOW_BUCKETS];               // a lower digit, entries of one prefix
-    __shared__ unsigned long long mass_of[LOW_BUCKETS];
+    extern __shared__ __align__(16) unsigned char sample_shared[];
+    // first digit, all entries of the row; then this block's own count of it, whose room is used
+    // afterwards, zeroed, for two histograms of a lower digit that take turns
+    unsigned long long* top_mass = reinterpret_cast<unsigned long long*>(sample_shared);
+    unsigned long long* own_mass = top_mass + TOP_BUCKETS;
+    unsigned* top_count = reinterpret_cast<unsigned*>(own_mass + TOP_BUCKETS);
+    unsigned* own_count = top_count + TOP_BUCKETS;
     __shared__ unsigned long long scan_scratch[33];
     __shared__ unsigned long long warp_ties[32], warp_mass[32];
+    __shared__ unsigned long long block_zeros[CLUSTER], block_mass[CLUSTER];
+    __shared__ unsigned long long block_ties[CLUSTER], block_kept[CLUSTER];
+    __shared__ float block_top[CLUSTER];
     __shared__ float fscratch[33];
     __shared__ int found;
     __shared__ unsigned long long found_above;
     __shared__ int chosen;
-    const int r = blockIdx.x;
+    const int r = blockIdx.x / CLUSTER;
+    const unsigned rank = CLUSTER > 1 ? cluster_rank() : 0u;
     const float* row = logits + (size_t)r * vocab;
     float* p = probabilities + (size_t)r * vocab;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    if (!(temperature[r] > 0.f)) {          // greedy row in a mixed batch
-        const int index = block_argmax(row, vocab);
-        if (tid == 0) out[r] = index;
+    if (!(temperature[r] > 0.f)) {          // greedy row in a mixed batch: the first block's work
+        if (rank == 0u) {
+            const int index = block_argmax(row, vocab);
+            if (tid == 0) out[r] = index;
+        }
         return;
     }
+    // this block's tokens: a stretch whose start keeps the 16-byte steps of the row
+    const int share = (((vocab + CLUSTER - 1) / CLUSTER) + 3) & ~3;
+    const int first = min((int)rank * share, vocab);
+    const int mine = min(share, vocab - first);
 
+    for (int b = tid; b < TOP_BUCKETS; b += blockDim.x) {
+        top_count[b] = 0u; top_mass[b] = 0ull; own_count[b] = 0u; own_mass[b] = 0ull;
+    }
     // ---- probabilities (numerators of the softmax; the largest is exactly 1) and the
     // histogram of their first digit
     float local_max = -INFINITY;
-    visit_row(row, vocab, [&](int, float v) { local_max = fmaxf(local_max, v); });
-    const float top = block_max(local_max, fscratch);
+    visit_row(row + first, mine, [&](int, float v) { local_max = fmaxf(local_max, v); });
+    local_max = block_max(local_max, fscratch);
+    if (tid < CLUSTER) remote_store(in_block(&block_top[rank], tid), local_max);
+    cluster_sync();
+    float top = block_top[0];
+#pragma unroll
+    for (int t = 1; t < CLUSTER; ++t) top = fmaxf(top, block_top[t]);
     const float inv_t = 1.0f / temperature[r];
-    for (int b = tid; b < TOP_BUCKETS; b += blockDim.x) { top_count[b] = 0u; top_mass[b] = 0ull; }
-    __syncthreads();
     const int k = top_k[r];
     const bool top_k_on = k > 0 && k < vocab;
     const float nucleus = top_p[r];
+    const bool truncating = top_k_on || nucleus < 1.0f;
     unsigned long long local_zeros = 0ull, local_mass = 0ull;
-    if (top_k_on || nucleus < 1.0f) {
+    if (truncating) {
         BucketRun run;
-        visit_row(row, vocab, [&](int i, float v) {
+        auto to_own = [&](unsigned d, unsigned count, unsigned long long mass) {
+            atomicAdd(&own_count[d], count);
+            add_wide(&own_mass[d], mass);
+        };
+        visit_row(row + first, mine, [&](int i, float v) {
             const float value = expf((v - top) * inv_t);
-            p[i] = value;
+            p[first + i] = value;
             const unsigned bits = __float_as_uint(value);
             local_zeros += bits == 0u;
-            run.add(bits >> 20, value, top_count, top_mass);
+            run.add(bits >> 20, value, to_own);
         });
-        run.flush(top_count, top_mass);
+        run.finish(to_own);
     } else {
-        visit_row(row, vocab, [&](int i, float v) {
+        visit_row(row + first, mine, [&](int i, float v) {
             const float value = expf((v - top) * inv_t);
-            p[i] = value;
+            p[first + i] = value;
             local_zeros += __float_as_uint(value) == 0u;
             local_mass += fixed_mass(value);
         });
     }
-    __syncthreads();
+    {
+        unsigned long long zeros_here, mass_here;
+        block_scan_exclusive(local_zeros, scan_scratch, &zeros_here);
+        block_scan_exclusive(local_mass, scan_scratch, &mass_here);
+        if (tid < CLUSTER) {
+            remote_store(in_block(&block_zeros[rank], tid), zeros_here);
+            remote_store(in_block(&block_mass[rank], tid), mass_here);
+        }
+    }
+    // what this block counted goes to every block's histogram, and its own room is left zeroed
+    for (int b = tid; b < TOP_BUCKETS; b += blockDim.x) {
+        const unsigned count = own_count[b];
+        if (count) {
+            const unsigned long long mass = own_mass[b];
+#pragma unroll
+            for (int t = 0; t < CLUSTER; ++t) {
+                remote_add(in_block(&top_count[b], t), count);
+                remote_add(in_block(&top_mass[b], t), mass);
+            }
+            own_count[b] = 0u;
+            own_mass[b] = 0ull;
+        }
+    }
+    cluster_sync();
+    unsigned long long zeros = 0ull, plain_mass = 0ull;
+#pragma unroll
+    for (int t = 0; t < CLUSTER; ++t) { zeros += block_zeros[t]; plain_mass += block_mass[t]; }
 
-    // Histogram, by the digit at `level` (1 or 2), of the entries whose higher digits are
-    // `prefix` and, with above_only, whose pattern lies beyond `floor_bits`.
+    // Histogram, by the digit at `level` (1 or 2), of the row's entries whose higher digits are
+    // `prefix` and, with above_only, whose pattern lies beyond `floor_bits`: every block adds
+    // its stretch's entries to every block's copy. The two copies take turns, and the one for
+    // the next call is zeroed before this call's barrier, after which blocks may add to it.
+    int turn = 0;
+    unsigned* count_of = own_count;
+    unsigned long long* mass_of = own_mass;
     auto histogram = [&](int level, unsigned prefix, bool above_only, unsigned floor_bits) {
         __syncthreads();
-        for (int b = tid; b < LOW_BUCKETS; b += blockDim.x) { count_of[b] = 0u; mass_of[b] = 0ull; }
-        __syncthreads();
+        count_of = own_count + turn * LOW_BUCKETS;
+        mass_of = own_mass + turn * LOW_BUCKETS;
+        unsigned* next_count = own_count + (turn ^ 1) * LOW_BUCKETS;
+        unsigned long long* next_mass = own_mass + (turn ^ 1) * LOW_BUCKETS;
+        for (int b = tid; b < LOW_BUCKETS; b += blockDim.x) { next_count[b] = 0u; next_mass[b] = 0ull; }
         BucketRun run;
-        visit_row(p, vocab, [&](int, float value) {
+        auto to_all = [&](unsigned d, unsigned count, unsigned long long mass) {
+#pragma unroll
+            for (int t = 0; t < CLUSTER; ++t) {
+                remote_add(in_block(&count_of[d], t), count);
+                remote_add(in_block(&mass_of[d], t), mass);
+            }
+        };
+        visit_row(p + first, mine, [&](int, float value) {
             const unsigned bits = __float_as_uint(value);
             if ((!above_only || bits > floor_bits) && digits_above(bits, level) == prefix)
-                run.add(digit_of(bits, level), value, count_of, mass_of);
+                run.add(digit_of(bits, level), value, to_all);
         });
-        run.flush(count_of, mass_of);
-        __syncthreads();
+        run.finish(to_all);
+        cluster_sync();
+        turn ^= 1;
     };
     auto mass_beyond = [&](const unsigned long long* hist, int buckets, int d) {
         unsigned long long beyond = 0ull, sum;
@@ -309,10 +423,7 @@ sample_kernel(const float* __restrict__ logits, int vocab, const float* __restri
         }
         kth = prefix;
     } else {
-        unsigned long long zeros;
-        if (nucleus < 1.0f) mass_above_k = mass_beyond(top_mass, TOP_BUCKETS, -1);
-        else block_scan_exclusive(local_mass, scan_scratch, &mass_above_k);
-        block_scan_exclusive(local_zeros, scan_scratch, &zeros);
+        mass_above_k = nucleus < 1.0f ? mass_beyond(top_mass, TOP_BUCKETS, -1) : plain_mass;
         above_k = (unsigned long long)vocab - zeros;
         equal_k = zeros;
     }
@@ -367,10 +478,11 @@ sample_kernel(const float* __restrict__ logits, int vocab, const float* __restri
     if (total > 0ull && target >= total) target = total - 1ull;
 
     // ---- the first kept token, in token order, whose running mass passes the target. Each warp
-    // owns a stretch of consecutive tokens; the warp in whose stretch the target falls walks it.
+    // owns a stretch of consecutive tokens of its block's stretch; the warp in whose stretch the
+    // target falls walks it.
     const int warps = blockDim.x >> 5;
-    const int stretch = (((vocab + warps - 1) / warps) + 31) & ~31;
-    const int begin = min(warp * stretch, vocab), end = min(begin + stretch, vocab);
+    const int stretch = (((mine + warps - 1) / warps) + 31) & ~31;
+    const int begin = first + min(warp * stretch, mine), end = min(begin + stretch, first + mine);
     unsigned long long ties_here = 0ull, mass_here = 0ull;
 #pragma unroll 4
     for (int i = begin + lane; i < end; i += 32) {
@@ -388,19 +500,29 @@ sample_kernel(const float* __restrict__ logits, int vocab, const float* __restri
     if (lane == 0) { warp_ties[warp] = ties_here; warp_mass[warp] = mass_here; }
     if (tid == 0) chosen = -1;
     __syncthreads();
-    unsigned long long ties_before = 0ull, mass_before = 0ull;
-    for (int w = 0; w < warp; ++w) {
-        const unsigned long long admitted =
-            ties_before >= ties_edge ? 0ull : min(warp_ties[w], ties_edge - ties_before);
-        mass_before += warp_mass[w] + admitted * edge_mass;
-        ties_before += warp_ties[w];
+    if (tid < CLUSTER) {             // this block's ties and mass beyond the edge, for every block
+        unsigned long long ties_sum = 0ull, mass_sum = 0ull;
+        for (int w = 0; w < warps; ++w) { ties_sum += warp_ties[w]; mass_sum += warp_mass[w]; }
+        remote_store(in_block(&block_ties[rank], tid), ties_sum);
+        remote_store(in_block(&block_kept[rank], tid), mass_sum);
     }
+    cluster_sync();
+    // ties are admitted in token order: blocks before this one, then warps before this one
+    unsigned long long ties_before = 0ull, mass_before = 0ull;
+    auto pass_over = [&](unsigned long long ties, unsigned long long mass) {
+        const unsigned long long admitted =
+            ties_before >= ties_edge ? 0ull : min(ties, ties_edge - ties_before);
+        mass_before += mass + admitted * edge_mass;
+        ties_before += ties;
+    };
+    for (int t = 0; t < (int)rank; ++t) pass_over(block_ties[t], block_kept[t]);
+    for (int w = 0; w < warp; ++w) pass_over(warp_ties[w], warp_mass[w]);
     {
         const unsigned long long admitted =
             ties_before >= ties_edge ? 0ull : min(ties_here, ties_edge - ties_before);
         mass_here += admitted * edge_mass;
     }
-    if (mass_before <= target && target < mass_before + mass_here) {       // one warp
+    if (mass_before <= target && target < mass_before + mass_here) {       // one warp of the row
         unsigned long long running = mass_before, ties_seen = ties_before;
         for (int base = begin; base < end; base += 32) {
             const int i = base + lane;
@@ -412,8 +534,8 @@ sample_kernel(const float* __restrict__ logits, int vocab, const float* __restri
             const unsigned long long tie_rank =
                 ties_seen + (unsigned long long)__popc(tie_lanes & ((2u << lane) - 1u));
             const bool kept = i < end && (bits > edge || (tie && tie_rank <= ties_edge));
-            const unsigned long long mine = !kept ? 0ull : tie ? edge_mass : fixed_mass(value);
-            unsigned long long inclusive = mine;
+            const unsigned long long weight = !kept ? 0ull : tie ? edge_mass : fixed_mass(value);
+            unsigned long long inclusive = weight;
 #pragma unroll
             for (int offset = 1; offset < 32; offset <<= 1) {
                 const unsigned long long other = __shfl_up_sync(0xffffffffu, inclusive, offset);
@@ -421,14 +543,15 @@ sample_kernel(const float* __restrict__ logits, int vocab, const float* __restri
             }
             const unsigned hit = __ballot_sync(0xffffffffu, kept && running + inclusive > target);
             if (hit) {
-                if (lane == 0) chosen = base + __ffs(hit) - 1;
+                if (lane == 0) remote_store(in_block(&chosen, 0u), base + __ffs(hit) - 1);
                 break;
             }
             running += __shfl_sync(0xffffffffu, inclusive, 31);
             ties_seen += (unsigned long long)__popc(tie_lanes);
         }
     }
-    __syncthreads();
+    cluster_sync();            // also: no block leaves while another may write to its memory
+    if (rank != 0u) return;
     if (chosen < 0) {
         // cannot happen while the kept mass is positive; the most probable token is always kept
         __syncthreads();
@@ -607,8 +730,35 @@ MLXONE_API int mlxone_sample(const float* logits, int rows, int vocab, const flo
     MLXONE_REQUIRE(rows > 0 && vocab > 0, "sample: bad sizes");
     MLXONE_REQUIRE(probabilities != nullptr, "sample: scratch for probabilities is missing");
     MLXONE_REQUIRE(vocab <= (1 << 20), "sample: at most 2^20 tokens in the vocabulary");
-    sample_kernel<<<rows, SAMPLE_THREADS, 0, stream>>>(logits, vocab, temperature, top_k, top_p, seed,
-                                               step, probabilities, out);
+    // As many blocks per row as let all rows run at once: a cluster lies within one of the
+    // GPU's eight groups of SMs, which hold two clusters of eight blocks, four of four.
+    const int cluster = rows <= 16 ? 8 : rows <= 32 ? 4 : rows <= 64 ? 2 : 1;
+    auto launch = [&](auto kernel) {
+        cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             SAMPLE_SHARED_BYTES);
+        cudaLaunchConfig_t config = {};
+        config.gridDim = dim3(rows * cluster);
+        config.blockDim = dim3(SAMPLE_THREADS);
+        config.dynamicSmemBytes = SAMPLE_SHARED_BYTES;
+        config.stream = stream;
+        cudaLaunchAttribute attribute[1];
+        attribute[0].id = cudaLaunchAttributeClusterDimension;
+        attribute[0].val.clusterDim.x = cluster;
+        attribute[0].val.clusterDim.y = 1;
+        attribute[0].val.clusterDim.z = 1;
+        config.attrs = attribute;
+        config.numAttrs = 1;
+        return cudaLaunchKernelEx(&config, kernel, logits, vocab, temperature, top_k, top_p, seed,
+                                  step, probabilities, out);
+    };
+    const cudaError_t err = cluster == 8   ? launch(sample_kernel<8>)
+                            : cluster == 4 ? launch(sample_kernel<4>)
+                            : cluster == 2 ? launch(sample_kernel<2>)
+                                           : launch(sample_kernel<1>);
+    if (err != cudaSuccess) {
+        mlxone_set_error("sample: launch failed: %s", cudaGetErrorString(err));
+        return 1;
+    }
     MLXONE_LAUNCH_CHECK("sample");
     return 0;
 }

@@ -544,6 +544,27 @@ def test_sampling_among_equal_probabilities(ops, vocab):
         check_draws(ops, logits, temperature, top_k, top_p, seed, step, range(rows))
 
 
+@pytest.mark.parametrize("rows", [20, 40, 80])
+def test_sampling_of_many_rows(ops, rows):
+    """More rows than the eight-block clusters have room for: a row is then shared by four, two
+    or one block. Every row has options of its own."""
+    torch.manual_seed(rows)
+    vocab = 4099
+    logits = torch.randn(rows, vocab) * 2.5
+    logits[1::5] = torch.round(logits[1::5] * 2) * 0.5            # rows full of ties
+    temperature = 0.5 + torch.rand(rows)
+    temperature[3::7] = 0.0                                        # greedy rows among them
+    top_k = torch.tensor([(0, 1, 13, 200, vocab + 5)[i % 5] for i in range(rows)], dtype=torch.int32)
+    top_p = torch.tensor([(1.0, 0.9, 0.35, 0.99)[i % 4] for i in range(rows)])
+    seed = torch.arange(rows, dtype=torch.int64) * 7 + 1
+    sampled = [r for r in range(rows) if float(temperature[r]) > 0]
+    for step in range(3):
+        got = check_draws(ops, logits, temperature, top_k, top_p, seed, step, sampled)
+        for r in range(rows):
+            if float(temperature[r]) <= 0:
+                assert got[r] == int(torch.argmax(logits[r]))
+
+
 def test_sampling_distribution(ops):
     """Over many steps the drawn tokens follow softmax(logits / T)."""
     logits = torch.tensor([[2.0, 1.0, 0.0, -1.0, 1.5]])
