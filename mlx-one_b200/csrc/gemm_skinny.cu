@@ -37,6 +37,7 @@ constexpr int SLICE = 64;         // K elements per slice
 constexpr int STAGES = 4;         // ring of slices per warp
 constexpr int SLICE_BYTES = ROWS * SLICE * 2;
 constexpr int WARPS = 16;
+constexpr size_t SHARED_LIMIT = 226 * 1024;      // of the 227 KB that a block may ask for
 
 enum : int { STORE_BF16 = 0, SWIGLU = 1, ADD_RESIDUAL = 2, STORE_F32 = 3, GATED_CONV = 4 };
 
@@ -473,7 +474,7 @@ cudaError_t launch(const void* a, int lda, const void* w, const float* bias, voi
     const size_t sums = (size_t)2 * WARPS * ROWS * 8 * NT * sizeof(float);
     const size_t resident = (size_t)8 * NT * ((k + 63) / 64) * 64 * 2;
     // activations in shared memory pay off when a block reuses them for several tiles
-    const bool fits = NT <= 2 && rings + sums + resident <= 200 * 1024;
+    const bool fits = NT <= 2 && rings + sums + resident <= SHARED_LIMIT;
     const bool use_resident = fits && (norm.source != nullptr || tiles_a_block >= 2);
     const size_t token_ring = !use_resident && NT == 1 ? (size_t)WARPS * STAGES * 8 * SLICE * 2 : 0;
     const size_t shared = rings + token_ring + sums + (use_resident ? resident : 0);
@@ -590,7 +591,7 @@ MLXONE_API int mlxone_gemm_skinny_norm_fits(int m, int k) {
     const int nt = m <= 8 ? 1 : 2;
     const size_t sums = (size_t)2 * WARPS * ROWS * 8 * nt * sizeof(float);
     const size_t resident = (size_t)8 * nt * ((k + 63) / 64) * 64 * 2;
-    return rings + sums + resident <= 200 * 1024 ? 1 : 0;
+    return rings + sums + resident <= SHARED_LIMIT ? 1 : 0;
 }
 
 // As mlxone_gemm_skinny with a = RMSNorm(source; norm_weight, eps) in bfloat16, the norm applied

@@ -292,7 +292,8 @@ def test_short_conv(ops, plain, dtype, hidden, taps, bias, decode):
 
 @pytest.mark.parametrize("rows,hidden,k,taps,bias", [
     (5, 40, 64, 3, True), (1, 2048, 2048, 3, False), (8, 136, 200, 4, False), (3, 24, 72, 1, True),
-    (17, 600, 96, 2, True), (32, 48, 2048, 3, False), (4, 40, 64, 5, True)])
+    (17, 600, 96, 2, True), (32, 48, 2048, 3, False), (4, 40, 64, 5, True),
+    (12, 2048, 2048, 3, True), (16, 136, 264, 3, False)])
 def test_linear_short_conv(ops, plain, rows, hidden, k, taps, bias):
     """The product with the convolution's decode update as its epilogue, against the plain
     convolution of the product that the kernel without that epilogue gives (the same sums in
