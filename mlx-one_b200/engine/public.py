@@ -10,6 +10,7 @@ weights has no tokenizer.
 
 from __future__ import annotations
 
+import threading
 import time
 from dataclasses import dataclass
 from pathlib import Path
@@ -70,7 +71,8 @@ class EngineRequestHandle:
         return self.request.phase is Phase.FINISHED
 
     def cancel(self) -> None:
-        self._engine._scheduler.cancel(self.request)
+        with self._engine._turn:
+            self._engine._scheduler.cancel(self.request)
 
     def result(self) -> GenerationResult:
         while not self.done():
@@ -109,6 +111,7 @@ class Engine:
         self._pinned: list[torch.Tensor | None] = [None, None]
         self._copy_turn = 0
         self._inflight: _InFlight | None = None
+        self._turn = threading.RLock()       # one thread at a time plans, launches and commits
 
     # ------------------------------------------------------------------ set-up
 
@@ -173,11 +176,12 @@ class Engine:
         if len(prompt) + options.max_tokens > limit:
             options = TextGenerationOptions(**{**options.__dict__,
                                                "max_tokens": limit - len(prompt)})
-        request = Request(self._scheduler.new_id(), prompt, options,
-                          eos_token_ids=self._loaded.spec.eos_token_ids)
-        self._scheduler.submit(request)
-        handle = EngineRequestHandle(self, request, prompt_text)
-        self._handles[request.request_id] = handle
+        with self._turn:
+            request = Request(self._scheduler.new_id(), prompt, options,
+                              eos_token_ids=self._loaded.spec.eos_token_ids)
+            self._scheduler.submit(request)
+            handle = EngineRequestHandle(self, request, prompt_text)
+            self._handles[request.request_id] = handle
         return handle
 
     def submit(self, prompt: str, options: TextGenerationOptions | None = None,
@@ -195,7 +199,15 @@ class Engine:
         (``pipeline_decode``), the next step is launched before the last one is committed: its
         input tokens are the ones the device has just chosen, so the host's bookkeeping runs
         under the GPU's work. A request then learns of its end-of-sequence token one step
-        late; the extra token computed for it is dropped."""
+        late; the extra token computed for it is dropped.
+
+        Turns exclude one another, so that several threads (``async_generate`` runs each
+        request's wait on a thread of its own) may drive the loop: whichever holds the turn
+        moves every running request on by one step."""
+        with self._turn:
+            return self._step()
+
+    def _step(self) -> list[Request]:
         previous = self._inflight
         if previous is not None:
             ahead = self._launch_ahead(previous)
@@ -346,6 +358,28 @@ class Engine:
     def generate(self, prompt: str, options: TextGenerationOptions | None = None,
                  **option_kwargs) -> GenerationResult:
         return self.submit(prompt, self._options(options, option_kwargs)).result()
+
+    async def async_generate_ids(self, prompt_ids: Sequence[int],
+                                 options: TextGenerationOptions | None = None,
+                                 **option_kwargs) -> GenerationResult:
+        """``generate_ids`` for coroutines: the request is submitted at once and awaited on a
+        worker thread that drives the loop, so requests of several coroutines are batched
+        together. A cancelled coroutine cancels its request."""
+        import asyncio
+
+        handle = self.submit_ids(prompt_ids, options, **option_kwargs)
+        try:
+            return await asyncio.get_running_loop().run_in_executor(None, handle.result)
+        except asyncio.CancelledError:
+            handle.cancel()
+            raise
+
+    async def async_generate(self, prompt: str, *, options: TextGenerationOptions | None = None,
+                             **option_kwargs) -> GenerationResult:
+        """As the reference's ``Engine.async_generate`` (src/mlx_one/engine/public.py:412-424)."""
+        return await self.async_generate_ids(self.encode(prompt),
+                                             self._options(options, option_kwargs),
+                                             prompt_text=prompt)
 
     def stream_ids(self, prompt_ids: Sequence[int], options: TextGenerationOptions | None = None,
                    **option_kwargs) -> Iterator[GenerationChunk]:

@@ -157,3 +157,39 @@ def test_pipelined_decode_gives_the_same_tokens(models, pipeline):
     assert (stats["steps_ahead"] > 0) == pipeline
     assert stats["running"] == 0 and stats["pages_free"] == stats["pages_total"]
     engine.cache.check()
+
+
+def test_coroutines_share_the_engine(models):
+    """``async_generate_ids`` from several coroutines at once: every request is waited for on a
+    thread of its own, the threads take turns at the loop, and each request gets the tokens it
+    gets alone. A cancelled coroutine ends its request and gives its pages back."""
+    import asyncio
+
+    folder, loaded, plain = models["B"]
+    config, _, page = CONFIGS["B"]
+    engine = Engine(loaded, cache_config=CacheConfig(block_size_tokens=page, capacity_tokens=512),
+                    batching_config=BatchingConfig(max_sequences=3, prefill_chunk_size=16,
+                                                   max_scheduled_tokens=24))
+    requests = prompts(config["vocab_size"], (5, 21, 40, 9), seed=12)
+
+    async def together():
+        return await asyncio.gather(*(engine.async_generate_ids(p, max_tokens=7) for p in requests))
+
+    for prompt, result in zip(requests, asyncio.run(together())):
+        assert list(result.token_ids) == plain.greedy(prompt, 7)
+
+    async def cancelled():
+        long = asyncio.ensure_future(engine.async_generate_ids(requests[2], max_tokens=200))
+        short = asyncio.ensure_future(engine.async_generate_ids(requests[0], max_tokens=3))
+        await short
+        long.cancel()
+        with pytest.raises(asyncio.CancelledError):
+            await long
+        return short.result()
+
+    short = asyncio.run(cancelled())
+    assert list(short.token_ids) == plain.greedy(requests[0], 3)
+    engine.run()
+    stats = engine.runtime_stats()
+    assert stats["running"] == 0 and stats["pages_free"] == stats["pages_total"]
+    engine.close()
