@@ -18,6 +18,9 @@ def main() -> None:
 @main.command("generate", help="Generate a completion for PROMPT with the model folder MODEL.")
 @click.argument("model")
 @click.argument("prompt")
+@click.option("--revision", default=None, help="Hub revision; local folders have none.")
+@click.option("--offline", is_flag=True, help="Never fetch a model (always so here).")
+@click.option("--cache-dir", default=None, help="Where fetched models would be kept (unused).")
 @click.option("--max-tokens", type=click.IntRange(min=1), default=128, show_default=True)
 @click.option("--temperature", type=click.FloatRange(min=0), default=0.0, show_default=True)
 @click.option("--top-k", type=click.IntRange(min=1))
@@ -32,7 +35,7 @@ def main() -> None:
 @click.option("--dtype", type=click.Choice(["bfloat16", "float32"]), default="bfloat16",
               show_default=True, help="Execution dtype.")
 @click.option("--device", default="cuda:0", show_default=True)
-def generate_command(model, prompt, max_tokens, temperature, top_k, top_p, seed, stop, stream,
+def generate_command(model, prompt, revision, offline, cache_dir, max_tokens, temperature, top_k, top_p, seed, stop, stream,
                      as_json, token_ids, dtype, device) -> None:
     from .engine import Engine
     from .sampling import TextGenerationOptions
@@ -40,7 +43,8 @@ def generate_command(model, prompt, max_tokens, temperature, top_k, top_p, seed,
     try:
         options = TextGenerationOptions(max_tokens=max_tokens, temperature=temperature,
                                         top_k=top_k, top_p=top_p, seed=seed, stop=stop)
-        engine = Engine(model, execution_dtype=dtype, device=device)
+        engine = Engine(model, execution_dtype=dtype, device=device, revision=revision,
+                        offline=True, cache_dir=cache_dir)
         ids = ([int(v) for v in prompt.replace(",", " ").split()] if token_ids
                else engine.encode(prompt))
         if stream:

@@ -84,9 +84,24 @@ class Engine:
     def __init__(self, model: str | Path | LoadedModel, *, cache_config: CacheConfig | None = None,
                  batching_config: BatchingConfig | None = None,
                  execution_dtype: str | None = None, device: str = "cuda:0",
-                 ops: Any = None) -> None:
+                 ops: Any = None, revision: str | None = None, offline: bool = True,
+                 cache_dir: str | Path | None = None,
+                 tokenizer_source: str | Path | None = None) -> None:
         """``model``: a model folder (config.json + safetensors) or a loaded model.
-        ``execution_dtype``: "bfloat16" (default) or "float32" (everything in true 32-bit)."""
+        ``execution_dtype``: "bfloat16" (default) or "float32" (everything in true 32-bit).
+        ``revision``, ``offline``, ``cache_dir``: the reference's names for fetching a model by
+        its hub id (src/mlx_one/engine/public.py:64-85). This engine loads local folders only:
+        they are accepted for a local folder (a revision must then be None) and a name that is
+        no folder is refused. ``tokenizer_source``: a folder with ``tokenizer.json``, or the
+        file, when it is not in the model folder."""
+        if not isinstance(model, LoadedModel):
+            if revision is not None:
+                raise ValueError("revision names a hub snapshot; this engine loads local folders")
+            if not Path(model).is_dir():
+                raise FileNotFoundError(
+                    f"{model!s} is no model folder; models are not fetched by name "
+                    f"(offline={offline}, cache_dir={cache_dir})")
+        self._tokenizer_source = None if tokenizer_source is None else Path(tokenizer_source)
         self._loaded = model if isinstance(model, LoadedModel) else load_model(
             model, execution_dtype or "bfloat16", device, ops)
         built = self._loaded.model
@@ -126,6 +141,11 @@ class Engine:
 
     def _load_tokenizer(self):
         path = self._loaded.path / "tokenizer.json" if self._loaded.path else None
+        if self._tokenizer_source is not None:
+            source = self._tokenizer_source
+            path = source / "tokenizer.json" if source.is_dir() else source
+            if not path.is_file():
+                raise FileNotFoundError(f"tokenizer_source: {path} does not exist")
         if path is None or not path.is_file():
             return None
         from tokenizers import Tokenizer

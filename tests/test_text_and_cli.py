@@ -72,6 +72,27 @@ def test_engine_without_tokenizer_asks_for_token_ids(tmp_path):
     assert engine.capabilities()["architecture"] == "lfm2"
 
 
+def test_the_reference_names_for_fetching_a_model(tmp_path):
+    """``revision``, ``offline`` and ``cache_dir`` are accepted for a local folder; a name that
+    is no folder and a revision are refused; ``tokenizer_source`` names a tokenizer elsewhere."""
+    folder = folder_with_tokenizer(tmp_path)
+    elsewhere = tmp_path / "tokenizer_only"
+    elsewhere.mkdir()
+    (folder / "tokenizer.json").rename(elsewhere / "tokenizer.json")
+    with pytest.raises(FileNotFoundError, match="no model folder"):
+        Engine("LiquidAI/LFM2-1.2B", offline=True, device="cpu", ops=PlainOps())
+    with pytest.raises(ValueError, match="revision"):
+        Engine(folder, revision="main", device="cpu", ops=PlainOps())
+    with pytest.raises(FileNotFoundError, match="tokenizer_source"):
+        Engine(folder, tokenizer_source=tmp_path / "nowhere", execution_dtype="float32",
+               device="cpu", ops=PlainOps())
+    for source in (elsewhere, elsewhere / "tokenizer.json"):
+        engine = Engine(folder, offline=True, cache_dir=tmp_path / "unused", tokenizer_source=source,
+                        execution_dtype="float32", device="cpu", ops=PlainOps(),
+                        cache_config=CacheConfig(block_size_tokens=4, capacity_tokens=64))
+        assert engine.encode("w5 w17") == [0, 7, 19]
+
+
 @pytest.mark.gpu
 def test_command_line_generates(tmp_path):
     folder = folder_with_tokenizer(tmp_path, dtype=torch.bfloat16)
@@ -79,7 +100,7 @@ def test_command_line_generates(tmp_path):
     run = lambda *args: subprocess.run([sys.executable, str(ROOT / "bin" / "mlx-one"), *args],
                                        capture_output=True, text=True, timeout=600)
     by_ids = run("generate", str(folder), "0 7 19 5", "--token-ids", "--max-tokens", "5",
-                 "--dtype", "float32")
+                 "--dtype", "float32", "--offline", "--cache-dir", str(tmp_path / "unused"))
     assert by_ids.returncode == 0, by_ids.stderr
     assert [int(t) for t in by_ids.stdout.split()] == plain.greedy([0, 7, 19, 5], 5)
     as_json = run("generate", str(folder), "w5 w17 w3", "--max-tokens", "4", "--json-output",
