@@ -426,7 +426,8 @@ class Engine:
                     safe = text if matched or handle.done() else self._hold_back(text, stop)
                     piece, text_sent = safe[len(text_sent):], max(safe, text_sent, key=len)
                     if matched:
-                        self._scheduler.finish(request, "stop")
+                        with self._turn:
+                            self._scheduler.finish(request, "stop")
                         yield GenerationChunk(request.output[sent - 1], piece, sent, "stop")
                         self._handles.pop(request.request_id, None)
                         return
