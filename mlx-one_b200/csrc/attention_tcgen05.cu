@@ -12,16 +12,20 @@
 // one before. The warps have roles:
 //   softmax warps (4 x PARTS): PARTS threads share query row r (lane r of tensor memory), each
 //              for its share of a tile's keys and of the output dimensions. Per tile a thread
-//              reads its scores with tcgen05.ld, the row's threads agree on the maximum, it
-//              writes exp2(score - max) as bfloat16 into shared memory in the operand layout of
-//              the second product, and then adds the previous tile's P V (read from tensor
-//              memory) into its output registers, scaled as the running maximum moved;
+//              reads its scores with tcgen05.ld, the row's threads agree on the maximum, and
+//              it writes exp2(score - m) as bfloat16 into shared memory in the operand layout
+//              of the second product. The output is summed over the item's tiles by the
+//              product warp in tensor memory; m follows the row's running maximum only when
+//              that has moved by more than 2^8, and only then do the row's threads rescale the
+//              output in tensor memory (tcgen05.ld, multiply, tcgen05.st) before they hand P
+//              over, so most tiles cost no pass over the output. At the item's end they read
+//              the output once, divide by the row's sum and store it;
 //   copy warp  the TMA loads: the query tile once (a 3-D box: head size x group x tokens),
 //              then per key tile lane b looks up page b and copies its K and V into a ring of
 //              three stages;
 //   product warp  allocates tensor memory; one thread issues the products: scores of tile j + 1
 //              are computed while the softmax warps work on tile j (two score buffers), P V
-//              of tile j runs while they work on tile j + 1 (two buffers for it as well).
+//              of tile j, added to the item's output, runs while they work on tile j + 1.
 // V is used as it lies in the cache ([key, head size], head size contiguous): the second
 // product takes it as an MN-major operand.
 //
@@ -50,7 +54,7 @@ constexpr int ERROR_WAIT = 9;
 constexpr int Q_BYTES = ROWS * HD * 2;
 
 // Two shapes of the kernel. With 128 keys a tile a block fills an SM (tensor memory: scores
-// 2 x 128 columns, P V 2 x 64); with 64 keys a tile two blocks share an SM, and while one waits
+// 2 x 128 columns, output 64); with 64 keys a tile two blocks share an SM, and while one waits
 // for a product or a barrier the other computes: faster when there are items for all of them,
 // slower when there are not, since a block then walks its keys in more, smaller steps.
 template <int KEYS_>
@@ -62,7 +66,7 @@ struct Shape {
     static constexpr int STAGE_BYTES = 2 * K_BYTES;
     static constexpr int P_BYTES = ROWS * KEYS * 2;
     static constexpr int SHARED_BYTES = Q_BUFFERS * Q_BYTES + STAGES * STAGE_BYTES + 2 * P_BYTES + 1024;
-    static constexpr int TMEM_COLUMNS = KEYS == 64 ? 256 : 512;    // scores 2 x KEYS, P V 2 x 64
+    static constexpr int TMEM_COLUMNS = KEYS == 64 ? 256 : 512;    // scores 2 x KEYS, output 64 (a power of two is allocated)
 };
 constexpr int MAX_ITEMS = 128;         // (token tile, key head) pairs one block may be given
 
@@ -161,6 +165,26 @@ __device__ __forceinline__ void tmem_load(uint32_t address, float (&v)[N]) {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
     for (int i = 0; i < N; ++i) v[i] = __uint_as_float(r[i]);
+}
+// Writes 16 consecutive 32-bit columns of this thread's lane of tensor memory.
+__device__ __forceinline__ void tmem_store_16(uint32_t address, const uint32_t* r) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+        "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+        ::"r"(address), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]),
+          "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]),
+          "r"(r[14]), "r"(r[15])
+        : "memory");
+}
+template <int N>
+__device__ __forceinline__ void tmem_store(uint32_t address, const float (&v)[N]) {
+    static_assert(N % 16 == 0, "whole stores of 16 columns");
+    uint32_t r[N];
+#pragma unroll
+    for (int i = 0; i < N; ++i) r[i] = __float_as_uint(v[i]);
+#pragma unroll
+    for (int c = 0; c < N / 16; ++c) tmem_store_16(address + c * 16, r + c * 16);
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
 __device__ __forceinline__ float fast_exp2(float x) {
     float y;
@@ -413,7 +437,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q,
                     const uint64_t p_desc =
                         operand_descriptor(p_tile + (kk / 4) * (ROWS * 128)) + 2 * (kk % 4);
                     const uint64_t v_desc = operand_descriptor(v_tile + kk * 2048);
-                    mma_bf16(tmem_base + 2 * KEYS + (now.t & 1) * HD, p_desc, v_desc, idesc_out, kk > 0);
+                    mma_bf16(tmem_base + 2 * KEYS, p_desc, v_desc, idesc_out, kk > 0 || now.j > 0);
                 }
                 mma_commit(kv_empty(s));                 // K and V of this tile are done with
                 mma_commit(o_ready(now.t & 1));
@@ -451,18 +475,16 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q,
             // first row's position; a block with rows beyond the portion's end always masks
             const bool whole = item.tokens_here == tile_tokens;
             const int open_lo = window > 0 ? max(last_position - window + 1, 0) : 0;
-            float m = -INFINITY, l = 0.f, correction = 1.f;
-            float o[MY_DIMS];
-#pragma unroll
-            for (int d = 0; d < MY_DIMS; ++d) o[d] = 0.f;
-            auto add_out = [&](int tile) {
-                // o = o * (how far the maximum moved when the tile was seen) + its P V
+            // m: the maximum that the exponentials are taken against. It follows the running
+            // maximum only when that has moved by more than LAZY (in powers of two), so that the
+            // output so far, which the product warp accumulates in tensor memory over the item's
+            // tiles, has to be rescaled there only then: P grows to 2^LAZY at most meanwhile.
+            constexpr float LAZY = 8.f;
+            float m = -INFINITY, l = 0.f;
+            const uint32_t my_out = tmem_base + lanes + 2 * KEYS + part * MY_DIMS;
+            auto out_ready = [&](int tile) {
                 if (!barrier_wait(o_ready(tile & 1), (tile >> 1) & 1, error_flag)) return false;
                 fence_after_sync();
-                float piece[MY_DIMS];
-                tmem_load<MY_DIMS>(tmem_base + lanes + 2 * KEYS + (tile & 1) * HD + part * MY_DIMS, piece);
-#pragma unroll
-                for (int i = 0; i < MY_DIMS; ++i) o[i] = fmaf(o[i], correction, piece[i]);
                 return true;
             };
             for (int j = 0; j < item.tile_count && ok; ++j, ++t) {
@@ -489,10 +511,26 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q,
 #pragma unroll
                 for (int other = 0; other < PARTS; ++other)
                     top = fmaxf(top, maxima[((t & 1) * PARTS + other) * ROWS + row]);
-                const float new_m = fmaxf(m, top * scale_log2);
-                const float previous = correction;
-                const float moved = new_m == -INFINITY ? 1.f : fast_exp2(m - new_m);
-                const float shift = new_m == -INFINITY ? 0.f : new_m;
+                const float running = fmaxf(m, top * scale_log2);
+                // both threads of a row see the same maxima and take the same decision
+                const bool follow = running > m + LAZY || (m == -INFINITY && running > m);
+                const float moved = !follow ? 1.f : m == -INFINITY ? 0.f : fast_exp2(m - running);
+                // what the product warp has summed so far is against the old maximum: bring it
+                // to the new one before the product of this tile is added (a row that has seen
+                // no key yet has summed zeros). All lanes of a warp go together.
+                const bool rescale = follow && m != -INFINITY && j > 0;
+                if (__any_sync(0xffffffffu, rescale)) {
+                    ok = out_ready(t - 1);
+                    if (!ok) break;
+                    float sofar[MY_DIMS];
+                    tmem_load<MY_DIMS>(my_out, sofar);
+                    const float factor = rescale ? moved : 1.f;
+#pragma unroll
+                    for (int i = 0; i < MY_DIMS; ++i) sofar[i] *= factor;
+                    tmem_store<MY_DIMS>(my_out, sofar);
+                }
+                if (follow) m = running;
+                const float shift = m == -INFINITY ? 0.f : m;
                 float partial[4] = {0.f, 0.f, 0.f, 0.f};
                 unsigned char* p_tile_row = p_row + (t & 1) * P_BYTES;
 #pragma unroll
@@ -512,18 +550,21 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q,
                         packed;
                 }
                 l = l * moved + (partial[0] + partial[1]) + (partial[2] + partial[3]);
-                m = new_m;
-                // P is written and the scores are read: tell the product warp
+                // P is written, the scores are read and the output is against m: tell the
+                // product warp
                 fence_async_shared();
                 fence_before_sync();
                 __syncwarp();
                 if (lane == 0) barrier_arrive(p_ready(t & 1));
-                // the previous tile's P V, scaled by how far the maximum had moved then
-                correction = previous;
-                if (j > 0) ok = add_out(t - 1);
-                correction = moved;
             }
-            if (ok) ok = add_out(t - 1);
+            float o[MY_DIMS];
+#pragma unroll
+            for (int d = 0; d < MY_DIMS; ++d) o[d] = 0.f;
+            if (ok) ok = out_ready(t - 1);
+            if (ok) tmem_load<MY_DIMS>(my_out, o);
+            // the next item's first product overwrites the output: it waits for this item's
+            // reads, since it needs that item's P, which these warps write after this
+            fence_before_sync();
             // the row's sum: all parts used the same maxima, so their sums add
             sums[part * ROWS + row] = l;
             asm volatile("bar.sync %0, %1;" ::"r"(row_barrier), "n"(PARTS * 32) : "memory");

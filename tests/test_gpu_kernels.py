@@ -374,11 +374,25 @@ def test_qk_norm_rope_store(ops, plain, dtype, heads, kv_heads, head_dim, rotary
 
 
 def attention_case(ops, plain, dtype, heads, kv_heads, head_dim, page_size, portions, histories,
-                   window, tensor_cores, seed=6, spike=None, tcgen05=False):
+                   window, tensor_cores, seed=6, spike=None, tcgen05=False, ramp=None):
     torch.manual_seed(seed)
     ctx, table, pages = make_batch(portions, histories, page_size, DEVICE, seed=seed)
     kv = torch.randn(2, pages, kv_heads, page_size, head_dim).to(dtype)
     q = torch.randn(ctx.tokens, heads, head_dim).to(dtype)
+    if ramp is not None:
+        # every query's scores rise by `ramp` (in units of e) per 64 keys along the context, so
+        # that the running maximum keeps moving and earlier keys still weigh in
+        scale = head_dim ** -0.5
+        direction = torch.zeros(head_dim)
+        direction[::2] = 1.0
+        direction /= direction.norm()
+        q = (q.float() * 0.3 + direction * 4.0).to(dtype)
+        for request, (portion, history) in enumerate(zip(portions, histories)):
+            for position in range(history + portion):
+                page = int(table[request, position // page_size])
+                rise = ramp * position / 64 / (4.0 * scale)
+                kv[0, page, :, position % page_size] = (
+                    kv[0, page, :, position % page_size].float() * 0.3 + direction * rise).to(dtype)
     if spike is not None:
         # one far key and the last query are scaled so that this key's score stands out:
         # an error in finding its page or position would change the output visibly
@@ -474,6 +488,18 @@ def test_attention_prefill_tcgen05_many_items(ops, plain, heads, kv_heads, page_
                    window=window, tensor_cores=True, tcgen05=True,
                    spike=(2, 5 if window is None else 2000))
     assert ops.launches - before == 1
+
+
+@pytest.mark.parametrize("ramp", [0.7, 3.0, 12.0])
+@pytest.mark.parametrize("portions,histories", [([300, 1, 128], [500, 900, 0]),
+                                                 ([2100, 2, 1900], [0, 64, 300])])
+def test_attention_prefill_tcgen05_rising_scores(ops, plain, ramp, portions, histories):
+    """Scores that rise along the context: the maximum that the exponentials are taken against
+    follows the running maximum only from time to time, and the output summed so far is then
+    rescaled in tensor memory. Slopes at which that happens every dozen tiles, every other tile
+    and at every tile, in both shapes of the kernel."""
+    attention_case(ops, plain, torch.bfloat16, 8, 2, 64, 16, portions=portions,
+                   histories=histories, window=None, tensor_cores=True, tcgen05=True, ramp=ramp)
 
 
 def test_decode_splits_are_used(ops):
