@@ -46,7 +46,11 @@ using bf16 = __nv_bfloat16;
 constexpr int HD = 64;
 constexpr int ROWS = 128;              // query rows per block
 constexpr int STAGES = 3;              // ring of key/value tiles
-constexpr int PARTS = 2;               // threads that share a query row
+// Threads that share a query row. One: a thread owns its row's scores of a tile and all of its
+// output, and the softmax warps exchange nothing. (Two threads per row, each with half of the keys
+// and of the output, were faster while the output was kept in registers; with the output in
+// tensor memory one is: 8192 tokens 556 -> 603 TFLOP/s.)
+constexpr int PARTS = 1;
 constexpr int COPY_WARP = 4 * PARTS, MMA_WARP = 4 * PARTS + 1;
 constexpr int THREADS = (4 * PARTS + 2) * 32;     // softmax warps, the copy warp, the product warp
 constexpr int WAIT_LIMIT = 1 << 24;
@@ -455,11 +459,9 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q,
         const int row = (warp & 3) * 32 + lane;
         const int token = row / group;
         const uint32_t lanes = (uint32_t)((warp & 3) * 32) << 16;
-        // this thread's pieces of P: block (of 64 keys) and first 16-byte piece within its row
-        const int first_piece = (part * MY_KEYS % 64) / 8;
+        // this thread's row of P in the first block of 64 keys; its keys may span several blocks
         unsigned char* p_row = generic_base + Q_BUFFERS * Q_BYTES + STAGES * STAGE_BYTES +
-                               (part * MY_KEYS / 64) * (ROWS * 128) + (row >> 3) * 1024 +
-                               (row & 7) * 128;
+                               (row >> 3) * 1024 + (row & 7) * 128;
         const int row_barrier = 1 + (warp & 3);            // named barrier of the row's warps
         bool ok = true;
         int t = 0;
@@ -506,11 +508,13 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q,
 #pragma unroll
                 for (int i = 0; i < MY_KEYS; ++i) tops[i & 3] = fmaxf(tops[i & 3], v[i]);
                 float top = fmaxf(fmaxf(tops[0], tops[1]), fmaxf(tops[2], tops[3]));
-                maxima[((t & 1) * PARTS + part) * ROWS + row] = top;
-                asm volatile("bar.sync %0, %1;" ::"r"(row_barrier), "n"(PARTS * 32) : "memory");
+                if (PARTS > 1) {
+                    maxima[((t & 1) * PARTS + part) * ROWS + row] = top;
+                    asm volatile("bar.sync %0, %1;" ::"r"(row_barrier), "n"(PARTS * 32) : "memory");
 #pragma unroll
-                for (int other = 0; other < PARTS; ++other)
-                    top = fmaxf(top, maxima[((t & 1) * PARTS + other) * ROWS + row]);
+                    for (int other = 0; other < PARTS; ++other)
+                        top = fmaxf(top, maxima[((t & 1) * PARTS + other) * ROWS + row]);
+                }
                 const float running = fmaxf(m, top * scale_log2);
                 // both threads of a row see the same maxima and take the same decision
                 const bool follow = running > m + LAZY || (m == -INFINITY && running > m);
@@ -546,8 +550,10 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q,
                     packed.y = pack_bf16(p[2], p[3]);
                     packed.z = pack_bf16(p[4], p[5]);
                     packed.w = pack_bf16(p[6], p[7]);
-                    *reinterpret_cast<uint4*>(p_tile_row + (((first_piece + piece) ^ (row & 7)) << 4)) =
-                        packed;
+                    // 16-byte piece `at` of the row: block at / 8 of 64 keys, swizzled within it
+                    const int at = (part * MY_KEYS) / 8 + piece;
+                    *reinterpret_cast<uint4*>(p_tile_row + (at >> 3) * (ROWS * 128) +
+                                              (((at & 7) ^ (row & 7)) << 4)) = packed;
                 }
                 l = l * moved + (partial[0] + partial[1]) + (partial[2] + partial[3]);
                 // P is written, the scores are read and the output is against m: tell the
@@ -566,11 +572,13 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q,
             // reads, since it needs that item's P, which these warps write after this
             fence_before_sync();
             // the row's sum: all parts used the same maxima, so their sums add
-            sums[part * ROWS + row] = l;
-            asm volatile("bar.sync %0, %1;" ::"r"(row_barrier), "n"(PARTS * 32) : "memory");
-            l = 0.f;
+            if (PARTS > 1) {
+                sums[part * ROWS + row] = l;
+                asm volatile("bar.sync %0, %1;" ::"r"(row_barrier), "n"(PARTS * 32) : "memory");
+                l = 0.f;
 #pragma unroll
-            for (int other = 0; other < PARTS; ++other) l += sums[other * ROWS + row];
+                for (int other = 0; other < PARTS; ++other) l += sums[other * ROWS + row];
+            }
             if (ok && valid) {
                 const float inv = l > 0.f ? 1.f / l : 0.f;
                 const int head = item.kv_head * group + row % group;
