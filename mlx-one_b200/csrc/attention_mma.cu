@@ -415,7 +415,6 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kv,
     constexpr int ROW_FLOATS = HD + 2;
     extern __shared__ __align__(16) unsigned char shared_bytes[];
     griddep_launch();
-    griddep_wait();
     const int group = heads / kv_heads;
     const int groups_of_8 = (group + DECODE_HEADS - 1) / DECODE_HEADS;
     const int kv_head = blockIdx.x / groups_of_8;
@@ -439,15 +438,22 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kv,
     constexpr int STAGE = 2 * KEYS * T::STRIDE;          // elements of a K and a V tile
     bf16* ring = reinterpret_cast<bf16*>(shared_bytes) + (size_t)warp * DECODE_STAGES * STAGE;
 
+    // The kernel before this one wrote the token's own key and value (and its query): the tiles
+    // before the one that holds them are what earlier steps left, and are asked for before that
+    // kernel is waited for, so that they are on their way while it finishes.
     int tile = my_first + warp;
-#pragma unroll
-    for (int ahead = 0; ahead < DECODE_STAGES - 1; ++ahead) {
+    const int newest = position / KEYS;
+    auto fetch = [&](int ahead) {
         const int coming = tile + ahead * DECODE_WARPS;
         if (coming <= my_last)
             load_tile<HD, KEYS>(ring + ahead * STAGE, ring + ahead * STAGE + KEYS * T::STRIDE, pages,
                                 coming * KEYS, lowest, position, lane, 32);
         copy_commit();
-    }
+    };
+    int ahead = 0;
+    for (; ahead < DECODE_STAGES - 1 && tile + ahead * DECODE_WARPS != newest; ++ahead) fetch(ahead);
+    griddep_wait();
+    for (; ahead < DECODE_STAGES - 1; ++ahead) fetch(ahead);
 
     // q^T as the 8-column operand: head g, dims 16 kk + 2t (+1) and + 8
     uint32_t qb[HD / 16][2];

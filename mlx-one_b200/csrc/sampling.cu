@@ -575,7 +575,9 @@ __global__ void decode_advance_kernel(const int* __restrict__ chosen, int* __res
                                       int* __restrict__ positions, int* __restrict__ history,
                                       int* __restrict__ record, int* __restrict__ counter,
                                       int requests, int max_steps) {
-    griddep_launch();
+    // No early start for what follows: kernels of the next step read positions before they wait
+    // for their predecessors (the decode attention asks for its old keys then), so the next
+    // step begins only when this kernel has ended.
     griddep_wait();
     const int r = blockIdx.x * blockDim.x + threadIdx.x;
     const int step = *counter;
