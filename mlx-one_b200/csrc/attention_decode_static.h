@@ -20,6 +20,12 @@
 //   kernel writes every partial result before it reads it, so nothing has to be cleared. Two
 //   calls that overlap on the GPU (different streams, no ordering between them) would write
 //   the same scratch and race: order them.
+// * The kernel is launched as a programmatic dependent of the kernel before it in the stream
+//   (unless dependent launches are switched off). Before it waits for that kernel it reads
+//   `positions`, `block_table` and the keys and values of positions before the newest one:
+//   a kernel that writes any of these and lets its dependents start early
+//   (griddepcontrol.launch_dependents) must not be the one before this call. Kernels that do
+//   not use that instruction, and copies, are safe.
 #pragma once
 
 #include <cuda_runtime.h>
