@@ -22,7 +22,8 @@ from ..cache.manager import CacheManager
 from ..sampling.options import GenerationChunk, GenerationResult, TextGenerationOptions
 from .loading import LoadedModel, load_model
 from .runner import Runner, StepEntry
-from .scheduler import BatchingConfig, Phase, Request, Scheduled, Scheduler
+from .scheduler import (BatchingConfig, Phase, Request, RequestTimeoutError, Scheduled,
+                        Scheduler)
 
 
 @dataclass(frozen=True)
@@ -275,6 +276,9 @@ class Engine:
         running = scheduler.running
         if any(id(r) not in drew or r.cancelled or r.options.stop for r in running):
             return None          # a prompt still in portions, decodes taking turns, a cancel
+        now = scheduler.clock()
+        if any(r.deadline is not None and now >= r.deadline for r in running):
+            return None          # a request's time is up: the next plan ends it
         going_on = [r for r in running if len(r.output) + 1 < r.options.max_tokens]
         if not going_on or len(going_on) > self.batching_config.max_scheduled_tokens:
             return None
@@ -338,6 +342,8 @@ class Engine:
     def _result(self, handle: EngineRequestHandle) -> GenerationResult:
         request = handle.request
         self._handles.pop(request.request_id, None)
+        if request.finish_reason == "timeout":
+            raise RequestTimeoutError("generation request timed out")
         finished = handle.finished_at or time.perf_counter()
         first = handle.first_token_at or finished
         count = len(request.output)
@@ -434,6 +440,9 @@ class Engine:
                 yield GenerationChunk(request.output[sent - 1], piece, sent)
             if handle.done():
                 reason = request.finish_reason or "length"
+                if reason == "timeout":
+                    self._handles.pop(request.request_id, None)
+                    raise RequestTimeoutError("generation request timed out")
                 yield GenerationChunk(None, "", sent, "stop" if reason == "cancelled" else reason,
                                       request.terminal_token_id)
                 self._handles.pop(request.request_id, None)

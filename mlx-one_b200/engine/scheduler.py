@@ -22,6 +22,7 @@ from __future__ import annotations
 
 import enum
 import itertools
+import time
 from collections import deque
 from dataclasses import dataclass, field
 from typing import Any, Sequence
@@ -41,6 +42,9 @@ class BatchingConfig:
     prefill_chunk_size: int = 512
     max_scheduled_tokens: int = 2048
     max_prefill_tokens: int = 1024
+    # seconds from its submission after which a request that has not finished is ended with
+    # RequestTimeoutError; 0: never
+    timeout: float = 600.0
     # not in the reference: while all running requests decode, launch the next step (its input
     # tokens taken on the device, where they were chosen) before the last step's tokens are read
     # back
@@ -52,10 +56,18 @@ class BatchingConfig:
             value = getattr(self, name)
             if isinstance(value, bool) or not isinstance(value, int) or value < 1:
                 raise ValueError(f"{name} must be positive")
+        if isinstance(self.timeout, bool) or not isinstance(self.timeout, (int, float)) \
+                or self.timeout < 0:
+            raise ValueError("timeout must be zero or positive")
 
 
 class QueueFullError(RuntimeError):
     """More requests are waiting than ``queue_size`` allows."""
+
+
+class RequestTimeoutError(RuntimeError):
+    """A request did not finish within ``BatchingConfig.timeout`` seconds of its submission
+    (the reference's RequestTimeoutError, src/mlx_one/engine/actor.py:429-438)."""
 
 
 class Phase(enum.Enum):
@@ -75,9 +87,10 @@ class Request:
     fed: int = 0                                     # prompt tokens already run
     output: list[int] = field(default_factory=list)
     next_token: int | None = None                    # sampled, to be fed by the next step
-    finish_reason: str | None = None                 # "stop" | "length" | "cancelled"
+    finish_reason: str | None = None                 # "stop" | "length" | "cancelled" | "timeout"
     terminal_token_id: int | None = None
     cancelled: bool = False
+    deadline: float | None = None                    # on the scheduler's clock; None: none
 
     @property
     def reserve_tokens(self) -> int:
@@ -95,9 +108,10 @@ class Scheduled:
 
 
 class Scheduler:
-    def __init__(self, config: BatchingConfig, cache: CacheManager) -> None:
+    def __init__(self, config: BatchingConfig, cache: CacheManager, clock=time.monotonic) -> None:
         self.config = config
         self.cache = cache
+        self.clock = clock
         self.waiting: deque[Request] = deque()
         self.running: list[Request] = []
         self._decode_turn = 0
@@ -120,6 +134,8 @@ class Scheduler:
                 f"tokens can never fit into a cache of {self.cache.capacity_tokens} tokens",
                 retryable=False)
         request.phase = Phase.WAITING
+        if self.config.timeout and request.deadline is None:
+            request.deadline = self.clock() + self.config.timeout
         self.waiting.append(request)
 
     def cancel(self, request: Request) -> None:
@@ -151,9 +167,16 @@ class Scheduler:
             self.running.append(request)
 
     def plan(self) -> list[Scheduled]:
-        """Frees cancelled requests, admits waiting ones and chooses the next step."""
+        """Frees cancelled requests and those whose time is up, admits waiting ones and chooses
+        the next step."""
+        now = self.clock()
         for request in [r for r in self.running if r.cancelled]:
             self._finish(request, "cancelled")
+        for request in [r for r in self.running if r.deadline is not None and now >= r.deadline]:
+            self._finish(request, "timeout")
+        for request in [r for r in self.waiting if r.deadline is not None and now >= r.deadline]:
+            self.waiting.remove(request)
+            self._finish(request, "timeout", held=False)
         self._admit()
         config = self.config
         budget = config.max_scheduled_tokens

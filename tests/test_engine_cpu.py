@@ -193,3 +193,42 @@ def test_coroutines_share_the_engine(models):
     stats = engine.runtime_stats()
     assert stats["running"] == 0 and stats["pages_free"] == stats["pages_total"]
     engine.close()
+
+
+@pytest.mark.parametrize("pipeline", [True, False])
+def test_a_timed_out_request_raises_and_the_others_finish(models, pipeline):
+    """The clock passes a request's deadline while it decodes (also while steps are launched
+    ahead): waiting for it raises RequestTimeoutError, the other request's tokens are what it
+    gets alone, and every page comes back."""
+    from mlx_one_b200.engine import RequestTimeoutError
+
+    folder, loaded, plain = models["A"]
+    config, _, page = CONFIGS["A"]
+    engine = Engine(loaded, cache_config=CacheConfig(block_size_tokens=page, capacity_tokens=512),
+                    batching_config=BatchingConfig(max_sequences=2, timeout=50.0,
+                                                   pipeline_decode=pipeline))
+    now = [0.0]
+    engine._scheduler.clock = lambda: now[0]
+    slow_prompt, quick_prompt = prompts(config["vocab_size"], (9, 14), seed=21)
+    slow = engine.submit_ids(slow_prompt, max_tokens=400, ignore_eos=True)
+    for _ in range(6):
+        engine.step()
+    now[0] = 40.0
+    quick = engine.submit_ids(quick_prompt, max_tokens=12, ignore_eos=True)
+    for _ in range(5):
+        engine.step()
+    now[0] = 55.0                                   # past the first deadline, before the second
+    assert list(quick.result().token_ids) == plain.greedy(quick_prompt, 12)
+    with pytest.raises(RequestTimeoutError):
+        slow.result()
+    assert 0 < len(slow.request.output) < 400
+    engine.run()
+    stats = engine.runtime_stats()
+    assert stats["running"] == 0 and stats["pages_free"] == stats["pages_total"]
+    with pytest.raises(RequestTimeoutError):
+        now[0] = 0.0
+        stream = engine.stream_ids(slow_prompt, max_tokens=400, ignore_eos=True)
+        for count, _ in enumerate(stream):
+            if count == 3:
+                now[0] = 1000.0
+    engine.close()

@@ -43,6 +43,9 @@ def test_batching_config_has_the_reference_names_and_checks():
             config.max_scheduled_tokens, config.max_prefill_tokens) == (1, 8, 512, 2048, 1024)
     with pytest.raises(ValueError):
         BatchingConfig(prefill_chunk_size=0)
+    assert config.timeout == 600.0
+    with pytest.raises(ValueError):
+        BatchingConfig(timeout=-1)
 
 
 def test_prompts_are_cut_under_the_budget_and_decodes_come_first():
@@ -167,3 +170,37 @@ def test_budget_of_one_alternates_between_decode_and_prompt():
         assert len(step) == 1
         kinds.append(step[0].request is a)
     assert True in kinds and False in kinds and b.phase is Phase.DECODE
+
+
+def test_a_request_whose_time_is_up_ends_and_frees_its_pages():
+    """``timeout`` seconds after its submission a request ends with the reason "timeout",
+    whether it runs or still waits; its pages and slot come back; others go on. 0: never."""
+    scheduler, cache = make(max_sequences=1, timeout=10.0)
+    now = [100.0]
+    scheduler.clock = lambda: now[0]
+    running = request(scheduler, 5, max_tokens=50)
+    scheduler.submit(running)
+    run_step(scheduler, cache)
+    waiting = request(scheduler, 5, max_tokens=50)
+    now[0] = 105.0
+    scheduler.submit(waiting)
+    assert (running.deadline, waiting.deadline) == (110.0, 115.0)
+    run_step(scheduler, cache)
+    assert running.phase is Phase.DECODE and waiting.phase is Phase.WAITING
+    now[0] = 110.0
+    step = run_step(scheduler, cache)
+    assert running.finish_reason == "timeout" and running.request_id not in cache
+    assert [s.request for s in step] == [waiting]            # the slot went to the next one
+    now[0] = 200.0
+    late = request(scheduler, 5)
+    scheduler.submit(late)
+    now[0] = 215.0
+    run_step(scheduler, cache)
+    assert waiting.finish_reason == "timeout" and late.finish_reason == "timeout"
+    assert not scheduler.has_work()
+    stats = cache.stats()
+    assert stats.pages_free == stats.pages_total and stats.slots_free == stats.slots_total
+    never, cache = make(timeout=0)
+    patient = request(never, 5)
+    never.submit(patient)
+    assert patient.deadline is None
