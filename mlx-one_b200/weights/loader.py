@@ -19,7 +19,7 @@ import torch
 
 from ..parts.model import expected_tensors
 from ..parts.spec import ModelSpec
-from .safetensors_io import SafetensorsFile, checkpoint_files
+from .safetensors_io import SafetensorsError, SafetensorsFile, checkpoint_files, checkpoint_index
 
 
 class WeightError(ValueError):
@@ -98,6 +98,19 @@ def load_weights(model_dir: str | Path, spec: ModelSpec, dtype: torch.dtype,
                 where[name] = handle
         if twice:
             raise WeightError((), (), (), sorted(twice))
+        weight_map = checkpoint_index(model_dir)
+        if weight_map is not None:
+            # the index and the shards must say the same (src/mlx_one/text/loading.py:547-554)
+            astray = sorted(name for name, handle in where.items()
+                            if weight_map.get(name) != handle.path.name)
+            absent = sorted(set(weight_map) - set(where))
+            if astray or absent:
+                raise SafetensorsError(
+                    "the index and the shards do not match: "
+                    + "; ".join(part for part in (
+                        f"not where the index says: {', '.join(astray[:8])}" if astray else "",
+                        f"in the index but in no shard: {', '.join(absent[:8])}" if absent else "")
+                        if part))
         bound = check_names(spec, stored)
         tensors = {}
         for name, (stored_name, axis) in bound.items():

@@ -86,23 +86,47 @@ class SafetensorsFile:
         self.close()
 
 
+def checkpoint_index(model_dir: str | Path) -> dict[str, str] | None:
+    """``weight_map`` of ``model.safetensors.index.json`` (tensor name -> file name), or None
+    if the folder has no index."""
+    index = Path(model_dir) / "model.safetensors.index.json"
+    if not index.is_file():
+        return None
+    try:
+        value = json.loads(index.read_text()).get("weight_map")
+    except (ValueError, AttributeError) as error:
+        raise SafetensorsError(f"{index}: not a JSON object ({error})") from error
+    if not isinstance(value, dict) or not value:
+        raise SafetensorsError(f"{index}: a non-empty weight_map is required")
+    if any(not isinstance(name, str) or not isinstance(file, str) for name, file in value.items()):
+        raise SafetensorsError(f"{index}: weight_map must map tensor names to file names")
+    return value
+
+
 def checkpoint_files(model_dir: str | Path) -> list[Path]:
-    """The safetensors files of a model folder: ``model.safetensors``, or the shards that
-    ``model.safetensors.index.json`` names (src/mlx_one/text/loading.py:538-610)."""
+    """The safetensors files of a model folder, by the reference's rules
+    (src/mlx_one/text/loading.py:571-610): one file, or the shards that
+    ``model.safetensors.index.json`` names; several files without an index are refused, so are
+    shards that are missing, lie outside the folder (also through a symbolic link) or are no
+    safetensors files, and folders that hold pickle checkpoints only."""
     root = Path(model_dir)
-    index = root / "model.safetensors.index.json"
-    if index.is_file():
-        names = sorted(set(json.loads(index.read_text())["weight_map"].values()))
-        files = [root / name for name in names]
-    elif (root / "model.safetensors").is_file():
-        files = [root / "model.safetensors"]
-    else:
-        files = sorted(root.glob("*.safetensors"))
+    files = sorted(root.glob("*.safetensors"))
     if not files:
-        raise FileNotFoundError(f"no safetensors file in {root}")
+        pickled = list(root.glob("*.bin")) + list(root.glob("*.pt"))
+        detail = "; pickle checkpoints (.bin, .pt) are not accepted" if pickled else ""
+        raise FileNotFoundError(f"no safetensors file in {root}{detail}")
+    weight_map = checkpoint_index(root)
+    if weight_map is not None:
+        files = sorted({root / name for name in weight_map.values()})
+        for path in files:
+            if path.parent != root or not path.is_file():
+                raise FileNotFoundError(f"{path} is named by the index but is no file of {root}")
+    elif len(files) != 1:
+        raise SafetensorsError(f"{root} holds {len(files)} safetensors files and no index")
+    inside = root.resolve()
     for path in files:
-        if not path.is_file():
-            raise FileNotFoundError(f"{path} is named by the index but does not exist")
+        if path.suffix != ".safetensors" or path.resolve().parent != inside:
+            raise SafetensorsError(f"{path} is no safetensors file inside {root}")
     return files
 
 

@@ -165,3 +165,57 @@ def test_random_weights_are_seeded_and_distributed(tmp_path):
     assert abs(float(norm.mean()) - 1) < 0.05 and 0.05 < float(norm.std()) < 0.15
     assert "lm_head.weight" in tensors and "model.layers.1.conv.conv_bias" in tensors
     check_names(spec, {k: tuple(v.shape) for k, v in tensors.items()})
+
+
+def test_shards_follow_the_index_and_stay_inside_the_folder(tmp_path):
+    """The reference's rules for checkpoint files (src/mlx_one/text/loading.py:538-610): shards
+    need an index that says where every tensor is; files outside the folder, pickle checkpoints
+    and several files without an index are refused."""
+    spec = describe(Lfm2Config.from_dict(TINY_A))
+    tensors = random_tensors(spec, 4)
+    names = sorted(tensors)
+    halves = {"model-00001-of-00002.safetensors": names[::2],
+              "model-00002-of-00002.safetensors": names[1::2]}
+    folder = tmp_path / "sharded"
+    folder.mkdir()
+    for file, part in halves.items():
+        write_safetensors(folder / file, {name: tensors[name] for name in part})
+    with pytest.raises(SafetensorsError, match="no index"):
+        load_weights(folder, spec, torch.bfloat16, "cpu")
+    weight_map = {name: file for file, part in halves.items() for name in part}
+    index = folder / "model.safetensors.index.json"
+    index.write_text(json.dumps({"weight_map": weight_map}))
+    loaded = load_weights(folder, spec, torch.bfloat16, "cpu")
+    assert all(torch.equal(loaded[name], tensors[name]) for name in names)
+    # a tensor that lies in another shard than the index says; a name that no shard holds
+    swapped = dict(weight_map)
+    swapped[names[0]] = "model-00002-of-00002.safetensors"
+    index.write_text(json.dumps({"weight_map": swapped}))
+    with pytest.raises(SafetensorsError, match="not where the index says"):
+        load_weights(folder, spec, torch.bfloat16, "cpu")
+    index.write_text(json.dumps({"weight_map": {**weight_map, "ghost.weight": next(iter(halves))}}))
+    with pytest.raises(SafetensorsError, match="in no shard"):
+        load_weights(folder, spec, torch.bfloat16, "cpu")
+    index.write_text(json.dumps({"weight_map": {}}))
+    with pytest.raises(SafetensorsError, match="weight_map"):
+        load_weights(folder, spec, torch.bfloat16, "cpu")
+    index.write_text(json.dumps({"weight_map": {**weight_map, names[0]: "gone.safetensors"}}))
+    with pytest.raises(FileNotFoundError, match="named by the index"):
+        load_weights(folder, spec, torch.bfloat16, "cpu")
+    index.write_text(json.dumps({"weight_map": {**weight_map, names[0]: "../model.safetensors"}}))
+    with pytest.raises(FileNotFoundError, match="named by the index"):
+        load_weights(folder, spec, torch.bfloat16, "cpu")
+    # a shard that is a link to a file elsewhere
+    outside = tmp_path / "elsewhere.safetensors"
+    write_safetensors(outside, tensors)
+    linked = tmp_path / "linked"
+    linked.mkdir()
+    (linked / "model.safetensors").symlink_to(outside)
+    with pytest.raises(SafetensorsError, match="inside"):
+        load_weights(linked, spec, torch.bfloat16, "cpu")
+    # pickle checkpoints are named in the error, not read
+    pickled = tmp_path / "pickled"
+    pickled.mkdir()
+    (pickled / "pytorch_model.bin").write_bytes(b"\x80\x02")
+    with pytest.raises(FileNotFoundError, match="pickle checkpoints"):
+        load_weights(pickled, spec, torch.bfloat16, "cpu")
