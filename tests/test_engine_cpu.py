@@ -232,3 +232,53 @@ def test_a_timed_out_request_raises_and_the_others_finish(models, pipeline):
             if count == 3:
                 now[0] = 1000.0
     engine.close()
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_random_load_on_the_entry_point(models, seed):
+    """Requests that arrive while others run, with random lengths, budgets, portion sizes and
+    numbers of sequences, a cache so small that some must wait, some cancelled on the way: every
+    finished request has the tokens it gets alone, nothing is lost and every page comes back."""
+    import random
+
+    rng = random.Random(seed)
+    name = rng.choice(["A", "B", "C"])
+    folder, loaded, plain = models[name]
+    config, _, page = CONFIGS[name]
+    budget = rng.choice([3, 8, 24, 64])
+    engine = Engine(loaded,
+                    cache_config=CacheConfig(block_size_tokens=page,
+                                             capacity_tokens=rng.choice([96, 160, 512])),
+                    batching_config=BatchingConfig(
+                        max_sequences=rng.choice([1, 2, 3, 5]), queue_size=64,
+                        prefill_chunk_size=rng.choice([2, 5, 16, 64]), max_scheduled_tokens=budget,
+                        max_prefill_tokens=rng.choice([budget, max(budget // 2, 1)]),
+                        pipeline_decode=rng.random() < 0.5))
+    lengths = [rng.choice([1, 2, rng.randint(3, 20), rng.randint(20, 45)]) for _ in range(9)]
+    waiting = list(zip(prompts(config["vocab_size"], lengths, seed=100 + seed),
+                       [rng.randint(1, 9) for _ in lengths]))
+    handles, cancelled = [], set()
+    while waiting or engine._scheduler.has_work() or engine._inflight is not None:
+        while waiting and rng.random() < 0.4:
+            prompt, count = waiting.pop(0)
+            handles.append((prompt, count, engine.submit_ids(prompt, max_tokens=count,
+                                                             ignore_eos=True)))
+        if handles and rng.random() < 0.05:
+            index = rng.randrange(len(handles))
+            if not handles[index][2].done():
+                handles[index][2].cancel()
+                cancelled.add(index)
+        engine.step()
+        engine.cache.check()
+    assert len(handles) == len(lengths)
+    for index, (prompt, count, handle) in enumerate(handles):
+        result = handle.result()
+        want = plain.greedy(prompt, count)
+        if index in cancelled:
+            assert list(result.token_ids) == want[:len(result.token_ids)]
+        else:
+            assert list(result.token_ids) == want and result.finish_reason == "length"
+    stats = engine.runtime_stats()
+    assert stats["running"] == 0 and stats["waiting"] == 0
+    assert stats["pages_free"] == stats["pages_total"]
+    engine.close()
