@@ -77,7 +77,7 @@ class EngineRequestHandle:
 
     def result(self) -> GenerationResult:
         while not self.done():
-            self._engine.step()
+            self._engine._drive_once()
         return self._engine._result(self)
 
 
@@ -128,6 +128,7 @@ class Engine:
         self._copy_turn = 0
         self._inflight: _InFlight | None = None
         self._turn = threading.RLock()       # one thread at a time plans, launches and commits
+        self._stepped = threading.Condition()   # notified after every turn
 
     # ------------------------------------------------------------------ set-up
 
@@ -226,7 +227,25 @@ class Engine:
         request's wait on a thread of its own) may drive the loop: whichever holds the turn
         moves every running request on by one step."""
         with self._turn:
-            return self._step()
+            touched = self._step()
+        with self._stepped:
+            self._stepped.notify_all()
+        return touched
+
+    def _drive_once(self) -> None:
+        """One turn of the loop if no other thread is in one; else a wait until that thread's
+        turn has ended. A thread that waits for its request thus sees it finish without having
+        to win the lock from the thread that keeps the loop going."""
+        if self._turn.acquire(blocking=False):
+            try:
+                self._step()
+            finally:
+                self._turn.release()
+            with self._stepped:
+                self._stepped.notify_all()
+        else:
+            with self._stepped:
+                self._stepped.wait(0.005)
 
     def _step(self) -> list[Request]:
         previous = self._inflight
@@ -422,7 +441,7 @@ class Engine:
         stop = request.options.stop
         while True:
             if not handle.done():
-                self.step()
+                self._drive_once()
             while sent < len(request.output):
                 sent += 1
                 piece = ""
