@@ -12,6 +12,7 @@ from __future__ import annotations
 
 import threading
 import time
+from collections import deque
 from dataclasses import dataclass
 from pathlib import Path
 from typing import Any, Iterator, Sequence
@@ -55,6 +56,9 @@ class _InFlight:
     event: Any
     draws: int
     chosen_on_device: bool
+    launched_at: float = 0.0
+    ahead: bool = False
+    prompt_tokens: int = 0
 
 
 class EngineRequestHandle:
@@ -87,14 +91,16 @@ class Engine:
                  execution_dtype: str | None = None, device: str = "cuda:0",
                  ops: Any = None, revision: str | None = None, offline: bool = True,
                  cache_dir: str | Path | None = None,
-                 tokenizer_source: str | Path | None = None) -> None:
+                 tokenizer_source: str | Path | None = None,
+                 trace_sink: Any = None) -> None:
         """``model``: a model folder (config.json + safetensors) or a loaded model.
         ``execution_dtype``: "bfloat16" (default) or "float32" (everything in true 32-bit).
         ``revision``, ``offline``, ``cache_dir``: the reference's names for fetching a model by
         its hub id (src/mlx_one/engine/public.py:64-85). This engine loads local folders only:
         they are accepted for a local folder (a revision must then be None) and a name that is
         no folder is refused. ``tokenizer_source``: a folder with ``tokenizer.json``, or the
-        file, when it is not in the model folder."""
+        file, when it is not in the model folder. ``trace_sink``: called with the record of
+        every committed step (see ``step_traces``)."""
         if not isinstance(model, LoadedModel):
             if revision is not None:
                 raise ValueError("revision names a hub snapshot; this engine loads local folders")
@@ -123,7 +129,10 @@ class Engine:
         self._scheduler = Scheduler(self.batching_config, self._cache)
         self._handles: dict[Any, EngineRequestHandle] = {}
         self._tokenizer = self._load_tokenizer()
-        self._stats = {"steps": 0, "steps_ahead": 0, "tokens_run": 0, "tokens_sampled": 0}
+        self._stats = {"steps": 0, "steps_ahead": 0, "steps_committed": 0, "tokens_run": 0,
+                       "tokens_sampled": 0}
+        self._traces: deque[dict[str, Any]] = deque(maxlen=4096)
+        self._trace_sink = trace_sink          # called with every step's record, if given
         self._pinned: list[torch.Tensor | None] = [None, None]
         self._copy_turn = 0
         self._inflight: _InFlight | None = None
@@ -267,6 +276,7 @@ class Engine:
         """Launches a step; the tokens of the requests that draw one are chosen on the device
         inside it (argmax, or the sampling kernel with each request's options, seed and count
         of tokens drawn so far; ``ahead``: tokens drawn but not yet committed)."""
+        started = time.perf_counter()
         if entries is None:
             entries = [StepEntry(item.request.request_id, item.tokens,
                                  (len(item.tokens) - 1,) if item.samples else ())
@@ -283,7 +293,12 @@ class Engine:
             host, event = self._start_copy(self._runner.last_greedy)
         self._stats["steps"] += 1
         self._stats["tokens_run"] += sum(len(item.tokens) for item in planned)
-        return _InFlight(list(planned), host, event, len(drawing), bool(drawing))
+        # a step launched ahead holds decode tokens only (a request whose last portion is not
+        # committed yet still counts as being in its prompt)
+        prompt_tokens = 0 if ahead else sum(len(item.tokens) for item in planned
+                                            if item.request.phase is Phase.PREFILL)
+        return _InFlight(list(planned), host, event, len(drawing), bool(drawing),
+                         launched_at=started, ahead=ahead > 0, prompt_tokens=prompt_tokens)
 
     def _launch_ahead(self, previous: "_InFlight"):
         """The step after ``previous``, launched before ``previous`` is committed, or None if
@@ -326,6 +341,7 @@ class Engine:
             planned, sampled = kept, tokens
         touched = self._scheduler.commit(planned, sampled)
         now = time.perf_counter()
+        self._trace(inflight, now)
         for request in touched:
             handle = self._handles.get(request.request_id)
             if handle is None:
@@ -336,6 +352,33 @@ class Engine:
                 handle.finished_at = now
         self._stats["tokens_sampled"] += len(sampled)
         return touched
+
+    def _trace(self, inflight: "_InFlight", committed_at: float) -> None:
+        """One record per step, as the reference's runners keep them
+        (src/mlx_one/engine/hybrid.py:242-251, kept in a deque of 4096 and handed to an optional
+        sink, src/mlx_one/engine/actor.py:77,481-500). Nothing is padded here, so the tokens are
+        the real ones; the duration is the host's, from the launch to the commit."""
+        items = inflight.planned
+        prompt_tokens = inflight.prompt_tokens
+        tokens = sum(len(item.tokens) for item in items)
+        record = {
+            "step": self._stats["steps_committed"],
+            "phase": "decode" if prompt_tokens == 0 else "prefill" if prompt_tokens == tokens
+                     else "mixed",
+            "request_ids": tuple(item.request.request_id for item in items),
+            "batch_size": len(items), "tokens": tokens, "prompt_tokens": prompt_tokens,
+            "decode_tokens": tokens - prompt_tokens, "draws": inflight.draws,
+            "launched_ahead": inflight.ahead,
+            "duration_s": committed_at - inflight.launched_at,
+        }
+        self._stats["steps_committed"] += 1
+        self._traces.append(record)
+        if self._trace_sink is not None:
+            self._trace_sink(record)
+
+    def step_traces(self) -> list[dict[str, Any]]:
+        """The records of the last steps (at most 4096), oldest first."""
+        return list(self._traces)
 
     def _start_copy(self, tokens: torch.Tensor):
         """Starts the copy of the chosen tokens to the host; returns (host buffer, event)."""

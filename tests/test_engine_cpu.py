@@ -282,3 +282,28 @@ def test_random_load_on_the_entry_point(models, seed):
     assert stats["running"] == 0 and stats["waiting"] == 0
     assert stats["pages_free"] == stats["pages_total"]
     engine.close()
+
+
+def test_every_step_leaves_a_record(models):
+    """Per-step records as the reference's runners keep them: which requests, how many prompt
+    and decode tokens, how many tokens were drawn, whether the step was launched ahead; the
+    sink gets every record."""
+    folder, loaded, plain = models["A"]
+    config, _, page = CONFIGS["A"]
+    seen = []
+    engine = Engine(loaded, cache_config=CacheConfig(block_size_tokens=page, capacity_tokens=256),
+                    batching_config=BatchingConfig(max_sequences=2, prefill_chunk_size=8,
+                                                   max_scheduled_tokens=16),
+                    trace_sink=seen.append)
+    first, second = prompts(config["vocab_size"], (19, 5), seed=4)
+    results = engine.generate_batch_ids([first, second], TextGenerationOptions(max_tokens=4))
+    records = engine.step_traces()
+    assert records == seen and [r["step"] for r in records] == list(range(len(records)))
+    assert sum(r["prompt_tokens"] for r in records) == len(first) + len(second)
+    assert sum(r["draws"] for r in records) >= sum(len(r.token_ids) for r in results)
+    assert records[0]["phase"] == "prefill" and records[0]["tokens"] <= 16
+    assert any(r["phase"] == "mixed" for r in records)       # a decode beside a prompt portion
+    assert records[-1]["phase"] == "decode" and records[-1]["prompt_tokens"] == 0
+    assert any(r["launched_ahead"] for r in records)
+    assert all(r["duration_s"] >= 0 and r["batch_size"] == len(r["request_ids"]) for r in records)
+    assert engine.runtime_stats()["steps_committed"] == len(records)
