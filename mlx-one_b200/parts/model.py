@@ -91,13 +91,22 @@ class Model:
             LayerCall(call.layer, index if call.cache is None else call.cache, call.writes_cache)
             for index, call in enumerate(spec.order))
         self.cache_needs = cache_entries(spec)
+        # For debugging: called as observer(place, residual, delta) after the embedding
+        # (place -1) and after every call of a layer (place = its number in the order); the
+        # hidden state there is residual + delta. It sees the step's own tensors: copy what is
+        # to be kept. Steps that are replayed from a CUDA graph do not call it.
+        self.observer = None
 
     def forward(self, ctx: StepContext):
         residual = self.ops.embedding(ctx.token_ids, self.embedding)
         delta = None
-        for call in self.order:
+        if self.observer is not None:
+            self.observer(-1, residual, delta)
+        for place, call in enumerate(self.order):
             delta = self.layers[call.layer].forward(residual, delta, ctx,
                                                     ctx.views.get(call.cache), call.writes_cache)
+            if self.observer is not None:
+                self.observer(place, residual, delta)
         return residual, delta
 
     def logits(self, residual, delta, rows: torch.Tensor) -> torch.Tensor:

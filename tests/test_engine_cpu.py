@@ -307,3 +307,31 @@ def test_every_step_leaves_a_record(models):
     assert any(r["launched_ahead"] for r in records)
     assert all(r["duration_s"] >= 0 and r["batch_size"] == len(r["request_ids"]) for r in records)
     assert engine.runtime_stats()["steps_committed"] == len(records)
+
+
+def test_hidden_states_can_be_watched_layer_by_layer(models):
+    """``Model.observer`` sees the stream after the embedding and after every layer: the hidden
+    states of a request cut into steps equal the plain implementation's, layer by layer."""
+    import plain_lfm2
+
+    folder, loaded, plain = models["C"]
+    config, _, page = CONFIGS["C"]
+    (tokens,) = prompts(config["vocab_size"], (23,), seed=17)
+    runner, cache = runner_for(loaded, page, 64)
+    seen = {}
+
+    def watch(place, residual, delta):
+        state = residual if delta is None else residual + delta.to(residual.dtype)
+        seen.setdefault(place, []).append(state.clone())
+
+    loaded.model.observer = watch
+    try:
+        replay(runner, cache, [([("r", tokens[:9])], []), ([("r", tokens[9:21])], []),
+                               ([("r", tokens[21:22])], []), ([("r", tokens[22:])], ["r"])])
+    finally:
+        loaded.model.observer = None
+    x = plain.w["model.embed_tokens.weight"][torch.tensor(tokens)]
+    assert torch.equal(torch.cat(seen[-1]), x)
+    for index in range(plain.cfg["num_hidden_layers"]):
+        x = plain_lfm2.decoder_layer(x, plain.w, index, plain.cfg)
+        torch.testing.assert_close(torch.cat(seen[index]), x, atol=1e-4, rtol=1e-4)
