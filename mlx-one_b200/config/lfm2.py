@@ -47,68 +47,92 @@ class Lfm2Config:
     extra: Mapping[str, Any] = field(default_factory=dict, repr=False)
 
     def __post_init__(self) -> None:
-        put = lambda name, value: object.__setattr__(self, name, value)
         if self.model_type != "lfm2":
-            raise ConfigError(f"Lfm2Config cannot hold model_type={self.model_type!r}")
-        for name in ("vocab_size", "hidden_size", "num_hidden_layers", "num_attention_heads",
-                     "num_key_value_heads", "max_position_embeddings", "conv_L_cache",
-                     "intermediate_size", "block_multiple_of"):
-            positive_int(name, getattr(self, name))
-        for name in ("norm_eps", "block_ffn_dim_multiplier", "rope_theta"):
-            positive(name, getattr(self, name))
-        for name in ("conv_bias", "block_auto_adjust_ff_dim", "block_use_swiglu",
-                     "tie_embedding", "use_cache", "use_pos_enc"):
-            boolean(name, getattr(self, name))
+            raise ConfigError(f"model_type {self.model_type!r} is not an LFM2 configuration")
+        self._check_scalars()
+        self._set(block_dim=self._block_dim(), block_ff_dim=self._block_ff_dim(),
+                  rope_theta=self._theta(), norm_eps=float(self.norm_eps))
+        kinds = self._layer_kinds()
+        attention = tuple(i for i, kind in enumerate(kinds) if kind in ATTENTION_TYPES)
+        if not attention:
+            raise ConfigError("no layer of this LFM2 model attends; at least one has to")
+        if "sliding_attention" in kinds:
+            if self.sliding_window is None:
+                raise ConfigError("a sliding_attention layer needs the key sliding_window")
+            positive_int("sliding_window", self.sliding_window)
+        if self.full_attn_idxs is not None and tuple(self.full_attn_idxs) != attention:
+            raise ConfigError(f"full_attn_idxs {tuple(self.full_attn_idxs)} names other layers "
+                              f"than layer_types does ({attention})")
+        self._set(layer_types=kinds, full_attn_idxs=attention)
+
+    def _set(self, **values: Any) -> None:
+        for name, value in values.items():
+            object.__setattr__(self, name, value)
+
+    def _check_scalars(self) -> None:
+        checks = {positive_int: ("vocab_size", "hidden_size", "num_hidden_layers",
+                                 "num_attention_heads", "num_key_value_heads",
+                                 "max_position_embeddings", "conv_L_cache", "intermediate_size",
+                                 "block_multiple_of"),
+                  positive: ("norm_eps", "block_ffn_dim_multiplier", "rope_theta"),
+                  boolean: ("conv_bias", "block_auto_adjust_ff_dim", "block_use_swiglu",
+                            "tie_embedding", "use_cache", "use_pos_enc")}
+        for check, names in checks.items():
+            for name in names:
+                check(name, getattr(self, name))
         divisible("hidden_size", self.hidden_size, "num_attention_heads",
                   self.num_attention_heads)
         divisible("num_attention_heads", self.num_attention_heads, "num_key_value_heads",
                   self.num_key_value_heads)
         if self.head_dim % 2:
-            raise ConfigError("attention head dimension must be even for RoPE")
+            raise ConfigError(f"head size {self.head_dim} is odd; the rotary encoding pairs "
+                              f"dimensions")
         if not self.block_use_swiglu:
-            raise ConfigError("only SwiGLU LFM2 blocks are supported")
+            raise ConfigError("block_use_swiglu=false: LFM2's feed-forward here is SwiGLU only")
         if not self.use_pos_enc:
-            raise ConfigError("LFM2 requires rotary positional encoding")
-        block_dim = self.hidden_size if self.block_dim is None else self.block_dim
-        if block_dim != self.hidden_size:
-            raise ConfigError("block_dim must equal hidden_size")
-        block_ff_dim = self.intermediate_size if self.block_ff_dim is None else self.block_ff_dim
-        positive_int("block_ff_dim", block_ff_dim)
+            raise ConfigError("use_pos_enc=false: LFM2's attention here always rotates by "
+                              "position")
+
+    def _block_dim(self) -> int:
+        if self.block_dim is not None and self.block_dim != self.hidden_size:
+            raise ConfigError(f"block_dim ({self.block_dim}) differs from hidden_size "
+                              f"({self.hidden_size})")
+        return self.hidden_size
+
+    def _block_ff_dim(self) -> int:
+        width = self.intermediate_size if self.block_ff_dim is None else self.block_ff_dim
+        positive_int("block_ff_dim", width)
+        return width
+
+    def _theta(self) -> float:
+        theta = self.rope_theta
         if self.rope_parameters is not None:
-            rope_type = self.rope_parameters.get("rope_type", "default")
-            if rope_type != "default":
-                raise ConfigError(f"unsupported LFM2 RoPE type: {rope_type}")
-            theta = self.rope_parameters.get("rope_theta", self.rope_theta)
-            positive("rope_theta", theta)
-            put("rope_theta", float(theta))
-        if self.layer_types is None:
-            attention = set(self.full_attn_idxs if self.full_attn_idxs is not None
-                            else range(3, self.num_hidden_layers, 4))
-            layer_types = tuple("full_attention" if i in attention else "conv"
-                                for i in range(self.num_hidden_layers))
+            kind = self.rope_parameters.get("rope_type", "default")
+            if kind != "default":
+                raise ConfigError(f"rope_parameters.rope_type {kind!r}: only \"default\" is "
+                                  f"implemented for LFM2")
+            theta = self.rope_parameters.get("rope_theta", theta)
+            positive("rope_parameters.rope_theta", theta)
+        return float(theta)
+
+    def _layer_kinds(self) -> tuple[str, ...]:
+        """One kind per layer: given, or attention at ``full_attn_idxs`` (else at every fourth
+        layer from the fourth) and convolution elsewhere."""
+        if self.layer_types is not None:
+            kinds = tuple(self.layer_types)
         else:
-            layer_types = tuple(self.layer_types)
-        if len(layer_types) != self.num_hidden_layers:
-            raise ConfigError("layer_types must contain one entry per hidden layer")
-        for kind in layer_types:
-            if kind not in LAYER_TYPES:
-                raise ConfigError(f"unsupported LFM2 layer type: {kind}")
-        attention_layers = tuple(i for i, kind in enumerate(layer_types)
-                                 if kind in ATTENTION_TYPES)
-        if not attention_layers:
-            raise ConfigError("LFM2 requires at least one attention layer")
-        if "sliding_attention" in layer_types:
-            if self.sliding_window is None:
-                raise ConfigError("sliding_attention requires sliding_window")
-            positive_int("sliding_window", self.sliding_window)
-        if self.full_attn_idxs is not None and tuple(self.full_attn_idxs) != attention_layers:
-            raise ConfigError("full_attn_idxs must match layer_types")
-        put("block_dim", block_dim)
-        put("block_ff_dim", block_ff_dim)
-        put("layer_types", layer_types)
-        put("full_attn_idxs", attention_layers)
-        put("rope_theta", float(self.rope_theta))
-        put("norm_eps", float(self.norm_eps))
+            where = (range(3, self.num_hidden_layers, 4) if self.full_attn_idxs is None
+                     else self.full_attn_idxs)
+            where = set(where)
+            kinds = tuple("full_attention" if i in where else "conv"
+                          for i in range(self.num_hidden_layers))
+        if len(kinds) != self.num_hidden_layers:
+            raise ConfigError(f"layer_types has {len(kinds)} entries for "
+                              f"{self.num_hidden_layers} layers")
+        strangers = sorted(set(kinds) - set(LAYER_TYPES))
+        if strangers:
+            raise ConfigError(f"layer_types names {strangers}; LFM2 layers are {LAYER_TYPES}")
+        return kinds
 
     @property
     def head_dim(self) -> int:
@@ -135,17 +159,17 @@ class Lfm2Config:
             return ()
         return tuple(int(v) for v in eos) if isinstance(eos, (list, tuple)) else (int(eos),)
 
+    # other spellings of a key that checkpoints use; the field's own name wins if both appear
+    ALIASES = {"tie_word_embeddings": "tie_embedding", "num_heads": "num_attention_heads"}
+
     @classmethod
     def from_dict(cls, data: Mapping[str, Any]) -> "Lfm2Config":
-        data = dict(data)
-        if "tie_embedding" not in data and "tie_word_embeddings" in data:
-            data["tie_embedding"] = data["tie_word_embeddings"]
-        if "num_attention_heads" not in data and "num_heads" in data:
-            data["num_attention_heads"] = data["num_heads"]
-        known = {item.name for item in fields(cls)} - {"extra"}
-        payload = {key: value for key, value in data.items() if key in known}
-        payload["extra"] = unknown_keys(data, known | {"tie_word_embeddings", "num_heads"})
-        return cls(**payload)
+        names = {item.name for item in fields(cls)} - {"extra"}
+        values = {key: data[key] for key in names if key in data}
+        for other, name in cls.ALIASES.items():
+            if other in data:
+                values.setdefault(name, data[other])
+        return cls(**values, extra=unknown_keys(data, names | set(cls.ALIASES)))
 
     def to_dict(self) -> dict[str, Any]:
         """The config.json keys that describe this configuration."""

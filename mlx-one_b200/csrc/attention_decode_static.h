@@ -15,7 +15,10 @@
 //   results need more than MLXONE_STATIC_SCRATCH_FLOATS floats is refused with an error text
 //   (mlxone_last_error) and nothing is launched; fewer splits or requests per call fit.
 // * The first call on a device looks up the array's device address (cudaGetSymbolAddress, with
-//   that device current) and keeps it. Make this first call before any stream capture begins.
+//   that device current) and keeps it. Make this first call before any stream capture begins;
+//   a first call that finds its stream capturing is refused with an error text. Devices 0 to 63
+//   are served. Calls from several host threads are safe: the address is kept with an atomic
+//   store, and threads that look it up at the same time store the same value.
 // * All calls on a device share the one array. It keeps what the last call left there; this
 //   kernel writes every partial result before it reads it, so nothing has to be cleared. Two
 //   calls that overlap on the GPU (different streams, no ordering between them) would write

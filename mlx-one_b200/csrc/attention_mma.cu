@@ -865,6 +865,8 @@ MLXONE_API int mlxone_attention_decode(const void* q, const void* kv, const int*
 static __device__ __align__(256) float g_static_scratch[MLXONE_STATIC_SCRATCH_FLOATS];
 
 namespace {
+// Device addresses of the array, looked up once per device. Threads may race to fill an entry;
+// they all store the same value, and the store and load are atomic, so any of them may win.
 constexpr int MAX_DEVICES = 64;
 float* g_static_scratch_address[MAX_DEVICES] = {};
 }  // namespace
@@ -890,18 +892,27 @@ MLXONE_API int mlxone_attention_decode_static(const void* q, const void* kv, con
                    requests, heads, splits, needed, MLXONE_STATIC_SCRATCH_FLOATS);
     int device = -1;
     cudaError_t err = cudaGetDevice(&device);
-    MLXONE_REQUIRE(err == cudaSuccess && device >= 0 && device < MAX_DEVICES,
+    MLXONE_REQUIRE(err == cudaSuccess && device >= 0,
                    "attention_decode_static: no current device (%s)", cudaGetErrorString(err));
-    if (g_static_scratch_address[device] == nullptr) {
-        // once per device, with that device current; not inside a stream capture
-        float* address = nullptr;
+    MLXONE_REQUIRE(device < MAX_DEVICES,
+                   "attention_decode_static: device %d; this entry point serves devices 0 to %d",
+                   device, MAX_DEVICES - 1);
+    float* address = __atomic_load_n(&g_static_scratch_address[device], __ATOMIC_ACQUIRE);
+    if (address == nullptr) {
+        // once per device, with that device current; not inside a stream capture, where the
+        // look-up (which may load the library's device image) is not allowed
+        cudaStreamCaptureStatus capturing = cudaStreamCaptureStatusNone;
+        err = cudaStreamIsCapturing(stream, &capturing);
+        MLXONE_REQUIRE(err == cudaSuccess && capturing == cudaStreamCaptureStatusNone,
+                       "attention_decode_static: the first call on device %d came inside a stream "
+                       "capture; make one call on this device before capturing", device);
         err = cudaGetSymbolAddress(reinterpret_cast<void**>(&address), g_static_scratch);
         MLXONE_REQUIRE(err == cudaSuccess && address != nullptr,
                        "attention_decode_static: cannot find the scratch array on device %d: %s",
                        device, cudaGetErrorString(err));
-        g_static_scratch_address[device] = address;
+        __atomic_store_n(&g_static_scratch_address[device], address, __ATOMIC_RELEASE);
     }
     return mlxone_attention_decode(q, kv, block_table, table_width, page_size, pages, positions,
-                                   out, g_static_scratch_address[device], requests, heads, kv_heads,
-                                   head_dim, splits, scale, window, stream);
+                                   out, address, requests, heads, kv_heads, head_dim, splits, scale,
+                                   window, stream);
 }

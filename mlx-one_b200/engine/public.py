@@ -3,7 +3,8 @@ reference's ``Engine`` (src/mlx_one/engine/public.py:61-485) and text API
 (src/mlx_one/text/generation.py:209-263).
 
 Differences that the GPU design brings: requests are batched continuously by one scheduler
-and run through one step function, the caller's thread drives the loop (no actor thread),
+and run through one step function; the loop is driven by the caller's thread, or by a thread
+of the engine's own with ``BatchingConfig(loop_thread=True)`` (the reference's actor thread);
 and there are entry points that take and return token ids, because a model with random
 weights has no tokenizer.
 """
@@ -62,7 +63,13 @@ class _InFlight:
 
 
 class EngineRequestHandle:
-    """A submitted request. ``result()`` drives the engine until the request is done."""
+    """A submitted request.
+
+    Without a loop thread (``BatchingConfig.loop_thread`` False, the default) nothing runs
+    until somebody drives the loop: ``result()`` does (until this request is done), and so do
+    ``Engine.step()``, ``Engine.run()``, ``generate*`` and the iterators of ``stream*``.
+    ``done()`` alone only looks; polling it without one of those calls waits for ever. With a
+    loop thread the engine drives itself and ``result()`` only waits."""
 
     def __init__(self, engine: "Engine", request: Request, prompt_text: str) -> None:
         self._engine = engine
@@ -71,6 +78,7 @@ class EngineRequestHandle:
         self.submitted_at = time.perf_counter()
         self.first_token_at: float | None = None
         self.finished_at: float | None = None
+        self.stopped_text: str | None = None      # the text up to a stop string that matched
 
     def done(self) -> bool:
         return self.request.phase is Phase.FINISHED
@@ -83,6 +91,22 @@ class EngineRequestHandle:
         while not self.done():
             self._engine._drive_once()
         return self._engine._result(self)
+
+    def tokens(self) -> Iterator[int]:
+        """The request's tokens as they are committed (this handle's output queue): blocks,
+        driving or waiting as ``result()`` does, until the request is done. A token that a
+        later stop-string match takes back may have been handed out already."""
+        sent = 0
+        while True:
+            if not self.done():
+                self._engine._drive_once()
+            finished = self.done()
+            output = self.request.output
+            while sent < len(output):
+                sent += 1
+                yield output[sent - 1]
+            if finished:
+                return
 
 
 class Engine:
@@ -138,6 +162,13 @@ class Engine:
         self._inflight: _InFlight | None = None
         self._turn = threading.RLock()       # one thread at a time plans, launches and commits
         self._stepped = threading.Condition()   # notified after every turn
+        self._wake = threading.Condition()      # the loop thread sleeps here while idle
+        self._closing = False
+        self._thread: threading.Thread | None = None
+        if self.batching_config.loop_thread:
+            self._thread = threading.Thread(target=self._loop, name="mlx-one_b200-loop",
+                                            daemon=True)
+            self._thread.start()
 
     # ------------------------------------------------------------------ set-up
 
@@ -205,18 +236,24 @@ class Engine:
         if len(prompt) >= limit:
             raise ValueError(f"prompt of {len(prompt)} tokens reaches the model's {limit} positions")
         if len(prompt) + options.max_tokens > limit:
-            options = TextGenerationOptions(**{**options.__dict__,
-                                               "max_tokens": limit - len(prompt)})
+            options = options.replace(max_tokens=limit - len(prompt))
         with self._turn:
             request = Request(self._scheduler.new_id(), prompt, options,
                               eos_token_ids=self._loaded.spec.eos_token_ids)
+            if options.stop and self._tokenizer is None:
+                raise ValueError("stop strings are matched in text; this model folder has no "
+                                 "tokenizer.json")
             self._scheduler.submit(request)
             handle = EngineRequestHandle(self, request, prompt_text)
             self._handles[request.request_id] = handle
+        with self._wake:
+            self._wake.notify_all()
         return handle
 
     def submit(self, prompt: str, options: TextGenerationOptions | None = None,
                **option_kwargs) -> EngineRequestHandle:
+        """Queues a request and returns at once. See ``EngineRequestHandle`` for who drives
+        the loop: without ``loop_thread`` the request makes no progress until a caller does."""
         return self.submit_ids(self.encode(prompt), self._options(options, option_kwargs),
                                prompt_text=prompt)
 
@@ -241,10 +278,41 @@ class Engine:
             self._stepped.notify_all()
         return touched
 
+    def _loop(self) -> None:
+        """The loop thread: turns while there is work, sleeps until a submit otherwise. A step
+        that raises ends the requests it held (their ``result()`` raises the error); the
+        thread goes on."""
+        if self.model.runtime.device.type == "cuda":
+            torch.cuda.set_device(self.model.runtime.device)
+        while not self._closing:
+            if self._scheduler.has_work() or self._inflight is not None:
+                try:
+                    self.step()
+                except BaseException as error:          # noqa: BLE001
+                    with self._turn:
+                        self._abandon(error)
+                    with self._stepped:
+                        self._stepped.notify_all()
+            else:
+                with self._wake:
+                    if not (self._closing or self._scheduler.has_work()):
+                        self._wake.wait(0.05)
+
+    def _abandon(self, error: BaseException) -> None:
+        """After a step that raised: nothing in flight is trusted, every running request ends
+        with ``error``."""
+        self._inflight = None
+        self._scheduler.fail(list(self._scheduler.running), error)
+
     def _drive_once(self) -> None:
         """One turn of the loop if no other thread is in one; else a wait until that thread's
         turn has ended. A thread that waits for its request thus sees it finish without having
-        to win the lock from the thread that keeps the loop going."""
+        to win the lock from the thread that keeps the loop going. With a loop thread the
+        caller never drives."""
+        if self._thread is not None:
+            with self._stepped:
+                self._stepped.wait(0.005)
+            return
         if self._turn.acquire(blocking=False):
             try:
                 self._step()
@@ -259,10 +327,8 @@ class Engine:
     def _step(self) -> list[Request]:
         previous = self._inflight
         if previous is not None:
-            ahead = self._launch_ahead(previous)
-            touched = self._finish(previous)
-            self._inflight = ahead
-            return touched
+            self._inflight = self._launch_ahead(previous)
+            return self._finish(previous)     # a kernel fault found there drops the new one too
         planned = self._scheduler.plan()
         if not planned:
             return []
@@ -327,6 +393,9 @@ class Engine:
             if inflight.event is not None:
                 inflight.event.synchronize()
             sampled = inflight.host[:inflight.draws].tolist()
+            code = int(inflight.host[inflight.draws])      # the kernels' error flag, same copy
+            if code:
+                return self._kernel_fault(code, inflight)
         planned = inflight.planned
         if any(item.request.phase is Phase.FINISHED for item in planned):
             # launched ahead for a request that has ended meanwhile: its token is dropped
@@ -339,7 +408,7 @@ class Engine:
                 if item.samples:
                     tokens.append(token)
             planned, sampled = kept, tokens
-        touched = self._scheduler.commit(planned, sampled)
+        touched = self._scheduler.commit(planned, sampled, stop_at=self._stop_at)
         now = time.perf_counter()
         self._trace(inflight, now)
         for request in touched:
@@ -352,6 +421,49 @@ class Engine:
                 handle.finished_at = now
         self._stats["tokens_sampled"] += len(sampled)
         return touched
+
+    def _kernel_fault(self, code: int, inflight: "_InFlight") -> list[Request]:
+        """A kernel of this step (or of one before it whose tokens were not read) set the
+        device's error flag: a wait that gave up, a key without a page, a token outside the
+        vocabulary. Its tokens are not committed; the step's requests and those of a step
+        launched ahead end with a ``KernelError`` and give their pages back."""
+        ops = self.model.ops
+        requests = [item.request for item in inflight.planned]
+        ahead = self._inflight
+        if ahead is not None and ahead is not inflight:
+            if ahead.event is not None:
+                ahead.event.synchronize()
+            requests += [item.request for item in ahead.planned]
+        self._inflight = None
+        ops.error_flag.zero_()
+        error = getattr(ops, "describe_error", lambda c: RuntimeError(f"kernel error {c}"))(code)
+        failed = list({id(r): r for r in requests if r.phase is not Phase.FINISHED}.values())
+        self._scheduler.fail(failed, error)
+        self._stats["kernel_faults"] = self._stats.get("kernel_faults", 0) + 1
+        now = time.perf_counter()
+        for request in failed:
+            handle = self._handles.get(request.request_id)
+            if handle is not None:
+                handle.finished_at = now
+        return failed
+
+    def _stop_at(self, request: Request, token: int) -> int | None:
+        """Whether the text of ``request`` with ``token`` appended contains one of its stop
+        strings; if so, how many of its tokens lie wholly before the match. The reference ends
+        a request on a stop string wherever its text is produced
+        (src/mlx_one/text/generation.py:266-290, 682-697)."""
+        tokens = request.output + [token]
+        text = self.decode(tokens)
+        cut, matched = self._apply_stop(text, request.options.stop)
+        if not matched:
+            return None
+        keep = 0
+        while keep < len(request.output) and len(self.decode(tokens[:keep + 1])) <= len(cut):
+            keep += 1
+        handle = self._handles.get(request.request_id)
+        if handle is not None:
+            handle.stopped_text = cut
+        return keep
 
     def _trace(self, inflight: "_InFlight", committed_at: float) -> None:
         """One record per step, as the reference's runners keep them
@@ -381,15 +493,24 @@ class Engine:
         return list(self._traces)
 
     def _start_copy(self, tokens: torch.Tensor):
-        """Starts the copy of the chosen tokens to the host; returns (host buffer, event)."""
+        """Starts the copy of the chosen tokens to the host, and behind them of the kernels'
+        error flag, so that a fault is seen with the tokens it spoilt and costs no wait of its
+        own; returns (host buffer, event)."""
+        count = tokens.numel()
+        flag = getattr(self.model.ops, "error_flag", None)
         if tokens.device.type != "cuda":
-            return tokens.clone(), None
+            tail = flag.to(torch.int32).cpu() if flag is not None else torch.zeros(1, dtype=torch.int32)
+            return torch.cat([tokens.to(torch.int32), tail]), None
         self._copy_turn ^= 1
         buffer = self._pinned[self._copy_turn]
-        if buffer is None or buffer.numel() < tokens.numel():
-            buffer = torch.empty(max(tokens.numel(), 256), dtype=torch.int32, pin_memory=True)
+        if buffer is None or buffer.numel() < count + 1:
+            buffer = torch.zeros(max(count + 1, 256), dtype=torch.int32, pin_memory=True)
             self._pinned[self._copy_turn] = buffer
-        buffer[:tokens.numel()].copy_(tokens, non_blocking=True)
+        buffer[:count].copy_(tokens, non_blocking=True)
+        if flag is not None:
+            buffer[count:count + 1].copy_(flag, non_blocking=True)
+        else:
+            buffer[count] = 0
         event = torch.cuda.Event()
         event.record()
         return buffer, event
@@ -406,6 +527,8 @@ class Engine:
         self._handles.pop(request.request_id, None)
         if request.finish_reason == "timeout":
             raise RequestTimeoutError("generation request timed out")
+        if request.finish_reason == "error":
+            raise request.error or RuntimeError("the request's step failed")
         finished = handle.finished_at or time.perf_counter()
         first = handle.first_token_at or finished
         count = len(request.output)
@@ -415,7 +538,8 @@ class Engine:
             # decoding speed leaves out the prompt and the first token, as the reference does
             timings["decode_tokens_per_s"] = (count - 1) / (finished - first)
         reason = request.finish_reason or "length"
-        text = self._apply_stop(self.decode(request.output), request.options.stop)[0]
+        text = (handle.stopped_text if handle.stopped_text is not None
+                else self.decode(request.output))
         return GenerationResult(
             prompt=handle.prompt_text, text=text, prompt_tokens=len(request.prompt),
             generation_tokens=count, finish_reason="stop" if reason == "cancelled" else reason,
@@ -480,34 +604,40 @@ class Engine:
         yield from self._stream(handle)
 
     def _stream(self, handle: EngineRequestHandle) -> Iterator[GenerationChunk]:
+        """Chunks of a request as its tokens are committed. With stop strings, text that may
+        still turn into one is held back; when one matches (seen where the token is committed,
+        so the request has ended and freed its pages already) the last chunk brings the text up
+        to the match."""
         request, sent, text_sent = handle.request, 0, ""
         stop = request.options.stop
         while True:
             if not handle.done():
                 self._drive_once()
-            while sent < len(request.output):
+            finished = handle.done()
+            output = list(request.output)
+            while sent < len(output):
                 sent += 1
                 piece = ""
                 if self._tokenizer is not None:
-                    text, matched = self._apply_stop(self.decode(request.output[:sent]), stop)
-                    # hold back text that may still turn into a stop string
-                    safe = text if matched or handle.done() else self._hold_back(text, stop)
-                    piece, text_sent = safe[len(text_sent):], max(safe, text_sent, key=len)
-                    if matched:
-                        with self._turn:
-                            self._scheduler.finish(request, "stop")
-                        yield GenerationChunk(request.output[sent - 1], piece, sent, "stop")
-                        self._handles.pop(request.request_id, None)
-                        return
-                yield GenerationChunk(request.output[sent - 1], piece, sent)
-            if handle.done():
+                    text = self.decode(output[:sent])
+                    if stop and not (finished and sent == len(output)):
+                        text = self._hold_back(text, stop)
+                    if len(text) > len(text_sent):
+                        piece, text_sent = text[len(text_sent):], text
+                yield GenerationChunk(output[sent - 1], piece, sent)
+            if finished:
+                self._handles.pop(request.request_id, None)
                 reason = request.finish_reason or "length"
                 if reason == "timeout":
-                    self._handles.pop(request.request_id, None)
                     raise RequestTimeoutError("generation request timed out")
-                yield GenerationChunk(None, "", sent, "stop" if reason == "cancelled" else reason,
+                if reason == "error":
+                    raise request.error or RuntimeError("the request's step failed")
+                trailing = ""
+                if handle.stopped_text is not None and len(handle.stopped_text) > len(text_sent):
+                    trailing = handle.stopped_text[len(text_sent):]
+                yield GenerationChunk(None, trailing, len(request.output),
+                                      "stop" if reason == "cancelled" else reason,
                                       request.terminal_token_id)
-                self._handles.pop(request.request_id, None)
                 return
 
     @staticmethod
@@ -539,13 +669,26 @@ class Engine:
                 "sampling": ["greedy", "temperature", "top_k", "top_p", "seed"]}
 
     def close(self) -> None:
-        if self._inflight is not None:
-            self._finish(self._inflight)
-            self._inflight = None
-        for request in list(self._scheduler.running) + list(self._scheduler.waiting):
-            self._scheduler.cancel(request)
-        self._scheduler.plan()
-        self._cache.close_all()
+        """Ends every request, gives all pages back and stops the loop thread. Raises the
+        ``KernelError`` of a fault that the device's error flag still holds, after cleaning
+        up."""
+        self._closing = True
+        with self._wake:
+            self._wake.notify_all()
+        if self._thread is not None and self._thread is not threading.current_thread():
+            self._thread.join(timeout=30)
+        self._thread = None
+        with self._turn:
+            if self._inflight is not None:
+                inflight, self._inflight = self._inflight, None
+                self._finish(inflight)
+            for request in list(self._scheduler.running) + list(self._scheduler.waiting):
+                self._scheduler.cancel(request)
+            self._scheduler.plan()
+            self._cache.close_all()
+        with self._stepped:
+            self._stepped.notify_all()
+        self.model.ops.check_errors()
 
     def __enter__(self) -> "Engine":
         return self

@@ -17,7 +17,7 @@ import numpy as np
 import torch
 
 from ..cache.manager import CacheManager
-from ..parts.base import StepContext
+from ..parts.base import NoHostValues, StepContext
 from ..parts.model import Model
 
 
@@ -78,7 +78,8 @@ class Runner:
         # tokens chosen on the device, by request number (see StepEntry.from_device)
         self.published = torch.zeros(cache.max_requests, dtype=torch.int32, device=self.device)
         # CUDA graphs of steps, keyed by shape (requests, tokens, table widths, wanted rows, ...)
-        self.use_graphs = self.device.type == "cuda"
+        # (only models whose parts all say that they can be captured: see Part.capturable)
+        self.use_graphs = self.device.type == "cuda" and model.capturable
         self._graphs: dict[tuple, _DecodeGraph] = {}
         self.graph_replays = 0
         # steps with portions: captured at their third occurrence if they have at most this many
@@ -86,6 +87,11 @@ class Runner:
         self.graph_token_limit = 1024
         self.portion_graphs = 8
         self._portion_keys: list[tuple] = []
+        # decode-only shapes kept (least recently used ones are dropped beyond this), and one
+        # memory pool for all captures, so that graphs share their activations' memory
+        self.decode_graphs = 48
+        self._decode_keys: list[tuple] = []
+        self._graph_pool = torch.cuda.graph_pool_handle() if self.use_graphs else None
         if self.use_graphs:
             # library handles must exist before a capture begins
             warm = torch.zeros((8, 8), dtype=torch.bfloat16, device=self.device)
@@ -278,8 +284,10 @@ class Runner:
                 captured = _DecodeGraph(torch.empty(cursor, dtype=torch.int32,
                                                     device=self.device))
                 self._graphs[key] = captured
-                if portions:
-                    self._forget_old_portion_graphs(key)
+            if portions:
+                self._forget_old_portion_graphs(key)
+            elif loop is None:
+                self._forget_old_decode_graphs(key)
             device = captured.meta
         device[:cursor].copy_(host[:cursor], non_blocking=True)
         if self.device.type == "cuda":
@@ -294,14 +302,23 @@ class Runner:
         tables = [on_device(f"table{g}").view(requests, widths[g]) for g in range(len(paged))]
         slots = [on_device(f"slots{g}") for g in range(len(states))]
         views = {entry: self.cache.view(entry, tables, slots) for entry in self.model.cache_needs}
+        if captured is None or not self.use_graphs:
+            max_portion = max(len(e.tokens) for e in entries)
+            max_context = max(h + len(e.tokens) for h, e in zip(history, entries))
+            host = {"history": history, "request_start": starts}
+        else:
+            # bounds that hold for every step of this shape, however its tokens are split
+            max_portion = tokens - requests + 1
+            max_context = min([self.model.spec.max_positions] +
+                              [w * self.cache.page_size for w, g in zip(widths, paged)
+                               if g.need.window is None])
+            host = NoHostValues()
         ctx = StepContext(
             tokens=tokens, requests=requests, token_ids=on_device("token_ids"),
             positions=on_device("positions"), token_request=on_device("token_request"),
             request_start=on_device("request_start"), history=on_device("history"),
-            max_portion=max(len(e.tokens) for e in entries),
-            max_context=max(h + len(e.tokens) for h, e in zip(history, entries)),
-            views=views,
-            host={"history": history, "request_start": starts})
+            max_portion=max_portion, max_context=max_context, views=views, host=host,
+            replayable=captured is not None and self.use_graphs)
 
         device_fed = any(e.from_device for e in entries)
 
@@ -357,18 +374,7 @@ class Runner:
             done = 1
             captured.uses += 1
         if done < steps and self.use_graphs and captured.graph is None:
-            graph = torch.cuda.CUDAGraph()
-            try:
-                torch.cuda.current_stream(self.device).synchronize()
-                with torch.cuda.graph(graph):
-                    one_step()
-                captured.graph = graph
-            except Exception as error:
-                import warnings
-
-                warnings.warn(f"CUDA graph capture failed ({error}); decode steps run eagerly")
-                self.use_graphs = False
-                torch.cuda.synchronize(self.device)
+            captured.graph = self._capture(one_step)[0]
         for _ in range(done, steps):
             if captured.graph is not None:
                 captured.graph.replay()
@@ -382,12 +388,41 @@ class Runner:
         self.last_shape = (len(entries), len(entries))
         return out
 
+    def _capture(self, run):
+        """Records ``run`` into a CUDA graph; returns (graph, what run returned). A model whose
+        parts all declare themselves capturable must be: a failure here is an error of a part
+        (it synchronised, or read host values), and is raised, not hidden."""
+        graph = torch.cuda.CUDAGraph()
+        torch.cuda.current_stream(self.device).synchronize()
+        try:
+            with torch.cuda.graph(graph, pool=self._graph_pool):
+                result = run()
+        except Exception as error:
+            torch.cuda.synchronize(self.device)
+            raise RuntimeError(
+                f"a step could not be captured as a CUDA graph ({error}); a part that "
+                "synchronises or reads host values must set `capturable = False`") from error
+        return graph, result
+
     def _forget_old_portion_graphs(self, newest: tuple) -> None:
         """A captured step keeps its activations' memory: of the shapes with portions only the
         ``portion_graphs`` most recently met are kept."""
         self._portion_keys = [k for k in self._portion_keys if k != newest] + [newest]
         while len(self._portion_keys) > self.portion_graphs:
             self._graphs.pop(self._portion_keys.pop(0), None)
+
+    def _forget_old_decode_graphs(self, newest: tuple) -> None:
+        """The same for decode-only shapes (batch sizes, table widths, greedy or sampled,
+        device-fed or not): the ``decode_graphs`` most recently used are kept."""
+        self._decode_keys = [k for k in self._decode_keys if k != newest] + [newest]
+        while len(self._decode_keys) > self.decode_graphs:
+            self._graphs.pop(self._decode_keys.pop(0), None)
+
+    def graph_stats(self) -> dict[str, int]:
+        """How many steps are kept as graphs, and how often one was replayed."""
+        kept = sum(1 for g in self._graphs.values() if g.graph is not None)
+        return {"graphs": kept, "graph_shapes": len(self._graphs),
+                "graph_replays": self.graph_replays}
 
     def _run_captured(self, captured: _DecodeGraph, run, eager_uses: int = 1):
         """Steps of one shape: the first ``eager_uses`` run eagerly, the next is captured as a
@@ -397,19 +432,7 @@ class Runner:
         if captured.uses <= eager_uses or not self.use_graphs:
             return run()
         if captured.graph is None:
-            graph = torch.cuda.CUDAGraph()
-            try:
-                torch.cuda.current_stream(self.device).synchronize()
-                with torch.cuda.graph(graph):
-                    captured.logits = run()
-            except Exception as error:        # capture is an optimisation, never a requirement
-                import warnings
-
-                warnings.warn(f"CUDA graph capture failed ({error}); decode steps run eagerly")
-                self.use_graphs = False
-                torch.cuda.synchronize(self.device)
-                return run()
-            captured.graph = graph
+            captured.graph, captured.logits = self._capture(run)
         captured.graph.replay()
         self.graph_replays += 1
         return captured.logits

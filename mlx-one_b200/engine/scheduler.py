@@ -49,6 +49,10 @@ class BatchingConfig:
     # tokens taken on the device, where they were chosen) before the last step's tokens are read
     # back
     pipeline_decode: bool = True
+    # True: the engine owns a thread that drives the loop while requests are waiting or running,
+    # as the reference's actor thread does (src/mlx_one/engine/actor.py:402-525); callers then
+    # only wait. False: whoever waits for a request drives the loop from its own thread
+    loop_thread: bool = False
 
     def __post_init__(self) -> None:
         for name in ("max_sequences", "queue_size", "prefill_chunk_size",
@@ -87,10 +91,11 @@ class Request:
     fed: int = 0                                     # prompt tokens already run
     output: list[int] = field(default_factory=list)
     next_token: int | None = None                    # sampled, to be fed by the next step
-    finish_reason: str | None = None                 # "stop" | "length" | "cancelled" | "timeout"
+    finish_reason: str | None = None     # "stop" | "length" | "cancelled" | "timeout" | "error"
     terminal_token_id: int | None = None
     cancelled: bool = False
     deadline: float | None = None                    # on the scheduler's clock; None: none
+    error: BaseException | None = None               # why finish_reason is "error"
 
     @property
     def reserve_tokens(self) -> int:
@@ -215,9 +220,13 @@ class Scheduler:
             prefill_budget -= size
         return step
 
-    def commit(self, step: Sequence[Scheduled], sampled: Sequence[int]) -> list[Request]:
+    def commit(self, step: Sequence[Scheduled], sampled: Sequence[int],
+               stop_at=None) -> list[Request]:
         """Records a finished step: ``sampled`` has one token per entry with ``samples``.
-        Returns the requests that produced a token or finished."""
+        Returns the requests that produced a token or finished. ``stop_at(request, token)`` is
+        asked for every drawn token of a request that has stop strings: None lets the token in;
+        a count means that the text with this token contains a stop string, and the request
+        ends with reason "stop" holding only that many of its tokens (those before the match)."""
         touched, drawn = [], iter(sampled)
         for item in step:
             request = item.request
@@ -232,16 +241,29 @@ class Scheduler:
                 request.terminal_token_id = token
                 self._finish(request, "stop")
                 continue
+            if stop_at is not None and request.options.stop:
+                keep = stop_at(request, token)
+                if keep is not None:
+                    del request.output[keep:]
+                    self._finish(request, "stop")
+                    continue
             request.output.append(token)
             request.next_token = token
             if len(request.output) >= request.options.max_tokens:
                 self._finish(request, "length")
         return touched
 
-    def finish(self, request: Request, reason: str) -> None:
-        """Ends a running request from outside (a stop string matched)."""
-        if request.phase is not Phase.FINISHED:
-            self._finish(request, reason)
+    def fail(self, requests: Sequence[Request], error: BaseException) -> None:
+        """Ends requests whose step could not be trusted (a kernel reported a fault, the step
+        raised): their pages come back and whoever waits for them is given ``error``."""
+        for request in requests:
+            if request.phase is not Phase.FINISHED:
+                request.error = error
+                if request in self.waiting:
+                    self.waiting.remove(request)
+                    self._finish(request, "error", held=False)
+                else:
+                    self._finish(request, "error")
 
     def _finish(self, request: Request, reason: str, held: bool = True) -> None:
         request.finish_reason = reason

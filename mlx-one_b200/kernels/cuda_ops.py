@@ -120,16 +120,20 @@ class CudaOps:
         its weights, while the one before it finishes."""
         self.lib.mlxone_set_pdl(1 if enabled else 0)
 
+    ERRORS = {1: "a token id outside the vocabulary",
+              2: "a key written to a position that has no page",
+              3: "a key read from a position that has no page",
+              9: "a wait inside a tcgen05 kernel that gave up"}
+
+    def describe_error(self, code: int) -> KernelError:
+        return KernelError(f"a kernel reported {self.ERRORS.get(code, f'code {code}')}")
+
     def check_errors(self) -> None:
         """Reads the device error flag (synchronises) and raises if a kernel set it."""
         code = int(self.error_flag.item())
         if code:
             self.error_flag.zero_()
-            what = {1: "a token id outside the vocabulary",
-                    2: "a key written to a position that has no page",
-                    3: "a key read from a position that has no page",
-                    9: "a wait inside the tcgen05 product that gave up"}.get(code, f"code {code}")
-            raise KernelError(f"a kernel reported {what}")
+            raise self.describe_error(code)
 
     # ------------------------------------------------------------------ size checks
 

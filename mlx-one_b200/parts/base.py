@@ -74,7 +74,17 @@ class StepContext:
     ``token_ids``/``positions``/``token_request`` have one entry per token; tokens of a
     request are consecutive and in order. ``request_start`` [requests + 1] are offsets
     into the tokens; ``history`` [requests] is each request's token count before this
-    step (the position of its first token here)."""
+    step (the position of its first token here).
+
+    Host values and CUDA graphs. A step whose shape (requests, tokens, table widths, wanted
+    rows) comes back may be captured as a CUDA graph and replayed with other contents: other
+    token ids, positions, tables, and another split of the tokens between the requests. What a
+    part reads on the host while it is captured is frozen into the graph. Therefore, in a step
+    that may be captured (``replayable`` True), ``max_portion`` and ``max_context`` are upper
+    bounds that hold for every step of that shape (``max_portion`` is 1 exactly when every
+    request brings one token), and ``host`` refuses to be read. A part that needs the step's
+    own host values (or synchronises, or runs host code per request) sets ``capturable =
+    False`` on its class; a model with such a part is never captured."""
 
     tokens: int
     requests: int
@@ -83,10 +93,28 @@ class StepContext:
     token_request: torch.Tensor
     request_start: torch.Tensor
     history: torch.Tensor
-    max_portion: int                  # most tokens any request brings (host)
-    max_context: int                  # largest history + portion (host)
+    max_portion: int                  # most tokens any request brings (host; see above)
+    max_context: int                  # largest history + portion (host; see above)
     views: Mapping[int, Any] = field(default_factory=dict)   # cache entry -> view
-    host: Mapping[str, Any] = field(default_factory=dict)    # host copies for tests/toys
+    # host copies of ``history`` and ``request_start`` (lists), for parts that are not capturable
+    host: Mapping[str, Any] = field(default_factory=dict)
+    replayable: bool = False
+
+
+class NoHostValues(Mapping):
+    """``StepContext.host`` of a step that may be replayed from a CUDA graph: reading it would
+    freeze one step's values into the graph, so it raises instead."""
+
+    def __getitem__(self, key):
+        raise RuntimeError(
+            f"StepContext.host[{key!r}] was read in a step that may be captured as a CUDA graph; "
+            "a part that needs host values sets `capturable = False` on its class")
+
+    def __iter__(self):
+        return iter(())
+
+    def __len__(self):
+        return 0
 
 
 class NormedInput:
@@ -109,6 +137,11 @@ class NormedInput:
 
 class Part:
     """Common construction: checks that the given tensors match ``tensors(spec)``."""
+
+    # False: this part's forward cannot be recorded into a CUDA graph and replayed with other
+    # contents (it reads ``StepContext.host``, copies to the host, or loops over requests in
+    # Python). A model that holds such a part runs every step eagerly.
+    capturable = True
 
     def __init__(self, spec: PartSpec, tensors: Mapping[str, torch.Tensor],
                  runtime: Runtime) -> None:

@@ -91,6 +91,15 @@ class Model:
             LayerCall(call.layer, index if call.cache is None else call.cache, call.writes_cache)
             for index, call in enumerate(spec.order))
         self.cache_needs = cache_entries(spec)
+        # whether steps of this model may be captured as CUDA graphs: every part says so
+        parts = [self.final_norm]
+        for block in self.layers:
+            parts += [block, block.mixer, block.mixer_norm, block.feed_forward,
+                      block.feed_forward_norm]
+            position = getattr(block.mixer, "position", None)
+            if position is not None:
+                parts.append(position)
+        self.capturable = all(getattr(part, "capturable", True) for part in parts)
         # For debugging: called as observer(place, residual, delta) after the embedding
         # (place -1) and after every call of a layer (place = its number in the order); the
         # hidden state there is residual + delta. It sees the step's own tensors: copy what is

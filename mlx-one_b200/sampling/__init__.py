@@ -1,4 +1,3 @@
 from .options import GenerationChunk, GenerationResult, TextGenerationOptions
-from .sampler import Sampler
 
-__all__ = ["GenerationChunk", "GenerationResult", "TextGenerationOptions", "Sampler"]
+__all__ = ["GenerationChunk", "GenerationResult", "TextGenerationOptions"]

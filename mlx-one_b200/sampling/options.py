@@ -1,11 +1,38 @@
-"""Generation options and results, with the reference's names, defaults and checks
-(src/mlx_one/text/schemas.py:10-70)."""
+"""What a caller may ask of a generation, and what comes back.
+
+The field names, their defaults and their meanings are the reference's
+(src/mlx_one/text/schemas.py:10-70), so that code written for its ``TextGenerationOptions``,
+``GenerationChunk`` and ``GenerationResult`` reads the same here. The checks are a table of
+(field, rule) pairs, one line per field, evaluated when the options are made.
+"""
 
 from __future__ import annotations
 
+import dataclasses
 import json
-from dataclasses import asdict, dataclass, field
-from typing import Any
+from dataclasses import dataclass, field
+from typing import Any, Callable
+
+
+def _is_int(value: Any) -> bool:
+    return isinstance(value, int) and not isinstance(value, bool)
+
+
+def _is_real(value: Any) -> bool:
+    return isinstance(value, (int, float)) and not isinstance(value, bool)
+
+
+# field -> (what a good value looks like, in words; the test that says so)
+_RULES: dict[str, tuple[str, Callable[[Any], bool]]] = {
+    "max_tokens": ("an integer of at least 1", lambda v: _is_int(v) and v >= 1),
+    "temperature": ("a number of at least 0 (0 means greedy)", lambda v: _is_real(v) and v >= 0),
+    "top_k": ("None or an integer of at least 1", lambda v: v is None or (_is_int(v) and v >= 1)),
+    "top_p": ("a number above 0 and at most 1", lambda v: _is_real(v) and 0 < v <= 1),
+    "seed": ("an integer", _is_int),
+    "stop": ("a sequence of strings, none of them empty",
+             lambda v: not isinstance(v, str) and all(isinstance(s, str) and s for s in v)),
+    "ignore_eos": ("a boolean", lambda v: isinstance(v, bool)),
+}
 
 
 @dataclass(frozen=True)
@@ -19,32 +46,20 @@ class TextGenerationOptions:
     ignore_eos: bool = False        # keep decoding past end-of-sequence tokens (benchmarks)
 
     def __post_init__(self) -> None:
-        def number(value: Any) -> bool:
-            return isinstance(value, (int, float)) and not isinstance(value, bool)
+        for name, (wanted, good) in _RULES.items():
+            value = getattr(self, name)
+            try:
+                accepted = good(value)
+            except TypeError:
+                accepted = False
+            if not accepted:
+                raise ValueError(f"option {name}={value!r}: expected {wanted}")
+        # normalised forms: floats as floats, stop strings as a tuple
+        for name, as_type in (("temperature", float), ("top_p", float), ("stop", tuple)):
+            object.__setattr__(self, name, as_type(getattr(self, name)))
 
-        if isinstance(self.max_tokens, bool) or not isinstance(self.max_tokens, int):
-            raise ValueError("max_tokens must be an integer")
-        if self.max_tokens < 1:
-            raise ValueError("max_tokens must be positive")
-        if not number(self.temperature):
-            raise ValueError("temperature must be a number")
-        if self.temperature < 0:
-            raise ValueError("temperature cannot be negative")
-        if self.top_k is not None and (isinstance(self.top_k, bool)
-                                       or not isinstance(self.top_k, int) or self.top_k < 1):
-            raise ValueError("top_k must be null or positive")
-        if not number(self.top_p):
-            raise ValueError("top_p must be a number")
-        if not 0 < self.top_p <= 1:
-            raise ValueError("top_p must be within (0, 1]")
-        if isinstance(self.seed, bool) or not isinstance(self.seed, int):
-            raise ValueError("seed must be an integer")
-        stop = tuple(self.stop)
-        if any(not isinstance(value, str) or not value for value in stop):
-            raise ValueError("stop sequences must be non-empty strings")
-        object.__setattr__(self, "temperature", float(self.temperature))
-        object.__setattr__(self, "top_p", float(self.top_p))
-        object.__setattr__(self, "stop", stop)
+    def replace(self, **changes: Any) -> "TextGenerationOptions":
+        return dataclasses.replace(self, **changes)
 
 
 @dataclass(frozen=True)
@@ -69,7 +84,7 @@ class GenerationResult:
     token_ids: tuple[int, ...] = ()
 
     def to_dict(self) -> dict[str, Any]:
-        return asdict(self)
+        return {f.name: getattr(self, f.name) for f in dataclasses.fields(self)}
 
     def to_json(self) -> str:
-        return json.dumps(self.to_dict(), indent=2, sort_keys=True)
+        return json.dumps(self.to_dict(), sort_keys=True, indent=2)

@@ -57,9 +57,17 @@ class SafetensorsFile:
             count = 1
             for extent in shape:
                 count *= extent
-            if end - begin != count * dtype.itemsize or self._data_start + end > size:
+            if not (isinstance(begin, int) and isinstance(end, int) and 0 <= begin <= end
+                    and end - begin == count * dtype.itemsize
+                    and self._data_start + end <= size):
                 raise SafetensorsError(f"{self.path}: {name} has inconsistent offsets")
             self.entries[name] = (dtype, shape)
+        # the format wants the tensors' byte ranges side by side: none may share bytes
+        ranges = sorted((info["data_offsets"][0], info["data_offsets"][1], name)
+                        for name, info in header.items())
+        for (_, before_end, before), (begin, _, name) in zip(ranges, ranges[1:]):
+            if begin < before_end:
+                raise SafetensorsError(f"{self.path}: {name} overlaps {before}")
 
     def tensor(self, name: str) -> torch.Tensor:
         """A host tensor that views the mapped file (copy it before the file closes)."""

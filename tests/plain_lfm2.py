@@ -155,7 +155,17 @@ def attention_mixer(n, w, prefix, cfg, window=None):
     k = rms_norm(k, w[prefix + "self_attn.k_layernorm.weight"], cfg["norm_eps"])
     angles = rope_angles(torch.arange(tokens), head_dim, cfg["rope_theta"])
     q, k = apply_rope(q, angles), apply_rope(k, angles)
-    group = heads // kv_heads
+    out = causal_attention(q, k, v, window)
+    return out.reshape(tokens, heads * head_dim) @ w[prefix + "self_attn.out_proj.weight"].T
+
+
+def causal_attention(q, k, v, window=None):
+    """softmax(q k^T hd^-0.5) v over a whole sequence from position 0, the query at position t
+    seeing keys at positions <= t (and > t - window); query head h reads key head
+    h // (heads / kv_heads) (src/mlx_one/engine/paged_attention.py:104-105, 222-226 for the
+    mapping and the bound). q: [T, heads, hd]; k, v: [T, kv_heads, hd]; returns [T, heads, hd]."""
+    tokens, heads, head_dim = q.shape
+    group = heads // k.shape[1]
     k = k.repeat_interleave(group, dim=1)
     v = v.repeat_interleave(group, dim=1)
     scores = torch.einsum("qhd,khd->hqk", q, k) * head_dim ** -0.5
@@ -165,8 +175,7 @@ def attention_mixer(n, w, prefix, cfg, window=None):
     if window is not None:
         allowed = allowed & (key > query - window)
     scores = scores.masked_fill(~allowed[None], float("-inf"))
-    out = torch.einsum("hqk,khd->qhd", torch.softmax(scores, dim=-1), v)
-    return out.reshape(tokens, heads * head_dim) @ w[prefix + "self_attn.out_proj.weight"].T
+    return torch.einsum("hqk,khd->qhd", torch.softmax(scores, dim=-1), v)
 
 
 def swiglu_feed_forward(n, w, prefix):

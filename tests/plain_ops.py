@@ -17,9 +17,17 @@ class PlainOps:
     def __init__(self, device="cpu"):
         self.device = torch.device(device)
         self.launches = 0
+        # stands in for the kernels' device flag: a test sets it to see the engine react
+        self.error_flag = torch.zeros(1, dtype=torch.int32, device=self.device)
+
+    def describe_error(self, code):
+        return RuntimeError(f"a kernel reported code {code}")
 
     def check_errors(self):
-        pass
+        code = int(self.error_flag.item())
+        if code:
+            self.error_flag.zero_()
+            raise self.describe_error(code)
 
     def check_attention_sizes(self, heads, kv_heads, head_dim):
         assert heads % kv_heads == 0

@@ -93,6 +93,22 @@ def test_safetensors_round_trip_and_errors(tmp_path):
     (tmp_path / "bad.safetensors").write_bytes(b"\x10\x00\x00\x00\x00\x00\x00\x00{not json")
     with pytest.raises(SafetensorsError):
         SafetensorsFile(tmp_path / "bad.safetensors")
+    # headers whose byte ranges run backwards, start before the data or share bytes
+    import json
+    import struct
+
+    def with_header(header, data=b"\0" * 16):
+        raw = json.dumps(header).encode()
+        target = tmp_path / "crafted.safetensors"
+        target.write_bytes(struct.pack("<Q", len(raw)) + raw + data)
+        return target
+
+    entry = lambda begin, end, shape: {"dtype": "F32", "shape": shape, "data_offsets": [begin, end]}
+    for header, what in (({"t": entry(-8, 0, [2])}, "inconsistent offsets"),
+                         ({"t": entry(8, 0, [-2])}, "inconsistent offsets"),
+                         ({"t": entry(0, 8, [2]), "u": entry(4, 12, [2])}, "overlaps")):
+        with pytest.raises(SafetensorsError, match=what):
+            SafetensorsFile(with_header(header))
 
 
 def test_one_error_lists_missing_unexpected_and_wrong_shapes(tmp_path):

@@ -1,5 +1,5 @@
-"""This repository's configuration, weight names, convolution state and sampling rule against
-outputs of the reference's own code (tests/golden/reference_pieces.json, written by
+"""This repository's configuration, weight names, convolution state, paged attention, rotary
+encoding and sampling rule against outputs of the reference's own code (tests/golden/reference_pieces.json, written by
 tests/golden/make_golden.py from the parts of the reference that import without MLX)."""
 
 import json
@@ -11,7 +11,8 @@ import torch
 from mlx_one_b200.config import ConfigError, Lfm2Config
 from mlx_one_b200.architectures.lfm2 import describe
 from mlx_one_b200.parts.model import expected_tensors
-from plain_lfm2 import feed_forward_width, read_config, sample_token
+from plain_lfm2 import (apply_rope, causal_attention, feed_forward_width, read_config,
+                        rope_angles, sample_token)
 from plain_ops import kept_set
 from tiny_models import TINY_A, TINY_B, TINY_C
 
@@ -101,6 +102,77 @@ def test_convolution_state_equals_the_reference_cache():
         ops.short_conv(bcx, kernel=torch.zeros(channels, taps), bias=None, taps=taps, ctx=ctx,
                        view=view, write=True)
         at += cut
+
+
+def test_paged_attention_equals_the_reference_oracle():
+    """The reference's NumPy paged attention (src/mlx_one/engine/paged_attention.py:209-246) on
+    two requests with shuffled pages: the plain kernel restatement reads the same pool through a
+    block table, and the plain model's whole-sequence attention sees the same keys in order.
+    Pins the mapping of query heads to key heads, the causal bound and the scale."""
+    from plain_ops import PlainOps
+    from mlx_one_b200.parts.base import PagedKeyValues, PagedView, StepContext
+
+    golden = GOLDEN["paged_attention"]
+    heads, kv_heads, head_dim, page = (golden[k] for k in ("heads", "kv_heads", "head_dim", "page"))
+    pool = torch.tensor(golden["pool"])                        # [2, pages, kv_heads, page, hd]
+    queries = torch.tensor(golden["queries"])                  # [requests, heads, 3, hd]
+    want = torch.tensor(golden["output"])
+    width = max(len(t) for t in golden["tables"])
+    table = torch.tensor([t + [-1] * (width - len(t)) for t in golden["tables"]], dtype=torch.int32)
+    as_int = lambda v: torch.tensor(v, dtype=torch.int32)
+    positions, owner, rows = [], [], []
+    for r, count in enumerate(golden["widths"]):
+        for i in range(count):
+            positions.append(golden["positions"][r][i])
+            owner.append(r)
+            rows.append((r, i))
+    q = torch.stack([queries[r, :, i] for r, i in rows])        # [tokens, heads, hd]
+    starts = [0, golden["widths"][0], sum(golden["widths"])]
+    ctx = StepContext(tokens=len(rows), requests=2, token_ids=as_int([0] * len(rows)),
+                      positions=as_int(positions), token_request=as_int(owner),
+                      request_start=as_int(starts),
+                      history=as_int([golden["positions"][0][0], golden["positions"][1][0]]),
+                      max_portion=3, max_context=max(golden["lengths"]))
+    view = PagedView(pool, table, page, PagedKeyValues(kv_heads, head_dim))
+    got = PlainOps().paged_attention(q, heads=heads, kv_heads=kv_heads, head_dim=head_dim,
+                                     scale=golden["scale"], window=None, ctx=ctx, view=view)
+    for t, (r, i) in enumerate(rows):
+        torch.testing.assert_close(got[t].view(heads, head_dim), want[r, :, i], atol=1e-5, rtol=1e-5)
+    # rows of request 1 that the oracle was not asked for stay zero (its widths say one query)
+    assert torch.all(want[1, :, 1:] == 0)
+    # the plain model's attention over request 0's keys in their logical order
+    length = golden["lengths"][0]
+    ordered = pool[:, golden["tables"][0]].permute(0, 1, 3, 2, 4).reshape(2, -1, kv_heads, head_dim)
+    full_q = torch.zeros(length, heads, head_dim)
+    for i, position in enumerate(golden["positions"][0]):
+        full_q[position] = queries[0, :, i]
+    whole = causal_attention(full_q, ordered[0, :length], ordered[1, :length])
+    for i, position in enumerate(golden["positions"][0]):
+        torch.testing.assert_close(whole[position], want[0, :, i], atol=1e-5, rtol=1e-5)
+
+
+@pytest.mark.parametrize("case", range(len(GOLDEN["rope"])))
+def test_rotary_encoding_equals_the_reference(case):
+    """The reference's apply_rope with explicit position_ids
+    (src/mlx_one/models/shared/transformer.py:27-29, 50-51, 67-72, 88-90) against the plain
+    implementation's angles and rotation, and against the engine's table of inverse
+    frequencies."""
+    from mlx_one_b200.parts.base import Runtime
+    from mlx_one_b200.parts.positions import RotaryEncoding
+    from mlx_one_b200.parts.spec import PartSpec
+
+    golden = GOLDEN["rope"][case]
+    value = torch.tensor(golden["value"])[0].permute(1, 0, 2)          # [tokens, heads, hd]
+    want = torch.tensor(golden["rotated"])[0].permute(1, 0, 2)
+    angles = rope_angles(torch.tensor(golden["positions"]), golden["head_dim"], golden["theta"])
+    torch.testing.assert_close(apply_rope(value, angles), want, atol=2e-6, rtol=2e-6)
+    part = RotaryEncoding(PartSpec("rope", {"theta": golden["theta"],
+                                            "rotary_dim": golden["head_dim"]}), {},
+                          Runtime(torch.float32, torch.device("cpu"), None))
+    inv_freq, rotary_dim = part.rotary_table()
+    assert rotary_dim == golden["head_dim"]
+    engine_angles = torch.tensor(golden["positions"], dtype=torch.float32)[:, None] * inv_freq[None]
+    torch.testing.assert_close(apply_rope(value, engine_angles), want, atol=2e-6, rtol=2e-6)
 
 
 @pytest.mark.parametrize("case", range(len(GOLDEN["sampling"])))

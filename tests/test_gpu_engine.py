@@ -92,15 +92,21 @@ def test_mixed_batches_with_page_reuse(folders, plain, name, dtype):
 def test_steps_of_a_repeated_shape_are_replayed(folders, plain, name, dtype):
     """Steps with portions whose shape comes back (two requests, 24 + 17 tokens, then a portion
     beside a decoded token) are captured as graphs at their third occurrence and replayed:
-    different tokens, different pages, different histories, the same shape."""
+    different tokens, different pages, different histories, the same shape. The shape says
+    how many tokens and requests a step has, not how the tokens are split between the requests:
+    later pairs bring 30 + 11 and 11 + 7 tokens to the graphs captured on 24 + 17 and 17 + 1."""
     config, _, page = CONFIGS[name]
     runner, cache = engine(folders[name], dtype, page, 512)
     requests = dict(enumerate(prompts(config["vocab_size"], [42, 35] * 6, seed=9)))
     for pair in range(6):
         a, b = requests[2 * pair], requests[2 * pair + 1]
-        steps = [([(2 * pair, a[:24]), (2 * pair + 1, b[:17])], []),
-                 ([(2 * pair, a[24:41]), (2 * pair + 1, b[17:18])], []),
-                 ([(2 * pair, a[41:]), (2 * pair + 1, b[18:])], [2 * pair, 2 * pair + 1])]
+        first, second = ((24, 17), (17, 1)) if pair < 3 or pair == 4 else ((30, 11), (11, 7))
+        a1, b1 = first[0], first[1]
+        a2, b2 = a1 + second[0], b1 + second[1]
+        assert (a2, b2) == (41, 18)
+        steps = [([(2 * pair, a[:a1]), (2 * pair + 1, b[:b1])], []),
+                 ([(2 * pair, a[a1:a2]), (2 * pair + 1, b[b1:b2])], []),
+                 ([(2 * pair, a[a2:]), (2 * pair + 1, b[b2:])], [2 * pair, 2 * pair + 1])]
         got = replay(runner, cache, steps)
         assert_close(got[2 * pair], plain[name].logits(a), dtype, f"{name} pair {pair} a")
         assert_close(got[2 * pair + 1], plain[name].logits(b), dtype, f"{name} pair {pair} b")

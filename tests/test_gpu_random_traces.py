@@ -10,7 +10,7 @@ import pytest
 import torch
 
 from plain_lfm2 import PlainModel
-from tiny_models import ALL_CONFIGS, TOLERANCE, make_model_dir
+from tiny_models import ALL_CONFIGS, make_model_dir, tolerance
 
 pytestmark = pytest.mark.gpu
 
@@ -74,7 +74,8 @@ def test_random_trace(folders, seed):
     compared = 0
     for dtype in ("float32", "bfloat16"):
         replay = Replay(folders[name], dtype=dtype, max_tokens=most, page_size=16)
-        atol, rtol = TOLERANCE[torch.float32 if dtype == "float32" else torch.bfloat16]
+        kind = torch.float32 if dtype == "float32" else torch.bfloat16
+        bounds = {request_id: tolerance(kind, logits) for request_id, logits in expected.items()}
         for number, (entries, end) in enumerate(steps):
             out = replay.run([{"id": e["id"], "tokens": e["tokens"], "want": e["want"]}
                               for e in entries], end)
@@ -83,6 +84,7 @@ def test_random_trace(folders, seed):
                 for place in entry["want"]:
                     got = torch.from_numpy(out[row])
                     want = expected[entry["id"]][entry["at"] + place]
+                    atol, rtol = bounds[entry["id"]]
                     excess = ((got - want).abs() - (atol + rtol * want.abs())).max().item()
                     assert excess <= 0, (f"{name} {dtype} seed {seed} step {number} request "
                                          f"{entry['id']} position {entry['at'] + place}: over the "

@@ -44,6 +44,9 @@ class DecayMixer(Mixer):
     """s_t = a * s_{t-1} + (1 - a) * x_t per channel, a = sigmoid(decay); out = W s_t.
     The state s is kept per request in a slot, in 32-bit."""
 
+    # forward loops over the requests on the host (ctx.host, .tolist()): not for CUDA graphs
+    capturable = False
+
     @classmethod
     def tensors(cls, spec):
         hidden = spec["hidden"]
@@ -70,6 +73,72 @@ class DecayMixer(Mixer):
             if write:
                 cache.state[slots[r]] = state
         return self.ops.linear(out.to(x.dtype), self.mix)
+
+
+class ShiftMixer(Mixer):
+    """out_t = W (x_t + x_{t-1}), where x_{t-1} is the request's previous token (zero before
+    its first). The state is the request's last input row. Written with torch operations on
+    the step's device tensors only (no host value, no wait), so its steps can be captured as
+    CUDA graphs and replayed with another split of the tokens."""
+
+    @classmethod
+    def tensors(cls, spec):
+        return {"mix.weight": TensorSpec((spec["hidden"], spec["hidden"]))}
+
+    @classmethod
+    def cache_need(cls, spec):
+        return FixedState((spec["hidden"],), dtype="float32")
+
+    def __init__(self, spec, tensors, runtime):
+        super().__init__(spec, tensors, runtime)
+        self.mix = self.matrix(tensors["mix.weight"])
+
+    def forward(self, x, ctx, cache, write):
+        owner = ctx.token_request.long()
+        first = ctx.positions == ctx.history[owner]             # a request's first token here
+        before = torch.roll(x.float(), 1, dims=0)
+        carried = cache.state[cache.slots.long()][owner]        # [tokens, hidden], 32-bit
+        previous = torch.where(first[:, None], carried, before)
+        if write:
+            last = (ctx.request_start[1:] - 1).long()
+            cache.state.index_copy_(0, cache.slots.long(), x.float()[last])
+        return self.ops.linear((x.float() + previous).to(x.dtype), self.mix)
+
+
+def describe_shift(config: ToyConfig) -> ModelSpec:
+    hidden = config.hidden_size
+    norm = lambda prefix: PartSpec("rmsnorm", {"size": hidden, "eps": config.eps}, prefix)
+    swiglu = PartSpec("swiglu", {"hidden": hidden, "width": config.width}, "ffn.")
+    shift = PartSpec("toy_shift", {"hidden": hidden}, "shift.")
+    conv = PartSpec("short_conv", {"hidden": hidden, "taps": 3, "bias": False}, "conv.")
+    layers = tuple(LayerSpec(f"layers.{i}.", PartSpec("prenorm"), mixer, norm("norm1."), swiglu,
+                             norm("norm2.")) for i, mixer in enumerate((shift, conv, shift)))
+    return ModelSpec(architecture="toy-shift", vocab_size=config.vocab_size, hidden_size=hidden,
+                     embedding="embed.weight", layers=layers,
+                     order=tuple(LayerCall(i) for i in range(3)),
+                     final_norm=norm("final_norm."), head=None, max_positions=4096)
+
+
+def plain_shift(w, cfg: ToyConfig, ids):
+    x = w["embed.weight"][torch.tensor(ids)]
+    for layer in range(3):
+        p = f"layers.{layer}."
+        n = rms_norm(x, w[p + "norm1.weight"], cfg.eps)
+        if layer == 1:
+            bcx = n @ w[p + "conv.in_proj.weight"].T
+            b, c, xs = bcx.chunk(3, dim=-1)
+            g = torch.cat([torch.zeros(2, cfg.hidden_size), b * xs])
+            kernel = w[p + "conv.conv"]
+            y = sum(kernel[:, k] * g[k:k + len(ids)] for k in range(3))
+            mixed = (c * y) @ w[p + "conv.out_proj.weight"].T
+        else:
+            previous = torch.cat([torch.zeros(1, cfg.hidden_size), n[:-1]])
+            mixed = (n + previous) @ w[p + "shift.mix.weight"].T
+        h = x + mixed
+        n = rms_norm(h, w[p + "norm2.weight"], cfg.eps)
+        gate, up = n @ w[p + "ffn.w1.weight"].T, n @ w[p + "ffn.w3.weight"].T
+        x = h + (torch.nn.functional.silu(gate) * up) @ w[p + "ffn.w2.weight"].T
+    return rms_norm(x, w["final_norm.weight"], cfg.eps) @ w["embed.weight"].T
 
 
 def describe(config: ToyConfig) -> ModelSpec:
@@ -186,3 +255,81 @@ def test_toy_architecture_on_the_cpu(tmp_path, toy_registered):
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_toy_architecture_on_the_gpu(tmp_path, toy_registered, dtype):
     run_toy(tmp_path, "cuda:0", dtype, None)
+
+
+@pytest.fixture()
+def shift_registered():
+    MIXERS.register("toy_shift", ShiftMixer)
+    register_architecture(Architecture("toy-shift", ToyConfig, describe_shift))
+    yield
+    unregister_architecture("toy-shift")
+    MIXERS.unregister("toy_shift")
+
+
+def run_shift(tmp_path, device, dtype, ops):
+    """Steps of two requests whose shape repeats with other splits of the tokens (24 + 17, then
+    30 + 11, 17 + 24 ...) and decode steps: on the GPU they are captured and replayed."""
+    import warnings
+
+    cfg = ToyConfig(model_type="toy-shift")
+    folder = write_random_model(tmp_path / "shift", cfg.to_dict(), seed=9, dtype=torch.float32)
+    loaded = load_model(folder, dtype, device, ops=ops)
+    model = loaded.model
+    assert model.capturable
+    cache = CacheManager(model.cache_needs, page_size=8, capacity_tokens=1024, max_requests=4,
+                         dtype=model.runtime.dtype, device=device)
+    runner = Runner(model, cache)
+    from safetensors.torch import load_file
+    weights = {k: v.float() for k, v in load_file(str(folder / "model.safetensors")).items()}
+    a, b = prompts(cfg.vocab_size, (160, 140), seed=2)
+    splits = [(24, 17), (24, 17), (24, 17), (30, 11), (17, 24), (1, 40), (39, 2)]
+    steps, at_a, at_b = [], 0, 0
+    for size_a, size_b in splits:
+        steps.append(([("a", a[at_a:at_a + size_a]), ("b", b[at_b:at_b + size_b])], []))
+        at_a, at_b = at_a + size_a, at_b + size_b
+    while at_a < len(a) or at_b < len(b):                     # the rest token by token
+        entries = []
+        if at_a < len(a):
+            entries.append(("a", [a[at_a]]))
+            at_a += 1
+        if at_b < len(b):
+            entries.append(("b", [b[at_b]]))
+            at_b += 1
+        steps.append((entries, []))
+    with warnings.catch_warnings():
+        warnings.simplefilter("error")                         # no capture warning either
+        got = replay(runner, cache, steps)
+    assert_close(got["a"], plain_shift(weights, cfg, a), model.runtime.dtype, "shift a")
+    assert_close(got["b"], plain_shift(weights, cfg, b), model.runtime.dtype, "shift b")
+    return runner
+
+
+def test_capturable_toy_on_the_cpu(tmp_path, shift_registered):
+    from plain_ops import PlainOps
+    run_shift(tmp_path, "cpu", torch.float32, PlainOps())
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_capturable_toy_is_replayed_from_graphs(tmp_path, shift_registered, dtype):
+    runner = run_shift(tmp_path, "cuda:0", dtype, None)
+    # the 41-token shape was met seven times (captured at the third), decode steps far more
+    assert runner.graph_replays >= 4 + 20
+
+
+@pytest.mark.gpu
+def test_toys_that_cannot_be_captured_run_eagerly(tmp_path, toy_registered):
+    """A model with a part that says ``capturable = False`` is never captured: no graph, no
+    warning; and a part that reads host values although it claims to be capturable is told."""
+    import warnings
+
+    with warnings.catch_warnings():
+        warnings.simplefilter("error")
+        run_toy(tmp_path, "cuda:0", torch.float32, None)
+    DecayMixer.capturable = True
+    try:
+        with pytest.raises(RuntimeError, match="capturable"):
+            run_toy(tmp_path / "again", "cuda:0", torch.float32, None)
+    finally:
+        DecayMixer.capturable = False
+        torch.cuda.synchronize()

@@ -50,6 +50,10 @@ class RoutedFeedForward(FeedForward):
     expert is w_out(gelu(w_in x)), scaled by the sigmoid of its logit. The router is made
     decisive (its weights are scaled up) so that rounding does not change a token's expert."""
 
+    # the rows of an expert are found with nonzero(), which waits for the device and gives
+    # tensors whose sizes depend on the data: such a step cannot be replayed from a graph
+    capturable = False
+
     @classmethod
     def tensors(cls, spec):
         hidden, width = spec["hidden"], spec["width"]

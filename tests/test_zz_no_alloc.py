@@ -56,31 +56,63 @@ def call(lib, name, q, kv, table, positions, pages, blocks, page_size, splits, p
     return code, out
 
 
+def plain_attention(q, kv, table, positions, page_size):
+    """softmax(q k^T / sqrt(d)) v over each request's pages, in 64-bit on the host."""
+    requests, heads, head_dim = q.shape
+    group = heads // kv.shape[2]
+    out = torch.empty(requests, heads * head_dim, dtype=torch.float64)
+    kv, q, table = kv.double().cpu(), q.double().cpu(), table.cpu()
+    for r in range(requests):
+        length = int(positions[r]) + 1
+        pages = table[r, :-(-length // page_size)].long()
+        keys = kv[0, pages].permute(1, 0, 2, 3).reshape(kv.shape[2], -1, head_dim)[:, :length]
+        values = kv[1, pages].permute(1, 0, 2, 3).reshape(kv.shape[2], -1, head_dim)[:, :length]
+        for h in range(heads):
+            scores = keys[h // group] @ q[r, h] * head_dim ** -0.5
+            out[r, h * head_dim:(h + 1) * head_dim] = torch.softmax(scores, 0) @ values[h // group]
+    return out
+
+
+def free_bytes():
+    """Free device memory as the driver counts it: an allocation by anyone in this process,
+    the library included, lowers it (torch's own counters would not see the library's)."""
+    torch.cuda.synchronize()
+    return torch.cuda.mem_get_info()[0]
+
+
 def test_static_scratch_entry_point_matches_the_allocating_one():
     lib = library()
     assert lib.mlxone_attention_decode_static_capacity() == 2 * 1024 * 1024
-    # two calls in a row: the second is smaller and of another shape, so the array still holds
-    # partial results of the first beyond what the second writes
-    for requests, context, heads, kv_heads, head_dim, page, splits, seed in (
-            (8, 1500, 32, 8, 64, 16, 4, 0), (3, 700, 6, 2, 48, 8, 3, 1)):
+    # calls in a row: each is of another shape than the one before, so the array still holds
+    # partial results that this call does not overwrite. The third nearly fills the array
+    # (2,095,104 of 2,097,152 floats), the fourth has a single split and needs no scratch.
+    for number, (requests, context, heads, kv_heads, head_dim, page, splits, seed) in enumerate((
+            (8, 1500, 32, 8, 64, 16, 4, 0), (3, 700, 6, 2, 48, 8, 3, 1),
+            (8, 4100, 32, 8, 64, 16, 124, 2), (2, 90, 4, 4, 32, 4, 1, 3))):
         q, kv, table, positions, pages, blocks = case(requests, context, heads, kv_heads,
                                                       head_dim, page, seed)
         floats = lib.mlxone_attention_decode_scratch(requests, heads, head_dim, splits)
-        partial = torch.empty(floats, dtype=torch.float32, device=DEVICE)
+        assert floats <= lib.mlxone_attention_decode_static_capacity()
+        partial = torch.empty(max(floats, 1), dtype=torch.float32, device=DEVICE)
         code, want = call(lib, "mlxone_attention_decode", q, kv, table, positions, pages, blocks,
                           page, splits, partial)
         assert code == 0, lib.mlxone_last_error().decode()
         got = empty_output(q)                   # the caller's buffers exist before the call
-        torch.cuda.synchronize()
-        before = torch.cuda.memory_allocated(), torch.cuda.memory_reserved()
+        before = (free_bytes(), torch.cuda.memory_allocated(), torch.cuda.memory_reserved())
         code, got = call(lib, "mlxone_attention_decode_static", q, kv, table, positions, pages,
                          blocks, page, splits, out=got)
         assert code == 0, lib.mlxone_last_error().decode()
-        torch.cuda.synchronize()
-        assert (torch.cuda.memory_allocated(), torch.cuda.memory_reserved()) == before
+        after = (free_bytes(), torch.cuda.memory_allocated(), torch.cuda.memory_reserved())
+        if number:
+            # (the very first call may make the driver load the library's device image, array
+            # included; from the second call on nothing in the process may take device memory)
+            assert after == before
         assert not torch.isnan(got.float()).any()
         torch.testing.assert_close(got.float(), want.float(), atol=2e-2, rtol=2e-2)
         assert torch.equal(got, want)          # same kernel, same order of operations
+        if requests * context <= 8 * 1500:
+            plain = plain_attention(q, kv, table, positions, page)
+            torch.testing.assert_close(got.double().cpu(), plain, atol=2e-2, rtol=2e-2)
 
 
 def test_static_scratch_entry_point_refuses_what_does_not_fit():
@@ -93,3 +125,12 @@ def test_static_scratch_entry_point_refuses_what_does_not_fit():
     assert "scratch" in message and "fewer splits" in message
     torch.cuda.synchronize()
     assert torch.isnan(out.float()).all()       # nothing was launched
+    # one split more than the array holds for this shape (124 fit, see the test above)
+    q, kv, table, positions, pages, blocks = case(8, 4100, 32, 8, 64, 16, 4)
+    assert lib.mlxone_attention_decode_scratch(8, 32, 64, 125) > \
+        lib.mlxone_attention_decode_static_capacity()
+    code, out = call(lib, "mlxone_attention_decode_static", q, kv, table, positions, pages,
+                     blocks, 16, 125)
+    assert code != 0 and "125 splits" in lib.mlxone_last_error().decode()
+    torch.cuda.synchronize()
+    assert torch.isnan(out.float()).all()

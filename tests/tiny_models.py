@@ -59,9 +59,22 @@ CONFIGS = {"A": (TINY_A, 0, 4), "B": (TINY_B, 1, 8), "C": (TINY_C, 2, 16),
            "D": (TINY_D, 5, 8)}   # config, seed, page
 ALL_CONFIGS = {**CONFIGS, "MID": (MID, 3, 16)}
 
-# (atol, rtol) on logits: |engine - plain| <= atol + rtol * |plain|, as the reference gates
-# its own parity runs (src/mlx_one/inference_baseline.py:30).
-TOLERANCE = {torch.float32: (1e-4, 1e-4), torch.bfloat16: (5e-2, 1e-2)}
+# (atol, rtol) on logits: |engine - plain| <= atol + rtol * |plain|. In 32-bit the bound is the
+# reference's for its own parity runs (src/mlx_one/inference_baseline.py:30). Its bfloat16 bound
+# (5e-2) is meant for checkpoints whose logits are an order of magnitude larger than those of
+# these random models (standard deviation 0.16 to 0.5), where it would be wider than the effect
+# of a wrong key. So the bfloat16 bound here is relative to the spread of the plain logits:
+# measured rounding of the bfloat16 engine is 1.5 to 5 % of that spread, one wrong prompt token
+# moves the last logits by 15 to 60 % of it.
+TOLERANCE = {torch.float32: (1e-4, 1e-4), torch.bfloat16: (None, 1e-2)}
+BF16_ATOL_OF_SPREAD = 0.08
+
+
+def tolerance(dtype, want: torch.Tensor) -> tuple[float, float]:
+    atol, rtol = TOLERANCE[dtype]
+    if atol is None:
+        atol = BF16_ATOL_OF_SPREAD * float(want.float().std())
+    return atol, rtol
 
 
 def make_model_dir(name: str, root: Path | None = None, dtype=torch.bfloat16) -> Path:
@@ -79,8 +92,8 @@ def prompts(vocab: int, lengths, seed: int = 0):
 
 
 def assert_close(got: torch.Tensor, want: torch.Tensor, dtype, what: str = "") -> None:
-    atol, rtol = TOLERANCE[dtype]
     got, want = got.float().cpu(), want.float().cpu()
+    atol, rtol = tolerance(dtype, want)
     excess = (got - want).abs() - (atol + rtol * want.abs())
     worst = excess.max().item()
     if not worst <= 0:
