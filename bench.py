@@ -12,6 +12,11 @@ entry point (``Engine.step``), token ids crossing the host in both directions ev
 decode step to the bytes it has to read: every weight once and the cache of the live
 requests. ``points`` holds decode at batch 1 and 64.
 
+Two more workloads, each printing one JSON line of its own (the default line is unchanged):
+
+    python bench.py --case batching     continuous batching of 128 requests at the LFM2-700M shape
+    python bench.py --case long         4 x 32,768-token prompts at the LFM2-350M shape, then decoding
+
 Data: seeded uniform-random token ids and N(0, 0.02) weights (norms 1 + N(0, 0.1)); there
 are no checkpoints offline. Working set per step (2.3 GB of weights) is far larger than L2,
 so no flush is needed between steps.
@@ -41,6 +46,15 @@ LFM2_1_2B = dict(
     block_auto_adjust_ff_dim=True, block_ff_dim=12288, block_multiple_of=256,
     block_ffn_dim_multiplier=1.0, vocab_size=65536, rope_theta=1000000.0, conv_L_cache=3,
     conv_bias=False, tie_embedding=True, norm_eps=1e-5, max_position_embeddings=128000)
+
+
+def _variant(**changes):
+    return {**LFM2_1_2B, **changes}
+
+
+# BASELINE.json configs[3] and configs[4]: same layer kinds, other widths
+LFM2_700M = _variant(hidden_size=1536, num_attention_heads=24, block_ff_dim=10240)
+LFM2_350M = _variant(hidden_size=1024, num_attention_heads=16, block_ff_dim=6656)
 PAGE_SIZE = 16
 PREFILL_TOKENS = 2048
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
@@ -67,16 +81,27 @@ class ClockSampler:
              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
              "clocks_event_reasons.sw_power_cap")
 
-    def __init__(self):
-        self.samples, self.reasons, self.max_mhz = [], set(), None
+    def __init__(self, gpu=None):
+        """``gpu``: what nvidia-smi's -i takes (index or UUID); None: the current CUDA device."""
+        self.samples, self.times, self.reasons, self.max_mhz = [], [], set(), None
         self._process = None
         self._thread = None
+        self.gpu = gpu
+
+    def _current_gpu(self):
+        if self.gpu is not None:
+            return str(self.gpu)
+        try:
+            import torch
+            return f"GPU-{torch.cuda.get_device_properties(torch.cuda.current_device()).uuid}"
+        except Exception:           # noqa: BLE001
+            return "0"
 
     def start(self):
         try:
             self._process = subprocess.Popen(
-                ["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}",
-                 "--format=csv,noheader,nounits", "-lms", "100"],
+                ["nvidia-smi", "-i", self._current_gpu(), f"--query-gpu={self.QUERY}",
+                 "--format=csv,noheader,nounits", "-lms", "50"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             return
@@ -94,20 +119,30 @@ class ClockSampler:
                 self.max_mhz = float(parts[1])
             except ValueError:
                 continue
+            self.times.append(time.perf_counter())
             for name, value in zip(names, parts[2:6]):
                 if value.lower().startswith("active"):
                     self.reasons.add(name)
 
-    def stop(self):
+    def stop(self, load_began=None, region=None):
+        """``load_began``: when the GPU began to run the measured kind of step without a pause
+        (samples before that describe an idle GPU and are left out of the median);
+        ``region``: (begin, end) of the timed steps on the host's clock."""
         if self._process is not None:
             self._process.terminate()
             try:
                 self._process.wait(timeout=5)
             except subprocess.TimeoutExpired:
                 self._process.kill()
-        return {"sm_mhz": statistics.median(self.samples) if self.samples else None,
+        loaded = [s for s, t in zip(self.samples, self.times)
+                  if load_began is None or t >= load_began + 0.06]
+        inside = sum(1 for t in self.times if region and region[0] <= t <= region[1] + 0.06)
+        return {"sm_mhz": statistics.median(loaded) if loaded else None,
                 "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
-                "samples": len(self.samples)}
+                "samples": len(self.samples), "samples_under_load": len(loaded),
+                "samples_in_timed_region": inside,
+                "how": "nvidia-smi every 50 ms while the same decode steps run untimed for about "
+                       "a second directly before the timed steps, and through them"}
 
 
 def reference_arm():
@@ -127,7 +162,8 @@ def reference_arm():
     return 0
 
 
-def build_engine(config, layers, batch, context, steps_ahead):
+def build_engine(config, layers, batch, context, steps_ahead, *, capacity=None, batching=None,
+                 name="random-lfm2-1.2b"):
     import torch
 
     from mlx_one_b200 import BatchingConfig, CacheConfig, Engine
@@ -145,16 +181,16 @@ def build_engine(config, layers, batch, context, steps_ahead):
     tensors = random_tensors(spec, seed=0, dtype=torch.bfloat16, device="cuda:0")
     model = build_model(spec, tensors, "bfloat16", "cuda:0")
     del tensors
-    loaded = LoadedModel(Path("random-lfm2-1.2b"), architecture, typed, spec, model)
-    capacity = batch * (-(-(context + steps_ahead + 128) // 64) * 64) + PREFILL_TOKENS + 64
-    engine = Engine(loaded,
-                    cache_config=CacheConfig(block_size_tokens=PAGE_SIZE, capacity_tokens=capacity,
-                                             max_requests=batch + 1),
-                    batching_config=BatchingConfig(max_sequences=batch, queue_size=batch + 1,
-                                                   prefill_chunk_size=2048,
-                                                   max_scheduled_tokens=4096,
-                                                   max_prefill_tokens=4096))
-    return engine
+    loaded = LoadedModel(Path(name), architecture, typed, spec, model)
+    if capacity is None:
+        capacity = batch * (-(-(context + steps_ahead + 128) // 64) * 64) + PREFILL_TOKENS + 64
+    if batching is None:
+        batching = BatchingConfig(max_sequences=batch, queue_size=batch + 1,
+                                  prefill_chunk_size=2048, max_scheduled_tokens=4096,
+                                  max_prefill_tokens=4096)
+    return Engine(loaded, batching_config=batching,
+                  cache_config=CacheConfig(block_size_tokens=PAGE_SIZE, capacity_tokens=capacity,
+                                           max_requests=batch + 1))
 
 
 def model_flops(spec, tokens):
@@ -186,7 +222,7 @@ def fill_requests(engine, prompts, ids):
     first decoded token of each."""
     from mlx_one_b200.engine.runner import StepEntry
 
-    runner, cache = engine._runner, engine.cache
+    runner, cache = engine.runner, engine.cache
     firsts = {}
     chunk = 1024
     for request_id in ids:
@@ -218,11 +254,14 @@ def time_decode(engine, batch, context, warmup, steps, seed, sampler=None):
     from mlx_one_b200.engine.runner import StepEntry
 
     vocab = engine.model.spec.vocab_size
-    prompt_length = context - warmup - steps - 1
+    load_steps = 0
+    if sampler:
+        load_steps = max(min(1024, context - warmup - steps - 65), 0) // 64 * 64
+    prompt_length = context - max(warmup, 3) - load_steps - steps - 1
     ids = [f"decode{batch}_{i}" for i in range(batch)]
     prompts = random_prompts(vocab, batch, prompt_length, seed)
     firsts = fill_requests(engine, prompts, ids)
-    runner = engine._runner
+    runner = engine.runner
     entries = [StepEntry(i, [t]) for i, t in zip(ids, firsts)]
     before = engine.model.ops.launches
     chosen = runner.decode_steps(entries, max(warmup, 3))
@@ -231,16 +270,28 @@ def time_decode(engine, batch, context, warmup, steps, seed, sampler=None):
     # launches of one eager step = what the first call launched before it captured
     entries = [StepEntry(i, [t]) for i, t in zip(ids, last)]
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    load_began = None
     if sampler:
+        # The timed region may last a few milliseconds, less than one sample of nvidia-smi. So the
+        # clocks are sampled while the same steps run, untimed, for about a second before it
+        # (the prompts are that much shorter, so the timed steps end at ``context`` all the same).
         sampler.start()
-        time.sleep(0.25)
+        time.sleep(0.15)
+        load_began = time.perf_counter()
+        for _ in range(load_steps // 64):
+            last = runner.decode_steps(entries, 64)[-1].tolist()
+            entries = [StepEntry(i, [t]) for i, t in zip(ids, last)]
     torch.cuda.synchronize()
+    began = time.perf_counter()
     start.record()
     runner.decode_steps(entries, steps)
     stop.record()
     torch.cuda.synchronize()
+    ended = time.perf_counter()
     seconds = start.elapsed_time(stop) / 1e3
-    clocks = sampler.stop() if sampler else None
+    clocks = sampler.stop(load_began, (began, ended)) if sampler else None
+    if clocks is not None:
+        clocks["untimed_load_steps"] = load_steps
     mean_context = context - 1 - steps / 2
     for request_id in ids:
         engine.cache.close(request_id)
@@ -253,7 +304,7 @@ def count_step_launches(engine, batch):
 
     from mlx_one_b200.engine.runner import StepEntry
 
-    runner, cache, ops = engine._runner, engine.cache, engine.model.ops
+    runner, cache, ops = engine.runner, engine.cache, engine.model.ops
     ids = [f"count{i}" for i in range(batch)]
     for request_id in ids:
         cache.open(request_id)
@@ -298,7 +349,7 @@ def time_e2e(engine, batch, context, warmup, steps, seed):
     torch.cuda.synchronize()
     seconds = time.perf_counter() - began
     produced = sum(len(h.request.output) for h in handles) - produced
-    meta_bytes = engine._runner.last_meta_bytes
+    meta_bytes = engine.runner.last_meta_bytes
     assert produced == batch * steps, (produced, batch, steps)
     for handle in handles:
         handle.cancel()
@@ -311,7 +362,7 @@ def time_prefill(engine, tokens, warmup, repeats, seed):
 
     from mlx_one_b200.engine.runner import StepEntry
 
-    runner, cache = engine._runner, engine.cache
+    runner, cache = engine.runner, engine.cache
     prompts = random_prompts(engine.model.spec.vocab_size, warmup + repeats, tokens, seed)
     times = []
     for index, prompt in enumerate(prompts):
@@ -327,6 +378,262 @@ def time_prefill(engine, tokens, warmup, repeats, seed):
             times.append(start.elapsed_time(stop) / 1e3)
         cache.close(request_id)
     return statistics.median(times)
+
+
+# --------------------------------------------------------------------------- other workloads
+
+
+def batching_workload(vocab, requests, prompt_range, output_range, seed):
+    """Seeded requests of the continuous-batching case: (prompt ids, new tokens) with lengths
+    uniform in the given ranges (both ends included)."""
+    import torch
+
+    generator = torch.Generator().manual_seed(seed)
+    draw = lambda low, high: int(torch.randint(low, high + 1, (1,), generator=generator))
+    out = []
+    for _ in range(requests):
+        length, new = draw(*prompt_range), draw(*output_range)
+        out.append((torch.randint(0, vocab, (length,), generator=generator).tolist(), new))
+    return out
+
+
+def run_batching(engine, workload):
+    """Submits every request of ``workload`` at once and drives the engine until all are done.
+    Returns (results in order, seconds on the host's clock around the run, the steps' records)."""
+    from mlx_one_b200 import TextGenerationOptions
+
+    import torch
+
+    records = []
+    engine._trace_sink = records.append
+    torch.cuda.synchronize()
+    began = time.perf_counter()
+    handles = [engine.submit_ids(prompt, TextGenerationOptions(max_tokens=new, ignore_eos=True))
+               for prompt, new in workload]
+    engine.run()
+    torch.cuda.synchronize()
+    seconds = time.perf_counter() - began
+    engine._trace_sink = None
+    return [handle.result() for handle in handles], seconds, records
+
+
+def summarize_steps(records):
+    """Step records by phase, and a histogram of their token counts."""
+    phases = {}
+    for record in records:
+        entry = phases.setdefault(record["phase"], {"steps": 0, "tokens": 0, "prompt_tokens": 0,
+                                                    "requests": 0})
+        entry["steps"] += 1
+        entry["tokens"] += record["tokens"]
+        entry["prompt_tokens"] += record["prompt_tokens"]
+        entry["requests"] += record["batch_size"]
+    for entry in phases.values():
+        entry["mean_tokens"] = round(entry["tokens"] / entry["steps"], 1)
+        entry["mean_requests"] = round(entry.pop("requests") / entry["steps"], 1)
+    edges = (1, 8, 32, 64, 128, 256, 512, 1024, 1 << 30)
+    histogram = {}
+    for record in records:
+        top = next(e for e in edges if record["tokens"] <= e)
+        label = f"<={top}" if top < 1 << 30 else ">1024"
+        histogram[label] = histogram.get(label, 0) + 1
+    return phases, histogram
+
+
+def case_batching(args) -> int:
+    """BASELINE.json configs[3]: continuous batching of 128 requests at the LFM2-700M shape,
+    prompts uniform in [16, 3072] tokens, outputs uniform in [16, 512], prompt portions of 512
+    tokens beside the running decodes. The protocol is the reference's for its decode runs
+    (src/mlx_one/p1_decode.py:15-107): one warm-up repetition, then ``--repeats`` measured ones
+    of the same requests, the median reported; the clock is the host's around submit + run."""
+    import torch
+
+    from mlx_one_b200 import BatchingConfig
+
+    peak = peaks()
+    requests, sequences = args.requests, args.sequences
+    batching = BatchingConfig(max_sequences=sequences, queue_size=requests,
+                              prefill_chunk_size=512, max_prefill_tokens=512,
+                              max_scheduled_tokens=512 + sequences, timeout=0)
+    capacity = sequences * (3072 + 512 + 64)
+    engine = build_engine(LFM2_700M, args.layers, sequences, 0, 0, capacity=capacity,
+                          batching=batching, name="random-lfm2-700m")
+    spec = engine.model.spec
+    workload = batching_workload(spec.vocab_size, requests, (16, 3072), (16, 512), seed=123)
+    prompt_tokens = sum(len(p) for p, _ in workload)
+    new_tokens = sum(n for _, n in workload)
+    samples = []
+    for repetition in range(args.repeats + 1):
+        replays = engine.runner.graph_replays
+        results, seconds, records = run_batching(engine, workload)
+        assert [r.generation_tokens for r in results] == [n for _, n in workload]
+        engine.model.ops.check_errors()
+        stats = engine.runtime_stats()
+        phases, histogram = summarize_steps(records)
+        samples.append({"phase": "warmup" if repetition == 0 else "measured",
+                        "seconds": round(seconds, 4), "steps": len(records),
+                        "graph_replay_share": round((engine.runner.graph_replays - replays)
+                                                    / max(len(records), 1), 3),
+                        "by_phase": phases, "tokens_per_step": histogram,
+                        "pages_low_water": stats["pages_low_water"][0],
+                        "pages_total": stats["pages_total"][0]})
+    measured = sorted(samples[1:], key=lambda sample: sample["seconds"])
+    middle = measured[len(measured) // 2]
+    line = {
+        "case": "batching", "metric": "tokens/s of 128 requests batched continuously "
+                                      "(LFM2-700M shape, bf16)",
+        "value": round((prompt_tokens + new_tokens) / middle["seconds"], 1),
+        "unit": "tokens/s (prompt + generated)",
+        "generated_tokens_per_s": round(new_tokens / middle["seconds"], 1),
+        "seconds_median": middle["seconds"],
+        "seconds_all": [sample["seconds"] for sample in samples[1:]],
+        "warmup_seconds": samples[0]["seconds"],
+        "requests": requests, "prompt_tokens": prompt_tokens, "generated_tokens": new_tokens,
+        "config": {"model": "LFM2-700M shape", "layers": args.layers, "hidden": spec.hidden_size,
+                   "ffn_width": spec.layers[0].feed_forward["width"], "vocab": spec.vocab_size,
+                   "max_sequences": sequences, "prefill_chunk_size": 512, "page_size": PAGE_SIZE,
+                   "prompts": "uniform 16..3072", "outputs": "uniform 16..512",
+                   "capacity_tokens": capacity, "peaks": peak["source"]},
+        "median_run": middle, "dtype": "bf16",
+        "data": "synthetic: random weights N(0,0.02), seeded uniform-random token ids",
+    }
+    print(json.dumps(line))
+    return 0
+
+
+def case_long(args) -> int:
+    """BASELINE.json configs[4]: four requests of 32,768 prompt tokens at the LFM2-350M shape,
+    prefilled in portions of 4,096 tokens, then 256 decode steps each. Prefill and decode are
+    timed on the device through the step function (CUDA events); the same work is then run
+    once more through the entry point on the host's clock."""
+    import torch
+
+    from mlx_one_b200 import BatchingConfig, TextGenerationOptions
+    from mlx_one_b200.engine.runner import StepEntry
+
+    peak = peaks()
+    count, prompt_length, portion, decode = 4, args.context or 32768, 4096, args.steps
+    batching = BatchingConfig(max_sequences=count, queue_size=count, prefill_chunk_size=portion,
+                              max_prefill_tokens=portion, max_scheduled_tokens=portion + count,
+                              timeout=0)
+    per_request = -(-(prompt_length + decode + 16) // 64) * 64
+    engine = build_engine(LFM2_350M, args.layers, count, 0, 0, capacity=count * per_request + 64,
+                          batching=batching, name="random-lfm2-350m")
+    model, spec, runner, cache = engine.model, engine.model.spec, engine.runner, engine.cache
+    prompts = random_prompts(spec.vocab_size, count, prompt_length, seed=5)
+    ids = [f"long{i}" for i in range(count)]
+    attention_layers = sum(1 for layer in spec.layers if layer.mixer.kind == "attention")
+    heads_width = spec.hidden_size
+    linear_flops = model_flops(spec, 1) - 2 * spec.vocab_size * spec.hidden_size \
+        - attention_layers * 4 * heads_width
+
+    # prefill, portion by portion, each timed on the device
+    portion_ms = []
+    firsts = []
+    for request_id, prompt in zip(ids, prompts):
+        cache.open(request_id)
+        for at in range(0, prompt_length, portion):
+            part = prompt[at:at + portion]
+            last = at + portion >= prompt_length
+            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            start.record()
+            logits = runner.step([StepEntry(request_id, part, (len(part) - 1,) if last else ())])
+            stop.record()
+            torch.cuda.synchronize()
+            if request_id != ids[0]:                          # the first request warms up
+                portion_ms.append((at, start.elapsed_time(stop)))
+            if last:
+                firsts.append(int(model.ops.argmax(logits)[0]))
+    pages_held = cache.get(ids[0]).live[0]
+    timed_requests = count - 1
+    prefill_seconds = sum(ms for _, ms in portion_ms) / 1e3
+    prefill_tokens = timed_requests * prompt_length
+    flops = timed_requests * sum(
+        linear_flops * min(portion, prompt_length - at)
+        + attention_layers * 4 * heads_width * sum(range(at + 1, min(at + portion, prompt_length) + 1))
+        for at in range(0, prompt_length, portion))
+    by_start = {}
+    for at, ms in portion_ms:
+        by_start.setdefault(at, []).append(ms)
+    first_ms = statistics.median(by_start[0])
+    last_start = max(by_start)
+    last_ms = statistics.median(by_start[last_start])
+
+    # decode: all four together, the chosen token fed back on the device
+    entries = [StepEntry(i, [t]) for i, t in zip(ids, firsts)]
+    chosen = runner.decode_steps(entries, 3)
+    entries = [StepEntry(i, [t]) for i, t in zip(ids, chosen[-1].tolist())]
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    start.record()
+    runner.decode_steps(entries, decode)
+    stop.record()
+    torch.cuda.synchronize()
+    decode_seconds = start.elapsed_time(stop) / 1e3
+    model.ops.check_errors()
+    mean_context = prompt_length + 3 + decode / 2
+    kv_per_token = engine.cache_bytes_per_token()
+    state_bytes = sum(g.storage[:, 0].numel() * g.storage.element_size() for g in cache.states)
+    step_bytes = model.weight_bytes() + count * (mean_context * kv_per_token + 2 * state_bytes)
+    achieved = step_bytes / (decode_seconds / decode) / 1e9
+    for request_id in ids:
+        cache.close(request_id)
+
+    # the same through the entry point: submit four requests, run, host clock
+    options = TextGenerationOptions(max_tokens=decode + 1, ignore_eos=True)
+    records = []
+    engine._trace_sink = records.append
+    torch.cuda.synchronize()
+    began = time.perf_counter()
+    handles = [engine.submit_ids(prompt, options) for prompt in prompts]
+    engine.run()
+    torch.cuda.synchronize()
+    e2e_seconds = time.perf_counter() - began
+    engine._trace_sink = None
+    results = [handle.result() for handle in handles]
+    assert all(r.generation_tokens == decode + 1 for r in results)
+    model.ops.check_errors()
+    phases, histogram = summarize_steps(records)
+    # decode through the entry point: the steps in which all four requests decode
+    full = [r for r in records if r["phase"] == "decode" and r["batch_size"] == count]
+    e2e_decode = None
+    if len(full) > 2:
+        e2e_decode = round(count * (len(full) - 1) / (full[-1]["committed_at"] - full[0]["committed_at"]), 1)
+    stats = engine.runtime_stats()
+    line = {
+        "case": "long", "metric": "prefill and decode tokens/s at 4 x 32,768 tokens of context "
+                                  "(LFM2-350M shape, bf16)",
+        "prefill": {"value": round(prefill_tokens / prefill_seconds, 1), "unit": "tokens/s",
+                    "tokens": prefill_tokens, "portion": portion,
+                    "ms_first_portion": round(first_ms, 3),
+                    "ms_last_portion": round(last_ms, 3),
+                    "frac": round(flops / prefill_seconds / (peak["bf16_tflops"] * 1e12), 4),
+                    "frac_last_portion": round(
+                        (linear_flops * portion + attention_layers * 4 * heads_width
+                         * sum(range(last_start + 1, last_start + portion + 1)))
+                        / (last_ms / 1e3) / (peak["bf16_tflops"] * 1e12), 4)},
+        "decode": {"value": round(count * decode / decode_seconds, 1), "unit": "tokens/s",
+                   "steps": decode, "ms_per_step": round(decode_seconds / decode * 1e3, 4),
+                   "mean_context": mean_context},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak["hbm_gbs"],
+                     "unit": "GB/s", "frac": round(achieved / peak["hbm_gbs"], 4),
+                     "bytes_per_step": int(step_bytes)},
+        "e2e": {"seconds": round(e2e_seconds, 4),
+                "value": round(count * (prompt_length + decode + 1) / e2e_seconds, 1),
+                "unit": "tokens/s (prompt + generated, host clock around submit + run)",
+                "decode_tokens_per_s_all_four": e2e_decode, "by_phase": phases,
+                "tokens_per_step": histogram},
+        "pages_per_request": pages_held, "pages_low_water": stats["pages_low_water"][0],
+        "pages_total": stats["pages_total"][0],
+        "config": {"model": "LFM2-350M shape", "layers": args.layers, "hidden": spec.hidden_size,
+                   "ffn_width": spec.layers[0].feed_forward["width"], "vocab": spec.vocab_size,
+                   "requests": count, "prompt_tokens": prompt_length, "portion": portion,
+                   "decode_steps": decode, "page_size": PAGE_SIZE, "peaks": peak["source"]},
+        "dtype": "bf16",
+        "data": "synthetic: random weights N(0,0.02), seeded uniform-random token ids",
+    }
+    print(json.dumps(line))
+    return 0
 
 
 def kernel_case(name: str, batch: int, context: int) -> int:
@@ -498,7 +805,16 @@ def main() -> int:
     parser.add_argument("--warmup", type=int, default=8)
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--batch", type=int, default=8)
-    parser.add_argument("--context", type=int, default=4096)
+    parser.add_argument("--context", type=int, default=None,
+                        help="context length (default 4096; --case long: prompt tokens, 32768)")
+    parser.add_argument("--case", default="decode", choices=["decode", "batching", "long"],
+                        help="decode: the default line; batching: 128 requests batched "
+                             "continuously (LFM2-700M shape); long: 4 x 32,768 tokens "
+                             "(LFM2-350M shape)")
+    parser.add_argument("--repeats", type=int, default=3, help="--case batching: measured runs")
+    parser.add_argument("--requests", type=int, default=128, help="--case batching")
+    parser.add_argument("--sequences", type=int, default=64,
+                        help="--case batching: requests that run at a time")
     parser.add_argument("--layers", type=int, default=LFM2_1_2B["num_hidden_layers"])
     parser.add_argument("--skip-points", action="store_true", help="leave out batch 1 and 64")
     parser.add_argument("--kernel", default=None,
@@ -513,6 +829,11 @@ def main() -> int:
     if args.gpus != 1:
         print(f"this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
+    if args.case == "batching":
+        return case_batching(args)
+    if args.case == "long":
+        return case_long(args)
+    args.context = args.context or 4096
     if args.kernel:
         return kernel_case(args.kernel, args.batch, args.context)
     warmup = max(args.warmup, 3)
@@ -526,7 +847,7 @@ def main() -> int:
     model, spec = engine.model, engine.model.spec
     model.ops.set_dependent_launches(bool(args.dependent_launches))
     weight_bytes = model.weight_bytes()
-    kv_per_token = engine._bytes_per_token()
+    kv_per_token = engine.cache_bytes_per_token()
     state_bytes = sum(g.storage[:, 0].numel() * g.storage.element_size()
                       for g in engine.cache.states)
 

@@ -202,6 +202,15 @@ class Engine:
     def cache(self) -> CacheManager:
         return self._cache
 
+    @property
+    def runner(self) -> Runner:
+        """The step function that this engine drives (for replay, tests and measurements)."""
+        return self._runner
+
+    def cache_bytes_per_token(self) -> int:
+        """Bytes of keys and values that one token of context holds, over all layers."""
+        return self._bytes_per_token()
+
     # ------------------------------------------------------------------ text <-> ids
 
     def encode(self, prompt: str) -> list[int]:
@@ -482,6 +491,7 @@ class Engine:
             "decode_tokens": tokens - prompt_tokens, "draws": inflight.draws,
             "launched_ahead": inflight.ahead,
             "duration_s": committed_at - inflight.launched_at,
+            "committed_at": committed_at,
         }
         self._stats["steps_committed"] += 1
         self._traces.append(record)
@@ -654,7 +664,8 @@ class Engine:
 
     def runtime_stats(self) -> dict[str, Any]:
         cache = self._cache.stats()
-        return {**self._stats, "waiting": len(self._scheduler.waiting),
+        return {**self._stats, **self._runner.graph_stats(),
+                "waiting": len(self._scheduler.waiting),
                 "running": len(self._scheduler.running), "pages_total": cache.pages_total,
                 "pages_free": cache.pages_free, "pages_low_water": cache.pages_low_water,
                 "slots_free": cache.slots_free, "kernel_launches": self.model.ops.launches}
