@@ -102,7 +102,8 @@ class CacheManager:
             if isinstance(need, PagedKeyValues):
                 storage = None
                 if allocate:
-                    storage = torch.zeros((len(entries), 2, pages, need.kv_heads, page_size,
+                    # one page beyond the pool's: the scratch page (see ``scratch_page``)
+                    storage = torch.zeros((len(entries), 2, pages + 1, need.kv_heads, page_size,
                                            need.head_dim), dtype=dtype, device=self.device)
                 group = len(self.paged)
                 self.paged.append(PagedGroup(need, tuple(entries), IndexPool(pages, "page"),
@@ -113,8 +114,9 @@ class CacheManager:
                 storage = None
                 if allocate:
                     kind = torch.float32 if need.dtype == "float32" else dtype
-                    storage = torch.zeros((len(entries), max_requests, *need.shape), dtype=kind,
-                                          device=self.device)
+                    # one slot beyond the pool's: the scratch slot
+                    storage = torch.zeros((len(entries), max_requests + 1, *need.shape),
+                                          dtype=kind, device=self.device)
                 group = len(self.states)
                 self.states.append(StateGroup(need, tuple(entries),
                                               IndexPool(max_requests, "slot"), storage))
@@ -124,6 +126,12 @@ class CacheManager:
                 raise TypeError(f"cache entry {entries[0]} has an unknown need {need!r}")
         self._requests: dict[Any, RequestCache] = {}
         self._indices = IndexPool(max_requests, "request number")
+        # A page and a slot that no request ever gets, in every group. The step function points
+        # the filler entries there with which it rounds a step's shape up (so that steps of few
+        # distinct shapes can be replayed as CUDA graphs): what fillers write lands there and
+        # is never read by a request.
+        self.scratch_page = pages
+        self.scratch_slot = max_requests
 
     # ------------------------------------------------------------------ sizes
 

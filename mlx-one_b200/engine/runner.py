@@ -76,7 +76,9 @@ class Runner:
         self.last_meta_bytes = 0
         self.last_greedy: torch.Tensor | None = None
         # tokens chosen on the device, by request number (see StepEntry.from_device)
-        self.published = torch.zeros(cache.max_requests, dtype=torch.int32, device=self.device)
+        # (one entry more than there are requests: where filler rows publish theirs)
+        self.published = torch.zeros(cache.max_requests + 1, dtype=torch.int32,
+                                     device=self.device)
         # CUDA graphs of steps, keyed by shape (requests, tokens, table widths, wanted rows, ...)
         # (only models whose parts all say that they can be captured: see Part.capturable)
         self.use_graphs = self.device.type == "cuda" and model.capturable
@@ -85,13 +87,19 @@ class Runner:
         # steps with portions: captured at their third occurrence if they have at most this many
         # tokens (larger ones keep the GPU busy longer than the host needs to launch them)
         self.graph_token_limit = 1024
-        self.portion_graphs = 8
+        self.portion_graphs = 64
         self._portion_keys: list[tuple] = []
-        # decode-only shapes kept (least recently used ones are dropped beyond this), and one
-        # memory pool for all captures, so that graphs share their activations' memory
+        # Steps that may be captured have their shape rounded up with filler entries, so that
+        # the steps of a changing batch fall on few shapes: tokens to a multiple of
+        # ``token_bucket`` (16 up to 128 tokens), requests and wanted rows to a multiple of
+        # ``request_bucket`` (decode-only steps of up to that many requests stay as they are)
+        self.token_bucket = 64
+        self.request_bucket = 8
+        # decode-only shapes kept; the least recently used ones are dropped beyond this. (Every
+        # graph keeps a memory pool of its own: its logits stay valid until its next replay,
+        # whatever other graphs run in between.)
         self.decode_graphs = 48
         self._decode_keys: list[tuple] = []
-        self._graph_pool = torch.cuda.graph_pool_handle() if self.use_graphs else None
         if self.use_graphs:
             # library handles must exist before a capture begins
             warm = torch.zeros((8, 8), dtype=torch.bfloat16, device=self.device)
@@ -194,9 +202,16 @@ class Runner:
         # enough to be bound by the host's launches rather than by the GPU's work.
         portions = (self.use_graphs and not decode_only and loop is None
                     and tokens <= self.graph_token_limit)
+        fill_requests = fill_tokens = fill_wanted = 0
         if decode_only or portions:
             # few distinct widths, so that few graphs are captured
             widths = [max(1 << (w - 1).bit_length(), 32) for w in widths]
+        if self.use_graphs and loop is None and (decode_only or portions):
+            fill_requests, fill_tokens, fill_wanted = self._fill(requests, tokens, wanted,
+                                                                 decode_only)
+        real_requests, real_tokens, real_wanted = requests, tokens, wanted
+        requests, tokens, wanted = (requests + fill_requests, tokens + fill_tokens,
+                                    wanted + fill_wanted)
 
         # one packed int32 buffer: five per-token and per-request lists, block tables, slots
         offsets, cursor = {}, 0
@@ -217,14 +232,14 @@ class Runner:
         for g in range(len(states)):
             region(f"slots{g}", requests)
         if draw is not None:
-            if len(draw) != wanted or not wanted:
+            if len(draw) != real_wanted or not real_wanted:
                 raise ValueError("draw needs one entry per wanted row")
             # the sampling kernel's arguments, per wanted row: floats by their bits, the seed
             # as two 32-bit halves
             for name in ("draw_temperature", "draw_top_k", "draw_top_p", "draw_step"):
                 region(name, wanted)
             region("draw_seed", 2 * wanted)
-            self.ops.reserve_sample_scratch(self.cache.max_requests, vocab)
+            self.ops.reserve_sample_scratch(self.cache.max_requests + self.request_bucket, vocab)
         host = self._host_buffer(cursor)
         data = host.numpy()
         self.last_meta_bytes = 4 * cursor
@@ -252,7 +267,21 @@ class Runner:
             want_index.extend([cache.index] * len(entry.want))
             if entry.from_device:
                 data[source_at + first] = cache.index
+        # filler entries: requests without history whose pages and slot are the scratch ones;
+        # the first takes whatever tokens are left over, the others one each
+        for filler in range(fill_requests):
+            n = fill_tokens - (fill_requests - 1) if filler == 0 else 1
+            first = starts[-1]
+            data[ids_at + first:ids_at + first + n] = 0
+            data[positions_at + first:positions_at + first + n] = np.arange(n, dtype=np.int32)
+            data[request_at + first:request_at + first + n] = real_requests + filler
+            starts.append(first + n)
+            history.append(0)
+        # filler rows of logits: any valid token row; their tokens are published to the spare entry
+        rows.extend([0] * fill_wanted)
+        want_index.extend([self.cache.max_requests] * fill_wanted)
         if draw is not None:
+            draw = list(draw) + [(1.0, 0, 1.0, 0, 0)] * fill_wanted
             def view(name, kind):
                 start, size = offsets[name]
                 return data[start:start + size].view(kind)
@@ -268,11 +297,13 @@ class Runner:
         for g in range(len(paged)):
             start, size = offsets[f"table{g}"]
             table = data[start:start + size].reshape(requests, widths[g])
-            table[:] = -1
+            table[:real_requests] = -1
+            table[real_requests:] = self.cache.scratch_page
             for r, cache in enumerate(caches):
                 table[r, :len(cache.tables[g])] = cache.tables[g]
         for g in range(len(states)):
-            put(f"slots{g}", [c.slots[g] for c in caches])
+            put(f"slots{g}", [c.slots[g] for c in caches]
+                + [self.cache.scratch_slot] * fill_requests)
 
         device = self._device_buffer
         captured = None
@@ -346,10 +377,13 @@ class Runner:
         if captured is None:
             logits = run()
         else:
-            logits = self._run_captured(captured, run, eager_uses=2 if portions else 1)
+            logits = self._run_captured(captured, run)
         self.last_greedy = None
         if isinstance(logits, tuple):
             logits, self.last_greedy = logits
+            self.last_greedy = self.last_greedy[:real_wanted]
+        if logits is not None:
+            logits = logits[:real_wanted] if real_wanted else None
         for entry in entries:
             self.cache.advance(entry.request_id, len(entry.tokens))
         self.steps += 1
@@ -388,6 +422,30 @@ class Runner:
         self.last_shape = (len(entries), len(entries))
         return out
 
+    def _fill(self, requests: int, tokens: int, wanted: int, decode_only: bool):
+        """How many filler requests, tokens and wanted rows round this step's shape up to the
+        next bucket. A filler request brings at least one token."""
+        up = lambda value, to: -(-value // to) * to
+        bucket = self.request_bucket
+        if decode_only:
+            if requests <= bucket:
+                return 0, 0, 0
+            more = up(requests, bucket) - requests
+            return more, more, (up(wanted, bucket) - wanted if wanted else 0)
+        to_requests = up(requests, bucket)
+        step = self.token_bucket if tokens > 128 else 16
+        to_tokens = up(tokens, step)
+        if (to_requests > requests) != (to_tokens > tokens):
+            # fillers need tokens, and filler tokens need a request to belong to
+            if to_requests == requests:
+                to_requests += bucket
+            else:
+                to_tokens += step
+        while to_tokens - tokens < to_requests - requests:
+            to_tokens += step
+        return (to_requests - requests, to_tokens - tokens,
+                up(wanted, bucket) - wanted if wanted else 0)
+
     def _capture(self, run):
         """Records ``run`` into a CUDA graph; returns (graph, what run returned). A model whose
         parts all declare themselves capturable must be: a failure here is an error of a part
@@ -395,7 +453,7 @@ class Runner:
         graph = torch.cuda.CUDAGraph()
         torch.cuda.current_stream(self.device).synchronize()
         try:
-            with torch.cuda.graph(graph, pool=self._graph_pool):
+            with torch.cuda.graph(graph):
                 result = run()
         except Exception as error:
             torch.cuda.synchronize(self.device)

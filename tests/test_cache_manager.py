@@ -42,8 +42,11 @@ def test_layers_with_equal_needs_share_a_group():
     assert len(cache.paged) == 3 and len(cache.states) == 1
     assert cache.locate(1)[:2] == cache.locate(3)[:2] == ("paged", 0)
     assert cache.locate(4)[1] != cache.locate(1)[1]          # the window has pages of its own
-    assert cache.paged[0].storage.shape == (2, 2, 16, 2, 4, 16)
-    assert cache.states[0].storage.shape == (2, 4, 2, 8)
+    # 16 pages and 4 slots for requests, and the scratch page and slot that none of them gets
+    assert cache.paged[0].storage.shape == (2, 2, 16 + 1, 2, 4, 16)
+    assert cache.states[0].storage.shape == (2, 4 + 1, 2, 8)
+    assert cache.scratch_page == 16 and cache.scratch_slot == 4
+    assert cache.paged[0].pool.count == 16 and cache.states[0].pool.count == 4
 
 
 def test_grow_advance_close_and_window_release():

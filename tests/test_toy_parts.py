@@ -313,8 +313,9 @@ def test_capturable_toy_on_the_cpu(tmp_path, shift_registered):
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_capturable_toy_is_replayed_from_graphs(tmp_path, shift_registered, dtype):
     runner = run_shift(tmp_path, "cuda:0", dtype, None)
-    # the 41-token shape was met seven times (captured at the third), decode steps far more
-    assert runner.graph_replays >= 4 + 20
+    # the 41-token shape was met seven times (captured at its second occurrence, so replayed six
+    # times, four of them with another split), the decode shape a dozen times
+    assert runner.graph_replays >= 6 + 8
 
 
 @pytest.mark.gpu
