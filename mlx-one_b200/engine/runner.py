@@ -193,6 +193,9 @@ class Runner:
         requests = len(entries)
         tokens = sum(len(e.tokens) for e in entries)
         wanted = sum(len(e.want) for e in entries)
+        # the requests at the head of the step that bring a single token each (running decodes,
+        # as the scheduler orders a step): kernels may treat them apart from the portions
+        singles = next((i for i, e in enumerate(entries) if len(e.tokens) != 1), requests)
         caches = [self.cache.get(e.request_id) for e in entries]
         paged, states = self.cache.paged, self.cache.states
         widths = [_align(max(max(len(c.tables[g]) for c in caches), 1), 8)
@@ -202,16 +205,27 @@ class Runner:
         # enough to be bound by the host's launches rather than by the GPU's work.
         portions = (self.use_graphs and not decode_only and loop is None
                     and tokens <= self.graph_token_limit)
-        fill_requests = fill_tokens = fill_wanted = 0
+        fill_singles = fill_others = fill_tokens = fill_wanted = 0
         if decode_only or portions:
             # few distinct widths, so that few graphs are captured
             widths = [max(1 << (w - 1).bit_length(), 32) for w in widths]
         if self.use_graphs and loop is None and (decode_only or portions):
-            fill_requests, fill_tokens, fill_wanted = self._fill(requests, tokens, wanted,
-                                                                 decode_only)
-        real_requests, real_tokens, real_wanted = requests, tokens, wanted
-        requests, tokens, wanted = (requests + fill_requests, tokens + fill_tokens,
-                                    wanted + fill_wanted)
+            fill_singles, fill_others, fill_tokens, fill_wanted = self._fill(
+                singles, requests - singles, tokens - singles, wanted)
+        real_wanted = wanted
+        # the step as it is packed: real singles, filler singles, the other entries, other fillers
+        # (a filler is a request without history whose pages and slot are the scratch ones)
+        packed: list[tuple] = [(e, c, a) for e, c, a in
+                               zip(entries[:singles], caches[:singles], arrays[:singles])]
+        packed += [(None, None, 1)] * fill_singles
+        packed += [(e, c, a) for e, c, a in
+                   zip(entries[singles:], caches[singles:], arrays[singles:])]
+        for filler in range(fill_others):
+            packed.append((None, None, fill_tokens - (fill_others - 1) if filler == 0 else 1))
+        singles += fill_singles
+        requests += fill_singles + fill_others
+        tokens += fill_singles + fill_tokens
+        wanted += fill_wanted
 
         # one packed int32 buffer: five per-token and per-request lists, block tables, slots
         offsets, cursor = {}, 0
@@ -254,29 +268,38 @@ class Runner:
         ids_at = offsets["token_ids"][0]
         positions_at = offsets["positions"][0]
         request_at = offsets["token_request"][0]
-        for r, (entry, cache, ids) in enumerate(zip(entries, caches, arrays)):
-            n = len(ids)
+        tables = []
+        for g in range(len(paged)):
+            start, size = offsets[f"table{g}"]
+            tables.append(data[start:start + size].reshape(requests, widths[g]))
+        slot_lists: list[list[int]] = [[] for _ in states]
+        for r, (entry, cache, ids) in enumerate(packed):
             first = starts[-1]
-            data[ids_at + first:ids_at + first + n] = ids
+            if entry is None:                       # a filler with ``ids`` tokens
+                n, length = ids, 0
+                data[ids_at + first:ids_at + first + n] = 0
+                for g, table in enumerate(tables):
+                    table[r] = self.cache.scratch_page
+                for slots in slot_lists:
+                    slots.append(self.cache.scratch_slot)
+            else:
+                n, length = len(ids), cache.length
+                data[ids_at + first:ids_at + first + n] = ids
+                rows.extend(first + int(place) for place in entry.want)
+                want_index.extend([cache.index] * len(entry.want))
+                if entry.from_device:
+                    data[source_at + first] = cache.index
+                for g, table in enumerate(tables):
+                    held = cache.tables[g]
+                    table[r, :len(held)] = held
+                    table[r, len(held):] = -1
+                for g, slots in enumerate(slot_lists):
+                    slots.append(cache.slots[g])
             data[positions_at + first:positions_at + first + n] = np.arange(
-                cache.length, cache.length + n, dtype=np.int32)
+                length, length + n, dtype=np.int32)
             data[request_at + first:request_at + first + n] = r
             starts.append(first + n)
-            history.append(cache.length)
-            rows.extend(first + int(place) for place in entry.want)
-            want_index.extend([cache.index] * len(entry.want))
-            if entry.from_device:
-                data[source_at + first] = cache.index
-        # filler entries: requests without history whose pages and slot are the scratch ones;
-        # the first takes whatever tokens are left over, the others one each
-        for filler in range(fill_requests):
-            n = fill_tokens - (fill_requests - 1) if filler == 0 else 1
-            first = starts[-1]
-            data[ids_at + first:ids_at + first + n] = 0
-            data[positions_at + first:positions_at + first + n] = np.arange(n, dtype=np.int32)
-            data[request_at + first:request_at + first + n] = real_requests + filler
-            starts.append(first + n)
-            history.append(0)
+            history.append(length)
         # filler rows of logits: any valid token row; their tokens are published to the spare entry
         rows.extend([0] * fill_wanted)
         want_index.extend([self.cache.max_requests] * fill_wanted)
@@ -294,21 +317,13 @@ class Runner:
         put("request_start", starts)
         put("history", history)
         put("rows", rows if rows else [0])
-        for g in range(len(paged)):
-            start, size = offsets[f"table{g}"]
-            table = data[start:start + size].reshape(requests, widths[g])
-            table[:real_requests] = -1
-            table[real_requests:] = self.cache.scratch_page
-            for r, cache in enumerate(caches):
-                table[r, :len(cache.tables[g])] = cache.tables[g]
-        for g in range(len(states)):
-            put(f"slots{g}", [c.slots[g] for c in caches]
-                + [self.cache.scratch_slot] * fill_requests)
+        for g, slots in enumerate(slot_lists):
+            put(f"slots{g}", slots)
 
         device = self._device_buffer
         captured = None
         if decode_only or portions:
-            key = (requests, tokens, tuple(widths), wanted, loop is not None, greedy,
+            key = (requests, singles, tokens, tuple(widths), wanted, loop is not None, greedy,
                    draw is not None, any(e.from_device for e in entries))
             captured = self._graphs.get(key)
             if captured is None:
@@ -335,7 +350,7 @@ class Runner:
         views = {entry: self.cache.view(entry, tables, slots) for entry in self.model.cache_needs}
         if captured is None or not self.use_graphs:
             max_portion = max(len(e.tokens) for e in entries)
-            max_context = max(h + len(e.tokens) for h, e in zip(history, entries))
+            max_context = max(c.length + len(e.tokens) for c, e in zip(caches, entries))
             host = {"history": history, "request_start": starts}
         else:
             # bounds that hold for every step of this shape, however its tokens are split
@@ -349,7 +364,7 @@ class Runner:
             positions=on_device("positions"), token_request=on_device("token_request"),
             request_start=on_device("request_start"), history=on_device("history"),
             max_portion=max_portion, max_context=max_context, views=views, host=host,
-            replayable=captured is not None and self.use_graphs)
+            replayable=captured is not None and self.use_graphs, leading_single=singles)
 
         device_fed = any(e.from_device for e in entries)
 
@@ -422,29 +437,28 @@ class Runner:
         self.last_shape = (len(entries), len(entries))
         return out
 
-    def _fill(self, requests: int, tokens: int, wanted: int, decode_only: bool):
-        """How many filler requests, tokens and wanted rows round this step's shape up to the
-        next bucket. A filler request brings at least one token."""
+    def _fill(self, singles: int, others: int, other_tokens: int, wanted: int):
+        """Fillers that round a step's shape up to the next bucket: how many single-token
+        requests after the leading ones, how many other requests with how many tokens between
+        them, and how many wanted rows. ``singles``: leading requests that bring one token;
+        ``others``: the requests after them, with ``other_tokens`` tokens together. A filler
+        request brings at least one token, and filler tokens belong to a filler request. A
+        decode-only step of up to ``request_bucket`` requests stays as it is."""
         up = lambda value, to: -(-value // to) * to
         bucket = self.request_bucket
-        if decode_only:
-            if requests <= bucket:
-                return 0, 0, 0
-            more = up(requests, bucket) - requests
-            return more, more, (up(wanted, bucket) - wanted if wanted else 0)
-        to_requests = up(requests, bucket)
-        step = self.token_bucket if tokens > 128 else 16
-        to_tokens = up(tokens, step)
-        if (to_requests > requests) != (to_tokens > tokens):
-            # fillers need tokens, and filler tokens need a request to belong to
-            if to_requests == requests:
-                to_requests += bucket
-            else:
-                to_tokens += step
-        while to_tokens - tokens < to_requests - requests:
+        fill_wanted = up(wanted, bucket) - wanted if wanted else 0
+        if others == 0:
+            if singles <= bucket:
+                return 0, 0, 0, 0
+            return up(singles, bucket) - singles, 0, 0, fill_wanted
+        fill_singles = up(singles, bucket) - singles
+        step = self.token_bucket if other_tokens > 128 else 16
+        to_others, to_tokens = up(others, 2), up(other_tokens, step)
+        if to_tokens > other_tokens and to_others == others:
+            to_others += 2
+        while to_tokens - other_tokens < to_others - others:
             to_tokens += step
-        return (to_requests - requests, to_tokens - tokens,
-                up(wanted, bucket) - wanted if wanted else 0)
+        return fill_singles, to_others - others, to_tokens - other_tokens, fill_wanted
 
     def _capture(self, run):
         """Records ``run`` into a CUDA graph; returns (graph, what run returned). A model whose

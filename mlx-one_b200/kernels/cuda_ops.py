@@ -72,6 +72,9 @@ class CudaOps:
         # (8 x 4096 keys 16.5 us against 17.9 us), inside the decode step slower (0.728 ms a step
         # against 0.717 ms)
         self.cluster_merge = False
+        # a mixed step's leading single-token requests go to the decode attention kernel when
+        # there are at least this many of them
+        self.split_singles_from = 1
         self.tcgen05_always = False       # tests: take the tcgen05 kernel whenever it can run
         self._sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
         # tcgen05 products (TMA + tensor memory) for more rows than the skinny kernel takes
@@ -452,38 +455,39 @@ class CudaOps:
         code = _dtype_code(q.dtype)
         if self.tensor_core_attention and self.lib.mlxone_attention_mma_supports(head_dim, code):
             if ctx.max_portion == 1 and tokens == ctx.requests:
-                splits = self.decode_splits(ctx.requests, heads, kv_heads, head_dim,
-                                            width * view.page_size, window)
-                if self.cluster_merge and 8 < splits <= 12 and width * view.page_size <= 8192:
-                    splits = 8          # with more keys a ninth split is worth more than the merge kernel
-                partial = None
-                if splits > 8 or (splits > 1 and not self.cluster_merge):
-                    partial = torch.empty(ctx.requests * heads * splits * (head_dim + 2),
-                                          dtype=torch.float32, device=self.device)
-                self._call("mlxone_attention_decode", _c_void_p(_ptr(q)), _c_void_p(_ptr(view.kv)),
-                           _c_void_p(_ptr(view.block_table)), _c_int(width),
-                           _c_int(view.page_size), _c_int(pages), _c_void_p(_ptr(ctx.positions)),
-                           _c_void_p(_ptr(out)), _c_void_p(_ptr(partial)), _c_int(ctx.requests),
-                           _c_int(heads), _c_int(kv_heads), _c_int(head_dim), _c_int(splits),
-                           _c_float(scale), _c_int(window or 0))
-                if partial is not None:
-                    self.launches += 1          # the merge kernel
-            elif (self.tcgen05_attention and q.dtype == torch.bfloat16
-                  and self.lib.mlxone_attention_tcgen05_supports(
-                      _c_int(head_dim), _c_int(heads), _c_int(kv_heads), _c_int(view.page_size))):
+                self._decode_attention(q, out, ctx.requests, heads, kv_heads, head_dim, scale,
+                                       window, ctx, view)
+                return out
+            # The decodes at the head of a mixed step go to the split-key kernel, which reads
+            # each request's keys once for all its query heads; as one-token portions in the
+            # prefill kernel they would each fill a tile of 64 or 128 query rows with one row.
+            singles = min(getattr(ctx, "leading_single", 0), ctx.requests)
+            if singles < self.split_singles_from:
+                singles = 0
+            if singles:
+                self._decode_attention(q, out, singles, heads, kv_heads, head_dim, scale, window,
+                                       ctx, view)
+            # the other requests: the tables, starts and histories from request ``singles`` on
+            # (token numbers in request_start stay those of the whole step)
+            rest = ctx.requests - singles
+            table = view.block_table[singles:]
+            starts, history = ctx.request_start[singles:], ctx.history[singles:]
+            if (self.tcgen05_attention and q.dtype == torch.bfloat16
+                    and self.lib.mlxone_attention_tcgen05_supports(
+                        _c_int(head_dim), _c_int(heads), _c_int(kv_heads), _c_int(view.page_size))):
                 self._call("mlxone_attention_prefill_tcgen05", _c_void_p(_ptr(q)),
-                           _c_void_p(_ptr(view.kv)), _c_void_p(_ptr(view.block_table)),
+                           _c_void_p(_ptr(view.kv)), _c_void_p(_ptr(table)),
                            _c_int(width), _c_int(view.page_size), _c_int(pages),
-                           _c_void_p(_ptr(ctx.request_start)), _c_void_p(_ptr(ctx.history)),
-                           _c_void_p(_ptr(out)), _c_int(tokens), _c_int(ctx.requests),
+                           _c_void_p(_ptr(starts)), _c_void_p(_ptr(history)),
+                           _c_void_p(_ptr(out)), _c_int(tokens), _c_int(rest),
                            _c_int(heads), _c_int(kv_heads), _c_int(head_dim), _c_float(scale),
                            _c_int(window or 0), _c_void_p(_ptr(self.error_flag)))
             else:
                 self._call("mlxone_attention_prefill", _c_void_p(_ptr(q)),
-                           _c_void_p(_ptr(view.kv)), _c_void_p(_ptr(view.block_table)),
+                           _c_void_p(_ptr(view.kv)), _c_void_p(_ptr(table)),
                            _c_int(width), _c_int(view.page_size), _c_int(pages),
-                           _c_void_p(_ptr(ctx.request_start)), _c_void_p(_ptr(ctx.history)),
-                           _c_void_p(_ptr(out)), _c_int(tokens), _c_int(ctx.requests),
+                           _c_void_p(_ptr(starts)), _c_void_p(_ptr(history)),
+                           _c_void_p(_ptr(out)), _c_int(tokens), _c_int(rest),
                            _c_int(heads), _c_int(kv_heads), _c_int(head_dim), _c_float(scale),
                            _c_int(window or 0))
             return out
@@ -495,6 +499,27 @@ class CudaOps:
                    _c_int(head_dim), _c_float(scale), _c_int(window or 0),
                    _c_int(code), _c_void_p(_ptr(self.error_flag)))
         return out
+
+    def _decode_attention(self, q, out, requests, heads, kv_heads, head_dim, scale, window, ctx,
+                          view) -> None:
+        """The split-key kernel for the first ``requests`` requests of the step, one token each
+        (token i is request i's): rows 0 to requests - 1 of q, positions, table and out."""
+        width = view.block_table.shape[1]
+        splits = self.decode_splits(requests, heads, kv_heads, head_dim, width * view.page_size,
+                                    window)
+        if self.cluster_merge and 8 < splits <= 12 and width * view.page_size <= 8192:
+            splits = 8          # with more keys a ninth split is worth more than the merge kernel
+        partial = None
+        if splits > 8 or (splits > 1 and not self.cluster_merge):
+            partial = torch.empty(requests * heads * splits * (head_dim + 2),
+                                  dtype=torch.float32, device=self.device)
+        self._call("mlxone_attention_decode", _c_void_p(_ptr(q)), _c_void_p(_ptr(view.kv)),
+                   _c_void_p(_ptr(view.block_table)), _c_int(width), _c_int(view.page_size),
+                   _c_int(view.kv.shape[1]), _c_void_p(_ptr(ctx.positions)), _c_void_p(_ptr(out)),
+                   _c_void_p(_ptr(partial)), _c_int(requests), _c_int(heads), _c_int(kv_heads),
+                   _c_int(head_dim), _c_int(splits), _c_float(scale), _c_int(window or 0))
+        if partial is not None:
+            self.launches += 1          # the merge kernel
 
     def decode_splits(self, requests: int, heads: int, kv_heads: int, head_dim: int,
                       context_bound: int, window: int | None) -> int:

@@ -99,6 +99,11 @@ class StepContext:
     # host copies of ``history`` and ``request_start`` (lists), for parts that are not capturable
     host: Mapping[str, Any] = field(default_factory=dict)
     replayable: bool = False
+    # The first ``leading_single`` requests bring exactly one token each (token i is request
+    # i's): the decodes at the head of a step. A host value that is part of a captured step's
+    # shape, so it holds for every replay. A mixer may give these tokens to a kernel made for
+    # single tokens and the rest to another.
+    leading_single: int = 0
 
 
 class NoHostValues(Mapping):

@@ -338,20 +338,28 @@ def test_hidden_states_can_be_watched_layer_by_layer(models):
 
 
 def test_shapes_are_rounded_up_with_fillers_that_have_tokens(models):
-    """The rule by which a step's shape is rounded up for CUDA graphs: requests and wanted rows
-    to a multiple of 8, tokens to a multiple of 64 (16 up to 128 tokens); a filler request has
-    at least one token, filler tokens belong to a filler request, and a decode-only step stays
-    decode-only (small ones stay as they are)."""
+    """The rule by which a step's shape is rounded up for CUDA graphs: the leading single-token
+    requests and the wanted rows to a multiple of 8, the other requests to a multiple of 2 and
+    their tokens to a multiple of 64 (16 up to 128 tokens); a filler request has at least one
+    token, filler tokens belong to a filler request, and a decode-only step stays decode-only
+    (small ones stay as they are)."""
     folder, loaded, plain = models["A"]
     runner, cache = runner_for(loaded, 4, 64)
-    for requests in range(1, 70):
-        for tokens in list(range(requests + 1, requests + 40)) + [requests + 200, requests + 511]:
-            for wanted in (0, 1, requests):
-                more_r, more_t, more_w = runner._fill(requests, tokens, wanted, False)
-                assert (requests + more_r) % 8 == 0 and (wanted + more_w) % 8 == 0
-                assert (tokens + more_t) % (64 if tokens > 128 else 16) == 0
-                assert more_t >= more_r >= 0 and (more_r > 0) == (more_t > 0)
-                assert more_t < 2 * 64 + 8 and (wanted > 0 or more_w == 0)
-        more_r, more_t, more_w = runner._fill(requests, requests, requests, True)
-        assert more_r == more_t and (requests + more_r) % 8 == 0 or requests <= 8 and more_r == 0
-        assert (requests + more_w) % 8 == 0 or requests <= 8
+    for singles in (0, 1, 7, 8, 9, 63):
+        for others in (1, 2, 3, 5):
+            for other_tokens in list(range(others, others + 40)) + [others + 200, others + 511]:
+                for wanted in (0, 1, singles + others):
+                    more_s, more_o, more_t, more_w = runner._fill(singles, others, other_tokens,
+                                                                  wanted)
+                    assert (singles + more_s) % 8 == 0 and (wanted + more_w) % 8 == 0
+                    assert (others + more_o) % 2 == 0
+                    assert (other_tokens + more_t) % (64 if other_tokens > 128 else 16) == 0
+                    assert more_t >= more_o >= 0 and (more_o > 0) == (more_t > 0)
+                    assert more_t < 2 * 64 and (wanted > 0 or more_w == 0)
+    for singles in range(1, 70):
+        more_s, more_o, more_t, more_w = runner._fill(singles, 0, 0, singles)
+        assert more_o == more_t == 0
+        if singles <= 8:
+            assert more_s == more_w == 0
+        else:
+            assert (singles + more_s) % 8 == 0 and (singles + more_w) % 8 == 0
