@@ -315,11 +315,12 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q,
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    // stages start as zeros: a page that is skipped must not show what shared memory held
+    // query buffers and stages start as zeros: a page that is skipped, and the query rows beyond
+    // a group that does not divide ROWS, must not show what shared memory held
     {
-        uint4* stage_words = reinterpret_cast<uint4*>(generic_base + Q_BUFFERS * Q_BYTES);
-        for (int i = threadIdx.x; i < STAGES * STAGE_BYTES / 16; i += THREADS)
-            stage_words[i] = make_uint4(0u, 0u, 0u, 0u);
+        uint4* words = reinterpret_cast<uint4*>(generic_base);
+        for (int i = threadIdx.x; i < (Q_BUFFERS * Q_BYTES + STAGES * STAGE_BYTES) / 16; i += THREADS)
+            words[i] = make_uint4(0u, 0u, 0u, 0u);
         fence_async_shared();
     }
     if (warp == MMA_WARP) tmem_alloc(shared_address(&tmem_base_slot), TMEM_COLUMNS);
@@ -346,7 +347,9 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q,
                 const int qb = taken % Q_BUFFERS;
                 ok = barrier_wait(q_empty(qb), ((taken / Q_BUFFERS) & 1) ^ 1, error_flag);
                 if (ok) {
-                    barrier_expect(q_full(qb), Q_BYTES);
+                    // the box holds tile_tokens x group rows: all ROWS, or a few less when the
+                    // group does not divide them (those rows stay zero and are never stored)
+                    barrier_expect(q_full(qb), (uint32_t)(tile_tokens * group) * HD * 2u);
                     tma_load_3d(q_tiles + qb * Q_BYTES, &map_q, 0, item.kv_head * group,
                                 item.q_token, q_full(qb));
                 }
@@ -629,7 +632,7 @@ bool find_encoder() {
 bool supported(int head_dim, int heads, int kv_heads, int page_size) {
     if (head_dim != HD || kv_heads <= 0 || heads % kv_heads != 0) return false;
     const int group = heads / kv_heads;
-    if (group > ROWS || ROWS % group != 0) return false;
+    if (group > ROWS) return false;          // (a group that does not divide the rows leaves some unused)
     if (page_size < 8 || page_size % 8 != 0) return false;
     // pages divide a tile of 64 keys (and so one of 128), or are whole tiles
     return page_size <= 64 ? 64 % page_size == 0 : page_size % 128 == 0;

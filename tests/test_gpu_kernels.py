@@ -462,7 +462,8 @@ def test_attention_decode_tensor_cores(ops, plain, heads, kv_heads, head_dim, pa
 
 
 @pytest.mark.parametrize("heads,kv_heads,page_size", [
-    (8, 8, 16), (32, 8, 16), (4, 2, 8), (16, 2, 64), (3, 3, 128), (8, 1, 256), (64, 1, 32)])
+    (8, 8, 16), (32, 8, 16), (4, 2, 8), (16, 2, 64), (3, 3, 128), (8, 1, 256), (64, 1, 32),
+    (24, 8, 16), (6, 2, 8), (5, 1, 64), (7, 1, 16)])       # groups of 3, 5, 7 do not divide 128 rows
 @pytest.mark.parametrize("window", [None, 37, 128, 300])
 def test_attention_prefill_tcgen05(ops, plain, heads, kv_heads, page_size, window):
     """The tcgen05 kernel (head size 64): query heads of a group stacked in one block; portions
@@ -477,7 +478,8 @@ def test_attention_prefill_tcgen05(ops, plain, heads, kv_heads, page_size, windo
     assert ops.launches - before == 1
 
 
-@pytest.mark.parametrize("heads,kv_heads,page_size", [(32, 8, 16), (8, 4, 8), (6, 6, 64)])
+@pytest.mark.parametrize("heads,kv_heads,page_size", [(32, 8, 16), (8, 4, 8), (6, 6, 64),
+                                                      (24, 8, 16)])
 @pytest.mark.parametrize("window", [None, 300])
 def test_attention_prefill_tcgen05_many_items(ops, plain, heads, kv_heads, page_size, window):
     """So many tokens that the kernel takes its shape with tiles of 64 keys and two blocks an
