@@ -703,6 +703,27 @@ def kernel_case(name: str, batch: int, context: int) -> int:
         w = weights(2 * width, hidden, 2)
         run = lambda i: ops.linear_swiglu(a, w[i % 2])
         work = f"{2 * PREFILL_TOKENS * 2 * width * hidden / 1e9:.1f} GFLOP"
+    elif name == "swapped_swiglu":
+        # the 33-to-128-row product with swapped operands (an option, off by default) on w13
+        rows = max(batch, 33)
+        a = torch.randn(rows, hidden, device=device).bfloat16()
+        w = weights(2 * width, hidden, 4)
+        ops.swapped_products = True
+        run = lambda i: ops.linear_swiglu(a, w[i % 4])
+        work = f"{2 * width * hidden * 2 / 1e6:.1f} MB of weights, {rows} rows"
+    elif name == "mixed_attention":
+        # attention of a mixed step at the LFM2-700M geometry (24 heads over 8 key heads): 63
+        # decodes at `context` keys beside one 512-token portion after 1024 tokens
+        heads, kv_heads = 24, 8
+        singles = 63
+        ctx, view = batch_context([1] * singles + [512], [context - 1] * singles + [1024])
+        ctx.leading_single = singles
+        q = torch.randn(singles + 512, heads, head_dim, device=device).bfloat16()
+        run = lambda i: ops.paged_attention(q, heads=heads, kv_heads=kv_heads, head_dim=head_dim,
+                                            scale=head_dim ** -0.5, window=None, ctx=ctx, view=view)
+        work = (f"{singles} single tokens over {context} keys "
+                f"({singles * context * 2 * kv_heads * head_dim * 2 / 1e6:.1f} MB) + 512 tokens "
+                f"after 1024")
     elif name == "sampling":
         vocab = LFM2_1_2B["vocab_size"]
         logits = [torch.randn(batch, vocab, device=device) * 3 for _ in range(4)]
@@ -820,7 +841,7 @@ def main() -> int:
     parser.add_argument("--kernel", default=None,
                         help="run one kernel alone instead of the benchmark: skinny_swiglu, "
                              "skinny_down, decode_attention, prefill_attention, tcgen05_swiglu, "
-                             "sampling")
+                             "swapped_swiglu, mixed_attention, sampling")
     parser.add_argument("--dependent-launches", type=int, default=1,
                         help="1: kernels of a decode step may start while the one before ends")
     args = parser.parse_args()
