@@ -24,8 +24,7 @@ from ..cache.manager import CacheManager
 from ..sampling.options import GenerationChunk, GenerationResult, TextGenerationOptions
 from .loading import LoadedModel, load_model
 from .runner import Runner, StepEntry
-from .scheduler import (BatchingConfig, Phase, Request, RequestTimeoutError, Scheduled,
-                        Scheduler)
+from .scheduler import (PENDING, BatchingConfig, Phase, Request, RequestTimeoutError, Scheduler)
 
 
 @dataclass(frozen=True)
@@ -272,11 +271,12 @@ class Engine:
         """One scheduler turn. Returns the requests that got a token or finished.
 
         A step is planned, launched, its chosen tokens are copied to pinned host memory, and
-        committed when that copy has landed. While every running request decodes
-        (``pipeline_decode``), the next step is launched before the last one is committed: its
-        input tokens are the ones the device has just chosen, so the host's bookkeeping runs
-        under the GPU's work. A request then learns of its end-of-sequence token one step
-        late; the extra token computed for it is dropped.
+        committed when that copy has landed. With ``pipeline_decode`` the next step (decodes,
+        prompt portions, newly admitted requests) is launched before the last one is
+        committed: a decode whose token is not known yet takes it on the device, where it was
+        chosen, so the host's planning and bookkeeping run under the GPU's work. A request
+        then learns of its end-of-sequence token one step late; the extra token computed for
+        it is dropped.
 
         Turns exclude one another, so that several threads (``async_generate`` runs each
         request's wait on a thread of its own) may drive the loop: whichever holds the turn
@@ -334,67 +334,62 @@ class Engine:
                 self._stepped.wait(0.005)
 
     def _step(self) -> list[Request]:
+        """Plans and launches the next step, then commits the step that was in flight. The
+        scheduler is told of a launch at once (``advance``: prompts move on, drawn tokens count
+        as pending), so the next step can be planned while the tokens of the last one are still
+        on their way; a decode whose token is pending takes it on the device."""
         previous = self._inflight
-        if previous is not None:
-            self._inflight = self._launch_ahead(previous)
-            return self._finish(previous)     # a kernel fault found there drops the new one too
-        planned = self._scheduler.plan()
-        if not planned:
-            return []
-        launched = self._launch(planned)
-        if self.batching_config.pipeline_decode and launched.chosen_on_device:
-            self._inflight = launched
-            return []
-        return self._finish(launched)
+        launched = None
+        if previous is None or self._may_run_ahead():
+            planned = self._scheduler.plan()
+            if planned:
+                launched = self._launch(planned, ahead=previous is not None)
+                self._scheduler.advance(planned)
+        self._inflight = launched          # (a kernel fault found in `previous` drops it too)
+        touched = self._finish(previous) if previous is not None else []
+        launched = self._inflight
+        if launched is not None and not self.batching_config.pipeline_decode:
+            self._inflight = None
+            touched += self._finish(launched)
+        return touched
 
-    def _launch(self, planned, entries=None, ahead: int = 0) -> "_InFlight":
+    def _may_run_ahead(self) -> bool:
+        """Whether the next step may be planned before the tokens of the step in flight are
+        known: not while a running request has stop strings, whose match must end the request
+        before anything else is run for it."""
+        if not self.batching_config.pipeline_decode:
+            return False
+        return not any(r.options.stop for r in self._scheduler.running)
+
+    def _launch(self, planned, ahead: bool = False) -> "_InFlight":
         """Launches a step; the tokens of the requests that draw one are chosen on the device
         inside it (argmax, or the sampling kernel with each request's options, seed and count
-        of tokens drawn so far; ``ahead``: tokens drawn but not yet committed)."""
+        of tokens drawn so far, pending ones included)."""
         started = time.perf_counter()
-        if entries is None:
-            entries = [StepEntry(item.request.request_id, item.tokens,
-                                 (len(item.tokens) - 1,) if item.samples else ())
-                       for item in planned]
+        entries = []
+        for item in planned:
+            want = (len(item.tokens) - 1,) if item.samples else ()
+            if item.tokens[0] == PENDING:
+                entries.append(StepEntry(item.request.request_id, (0,), want, from_device=True))
+            else:
+                entries.append(StepEntry(item.request.request_id, item.tokens, want))
         drawing = [item.request for item in planned if item.samples]
         greedy = bool(drawing) and all(r.options.temperature == 0 for r in drawing)
         draw = None
         if drawing and not greedy:
             draw = [(r.options.temperature, r.options.top_k or 0, r.options.top_p, r.options.seed,
-                     len(r.output) + ahead) for r in drawing]
+                     len(r.output) + r.pending) for r in drawing]
         self._runner.step(entries, greedy=greedy, draw=draw)
         host = event = None
         if drawing:
             host, event = self._start_copy(self._runner.last_greedy)
         self._stats["steps"] += 1
+        self._stats["steps_ahead"] += 1 if ahead else 0
         self._stats["tokens_run"] += sum(len(item.tokens) for item in planned)
-        # a step launched ahead holds decode tokens only (a request whose last portion is not
-        # committed yet still counts as being in its prompt)
-        prompt_tokens = 0 if ahead else sum(len(item.tokens) for item in planned
-                                            if item.request.phase is Phase.PREFILL)
+        prompt_tokens = sum(len(item.tokens) for item in planned
+                            if item.request.phase is Phase.PREFILL)
         return _InFlight(list(planned), host, event, len(drawing), bool(drawing),
-                         launched_at=started, ahead=ahead > 0, prompt_tokens=prompt_tokens)
-
-    def _launch_ahead(self, previous: "_InFlight"):
-        """The step after ``previous``, launched before ``previous`` is committed, or None if
-        it cannot be known yet what that step will be."""
-        scheduler = self._scheduler
-        if not (self.batching_config.pipeline_decode and previous.chosen_on_device) or scheduler.waiting:
-            return None
-        drew = {id(item.request) for item in previous.planned if item.samples}
-        running = scheduler.running
-        if any(id(r) not in drew or r.cancelled or r.options.stop for r in running):
-            return None          # a prompt still in portions, decodes taking turns, a cancel
-        now = scheduler.clock()
-        if any(r.deadline is not None and now >= r.deadline for r in running):
-            return None          # a request's time is up: the next plan ends it
-        going_on = [r for r in running if len(r.output) + 1 < r.options.max_tokens]
-        if not going_on or len(going_on) > self.batching_config.max_scheduled_tokens:
-            return None
-        planned = [Scheduled(r, (0,), True) for r in going_on]
-        entries = [StepEntry(r.request_id, (0,), (0,), from_device=True) for r in going_on]
-        self._stats["steps_ahead"] += 1
-        return self._launch(planned, entries, ahead=1)
+                         launched_at=started, ahead=ahead, prompt_tokens=prompt_tokens)
 
     def _finish(self, inflight: "_InFlight") -> list[Request]:
         sampled: list[int] = []
@@ -406,18 +401,8 @@ class Engine:
             if code:
                 return self._kernel_fault(code, inflight)
         planned = inflight.planned
-        if any(item.request.phase is Phase.FINISHED for item in planned):
-            # launched ahead for a request that has ended meanwhile: its token is dropped
-            kept, tokens, drawn = [], [], iter(sampled)
-            for item in planned:
-                token = next(drawn) if item.samples else None
-                if item.request.phase is Phase.FINISHED:
-                    continue
-                kept.append(item)
-                if item.samples:
-                    tokens.append(token)
-            planned, sampled = kept, tokens
-        touched = self._scheduler.commit(planned, sampled, stop_at=self._stop_at)
+        # (a request that has ended since this step was launched drops its token there)
+        touched = self._scheduler.resolve(planned, sampled, stop_at=self._stop_at)
         now = time.perf_counter()
         self._trace(inflight, now)
         for request in touched:

@@ -45,9 +45,9 @@ class BatchingConfig:
     # seconds from its submission after which a request that has not finished is ended with
     # RequestTimeoutError; 0: never
     timeout: float = 600.0
-    # not in the reference: while all running requests decode, launch the next step (its input
-    # tokens taken on the device, where they were chosen) before the last step's tokens are read
-    # back
+    # not in the reference: launch the next step (the tokens that the step before it has just
+    # chosen are taken on the device, where they were chosen) before that step's tokens have been
+    # read back, so that the host's planning and bookkeeping run under the GPU's work
     pipeline_decode: bool = True
     # True: the engine owns a thread that drives the loop while requests are waiting or running,
     # as the reference's actor thread does (src/mlx_one/engine/actor.py:402-525); callers then
@@ -74,6 +74,10 @@ class RequestTimeoutError(RuntimeError):
     (the reference's RequestTimeoutError, src/mlx_one/engine/actor.py:429-438)."""
 
 
+# the token of a decode whose value is still on the device (chosen by a step that is in flight)
+PENDING = -1
+
+
 class Phase(enum.Enum):
     WAITING = "waiting"
     PREFILL = "prefill"
@@ -96,6 +100,7 @@ class Request:
     cancelled: bool = False
     deadline: float | None = None                    # on the scheduler's clock; None: none
     error: BaseException | None = None               # why finish_reason is "error"
+    pending: int = 0                                 # tokens drawn by steps whose result is not in yet
 
     @property
     def reserve_tokens(self) -> int:
@@ -186,7 +191,9 @@ class Scheduler:
         config = self.config
         budget = config.max_scheduled_tokens
         step: list[Scheduled] = []
-        decodes = [r for r in self.running if r.phase is Phase.DECODE]
+        # (a request whose last token is being drawn by a step in flight has nothing to run)
+        decodes = [r for r in self.running if r.phase is Phase.DECODE
+                   and len(r.output) + r.pending < r.options.max_tokens]
         prefills = [r for r in self.running if r.phase is Phase.PREFILL]
         if decodes and prefills:
             # decodes must not starve prompts: room is kept for a portion of the oldest one,
@@ -206,7 +213,8 @@ class Scheduler:
             decodes = (decodes[start:] + decodes[:start])[:budget_for_decodes]
             self._decode_turn += budget_for_decodes
         for request in decodes:
-            step.append(Scheduled(request, (request.next_token,), True))
+            token = PENDING if request.pending else request.next_token
+            step.append(Scheduled(request, (token,), True))
         budget -= len(decodes)
         prefill_budget = min(budget, config.max_prefill_tokens)
         for request in self.running:
@@ -220,22 +228,37 @@ class Scheduler:
             prefill_budget -= size
         return step
 
-    def commit(self, step: Sequence[Scheduled], sampled: Sequence[int],
-               stop_at=None) -> list[Request]:
-        """Records a finished step: ``sampled`` has one token per entry with ``samples``.
-        Returns the requests that produced a token or finished. ``stop_at(request, token)`` is
-        asked for every drawn token of a request that has stop strings: None lets the token in;
-        a count means that the text with this token contains a stop string, and the request
-        ends with reason "stop" holding only that many of its tokens (those before the match)."""
-        touched, drawn = [], iter(sampled)
+    def advance(self, step: Sequence[Scheduled]) -> None:
+        """Records that ``step`` has been launched: prompts move on by their portions, requests
+        that draw a token in it count that token as pending. The next step can be planned from
+        this before the step's tokens are known."""
         for item in step:
             request = item.request
             if request.phase is Phase.PREFILL:
                 request.fed += len(item.tokens)
+            if item.samples:
+                request.phase = Phase.DECODE
+                request.pending += 1
+
+    def resolve(self, step: Sequence[Scheduled], sampled: Sequence[int],
+                stop_at=None) -> list[Request]:
+        """Records the tokens that an advanced step drew: ``sampled`` has one token per entry
+        with ``samples``. Returns the requests that produced a token or finished. A request
+        that has ended since the step was launched (cancelled, timed out, or ended by an earlier
+        step's token that was read after this step's launch) drops its token.
+        ``stop_at(request, token)`` is asked for every drawn token of a request that has stop
+        strings: None lets the token in; a count means that the text with this token contains a
+        stop string, and the request ends with reason "stop" holding only that many of its
+        tokens (those before the match)."""
+        touched, drawn = [], iter(sampled)
+        for item in step:
             if not item.samples:
                 continue
             token = int(next(drawn))
-            request.phase = Phase.DECODE
+            request = item.request
+            if request.phase is Phase.FINISHED:
+                continue
+            request.pending -= 1
             touched.append(request)
             if token in request.eos_token_ids and not request.options.ignore_eos:
                 request.terminal_token_id = token
@@ -253,6 +276,13 @@ class Scheduler:
                 self._finish(request, "length")
         return touched
 
+    def commit(self, step: Sequence[Scheduled], sampled: Sequence[int],
+               stop_at=None) -> list[Request]:
+        """``advance`` and ``resolve`` in one: a step whose tokens are known before the next
+        step is planned."""
+        self.advance(step)
+        return self.resolve(step, sampled, stop_at)
+
     def fail(self, requests: Sequence[Request], error: BaseException) -> None:
         """Ends requests whose step could not be trusted (a kernel reported a fault, the step
         raised): their pages come back and whoever waits for them is given ``error``."""
@@ -269,6 +299,7 @@ class Scheduler:
         request.finish_reason = reason
         request.phase = Phase.FINISHED
         request.next_token = None
+        request.pending = 0
         if request in self.running:
             self.running.remove(request)
         if held and request.request_id in self.cache:

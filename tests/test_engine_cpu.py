@@ -304,7 +304,12 @@ def test_every_step_leaves_a_record(models):
     assert records[0]["phase"] == "prefill" and records[0]["tokens"] <= 16
     assert any(r["phase"] == "mixed" for r in records)       # a decode beside a prompt portion
     assert records[-1]["phase"] == "decode" and records[-1]["prompt_tokens"] == 0
-    assert any(r["launched_ahead"] for r in records)
+    # every step but the first is launched while the one before it is still in flight, steps
+    # with prompt portions too
+    assert all(r["launched_ahead"] for r in records[1:]) and not records[0]["launched_ahead"]
+    assert any(r["launched_ahead"] and r["phase"] == "mixed" for r in records)
+    for prompt, result in zip((first, second), results):
+        assert list(result.token_ids) == plain.greedy(prompt, 4)
     assert all(r["duration_s"] >= 0 and r["batch_size"] == len(r["request_ids"]) for r in records)
     assert engine.runtime_stats()["steps_committed"] == len(records)
 

@@ -204,3 +204,48 @@ def test_a_request_whose_time_is_up_ends_and_frees_its_pages():
     patient = request(never, 5)
     never.submit(patient)
     assert patient.deadline is None
+
+
+def test_a_step_can_be_planned_before_the_last_one_is_resolved():
+    """``advance`` tells the scheduler that a step was launched; the next plan then holds
+    decodes whose token is still pending, and prompt portions that follow on. ``resolve`` brings
+    the tokens later: a request that an earlier token has ended drops the token that a later
+    step drew for it, and a request that is drawing its last token is not planned again."""
+    from mlx_one_b200.engine.scheduler import PENDING
+
+    scheduler, cache = make(max_scheduled_tokens=32, max_prefill_tokens=24, prefill_chunk_size=16)
+    a = request(scheduler, 3, max_tokens=3, eos=(7,))
+    b = request(scheduler, 20, max_tokens=2)
+    scheduler.submit(a)
+    scheduler.submit(b)
+
+    def launch():
+        step = scheduler.plan()
+        for item in step:
+            cache.grow(item.request.request_id, len(item.tokens))
+            cache.advance(item.request.request_id, len(item.tokens))
+        scheduler.advance(step)
+        return step
+
+    first = launch()                                  # a's whole prompt (draws), 16 tokens of b
+    assert [(s.request, len(s.tokens), s.samples) for s in first] == [(a, 3, True), (b, 16, False)]
+    assert a.pending == 1 and a.phase is Phase.DECODE and b.fed == 16
+    second = launch()                                 # planned before a's first token is known
+    assert [(s.request, s.tokens, s.samples) for s in second] == \
+        [(a, (PENDING,), True), (b, tuple(range(17, 21)), True)]
+    assert a.pending == 2 and b.pending == 1
+    assert scheduler.resolve(first, [5]) == [a] and a.output == [5] and a.pending == 1
+    third = launch()                                  # a draws its third (last) token; b decodes
+    assert [(s.request, s.tokens) for s in third] == [(a, (PENDING,)), (b, (PENDING,))]
+    assert scheduler.plan() == []                     # both are drawing their last tokens
+    # the second step's token for a is the end-of-sequence token: a ends, b goes on
+    touched = scheduler.resolve(second, [7, 9])
+    assert touched == [a, b] and a.phase is Phase.FINISHED and a.finish_reason == "stop"
+    assert a.output == [5] and a.terminal_token_id == 7 and b.output == [9]
+    assert a.request_id not in cache                  # its pages are back
+    # the third step's token for a is dropped; b's second token ends it by length
+    touched = scheduler.resolve(third, [11, 12])
+    assert touched == [b] and a.output == [5] and b.output == [9, 12]
+    assert b.finish_reason == "length" and not scheduler.has_work()
+    cache.check()
+    assert not cache.requests()
