@@ -475,7 +475,10 @@ def case_batching(args) -> int:
                                                     / max(len(records), 1), 3),
                         "by_phase": phases, "tokens_per_step": histogram,
                         "pages_low_water": stats["pages_low_water"][0],
-                        "pages_total": stats["pages_total"][0]})
+                        "pages_total": stats["pages_total"][0],
+                        "graphs_kept": stats["graphs"], "graph_captures_so_far":
+                            stats["graph_captures"],
+                        "device_memory_gb": round(torch.cuda.memory_reserved() / 1e9, 2)})
     measured = sorted(samples[1:], key=lambda sample: sample["seconds"])
     middle = measured[len(measured) // 2]
     line = {

@@ -378,6 +378,7 @@ typedef CUresult (*EncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, v
                                 const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                 CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 EncodeTiled g_encode = nullptr;
+int g_tile_choice = 0;
 int g_sm_count = 0;
 
 bool find_encoder() {
@@ -439,6 +440,9 @@ int launch(const void* a, int lda, const void* w, const float* bias, void* out, 
 
 }  // namespace
 
+// Tile width for measurements: 0 = the rule, 1 = 128 x 128 tiles, 2 = 128 x 256 tiles.
+MLXONE_API void mlxone_gemm_tcgen05_tiles(int choice) { g_tile_choice = choice; }
+
 // 1 if this build and driver can run the tcgen05 product (the tensor-map encoder was found).
 MLXONE_API int mlxone_gemm_tcgen05_available() { return find_encoder() ? 1 : 0; }
 
@@ -458,7 +462,7 @@ MLXONE_API int mlxone_gemm_tcgen05(const void* a, int lda, const void* w, const 
     int code;
     // 128 x 256 tiles unless the output is narrower: a 128 x 128 product reads its operands
     // from shared memory twice as often per flop and is bound by that
-    const bool wide = n > 128;
+    const bool wide = g_tile_choice == 0 ? n > 128 : g_tile_choice == 2;
     switch (epilogue) {
         case STORE_BF16:
             code = wide ? launch<256, STORE_BF16, WIDE_STAGES>(a, lda, w, bias, out, ldo, m, n, k, 0, error_flag, stream)

@@ -84,6 +84,7 @@ class Runner:
         self.use_graphs = self.device.type == "cuda" and model.capturable
         self._graphs: dict[tuple, _DecodeGraph] = {}
         self.graph_replays = 0
+        self.graph_captures = 0
         # steps with portions: captured at their third occurrence if they have at most this many
         # tokens (larger ones keep the GPU busy longer than the host needs to launch them)
         self.graph_token_limit = 1024
@@ -465,6 +466,7 @@ class Runner:
         parts all declare themselves capturable must be: a failure here is an error of a part
         (it synchronised, or read host values), and is raised, not hidden."""
         graph = torch.cuda.CUDAGraph()
+        self.graph_captures += 1
         torch.cuda.current_stream(self.device).synchronize()
         try:
             with torch.cuda.graph(graph):
@@ -494,7 +496,7 @@ class Runner:
         """How many steps are kept as graphs, and how often one was replayed."""
         kept = sum(1 for g in self._graphs.values() if g.graph is not None)
         return {"graphs": kept, "graph_shapes": len(self._graphs),
-                "graph_replays": self.graph_replays}
+                "graph_replays": self.graph_replays, "graph_captures": self.graph_captures}
 
     def _run_captured(self, captured: _DecodeGraph, run, eager_uses: int = 1):
         """Steps of one shape: the first ``eager_uses`` run eagerly, the next is captured as a
