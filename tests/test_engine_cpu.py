@@ -234,17 +234,25 @@ def test_a_timed_out_request_raises_and_the_others_finish(models, pipeline):
     engine.close()
 
 
-@pytest.mark.parametrize("seed", range(6))
+@pytest.mark.parametrize("seed", range(12))
 def test_random_load_on_the_entry_point(models, seed):
     """Requests that arrive while others run, with random lengths, budgets, portion sizes and
     numbers of sequences, a cache so small that some must wait, some cancelled on the way: every
-    finished request has the tokens it gets alone, nothing is lost and every page comes back."""
+    finished request has the tokens it gets alone, nothing is lost and every page comes back.
+    In half of the runs a sixth of the vocabulary ends a sequence, so that requests end on a
+    token that a step launched ahead has already been planned past."""
+    import dataclasses
     import random
 
     rng = random.Random(seed)
     name = rng.choice(["A", "B", "C"])
     folder, loaded, plain = models[name]
     config, _, page = CONFIGS[name]
+    ends = ()
+    if seed >= 6:
+        ends = tuple(rng.sample(range(config["vocab_size"]), config["vocab_size"] // 6))
+        loaded = dataclasses.replace(loaded, spec=dataclasses.replace(loaded.spec,
+                                                                      eos_token_ids=ends))
     budget = rng.choice([3, 8, 24, 64])
     engine = Engine(loaded,
                     cache_config=CacheConfig(block_size_tokens=page,
@@ -262,7 +270,7 @@ def test_random_load_on_the_entry_point(models, seed):
         while waiting and rng.random() < 0.4:
             prompt, count = waiting.pop(0)
             handles.append((prompt, count, engine.submit_ids(prompt, max_tokens=count,
-                                                             ignore_eos=True)))
+                                                             ignore_eos=not ends)))
         if handles and rng.random() < 0.05:
             index = rng.randrange(len(handles))
             if not handles[index][2].done():
@@ -274,8 +282,12 @@ def test_random_load_on_the_entry_point(models, seed):
     for index, (prompt, count, handle) in enumerate(handles):
         result = handle.result()
         want = plain.greedy(prompt, count)
+        ended = next((i for i, token in enumerate(want) if token in ends), None)
         if index in cancelled:
             assert list(result.token_ids) == want[:len(result.token_ids)]
+            assert ended is None or len(result.token_ids) <= ended
+        elif ended is not None:
+            assert list(result.token_ids) == want[:ended] and result.finish_reason == "stop"
         else:
             assert list(result.token_ids) == want and result.finish_reason == "length"
     stats = engine.runtime_stats()
@@ -368,3 +380,37 @@ def test_shapes_are_rounded_up_with_fillers_that_have_tokens(models):
             assert more_s == more_w == 0
         else:
             assert (singles + more_s) % 8 == 0 and (singles + more_w) % 8 == 0
+
+
+def test_threads_submit_while_the_loop_thread_runs(models):
+    """Several caller threads submit requests and wait for them while the engine's own thread
+    drives the loop: every request gets the tokens it gets alone, and the engine ends clean."""
+    import threading
+
+    folder, loaded, plain = models["B"]
+    config, _, page = CONFIGS["B"]
+    engine = Engine(loaded, cache_config=CacheConfig(block_size_tokens=page, capacity_tokens=512),
+                    batching_config=BatchingConfig(max_sequences=3, queue_size=32,
+                                                   prefill_chunk_size=8, max_scheduled_tokens=16,
+                                                   loop_thread=True))
+    requests = prompts(config["vocab_size"], (3, 17, 9, 30, 1, 12, 25, 6), seed=21)
+    results, errors = {}, []
+
+    def caller(numbers):
+        try:
+            for number in numbers:
+                handle = engine.submit_ids(requests[number], max_tokens=5, ignore_eos=True)
+                results[number] = list(handle.result().token_ids)
+        except BaseException as error:          # noqa: BLE001
+            errors.append(error)
+
+    threads = [threading.Thread(target=caller, args=(range(start, 8, 3),)) for start in range(3)]
+    for thread in threads:
+        thread.start()
+    for thread in threads:
+        thread.join(timeout=120)
+    assert not errors and not any(thread.is_alive() for thread in threads)
+    for number, prompt in enumerate(requests):
+        assert results[number] == plain.greedy(prompt, 5)
+    engine.close()
+    assert not engine.cache.requests() and engine._thread is None
