@@ -350,11 +350,12 @@ def time_e2e(engine, batch, context, warmup, steps, seed):
     seconds = time.perf_counter() - began
     produced = sum(len(h.request.output) for h in handles) - produced
     meta_bytes = engine.runner.last_meta_bytes
+    report_bytes = 4 * engine.runner.last_report.numel()      # chosen tokens + the error flag
     assert produced == batch * steps, (produced, batch, steps)
     for handle in handles:
         handle.cancel()
     engine.step()
-    return seconds, meta_bytes
+    return seconds, meta_bytes, report_bytes
 
 
 def time_prefill(engine, tokens, warmup, repeats, seed):
@@ -889,7 +890,7 @@ def main() -> int:
             s, _, _, _ = time_decode(engine, batch, args.context, warmup, args.steps, seed=2 + batch)
             points[f"decode_b{batch}"] = round(batch * args.steps / s, 1)
 
-    e2e_seconds, h2d = time_e2e(engine, args.batch, args.context, warmup, args.steps, seed=7)
+    e2e_seconds, h2d, d2h = time_e2e(engine, args.batch, args.context, warmup, args.steps, seed=7)
     e2e_value = args.batch * args.steps / e2e_seconds
 
     prefill_seconds = time_prefill(engine, PREFILL_TOKENS, 2, 3, seed=11)
@@ -918,7 +919,7 @@ def main() -> int:
         },
         "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s",
                 "ms_per_step": round(e2e_seconds / args.steps * 1e3, 4),
-                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4 * args.batch},
+                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
         "gpu_launches": launches_per_step * args.steps,
         "launches_per_step": launches_per_step,
         "prefill": {"value": round(PREFILL_TOKENS / prefill_seconds, 1), "tokens": PREFILL_TOKENS,

@@ -593,12 +593,19 @@ __global__ void decode_advance_kernel(const int* __restrict__ chosen, int* __res
 
 // Token ids that the device chose in an earlier step, kept per request so that a later step can
 // take its input from here instead of from the host: published[index of request] = token.
+// With `report`, the tokens are also left there one after the other, followed by the value of the
+// kernels' error flag: what the host reads back after a step, in one copy.
 __global__ void publish_tokens_kernel(const int* __restrict__ chosen, const int* __restrict__ index,
-                                      int* __restrict__ published, int count, int capacity) {
+                                      int* __restrict__ published, int count, int capacity,
+                                      int* __restrict__ report, const int* __restrict__ error_flag) {
     griddep_launch();
     griddep_wait();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i < count && index[i] >= 0 && index[i] < capacity) published[index[i]] = chosen[i];
+    if (report != nullptr) {
+        if (i < count) report[i] = chosen[i];
+        if (i == count) report[count] = error_flag != nullptr ? *error_flag : 0;
+    }
 }
 
 // token_ids[t] = published[source[t]] wherever source[t] >= 0 (else the host's id stays).
@@ -610,12 +617,14 @@ __global__ void resolve_tokens_kernel(int* __restrict__ token_ids, const int* __
     if (i < count && source[i] >= 0 && source[i] < capacity) token_ids[i] = published[source[i]];
 }
 
+// report: null, or count + 1 entries (the tokens, then the error flag's value).
 MLXONE_API int mlxone_publish_tokens(const int* chosen, const int* index, int* published, int count,
-                                     int capacity, cudaStream_t stream) {
+                                     int capacity, int* report, const int* error_flag,
+                                     cudaStream_t stream) {
     if (count == 0) return 0;
     MLXONE_REQUIRE(count > 0 && capacity > 0, "publish_tokens: bad sizes");
-    launch_kernel(publish_tokens_kernel, dim3((count + 255) / 256), dim3(256), 0, stream, true, chosen,
-                  index, published, count, capacity);
+    launch_kernel(publish_tokens_kernel, dim3((count + 256) / 256), dim3(256), 0, stream, true, chosen,
+                  index, published, count, capacity, report, error_flag);
     MLXONE_LAUNCH_CHECK("publish_tokens");
     return 0;
 }

@@ -59,6 +59,7 @@ class _InFlight:
     launched_at: float = 0.0
     ahead: bool = False
     prompt_tokens: int = 0
+    flag_at: int = 0                  # where in ``host`` the kernels' error flag lies
 
 
 class EngineRequestHandle:
@@ -381,15 +382,19 @@ class Engine:
                      len(r.output) + r.pending) for r in drawing]
         self._runner.step(entries, greedy=greedy, draw=draw)
         host = event = None
+        flag_at = 0
         if drawing:
-            host, event = self._start_copy(self._runner.last_greedy)
+            report = self._runner.last_report
+            flag_at = report.numel() - 1
+            host, event = self._start_copy(report)
         self._stats["steps"] += 1
         self._stats["steps_ahead"] += 1 if ahead else 0
         self._stats["tokens_run"] += sum(len(item.tokens) for item in planned)
         prompt_tokens = sum(len(item.tokens) for item in planned
                             if item.request.phase is Phase.PREFILL)
         return _InFlight(list(planned), host, event, len(drawing), bool(drawing),
-                         launched_at=started, ahead=ahead, prompt_tokens=prompt_tokens)
+                         launched_at=started, ahead=ahead, prompt_tokens=prompt_tokens,
+                         flag_at=flag_at)
 
     def _finish(self, inflight: "_InFlight") -> list[Request]:
         sampled: list[int] = []
@@ -397,7 +402,7 @@ class Engine:
             if inflight.event is not None:
                 inflight.event.synchronize()
             sampled = inflight.host[:inflight.draws].tolist()
-            code = int(inflight.host[inflight.draws])      # the kernels' error flag, same copy
+            code = int(inflight.host[inflight.flag_at])    # the kernels' error flag, same copy
             if code:
                 return self._kernel_fault(code, inflight)
         planned = inflight.planned
@@ -487,25 +492,20 @@ class Engine:
         """The records of the last steps (at most 4096), oldest first."""
         return list(self._traces)
 
-    def _start_copy(self, tokens: torch.Tensor):
-        """Starts the copy of the chosen tokens to the host, and behind them of the kernels'
-        error flag, so that a fault is seen with the tokens it spoilt and costs no wait of its
-        own; returns (host buffer, event)."""
-        count = tokens.numel()
-        flag = getattr(self.model.ops, "error_flag", None)
-        if tokens.device.type != "cuda":
-            tail = flag.to(torch.int32).cpu() if flag is not None else torch.zeros(1, dtype=torch.int32)
-            return torch.cat([tokens.to(torch.int32), tail]), None
+    def _start_copy(self, report: torch.Tensor):
+        """Starts the copy of a step's report to the host: the chosen tokens and, behind them,
+        the kernels' error flag as it stood at the end of the step, so that a fault is seen
+        with the tokens it spoilt and costs neither a copy nor a wait of its own. Returns (host
+        buffer, event); the flag is the buffer's last copied entry."""
+        count = report.numel()
+        if report.device.type != "cuda":
+            return report.clone(), None
         self._copy_turn ^= 1
         buffer = self._pinned[self._copy_turn]
-        if buffer is None or buffer.numel() < count + 1:
-            buffer = torch.zeros(max(count + 1, 256), dtype=torch.int32, pin_memory=True)
+        if buffer is None or buffer.numel() < count:
+            buffer = torch.zeros(max(count, 256), dtype=torch.int32, pin_memory=True)
             self._pinned[self._copy_turn] = buffer
-        buffer[:count].copy_(tokens, non_blocking=True)
-        if flag is not None:
-            buffer[count:count + 1].copy_(flag, non_blocking=True)
-        else:
-            buffer[count] = 0
+        buffer[:count].copy_(report, non_blocking=True)
         event = torch.cuda.Event()
         event.record()
         return buffer, event

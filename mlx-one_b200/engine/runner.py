@@ -75,6 +75,9 @@ class Runner:
         self.last_shape = (0, 0)
         self.last_meta_bytes = 0
         self.last_greedy: torch.Tensor | None = None
+        # what the host reads back after a step that chose tokens: int32, the tokens of the
+        # wanted rows (``last_greedy``, then any filler rows'), then the kernels' error flag
+        self.last_report: torch.Tensor | None = None
         # tokens chosen on the device, by request number (see StepEntry.from_device)
         # (one entry more than there are requests: where filler rows publish theirs)
         self.published = torch.zeros(cache.max_requests + 1, dtype=torch.int32,
@@ -384,8 +387,9 @@ class Runner:
                         on_device("draw_seed").view(torch.int64), on_device("draw_step"))
                 else:
                     chosen = self.ops.argmax(logits)
-                self.ops.publish_tokens(chosen, on_device("want_index")[:wanted], self.published)
-                return logits, chosen
+                report = self.ops.publish_tokens(chosen, on_device("want_index")[:wanted],
+                                                 self.published)
+                return logits, chosen, report
             return logits
 
         if loop is not None:
@@ -394,10 +398,12 @@ class Runner:
             logits = run()
         else:
             logits = self._run_captured(captured, run)
-        self.last_greedy = None
+        self.last_greedy = self.last_report = None
         if isinstance(logits, tuple):
-            logits, self.last_greedy = logits
-            self.last_greedy = self.last_greedy[:real_wanted]
+            logits, chosen, report = logits
+            self.last_greedy = chosen[:real_wanted]
+            # tokens of all wanted rows (fillers' after the real ones), then the error flag
+            self.last_report = report
         if logits is not None:
             logits = logits[:real_wanted] if real_wanted else None
         for entry in entries:

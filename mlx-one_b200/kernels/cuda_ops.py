@@ -553,9 +553,14 @@ class CudaOps:
                    _c_void_p(_ptr(counter)), _c_int(chosen.numel()), _c_int(record.shape[0]))
 
     def publish_tokens(self, chosen, index, published):
-        """published[index[i]] = chosen[i] (all int32 on the device)."""
+        """published[index[i]] = chosen[i] (all int32 on the device). Returns the step's report
+        for the host: the chosen tokens followed by the value of the kernels' error flag, so
+        that one copy brings both."""
+        report = torch.empty(chosen.numel() + 1, dtype=torch.int32, device=self.device)
         self._call("mlxone_publish_tokens", _c_void_p(_ptr(chosen)), _c_void_p(_ptr(index)),
-                   _c_void_p(_ptr(published)), _c_int(chosen.numel()), _c_int(published.numel()))
+                   _c_void_p(_ptr(published)), _c_int(chosen.numel()), _c_int(published.numel()),
+                   _c_void_p(_ptr(report)), _c_void_p(_ptr(self.error_flag)))
+        return report
 
     def resolve_tokens(self, token_ids, source, published):
         """token_ids[t] = published[source[t]] where source[t] >= 0, in place."""

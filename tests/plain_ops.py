@@ -170,6 +170,7 @@ class PlainOps:
 
     def publish_tokens(self, chosen, index, published):
         published[index.long()] = chosen
+        return torch.cat([chosen.to(torch.int32), self.error_flag.to(torch.int32)])
 
     def resolve_tokens(self, token_ids, source, published):
         taken = source >= 0
