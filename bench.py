@@ -640,12 +640,47 @@ def case_long(args) -> int:
     return 0
 
 
+def decode_step_case(batch: int, context: int) -> int:
+    """A few eager decode steps of the whole model at the benchmark's sizes, for a list of the
+    step's launches (`ncu --metrics gpu__time_duration.sum`): the prompts are fed first, the last
+    launches are the decode steps'."""
+    import torch
+
+    from mlx_one_b200.engine.runner import StepEntry
+
+    engine = build_engine(LFM2_1_2B, LFM2_1_2B["num_hidden_layers"], batch, context, 16)
+    engine.model.ops.set_dependent_launches(True)
+    runner = engine.runner
+    runner.use_graphs = False
+    ids = [f"step{i}" for i in range(batch)]
+    prompts = random_prompts(engine.model.spec.vocab_size, batch, context - 8, seed=3)
+    firsts = fill_requests(engine, prompts, ids)
+    before = engine.model.ops.launches
+    torch.cuda.synchronize()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    tokens = firsts
+    for _ in range(4):
+        runner.step([StepEntry(i, [t], (0,)) for i, t in zip(ids, tokens)], greedy=True)
+        tokens = runner.last_greedy.tolist()
+    stop.record()
+    torch.cuda.synchronize()
+    engine.model.ops.check_errors()
+    print(json.dumps({"kernel": "decode_step", "batch": batch, "context": context,
+                      "launches_per_step": (engine.model.ops.launches - before) // 4,
+                      "eager_ms_per_step": round(start.elapsed_time(stop) / 4, 3)}))
+    return 0
+
+
 def kernel_case(name: str, batch: int, context: int) -> int:
     """Runs one kernel of the step alone a few times at the benchmark's sizes and prints its
     time: the case that the ncu summaries under profiles/ were captured on."""
     import math
 
     import torch
+
+    if name == "decode_step":
+        return decode_step_case(batch, context)
 
     from mlx_one_b200.kernels import default_ops
     from mlx_one_b200.parts.base import PagedKeyValues, PagedView, StepContext
@@ -845,7 +880,8 @@ def main() -> int:
     parser.add_argument("--kernel", default=None,
                         help="run one kernel alone instead of the benchmark: skinny_swiglu, "
                              "skinny_down, decode_attention, prefill_attention, tcgen05_swiglu, "
-                             "swapped_swiglu, mixed_attention, sampling")
+                             "swapped_swiglu, mixed_attention, sampling, decode_step (the "
+                             "whole step, eager, for a launch list)")
     parser.add_argument("--dependent-launches", type=int, default=1,
                         help="1: kernels of a decode step may start while the one before ends")
     args = parser.parse_args()
