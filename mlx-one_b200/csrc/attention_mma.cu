@@ -403,13 +403,30 @@ constexpr int DECODE_HEADS = 8;      // query heads per block (the 8-column oper
 // split, at most 8): they leave their partial results in their own shared memory, and after a
 // barrier over the cluster block r merges head r from the others' shared memory (distributed
 // shared memory), so that neither a scratch buffer nor a merge kernel is needed.
-template <int HD, bool CLUSTER>
+// With PREP the kernel starts from the step's fused projection instead of prepared queries: `q` is
+// qkv [requests, (heads + 2 kv_heads) * HD], and the kernel applies the per-head RMSNorm and the
+// rotation to its own query heads in registers, and to the token's new key where it meets the
+// tile that holds the token's position; key and value of the token are put into that tile in
+// shared memory and (by one block per request and key head) into the request's page. A step of
+// single tokens then needs no kernel of its own for the preparation. HD must be a multiple of 32
+// (a rotation pair then sits in one lane) and the rotation covers the whole head or nothing.
+struct DecodePrep {
+    const float* q_weight = nullptr;      // [HD] or null: no norm
+    const float* k_weight = nullptr;
+    float eps = 0.f;
+    const float* inv_freq = nullptr;      // [HD / 2] or null: no rotation
+    bf16* cache = nullptr;                // the writable cache (keys, then values after kv_half)
+    int write_kv = 0;
+    int* error_flag = nullptr;
+};
+
+template <int HD, bool CLUSTER, bool PREP>
 __global__ void __launch_bounds__(DECODE_WARPS * 32)
 attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kv, long long kv_half,
                         const int* __restrict__ block_table, int table_width, int page_size,
                         const int* __restrict__ positions, bf16* __restrict__ out,
                         float* __restrict__ partial, int heads, int kv_heads, int splits,
-                        float scale_log2, int window) {
+                        float scale_log2, int window, DecodePrep prep) {
     using T = Tile<HD>;
     constexpr int KEYS = DECODE_KEYS;
     constexpr int ROW_FLOATS = HD + 2;
@@ -451,7 +468,10 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kv,
         copy_commit();
     };
     int ahead = 0;
-    for (; ahead < DECODE_STAGES - 1 && tile + ahead * DECODE_WARPS != newest; ++ahead) fetch(ahead);
+    // (with PREP nobody writes the cache before this kernel: the token's own row of the newest
+    // tile is put into shared memory below, over whatever the copy brought)
+    for (; ahead < DECODE_STAGES - 1 && (PREP || tile + ahead * DECODE_WARPS != newest); ++ahead)
+        fetch(ahead);
     griddep_wait();
     for (; ahead < DECODE_STAGES - 1; ++ahead) fetch(ahead);
 
@@ -459,11 +479,57 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kv,
     uint32_t qb[HD / 16][2];
     {
         const bool live = g < rows;
-        const bf16* row = q + ((size_t)request * heads + head0 + (live ? g : 0)) * HD;
+        const size_t row_stride = PREP ? (size_t)(heads + 2 * kv_heads) * HD : (size_t)heads * HD;
+        const bf16* row = q + (size_t)request * row_stride + (size_t)(head0 + (live ? g : 0)) * HD;
 #pragma unroll
         for (int kk = 0; kk < HD / 16; ++kk) {
             qb[kk][0] = live ? *reinterpret_cast<const uint32_t*>(row + kk * 16 + 2 * t) : 0u;
             qb[kk][1] = live ? *reinterpret_cast<const uint32_t*>(row + kk * 16 + 8 + 2 * t) : 0u;
+        }
+        if (PREP) {
+            // this lane's 4 values of every 16-wide piece: dims 16 kk + 2t, +1, +8 + 2t, +9 + 2t;
+            // the four lanes of a head hold all HD between them
+            float v[HD / 16][4];
+            float sum = 0.f;
+#pragma unroll
+            for (int kk = 0; kk < HD / 16; ++kk) {
+                const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(&qb[kk][0]);
+                const __nv_bfloat162 hi = *reinterpret_cast<const __nv_bfloat162*>(&qb[kk][1]);
+                v[kk][0] = __low2float(lo); v[kk][1] = __high2float(lo);
+                v[kk][2] = __low2float(hi); v[kk][3] = __high2float(hi);
+#pragma unroll
+                for (int c = 0; c < 4; ++c) sum += v[kk][c] * v[kk][c];
+            }
+            if (prep.q_weight != nullptr) {
+                sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+                sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+                const float inv = rsqrtf(sum / (float)HD + prep.eps);
+#pragma unroll
+                for (int kk = 0; kk < HD / 16; ++kk)
+#pragma unroll
+                    for (int c = 0; c < 4; ++c)
+                        v[kk][c] = v[kk][c] * inv *
+                                   prep.q_weight[kk * 16 + (c >> 1) * 8 + 2 * t + (c & 1)];
+            }
+            if (prep.inv_freq != nullptr) {
+                // dimension j of the first half pairs with j + HD / 2: piece kk with piece kk + HD / 32
+#pragma unroll
+                for (int kk = 0; kk < HD / 32; ++kk)
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        const int j = kk * 16 + (c >> 1) * 8 + 2 * t + (c & 1);
+                        float sine, cosine;
+                        sincosf((float)position * prep.inv_freq[j], &sine, &cosine);
+                        const float a = v[kk][c], b = v[kk + HD / 32][c];
+                        v[kk][c] = a * cosine - b * sine;
+                        v[kk + HD / 32][c] = b * cosine + a * sine;
+                    }
+            }
+#pragma unroll
+            for (int kk = 0; kk < HD / 16; ++kk) {
+                qb[kk][0] = live ? pack_bf16(v[kk][0], v[kk][1]) : 0u;
+                qb[kk][1] = live ? pack_bf16(v[kk][2], v[kk][3]) : 0u;
+            }
         }
     }
     const bool head_live[2] = {2 * t < rows, 2 * t + 1 < rows};
@@ -489,6 +555,77 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kv,
         const bf16* k_tile = ring + stage * STAGE;
         const bf16* v_tile = k_tile + KEYS * T::STRIDE;
         const int first = tile * KEYS;
+        if (PREP && tile == newest && prep.write_kv) {
+            // The token's own key and value: normed and rotated here from the projection's row,
+            // put into the tile over what the copy brought, and written to the request's page by
+            // the first block of this key head. Lane e takes dims e, e + 32, ...: a rotation
+            // pair (j, j + HD / 2) lies in one lane.
+            constexpr int HALF = HD / 2;
+            constexpr int PAIRS = (HALF + 31) / 32;      // pairs (j, j + HALF) of a lane: j = lane + 32 i
+            const bf16* row = q + (size_t)request * (heads + 2 * kv_heads) * HD;
+            const bf16* k_src = row + (size_t)(heads + kv_head) * HD;
+            const bf16* v_src = row + (size_t)(heads + kv_heads + kv_head) * HD;
+            float k_lo[PAIRS], k_hi[PAIRS], v_lo[PAIRS], v_hi[PAIRS];
+            float sum = 0.f;
+#pragma unroll
+            for (int i = 0; i < PAIRS; ++i) {
+                const int j = lane + 32 * i;
+                const bool mine = j < HALF;
+                k_lo[i] = mine ? __bfloat162float(k_src[j]) : 0.f;
+                k_hi[i] = mine ? __bfloat162float(k_src[j + HALF]) : 0.f;
+                v_lo[i] = mine ? __bfloat162float(v_src[j]) : 0.f;
+                v_hi[i] = mine ? __bfloat162float(v_src[j + HALF]) : 0.f;
+                sum += k_lo[i] * k_lo[i] + k_hi[i] * k_hi[i];
+            }
+            if (prep.k_weight != nullptr) {
+                sum = warp_sum(sum);
+                const float inv = rsqrtf(sum / (float)HD + prep.eps);
+#pragma unroll
+                for (int i = 0; i < PAIRS; ++i) {
+                    const int j = lane + 32 * i;
+                    if (j < HALF) {
+                        k_lo[i] = k_lo[i] * inv * prep.k_weight[j];
+                        k_hi[i] = k_hi[i] * inv * prep.k_weight[j + HALF];
+                    }
+                }
+            }
+            if (prep.inv_freq != nullptr) {
+#pragma unroll
+                for (int i = 0; i < PAIRS; ++i) {
+                    const int j = lane + 32 * i;
+                    if (j < HALF) {
+                        float sine, cosine;
+                        sincosf((float)position * prep.inv_freq[j], &sine, &cosine);
+                        const float a = k_lo[i], b = k_hi[i];
+                        k_lo[i] = a * cosine - b * sine;
+                        k_hi[i] = b * cosine + a * sine;
+                    }
+                }
+            }
+            bf16* k_row = const_cast<bf16*>(k_tile) + (size_t)(position - first) * T::STRIDE;
+            bf16* v_row = const_cast<bf16*>(v_tile) + (size_t)(position - first) * T::STRIDE;
+            const int block = pages.page_shift >= 0 ? position >> pages.page_shift
+                                                    : position / page_size;
+            const int page = block < table_width ? pages.table[block] : -1;
+            const bool writer = blockIdx.x % groups_of_8 == 0 && page >= 0;
+            if (page < 0 && lane == 0 && prep.error_flag != nullptr) atomicExch(prep.error_flag, 2);
+            const size_t at = (((size_t)(page < 0 ? 0 : page) * kv_heads + kv_head) * page_size +
+                               (position - block * page_size)) * HD;
+#pragma unroll
+            for (int i = 0; i < PAIRS; ++i) {
+                const int j = lane + 32 * i;
+                if (j >= HALF) continue;
+                const bf16 ka = __float2bfloat16_rn(k_lo[i]), kb = __float2bfloat16_rn(k_hi[i]);
+                const bf16 va = __float2bfloat16_rn(v_lo[i]), vb = __float2bfloat16_rn(v_hi[i]);
+                k_row[j] = ka; k_row[j + HALF] = kb;
+                v_row[j] = va; v_row[j + HALF] = vb;
+                if (writer) {
+                    prep.cache[at + j] = ka; prep.cache[at + j + HALF] = kb;
+                    prep.cache[kv_half + at + j] = va; prep.cache[kv_half + at + j + HALF] = vb;
+                }
+            }
+            __syncwarp();
+        }
         float s[KEYS / 16][4];
 #pragma unroll
         for (int mt = 0; mt < KEYS / 16; ++mt) {
@@ -717,11 +854,11 @@ size_t decode_shared_bytes(int head_dim) {
     return tiles > merge ? tiles : merge;
 }
 
-template <int HD>
+template <int HD, bool PREP>
 int launch_decode(const void* q, const void* kv, long long kv_half, const int* block_table,
                   int table_width, int page_size, const int* positions, void* out, float* partial,
                   int requests, int heads, int kv_heads, int splits, float scale, int window,
-                  cudaStream_t stream) {
+                  cudaStream_t stream, DecodePrep prep = DecodePrep()) {
     using T = Tile<HD>;
     const size_t shared = decode_shared_bytes(HD);
     const int group = heads / kv_heads;
@@ -729,7 +866,7 @@ int launch_decode(const void* q, const void* kv, long long kv_half, const int* b
     const float scale_log2 = scale * LOG2E;
     // 2 to 8 splits without a scratch buffer: a cluster of the splits' blocks merges them itself
     if (splits > 1 && splits <= 8 && partial == nullptr) {
-        auto kernel = attention_decode_kernel<HD, true>;
+        auto kernel = attention_decode_kernel<HD, true, PREP>;
         if (shared > 48 * 1024)
             cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
         cudaLaunchConfig_t config = {};
@@ -749,19 +886,19 @@ int launch_decode(const void* q, const void* kv, long long kv_half, const int* b
         const cudaError_t err = cudaLaunchKernelEx(
             &config, kernel, (const bf16*)q, (const bf16*)kv, kv_half, block_table, table_width,
             page_size, positions, (bf16*)out, (float*)nullptr, heads, kv_heads, splits, scale_log2,
-            window);
+            window, prep);
         if (err != cudaSuccess) {
             mlxone_set_error("attention_decode: cluster launch failed: %s", cudaGetErrorString(err));
             return 2;
         }
         return 0;
     }
-    auto kernel = attention_decode_kernel<HD, false>;
+    auto kernel = attention_decode_kernel<HD, false, PREP>;
     if (shared > 48 * 1024)
         cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
     launch_kernel(kernel, grid, dim3(DECODE_WARPS * 32), shared, stream, true, (const bf16*)q,
                   (const bf16*)kv, kv_half, block_table, table_width, page_size, positions,
-                  (bf16*)out, partial, heads, kv_heads, splits, scale_log2, window);
+                  (bf16*)out, partial, heads, kv_heads, splits, scale_log2, window, prep);
     if (splits > 1) {
         const int items = requests * heads;
         launch_kernel(attention_merge_kernel<HD>, dim3((items + 3) / 4), dim3(128), 0, stream, true,
@@ -848,11 +985,63 @@ MLXONE_API int mlxone_attention_decode(const void* q, const void* kv, const int*
                    "attention_decode: bad page geometry");
     const long long kv_half = (long long)pages * kv_heads * page_size * head_dim;
 #define CALL(HD)                                                                               \
-    launch_decode<HD>(q, kv, kv_half, block_table, table_width, page_size, positions, out,     \
-                      partial, requests, heads, kv_heads, splits, scale, window, stream)
+    launch_decode<HD, false>(q, kv, kv_half, block_table, table_width, page_size, positions, out, \
+                             partial, requests, heads, kv_heads, splits, scale, window, stream)
     MLXONE_HEAD_DIMS(CALL)
 #undef CALL
     MLXONE_LAUNCH_CHECK("attention_decode");
+    return 0;
+}
+
+// 1 if mlxone_attention_decode_fused takes this head size: a multiple of 32 up to 128.
+MLXONE_API int mlxone_attention_decode_fused_supports(int head_dim) {
+    return head_dim % 32 == 0 && head_dim >= 32 && head_dim <= 128 ? 1 : 0;
+}
+
+// Decode attention straight from the step's fused projection: qkv [requests, (heads + 2 kv_heads)
+// * head_dim] bfloat16, one token per request. Per-head RMSNorm of queries and keys (q_weight,
+// k_weight float32 [head_dim], or null for none), rotation of the whole head by positions *
+// inv_freq (float32 [head_dim / 2], or null for none), the token's key and value written into
+// its page (write_kv), attention over the request's pages: what mlxone_qk_prep followed by
+// mlxone_attention_decode compute, in one kernel. kv is the writable cache.
+MLXONE_API int mlxone_attention_decode_fused(const void* qkv, const float* q_weight,
+                                             const float* k_weight, float eps,
+                                             const float* inv_freq, void* kv,
+                                             const int* block_table, int table_width,
+                                             int page_size, int pages, const int* positions,
+                                             void* out, float* partial, int requests, int heads,
+                                             int kv_heads, int head_dim, int splits, float scale,
+                                             int window, int write_kv, int* error_flag,
+                                             cudaStream_t stream) {
+    if (requests == 0) return 0;
+    MLXONE_REQUIRE(mlxone_attention_decode_fused_supports(head_dim),
+                   "attention_decode_fused: head size %d is no multiple of 32 up to 128", head_dim);
+    MLXONE_REQUIRE(requests > 0 && heads > 0 && kv_heads > 0 && heads % kv_heads == 0,
+                   "attention_decode_fused: bad sizes");
+    MLXONE_REQUIRE(requests <= 65535 && splits >= 1 && splits <= 65535,
+                   "attention_decode_fused: at most 65535 requests and splits");
+    MLXONE_REQUIRE(splits <= 8 || partial != nullptr,
+                   "attention_decode_fused: more than 8 splits need a scratch buffer");
+    MLXONE_REQUIRE(page_size > 0 && pages > 0 && table_width > 0,
+                   "attention_decode_fused: bad page geometry");
+    const long long kv_half = (long long)pages * kv_heads * page_size * head_dim;
+    DecodePrep prep;
+    prep.q_weight = q_weight; prep.k_weight = k_weight; prep.eps = eps; prep.inv_freq = inv_freq;
+    prep.cache = static_cast<bf16*>(kv); prep.write_kv = write_kv; prep.error_flag = error_flag;
+    int code = 0;
+    switch (head_dim) {
+#define CASE(HD)                                                                                  \
+        case HD:                                                                                  \
+            code = launch_decode<HD, true>(qkv, kv, kv_half, block_table, table_width, page_size, \
+                                           positions, out, partial, requests, heads, kv_heads,    \
+                                           splits, scale, window, stream, prep);                  \
+            break;
+        CASE(32) CASE(64) CASE(96) CASE(128)
+#undef CASE
+        default: break;
+    }
+    if (code != 0) return code;
+    MLXONE_LAUNCH_CHECK("attention_decode_fused");
     return 0;
 }
 

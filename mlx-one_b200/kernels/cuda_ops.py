@@ -73,6 +73,9 @@ class CudaOps:
         # against 0.645 / 0.684 / 0.702 ms with the merge kernel; batch 8 at 8192 keys, batch 1
         # and batch 2 at 32768 keys the same either way (more than 12 splits keep the merge kernel)
         self.cluster_merge = True
+        # a step of single tokens: q/k norm, rotation and the page write inside the decode
+        # attention kernel instead of a kernel of their own before it
+        self.fused_decode_attention = True
         # a mixed step's leading single-token requests go to the decode attention kernel when
         # there are at least this many of them
         self.split_singles_from = 1
@@ -441,6 +444,46 @@ class CudaOps:
                    _c_void_p(_ptr(self.error_flag)))
         return q
 
+    def qkv_attention(self, qkv, *, heads, kv_heads, head_dim, q_weight, k_weight, eps, rotary,
+                      scale, window, ctx, view, write):
+        """From the fused projection qkv [tokens, (heads + 2 kv_heads) * head_dim] to the mixed
+        heads [tokens, heads * head_dim]: per-head norm of queries and keys, rotation, keys and
+        values appended to the pages, attention. A step of single tokens in bfloat16 whose head
+        size is a multiple of 32 and whose rotation covers the whole head (or is none) runs as
+        one kernel; everything else as the preparation kernel followed by attention."""
+        tokens = qkv.shape[0]
+        inv_freq, rotary_dim = (None, 0) if rotary is None else rotary
+        if (self.fused_decode_attention and qkv.dtype == torch.bfloat16
+                and ctx.max_portion == 1 and tokens == ctx.requests
+                and self.tensor_core_attention
+                and self.lib.mlxone_attention_decode_fused_supports(_c_int(head_dim))
+                and (inv_freq is None or rotary_dim == head_dim)
+                and (q_weight is None) == (k_weight is None)):
+            self._need(qkv, view.kv.dtype, "qkv")
+            if qkv.shape[1] != (heads + 2 * kv_heads) * head_dim:
+                raise KernelError("qkv width does not match the head counts")
+            out = torch.empty((tokens, heads * head_dim), dtype=qkv.dtype, device=self.device)
+            width = view.block_table.shape[1]
+            splits, partial = self._decode_plan(tokens, heads, kv_heads, head_dim, width, window,
+                                                view)
+            self._call("mlxone_attention_decode_fused", _c_void_p(_ptr(qkv)),
+                       _c_void_p(_ptr(q_weight)), _c_void_p(_ptr(k_weight)),
+                       _c_float(0.0 if eps is None else eps), _c_void_p(_ptr(inv_freq)),
+                       _c_void_p(_ptr(view.kv)), _c_void_p(_ptr(view.block_table)), _c_int(width),
+                       _c_int(view.page_size), _c_int(view.kv.shape[1]),
+                       _c_void_p(_ptr(ctx.positions)), _c_void_p(_ptr(out)),
+                       _c_void_p(_ptr(partial)), _c_int(tokens), _c_int(heads), _c_int(kv_heads),
+                       _c_int(head_dim), _c_int(splits), _c_float(scale), _c_int(window or 0),
+                       _c_int(1 if write else 0), _c_void_p(_ptr(self.error_flag)))
+            if partial is not None:
+                self.launches += 1          # the merge kernel
+            return out
+        q = self.qk_norm_rope_store(qkv, heads=heads, kv_heads=kv_heads, head_dim=head_dim,
+                                    q_weight=q_weight, k_weight=k_weight, eps=eps, rotary=rotary,
+                                    ctx=ctx, view=view, write=write)
+        return self.paged_attention(q, heads=heads, kv_heads=kv_heads, head_dim=head_dim,
+                                    scale=scale, window=window, ctx=ctx, view=view)
+
     def paged_attention(self, q, *, heads, kv_heads, head_dim, scale, window, ctx, view):
         """Attention of every token over its request's pages. bfloat16 with a head size that
         is a multiple of 16 up to 128 runs on tensor cores: the split-key decode kernel when
@@ -503,6 +546,19 @@ class CudaOps:
         """The split-key kernel for the first ``requests`` requests of the step, one token each
         (token i is request i's): rows 0 to requests - 1 of q, positions, table and out."""
         width = view.block_table.shape[1]
+        splits, partial = self._decode_plan(requests, heads, kv_heads, head_dim, width, window,
+                                            view)
+        self._call("mlxone_attention_decode", _c_void_p(_ptr(q)), _c_void_p(_ptr(view.kv)),
+                   _c_void_p(_ptr(view.block_table)), _c_int(width), _c_int(view.page_size),
+                   _c_int(view.kv.shape[1]), _c_void_p(_ptr(ctx.positions)), _c_void_p(_ptr(out)),
+                   _c_void_p(_ptr(partial)), _c_int(requests), _c_int(heads), _c_int(kv_heads),
+                   _c_int(head_dim), _c_int(splits), _c_float(scale), _c_int(window or 0))
+        if partial is not None:
+            self.launches += 1          # the merge kernel
+
+    def _decode_plan(self, requests, heads, kv_heads, head_dim, width, window, view):
+        """Key splits of a decode attention launch and the scratch for their partial results
+        (None when a thread-block cluster merges them, or there is one split)."""
         splits = self.decode_splits(requests, heads, kv_heads, head_dim, width * view.page_size,
                                     window)
         if self.cluster_merge and 8 < splits <= 12 and width * view.page_size <= 8192:
@@ -511,13 +567,7 @@ class CudaOps:
         if splits > 8 or (splits > 1 and not self.cluster_merge):
             partial = torch.empty(requests * heads * splits * (head_dim + 2),
                                   dtype=torch.float32, device=self.device)
-        self._call("mlxone_attention_decode", _c_void_p(_ptr(q)), _c_void_p(_ptr(view.kv)),
-                   _c_void_p(_ptr(view.block_table)), _c_int(width), _c_int(view.page_size),
-                   _c_int(view.kv.shape[1]), _c_void_p(_ptr(ctx.positions)), _c_void_p(_ptr(out)),
-                   _c_void_p(_ptr(partial)), _c_int(requests), _c_int(heads), _c_int(kv_heads),
-                   _c_int(head_dim), _c_int(splits), _c_float(scale), _c_int(window or 0))
-        if partial is not None:
-            self.launches += 1          # the merge kernel
+        return splits, partial
 
     def decode_splits(self, requests: int, heads: int, kv_heads: int, head_dim: int,
                       context_bound: int, window: int | None) -> int:

@@ -67,13 +67,11 @@ class Attention(Mixer):
 
     def forward(self, x, ctx, cache, write, residual=None):
         qkv = self.ops.linear(x, self.qkv)
-        q = self.ops.qk_norm_rope_store(
+        mixed = self.ops.qkv_attention(
             qkv, heads=self.heads, kv_heads=self.kv_heads, head_dim=self.head_dim,
             q_weight=self.q_norm, k_weight=self.k_norm, eps=self.eps,
-            rotary=self.position.rotary_table(), ctx=ctx, view=cache, write=write)
-        mixed = self.ops.paged_attention(
-            q, heads=self.heads, kv_heads=self.kv_heads, head_dim=self.head_dim,
-            scale=self.scale, window=self.window, ctx=ctx, view=cache)
+            rotary=self.position.rotary_table(), scale=self.scale, window=self.window, ctx=ctx,
+            view=cache, write=write)
         if residual is None:
             return self.ops.linear(mixed, self.out)
         return self.ops.linear_add(mixed, self.out, None, residual)

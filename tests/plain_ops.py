@@ -134,6 +134,14 @@ class PlainOps:
                 view.kv[1, page, :, offset] = v[t].to(dtype)
         return q.contiguous()
 
+    def qkv_attention(self, qkv, *, heads, kv_heads, head_dim, q_weight, k_weight, eps, rotary,
+                      scale, window, ctx, view, write):
+        q = self.qk_norm_rope_store(qkv, heads=heads, kv_heads=kv_heads, head_dim=head_dim,
+                                    q_weight=q_weight, k_weight=k_weight, eps=eps, rotary=rotary,
+                                    ctx=ctx, view=view, write=write)
+        return self.paged_attention(q, heads=heads, kv_heads=kv_heads, head_dim=head_dim,
+                                    scale=scale, window=window, ctx=ctx, view=view)
+
     def paged_attention(self, q, *, heads, kv_heads, head_dim, scale, window, ctx, view):
         tokens = q.shape[0]
         out = torch.empty(tokens, heads, head_dim)

@@ -504,6 +504,72 @@ def test_attention_prefill_tcgen05_rising_scores(ops, plain, ramp, portions, his
                    histories=histories, window=None, tensor_cores=True, tcgen05=True, ramp=ramp)
 
 
+@pytest.mark.parametrize("heads,kv_heads,head_dim,page_size", [
+    (32, 8, 64, 16), (24, 8, 64, 16), (3, 1, 32, 8), (20, 2, 128, 32), (6, 3, 96, 4), (4, 2, 64, 1)])
+@pytest.mark.parametrize("norm,rotate,window", [(True, True, None), (False, True, 70),
+                                                 (True, False, None), (False, False, 33)])
+@pytest.mark.parametrize("cluster", [False, True])
+def test_decode_attention_from_the_fused_projection(ops, plain, heads, kv_heads, head_dim,
+                                                    page_size, norm, rotate, window, cluster):
+    """A step of single tokens: q/k norm, rotation, the write of key and value into the page and
+    attention in one kernel, against the plain preparation followed by plain attention: the
+    mixed heads and the cache afterwards. Contexts from one key (the token's own) to several
+    splits, positions at the edges of tiles of 32 keys and of pages; one request's query is made
+    to pick out its own new key, which only the fused kernel's shared-memory copy can serve."""
+    torch.manual_seed(heads * 7 + head_dim)
+    histories = [0, 1, 31, 32, 63, 64, 200, 1023, 1500]
+    portions = [1] * len(histories)
+    ctx, table, pages = make_batch(portions, histories, page_size, DEVICE, seed=3)
+    assert ops.lib.mlxone_attention_decode_fused_supports(head_dim)
+    kv = torch.randn(2, pages, kv_heads, page_size, head_dim).bfloat16()
+    width = (heads + 2 * kv_heads) * head_dim
+    qkv = torch.randn(ctx.tokens, width).bfloat16()
+    # request 6: the query heads equal the new key (before norm and rotation both are scaled
+    # alike), times a large factor, so that its own position dominates the softmax
+    group = heads // kv_heads
+    for h in range(heads):
+        k_at = (heads + h // group) * head_dim
+        qkv[6, h * head_dim:(h + 1) * head_dim] = qkv[6, k_at:k_at + head_dim] * 3
+    q_weight = (1 + 0.1 * torch.randn(head_dim)) if norm else None
+    k_weight = (1 + 0.1 * torch.randn(head_dim)) if norm else None
+    rotary = None
+    if rotate:
+        half = head_dim // 2
+        rotary = (torch.pow(torch.tensor(10000.0), -torch.arange(half, dtype=torch.float32) / half),
+                  head_dim)
+    need = PagedKeyValues(kv_heads, head_dim, window)
+    arguments = dict(heads=heads, kv_heads=kv_heads, head_dim=head_dim, eps=1e-5 if norm else None,
+                     scale=head_dim ** -0.5, window=window, write=True)
+    kv_gpu = kv.clone().to(DEVICE)
+    on_gpu = lambda v: None if v is None else v.to(DEVICE)
+    ops.cluster_merge = cluster
+    before = ops.launches
+    try:
+        got = ops.qkv_attention(qkv.to(DEVICE), q_weight=on_gpu(q_weight), k_weight=on_gpu(k_weight),
+                                rotary=None if rotary is None else (rotary[0].to(DEVICE), head_dim),
+                                ctx=ctx, view=PagedView(kv_gpu, table, page_size, need), **arguments)
+    finally:
+        ops.cluster_merge = True
+    assert ops.launches - before <= 2                   # one kernel, or one and the merge kernel
+    kv_cpu = kv.clone()
+    want = plain.qkv_attention(qkv, q_weight=q_weight, k_weight=k_weight, rotary=rotary,
+                               ctx=on_cpu(ctx), view=PagedView(kv_cpu, table.cpu(), page_size, need),
+                               **arguments)
+    ops.check_errors()
+    torch.testing.assert_close(got.cpu().float(), want.float(), **tolerance(torch.bfloat16))
+    # the cache: only the new rows changed, and they hold the plain preparation's keys and values
+    assert not torch.equal(kv_cpu, kv)
+    torch.testing.assert_close(kv_gpu.cpu().float(), kv_cpu.float(), atol=2e-2, rtol=2e-2)
+    # read-only call: nothing is written, and the token's row in the cache is what is attended to
+    kv_gpu2 = kv_cpu.clone().to(DEVICE)
+    again = ops.qkv_attention(qkv.to(DEVICE), q_weight=on_gpu(q_weight), k_weight=on_gpu(k_weight),
+                              rotary=None if rotary is None else (rotary[0].to(DEVICE), head_dim),
+                              ctx=ctx, view=PagedView(kv_gpu2, table, page_size, need),
+                              **{**arguments, "write": False})
+    assert torch.equal(kv_gpu2.cpu(), kv_cpu)
+    torch.testing.assert_close(again.cpu().float(), want.float(), **tolerance(torch.bfloat16))
+
+
 def test_decode_splits_are_used(ops):
     assert ops.decode_splits(1, 32, 8, 64, 4096, None) > 1
     assert ops.decode_splits(64, 32, 8, 64, 4096, None) == 1
