@@ -406,7 +406,7 @@ def run_batching(engine, workload):
     import torch
 
     records = []
-    engine._trace_sink = records.append
+    engine.set_trace_sink(records.append)
     torch.cuda.synchronize()
     began = time.perf_counter()
     handles = [engine.submit_ids(prompt, TextGenerationOptions(max_tokens=new, ignore_eos=True))
@@ -414,7 +414,7 @@ def run_batching(engine, workload):
     engine.run()
     torch.cuda.synchronize()
     seconds = time.perf_counter() - began
-    engine._trace_sink = None
+    engine.set_trace_sink(None)
     return [handle.result() for handle in handles], seconds, records
 
 
@@ -479,6 +479,7 @@ def case_batching(args) -> int:
                         "pages_total": stats["pages_total"][0],
                         "graphs_kept": stats["graphs"], "graph_captures_so_far":
                             stats["graph_captures"],
+                        "graph_memory_gb": round(stats["graph_memory_bytes"] / 1e9, 2),
                         "device_memory_gb": round(torch.cuda.memory_reserved() / 1e9, 2)})
     measured = sorted(samples[1:], key=lambda sample: sample["seconds"])
     middle = measured[len(measured) // 2]
@@ -586,14 +587,14 @@ def case_long(args) -> int:
     # the same through the entry point: submit four requests, run, host clock
     options = TextGenerationOptions(max_tokens=decode + 1, ignore_eos=True)
     records = []
-    engine._trace_sink = records.append
+    engine.set_trace_sink(records.append)
     torch.cuda.synchronize()
     began = time.perf_counter()
     handles = [engine.submit_ids(prompt, options) for prompt in prompts]
     engine.run()
     torch.cuda.synchronize()
     e2e_seconds = time.perf_counter() - began
-    engine._trace_sink = None
+    engine.set_trace_sink(None)
     results = [handle.result() for handle in handles]
     assert all(r.generation_tokens == decode + 1 for r in results)
     model.ops.check_errors()

@@ -488,6 +488,11 @@ class Engine:
         if self._trace_sink is not None:
             self._trace_sink(record)
 
+    def set_trace_sink(self, sink) -> None:
+        """``sink(record)`` is called with every committed step's record from now on (None:
+        nobody)."""
+        self._trace_sink = sink
+
     def step_traces(self) -> list[dict[str, Any]]:
         """The records of the last steps (at most 4096), oldest first."""
         return list(self._traces)

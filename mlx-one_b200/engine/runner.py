@@ -88,6 +88,7 @@ class Runner:
         self._graphs: dict[tuple, _DecodeGraph] = {}
         self.graph_replays = 0
         self.graph_captures = 0
+        self.graph_memory_bytes = 0         # device memory that captures have added to the allocator
         # steps with portions: captured at their third occurrence if they have at most this many
         # tokens (larger ones keep the GPU busy longer than the host needs to launch them)
         self.graph_token_limit = 1024
@@ -474,9 +475,13 @@ class Runner:
         graph = torch.cuda.CUDAGraph()
         self.graph_captures += 1
         torch.cuda.current_stream(self.device).synchronize()
+        reserved = torch.cuda.memory_reserved(self.device)
         try:
             with torch.cuda.graph(graph):
                 result = run()
+            # a graph keeps a memory pool of its own (its activations and logits): count what the
+            # capture made the allocator reserve, so that it can be set against the cache's budget
+            self.graph_memory_bytes += max(torch.cuda.memory_reserved(self.device) - reserved, 0)
         except Exception as error:
             torch.cuda.synchronize(self.device)
             raise RuntimeError(
@@ -502,7 +507,8 @@ class Runner:
         """How many steps are kept as graphs, and how often one was replayed."""
         kept = sum(1 for g in self._graphs.values() if g.graph is not None)
         return {"graphs": kept, "graph_shapes": len(self._graphs),
-                "graph_replays": self.graph_replays, "graph_captures": self.graph_captures}
+                "graph_replays": self.graph_replays, "graph_captures": self.graph_captures,
+                "graph_memory_bytes": self.graph_memory_bytes}
 
     def _run_captured(self, captured: _DecodeGraph, run, eager_uses: int = 1):
         """Steps of one shape: the first ``eager_uses`` run eagerly, the next is captured as a
