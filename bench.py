@@ -101,7 +101,7 @@ class ClockSampler:
         try:
             self._process = subprocess.Popen(
                 ["nvidia-smi", "-i", self._current_gpu(), f"--query-gpu={self.QUERY}",
-                 "--format=csv,noheader,nounits", "-lms", "50"],
+                 "--format=csv,noheader,nounits", "-lms", "200"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             return
@@ -141,8 +141,9 @@ class ClockSampler:
                 "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
                 "samples": len(self.samples), "samples_under_load": len(loaded),
                 "samples_in_timed_region": inside,
-                "how": "nvidia-smi every 50 ms while the same decode steps run untimed for about "
-                       "a second directly before the timed steps, and through them"}
+                "how": "nvidia-smi every 200 ms (a query can hold the GPU up for a millisecond, so "
+                       "not more often) while the same decode steps run untimed for about a "
+                       "second directly before the timed steps, and through them"}
 
 
 def reference_arm():
@@ -256,7 +257,7 @@ def time_decode(engine, batch, context, warmup, steps, seed, sampler=None):
     vocab = engine.model.spec.vocab_size
     load_steps = 0
     if sampler:
-        load_steps = max(min(1024, context - warmup - steps - 65), 0) // 64 * 64
+        load_steps = max(min(2048, context - warmup - steps - 65), 0) // 64 * 64
     prompt_length = context - max(warmup, 3) - load_steps - steps - 1
     ids = [f"decode{batch}_{i}" for i in range(batch)]
     prompts = random_prompts(vocab, batch, prompt_length, seed)
@@ -273,19 +274,19 @@ def time_decode(engine, batch, context, warmup, steps, seed, sampler=None):
     load_began = None
     if sampler:
         # The timed region may last a few milliseconds, less than one sample of nvidia-smi. So the
-        # clocks are sampled while the same steps run, untimed, for about a second before it
+        # clocks are sampled while the same steps run, untimed, for a second or more before it
         # (the prompts are that much shorter, so the timed steps end at ``context`` all the same).
         sampler.start()
-        time.sleep(0.15)
+        time.sleep(0.25)
         load_began = time.perf_counter()
         for _ in range(load_steps // 64):
             last = runner.decode_steps(entries, 64)[-1].tolist()
             entries = [StepEntry(i, [t]) for i, t in zip(ids, last)]
     torch.cuda.synchronize()
     began = time.perf_counter()
-    start.record()
-    runner.decode_steps(entries, steps)
-    stop.record()
+    # (the events are recorded around the steps' launches, after the host has packed the loop's
+    # metadata: exactly `steps` steps lie between them)
+    runner.decode_steps(entries, steps, events=(start, stop))
     torch.cuda.synchronize()
     ended = time.perf_counter()
     seconds = start.elapsed_time(stop) / 1e3
@@ -332,14 +333,16 @@ def time_e2e(engine, batch, context, warmup, steps, seed):
     # has decoded some tokens when the last one starts; `slack` keeps every request decoding
     # through the timed steps
     slack = batch * (context // PREFILL_TOKENS + 2) + 8
-    prompt_length = context - warmup - steps - slack
+    prompt_length = context - max(warmup, 24) - steps - slack
     prompts = random_prompts(vocab, batch, prompt_length, seed + 1)
-    options = TextGenerationOptions(max_tokens=warmup + steps + slack, ignore_eos=True)
+    options = TextGenerationOptions(max_tokens=max(warmup, 24) + steps + slack, ignore_eos=True)
     handles = [engine.submit_ids(p, options) for p in prompts]
     from mlx_one_b200.engine.scheduler import Phase
     while any(h.request.phase is not Phase.DECODE for h in handles):
         engine.step()
-    for _ in range(warmup):
+    # untimed steps until the pipeline of launches ahead is in its steady state (the step's graph
+    # is captured at its second occurrence); at least the warm-up asked for
+    for _ in range(max(warmup, 24)):
         engine.step()
     torch.cuda.synchronize()
     produced = sum(len(h.request.output) for h in handles)

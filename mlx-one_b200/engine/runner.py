@@ -140,11 +140,14 @@ class Runner:
         (temperature, top_k, top_p, seed, tokens drawn so far); a temperature of 0 is greedy."""
         return self._step(entries, greedy=greedy, draw=draw)
 
-    def decode_steps(self, entries: Sequence[StepEntry], steps: int) -> torch.Tensor:
+    def decode_steps(self, entries: Sequence[StepEntry], steps: int,
+                     events: tuple | None = None) -> torch.Tensor:
         """``steps`` greedy decode steps in a row without the host in between: every entry
         brings its next token; each step's argmax becomes the next step's input on the
         device. Pages for all steps are taken first. Returns the chosen tokens as int32
-        [steps, requests] on the device (not synchronised)."""
+        [steps, requests] on the device (not synchronised). ``events``: two CUDA events that
+        are recorded directly before the first step's launch and after the last one's, for
+        timing the steps without the host's preparation of the loop."""
         if steps < 1 or any(len(e.tokens) != 1 for e in entries):
             raise ValueError("decode_steps takes one token per request and at least one step")
         limit = self.model.spec.max_positions
@@ -156,7 +159,7 @@ class Runner:
             self.cache.grow(entry.request_id, steps)
         entries = [StepEntry(e.request_id, e.tokens, (0,)) for e in entries]
         record = torch.zeros((steps, len(entries)), dtype=torch.int32, device=self.device)
-        return self._step(entries, loop=(steps, record))
+        return self._step(entries, loop=(steps, record, events))
 
     def _step(self, entries: Sequence[StepEntry], loop=None, greedy: bool = False, draw=None):
         """Runs the entries as one batch. Returns float32 logits [wanted, vocab] on the
@@ -413,7 +416,7 @@ class Runner:
         self.last_shape = (requests, tokens)
         return logits
 
-    def _run_loop(self, captured, run, ctx, entries, steps, record) -> torch.Tensor:
+    def _run_loop(self, captured, run, ctx, entries, steps, record, events=None) -> torch.Tensor:
         if captured.counter is None:
             captured.counter = torch.zeros(1, dtype=torch.int32, device=self.device)
         captured.counter.zero_()
@@ -426,6 +429,8 @@ class Runner:
                                     captured.record_buffer(record), captured.counter)
 
         done = 0
+        if events is not None:
+            events[0].record()
         if captured.graph is None or not self.use_graphs:
             one_step()
             done = 1
@@ -438,6 +443,8 @@ class Runner:
                 self.graph_replays += 1
             else:
                 one_step()
+        if events is not None:
+            events[1].record()
         out = captured.record_buffer(record)[:steps].clone()
         for entry in entries:
             self.cache.advance(entry.request_id, steps)
