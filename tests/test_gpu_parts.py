@@ -227,6 +227,44 @@ def test_entry_point_generates_greedily(folders, dtype):
     engine.close()
 
 
+def test_entry_point_with_its_own_loop_thread(folders):
+    """The engine's thread launches the kernels and captures the graphs; callers on other threads
+    submit and wait. In 32-bit every token equals the plain model's."""
+    import threading
+
+    from mlx_one_b200 import BatchingConfig, CacheConfig, Engine
+    name = "B"
+    config, _, page = CONFIGS[name]
+    model = plain.PlainModel(folders[name])
+    engine = Engine(folders[name], execution_dtype="float32", device=DEVICE,
+                    cache_config=CacheConfig(block_size_tokens=page, capacity_tokens=1024),
+                    batching_config=BatchingConfig(max_sequences=4, queue_size=16,
+                                                   prefill_chunk_size=16, max_scheduled_tokens=32,
+                                                   loop_thread=True))
+    requests = prompts(config["vocab_size"], (5, 40, 17, 1, 33, 9), seed=17)
+    got, errors = {}, []
+
+    def caller(numbers):
+        try:
+            for number in numbers:
+                got[number] = list(engine.submit_ids(requests[number], max_tokens=12,
+                                                     ignore_eos=True).result().token_ids)
+        except BaseException as error:          # noqa: BLE001
+            errors.append(error)
+
+    threads = [threading.Thread(target=caller, args=(range(start, 6, 2),)) for start in range(2)]
+    for thread in threads:
+        thread.start()
+    for thread in threads:
+        thread.join(timeout=300)
+    assert not errors and not any(thread.is_alive() for thread in threads)
+    for number, prompt in enumerate(requests):
+        assert got[number] == model.greedy(prompt, 12)
+    assert engine.runtime_stats()["graph_replays"] > 0
+    engine.close()
+    assert not engine.cache.requests()
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_replay_program(folders, dtype, tmp_path):
     """bin/trace_run as a user starts it: steps on standard input, logits in files."""
