@@ -10,7 +10,7 @@ chosen token fed to the next step on the device). ``e2e`` is the same through th
 entry point (``Engine.step``), token ids crossing the host in both directions every step.
 ``prefill`` is one 2,048-token prompt through the step function. ``roofline`` relates the
 decode step to the bytes it has to read: every weight once and the cache of the live
-requests. ``points`` holds decode at batch 1 and 64.
+requests. ``points`` holds decode at batch 1, 16, 32 and 64 and at contexts of 512 and 32,768.
 
 Two more workloads, each printing one JSON line of its own (the default line is unchanged):
 
@@ -723,6 +723,12 @@ def kernel_case(name: str, batch: int, context: int) -> int:
         w = weights(2 * width, hidden, 4)
         run = lambda i: ops.linear_swiglu(a, w[i % 4])
         work = f"{2 * width * hidden * 2 / 1e6:.1f} MB of weights"
+    elif name == "skinny_in_proj":
+        a = torch.randn(batch, hidden, device=device).bfloat16()
+        w = weights(3 * hidden, hidden, 8)
+        ops.skinny_max_rows = max(ops.skinny_max_rows, min(batch, 32))     # this kernel, not the library's
+        run = lambda i: ops.linear(a, w[i % 8])
+        work = f"{3 * hidden * hidden * 2 / 1e6:.1f} MB of weights"
     elif name == "skinny_down":
         a = torch.randn(batch, width, device=device).bfloat16()
         w = weights(hidden, width, 8)
@@ -880,10 +886,10 @@ def main() -> int:
     parser.add_argument("--sequences", type=int, default=64,
                         help="--case batching: requests that run at a time")
     parser.add_argument("--layers", type=int, default=LFM2_1_2B["num_hidden_layers"])
-    parser.add_argument("--skip-points", action="store_true", help="leave out batch 1 and 64")
+    parser.add_argument("--skip-points", action="store_true", help="leave out the other batches and contexts")
     parser.add_argument("--kernel", default=None,
                         help="run one kernel alone instead of the benchmark: skinny_swiglu, "
-                             "skinny_down, decode_attention, prefill_attention, tcgen05_swiglu, "
+                             "skinny_in_proj, skinny_down, decode_attention, prefill_attention, tcgen05_swiglu, "
                              "swapped_swiglu, mixed_attention, sampling, decode_step (the "
                              "whole step, eager, for a launch list)")
     parser.add_argument("--dependent-launches", type=int, default=1,
@@ -926,9 +932,16 @@ def main() -> int:
 
     points = {}
     if not args.skip_points:
-        for batch in (1, 64):
+        for batch in (1, 16, 32, 64):
             s, _, _, _ = time_decode(engine, batch, args.context, warmup, args.steps, seed=2 + batch)
             points[f"decode_b{batch}"] = round(batch * args.steps / s, 1)
+        # other context lengths at the default batch, as far as the pool made for batch 64 holds
+        for context in (512, 32768):
+            if context != args.context and args.batch * context <= 64 * args.context \
+                    and context > warmup + args.steps + 66:
+                s, _, _, _ = time_decode(engine, args.batch, context, warmup, args.steps,
+                                         seed=100 + context)
+                points[f"decode_b{args.batch}_context{context}"] = round(args.batch * args.steps / s, 1)
 
     e2e_seconds, h2d, d2h = time_e2e(engine, args.batch, args.context, warmup, args.steps, seed=7)
     e2e_value = args.batch * args.steps / e2e_seconds

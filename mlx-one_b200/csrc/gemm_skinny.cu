@@ -134,50 +134,78 @@ skinny_gemm_kernel(const bf16* a, int lda, const bf16* __restrict__ w,
 
     // Copies the next slice of this warp's stream into its ring: 16 rows x 8 pieces of 16 B;
     // piece c of row r is stored at piece c ^ ((r & 1) << 2), which keeps the 16-byte reads of a
-    // quarter warp on different banks. What depends only on the lane is worked out once.
+    // quarter warp on different banks. A lane copies piece c = lane % 8 of the rows lane / 8,
+    // + 4, + 8, + 12. The kernel's time is the number of instructions that a warp issues (four
+    // warps a scheduler, each waiting on its own copies), so the walk keeps a pointer and adds
+    // to it instead of working the address out for every slice, and a slice that lies inside
+    // K and a row that lies inside the block's range are the cases without a test.
     static_assert((STAGES & (STAGES - 1)) == 0, "the ring size must be a power of two");
-    uint32_t piece_dst[4];
-    int piece_row[4], piece_k[4];
-    size_t piece_src[4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const int piece = lane + 32 * i;
-        const int r = piece >> 3, c = piece & 7;
-        piece_row[i] = r;
-        piece_k[i] = c * 8;
-        piece_dst[i] = ring_address + r * 128 + ((c ^ ((r & 1) << 2)) << 4);
-        piece_src[i] = (size_t)r * k + c * 8;
-    }
+    const int piece_row = lane >> 3, piece_k = (lane & 7) * 8;
+    const uint32_t piece_dst = ring_address + piece_row * 128 + (((lane & 7) ^ ((piece_row & 1) << 2)) << 4);
+    const size_t slice_step = (size_t)WARPS_K * SLICE;         // elements between a warp's slices
+    const size_t four_rows = (size_t)4 * k;
     int fetch_tile = 0, fetch_slice = 0, fetched = 0;
-    auto fetch = [&]() {
-        const int k0 = (wk + fetch_slice * WARPS_K) * SLICE;
-        const uint32_t buffer = (fetched & (STAGES - 1)) * SLOT_BYTES;
+    const bf16* fetch_from = w;       // piece (piece_row, piece_k) of the next slice
+    int fetch_k0 = 0, fetch_rows = 0; // its K offset; rows of its tile from piece_row on
+    auto fetch_position = [&]() {     // at the first slice of `fetch_tile`
         const int row0 = row_begin + (fetch_tile / PARTS) * ROWS;
-        const bf16* base =
-            w + (size_t)(row0 + half * up_offset + (fetch_tile % PARTS) * columns) * k + k0;
+        fetch_k0 = wk * SLICE;
+        fetch_rows = row_end - row0 - piece_row;
+        fetch_from = w + (size_t)(row0 + half * up_offset + (fetch_tile % PARTS) * columns + piece_row) * k +
+                     fetch_k0 + piece_k;
+    };
+    fetch_position();
+    auto fetch = [&]() {
+        const uint32_t to = piece_dst + (fetched & (STAGES - 1)) * SLOT_BYTES;
+        if (fetch_k0 + SLICE <= k) {
+            // rows beyond the block's range are not copied: what the ring holds there only
+            // reaches sums that are never stored
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const bool live = row0 + piece_row[i] < row_end && k0 + piece_k[i] < k;
-            copy16(piece_dst[i] + buffer, live ? base + piece_src[i] : w, live);
+            for (int i = 0; i < 4; ++i)
+                if (4 * i < fetch_rows) copy16(to + i * 4 * 128, fetch_from + i * four_rows, true);
+        } else {                                       // K ends inside the slice: zeros beyond it
+            const bool inside = fetch_k0 + piece_k < k;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const bool live = inside && 4 * i < fetch_rows;
+                copy16(to + i * 4 * 128, live ? fetch_from + i * four_rows : w, live);
+            }
         }
         ++fetched;
-        if (++fetch_slice == mine) { fetch_slice = 0; ++fetch_tile; }
+        if (++fetch_slice == mine) {
+            fetch_slice = 0;
+            ++fetch_tile;
+            fetch_position();
+        } else {
+            fetch_from += slice_step;
+            fetch_k0 += (int)slice_step;
+        }
     };
-    // the activations of the next slice of the stream (TOKEN_RING): 8 tokens x 8 pieces
+    // the activations of the next slice of the stream (TOKEN_RING): 8 tokens x 8 pieces, a lane
+    // piece lane % 8 of the tokens lane / 8 and lane / 8 + 4
     int token_slice = 0, tokens_fetched = 0;
+    const bf16* const tokens_first = a + (size_t)piece_row * lda + wk * SLICE + piece_k;
+    const bf16* tokens_from = tokens_first;
+    int tokens_k0 = wk * SLICE;
+    const uint32_t tokens_dst = piece_dst + SLICE_BYTES;
+    const size_t four_tokens = (size_t)4 * lda;
     auto fetch_tokens = [&]() {
-        const int k0 = (wk + token_slice * WARPS_K) * SLICE;
-        const uint32_t buffer = (tokens_fetched & (STAGES - 1)) * SLOT_BYTES + SLICE_BYTES;
+        const uint32_t to = tokens_dst + (tokens_fetched & (STAGES - 1)) * SLOT_BYTES;
+        const bool inside = tokens_k0 + piece_k < k;
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
-            const int piece = lane + 32 * i;
-            const int token = piece >> 3, c = piece & 7;
-            const bool live = token < m && k0 + c * 8 < k;
-            copy16(ring_address + buffer + token * 128 + ((c ^ ((token & 1) << 2)) << 4),
-                   live ? a + (size_t)token * lda + k0 + c * 8 : a, live);
+            const bool live = inside && piece_row + 4 * i < m;
+            copy16(to + i * 4 * 128, live ? tokens_from + i * four_tokens : a, live);
         }
         ++tokens_fetched;
-        if (++token_slice == mine) token_slice = 0;
+        if (++token_slice == mine) {
+            token_slice = 0;
+            tokens_from = tokens_first;
+            tokens_k0 = wk * SLICE;
+        } else {
+            tokens_from += slice_step;
+            tokens_k0 += (int)slice_step;
+        }
     };
 
 #pragma unroll
@@ -271,12 +299,13 @@ skinny_gemm_kernel(const bf16* a, int lda, const bf16* __restrict__ w,
         __syncthreads();
     } else if (RESIDENT) {
         const int pieces = resident_stride / 16;
-        for (int item = threadIdx.x; item < TOKENS * pieces; item += WARPS * 32) {
-            const int token = item / pieces, c = item % pieces;
-            const bool live = token < m && c * 8 < k;
-            copy16(shared_address(resident) + token * resident_stride +
-                       ((c ^ ((token & 1) << 2)) << 4),
-                   a + (live ? (size_t)token * lda + c * 8 : 0), live);
+        for (int token = warp; token < TOKENS; token += WARPS) {       // a warp a token
+            const uint32_t row_to = shared_address(resident) + token * resident_stride;
+            const bf16* row_from = a + (size_t)token * lda;
+            for (int c = lane; c < pieces; c += 32) {
+                const bool live = token < m && c * 8 < k;
+                copy16(row_to + ((c ^ ((token & 1) << 2)) << 4), live ? row_from + c * 8 : a, live);
+            }
         }
         copy_commit();
         copy_wait<0>();        // also completes the ring's first slices; they are needed at once
@@ -284,19 +313,26 @@ skinny_gemm_kernel(const bf16* a, int lda, const bf16* __restrict__ w,
     }
 
     // activations of the slice at K offset k0: [piece of 32][token group] -> 16 bytes
+    // (resident: a slice is 128 bytes of a token's row, which the swizzle stays inside, so the
+    // lane's place within a slice is worked out once)
+    const unsigned char* resident_lane[2];
+#pragma unroll
+    for (int q = 0; q < 2; ++q)
+        resident_lane[q] = resident + g * resident_stride + (((q * 4 + t) ^ ((g & 1) << 2)) << 4);
+    const bf16* const tokens_lane = a + (size_t)g * lda + t * 8;
     auto load_tokens = [&](int k0, uint4 (&regs)[2][NT]) {
 #pragma unroll
         for (int q = 0; q < 2; ++q)
 #pragma unroll
             for (int nt = 0; nt < NT; ++nt) {
-                const int token = nt * 8 + g, kk = k0 + q * 32 + t * 8;
                 if (RESIDENT) {
-                    const int c = kk >> 3;
                     regs[q][nt] = *reinterpret_cast<const uint4*>(
-                        resident + token * resident_stride + ((c ^ ((token & 1) << 2)) << 4));
+                        resident_lane[q] + nt * 8 * resident_stride + k0 * 2);
                 } else {
-                    regs[q][nt] = (token < m && kk < k) ? load_l2(a + (size_t)token * lda + kk)
-                                                        : make_uint4(0u, 0u, 0u, 0u);
+                    const int token = nt * 8 + g, kk = k0 + q * 32 + t * 8;
+                    regs[q][nt] = (token < m && kk < k)
+                                      ? load_l2(tokens_lane + (size_t)nt * 8 * lda + kk - t * 8)
+                                      : make_uint4(0u, 0u, 0u, 0u);
                 }
             }
     };
@@ -317,15 +353,48 @@ skinny_gemm_kernel(const bf16* a, int lda, const bf16* __restrict__ w,
     }
     int next_slice = mine > 1 ? 1 : 0;       // the slice (within a tile) whose tokens are fetched next
 
-    float held_b = 0.f, held_c = 0.f;        // gated convolution: this thread's B and C
+    // The sum that this thread finishes after every tile (see below): row `r` of the tile for
+    // token `token`, a share of it.
+    constexpr int SPLIT = WARPS * 32 / (ROWS * TOKENS);       // threads a sum: 4, 2 or 1
+    const int item = threadIdx.x / SPLIT, share = threadIdx.x % SPLIT;
+    const int token = item / ROWS, r = item % ROWS;           // rows fastest: neighbours in memory
+    const bool owner = share == 0 && token < m;
+
+    // Gated convolution: this thread's B and C, and what its update reads beside the product.
+    // Those loads are issued before the group's slices are multiplied, not after: three global
+    // round trips in a row at the kernel's end would cost more than the product's stream.
+    float held_b = 0.f, held_c = 0.f;
+    int conv_position = 0;
+    bf16* conv_rows = nullptr;
+    float conv_kept[3] = {0.f, 0.f, 0.f}, conv_weight[4] = {0.f, 0.f, 0.f, 0.f}, conv_bias_value = 0.f;
+    if (EPILOGUE == GATED_CONV && owner) {
+        conv_position = conv.history[token];
+        conv_rows = conv.state + (size_t)conv.slots[token] * (conv.taps - 1) * columns;
+    }
     int index = 0;
     for (int tile = 0; tile < tile_count; ++tile) {
+        if (EPILOGUE == GATED_CONV && tile % PARTS == 0) {
+            const int column = row_begin + (tile / PARTS) * ROWS + r;
+            if (owner && column < row_end) {
+                conv_bias_value = conv.bias != nullptr ? conv.bias[column] : 0.f;
+#pragma unroll
+                for (int s = 0; s < 4; ++s)
+                    if (s < conv.taps) conv_weight[s] = conv.kernel[(size_t)column * conv.taps + s];
+#pragma unroll
+                for (int s = 0; s < 3; ++s)
+                    if (s < conv.taps - 1)     // state row s holds position - (taps - 1) + s; zero before the start
+                        conv_kept[s] = conv_position - (conv.taps - 1) + s >= 0
+                                           ? __bfloat162float(conv_rows[(size_t)s * columns + column]) : 0.f;
+            }
+        }
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
             for (int c = 0; c < 4; ++c) acc[nt][c] = 0.f;
 
-        for (int i = 0; i < mine; ++i, ++index) {
+        // One slice of the stream: `now` holds its activations; without a copy in shared
+        // memory, `next` is loaded for the slice after it.
+        auto consume = [&](int i, uint4 (&now)[2][NT], uint4 (&next)[2][NT]) {
             copy_wait<STAGES - 2>();
             __syncwarp();
             if (fetched < total) {
@@ -335,14 +404,14 @@ skinny_gemm_kernel(const bf16* a, int lda, const bf16* __restrict__ w,
             copy_commit();
             const unsigned char* slice = ring + (index & (STAGES - 1)) * SLOT_BYTES;
             if (RESIDENT) {
-                load_tokens((wk + i * WARPS_K) * SLICE, tokens_now);
+                load_tokens((wk + i * WARPS_K) * SLICE, now);
             } else if (TOKEN_RING) {
 #pragma unroll
                 for (int q = 0; q < 2; ++q)
-                    tokens_now[q][0] = *reinterpret_cast<const uint4*>(
+                    now[q][0] = *reinterpret_cast<const uint4*>(
                         slice + SLICE_BYTES + g * 128 + (((q * 4 + t) ^ ((g & 1) << 2)) << 4));
             } else if (index + 1 < total) {
-                load_tokens((wk + next_slice * WARPS_K) * SLICE, tokens_next);
+                load_tokens((wk + next_slice * WARPS_K) * SLICE, next);
                 if (++next_slice == mine) next_slice = 0;
             }
 #pragma unroll
@@ -354,13 +423,26 @@ skinny_gemm_kernel(const bf16* a, int lda, const bf16* __restrict__ w,
                     slice + (g + 8) * 128 + ((c ^ ((g & 1) << 2)) << 4));
 #pragma unroll
                 for (int nt = 0; nt < NT; ++nt) {
-                    mma_16816(acc[nt], lo.x, hi.x, lo.y, hi.y, tokens_now[q][nt].x,
-                              tokens_now[q][nt].y);
-                    mma_16816(acc[nt], lo.z, hi.z, lo.w, hi.w, tokens_now[q][nt].z,
-                              tokens_now[q][nt].w);
+                    mma_16816(acc[nt], lo.x, hi.x, lo.y, hi.y, now[q][nt].x, now[q][nt].y);
+                    mma_16816(acc[nt], lo.z, hi.z, lo.w, hi.w, now[q][nt].z, now[q][nt].w);
                 }
             }
-            if (!RESIDENT && !TOKEN_RING) {
+            ++index;
+        };
+        if (RESIDENT || TOKEN_RING) {
+            for (int i = 0; i < mine; ++i) consume(i, tokens_now, tokens_next);
+        } else {
+            // The activations come from L2 one slice ahead. Two slices a turn, the two sets of
+            // registers changing roles: a set is first read a whole slice after its loads were
+            // issued. (Moving `next` into `now` at the end of every slice made each slice wait
+            // for its successor's loads.) An odd slice at a tile's end pays that move once.
+            int i = 0;
+            for (; i + 1 < mine; i += 2) {
+                consume(i, tokens_now, tokens_next);
+                consume(i + 1, tokens_next, tokens_now);
+            }
+            if (i < mine) {
+                consume(i, tokens_now, tokens_next);
 #pragma unroll
                 for (int q = 0; q < 2; ++q)
 #pragma unroll
@@ -368,25 +450,55 @@ skinny_gemm_kernel(const bf16* a, int lda, const bf16* __restrict__ w,
             }
         }
 
-        // partial sums of this tile: [warp][row 0..15][token]
+        // Partial sums of this tile: [warp][token][row 0..15]. Every thread of the block adds a
+        // share of one sum (SPLIT threads a sum, neighbours in a warp, each SHARE warps' parts),
+        // then the shares meet by shuffles. So that a warp's loads fall on 32 different banks, the
+        // rows of every second pair of tokens are stored with halves swapped, and a warp's whole
+        // set is turned (its index XOR a multiple of 8 or 16) by the share that will read it.
+        constexpr int SHARE = WARPS_K / SPLIT;
+        constexpr int TURN = SPLIT == 4 ? 8 : 16;
+        static_assert(SPLIT >= 1 && SHARE >= 1 && SPLIT * ROWS * TOKENS == WARPS * 32,
+                      "one share of one sum for every thread");
         float* sums = sums_base + (size_t)(tile & 1) * WARPS * ROWS * TOKENS;
         float* mine_sums = sums + (size_t)warp * ROWS * TOKENS;
+        auto place = [](int token, int r) { return token * ROWS + (r ^ (((token >> 1) & 1) << 3)); };
+        const int my_turn = (wk / SHARE) * TURN;
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
-            mine_sums[g * TOKENS + nt * 8 + 2 * t] = acc[nt][0];
-            mine_sums[g * TOKENS + nt * 8 + 2 * t + 1] = acc[nt][1];
-            mine_sums[(g + 8) * TOKENS + nt * 8 + 2 * t] = acc[nt][2];
-            mine_sums[(g + 8) * TOKENS + nt * 8 + 2 * t + 1] = acc[nt][3];
+            mine_sums[place(nt * 8 + 2 * t, g) ^ my_turn] = acc[nt][0];
+            mine_sums[place(nt * 8 + 2 * t + 1, g) ^ my_turn] = acc[nt][1];
+            mine_sums[place(nt * 8 + 2 * t, g + 8) ^ my_turn] = acc[nt][2];
+            mine_sums[place(nt * 8 + 2 * t + 1, g + 8) ^ my_turn] = acc[nt][3];
         }
         __syncthreads();
-        for (int item = threadIdx.x; item < ROWS * TOKENS; item += WARPS * 32) {
-            const int token = item / ROWS, r = item % ROWS;     // rows fastest: neighbours in memory
-            const int column = row_begin + (tile / PARTS) * ROWS + r;
-            if (token >= m || column >= row_end) continue;
-            float value = 0.f;
+        const int column = row_begin + (tile / PARTS) * ROWS + r;
+        const float* my_share = sums + (size_t)share * SHARE * ROWS * TOKENS + (place(token, r) ^ (share * TURN));
+        // The order of the additions is the same for every number of tokens, so that a token's
+        // result does not depend on how many others the call has: the warps' parts in four
+        // groups, each added up in turn, then (group 0 + group 1) + (group 2 + group 3). A
+        // thread adds 4 / SPLIT of the groups, the shuffles finish the tree.
+        constexpr int LEAF = WARPS_K / 4, GROUPS = 4 / SPLIT;
+        auto shares_sum = [&](const float* from) {
+            float group[GROUPS];
 #pragma unroll
-            for (int wi = 0; wi < WARPS_K; ++wi)
-                value += sums[((size_t)wi * ROWS + r) * TOKENS + token];
+            for (int j = 0; j < GROUPS; ++j) {
+                group[j] = 0.f;
+#pragma unroll
+                for (int wi = 0; wi < LEAF; ++wi)
+                    group[j] += from[(size_t)(j * LEAF + wi) * ROWS * TOKENS];
+            }
+            if (GROUPS == 4) return (group[0] + group[1]) + (group[2] + group[GROUPS - 1]);
+            if (GROUPS == 2) return group[0] + group[GROUPS - 1];
+            return group[0];
+        };
+        float value = shares_sum(my_share), up = 0.f;
+        if (EPILOGUE == SWIGLU) up = shares_sum(my_share + (size_t)WARPS_K * ROWS * TOKENS);
+#pragma unroll
+        for (int across = 1; across < SPLIT; across <<= 1) {
+            value += __shfl_xor_sync(0xffffffffu, value, across);
+            if (EPILOGUE == SWIGLU) up += __shfl_xor_sync(0xffffffffu, up, across);
+        }
+        if (owner && column < row_end) {
             if (bias != nullptr) value += bias[(tile % PARTS) * columns + column];
             if (EPILOGUE == GATED_CONV) {
                 // the three projections are rounded as if they had been stored; a block has one
@@ -398,36 +510,28 @@ skinny_gemm_kernel(const bf16* a, int lda, const bf16* __restrict__ w,
                 } else if (part == 1) {
                     held_c = value;
                 } else {
-                    const int position = conv.history[token];
-                    bf16* rows = conv.state + (size_t)conv.slots[token] * (conv.taps - 1) * columns;
                     const float now = __bfloat162float(__float2bfloat16_rn(held_b * value));
-                    float kept[3] = {0.f, 0.f, 0.f};
-                    float y = conv.bias != nullptr ? conv.bias[column] : 0.f;
+                    float y = conv_bias_value;
 #pragma unroll
                     for (int s = 0; s < 3; ++s)
-                        if (s < conv.taps - 1) {
-                            // state row s holds position - (taps - 1) + s; zero before the start
-                            kept[s] = position - (conv.taps - 1) + s >= 0
-                                          ? __bfloat162float(rows[(size_t)s * columns + column]) : 0.f;
-                            y = fmaf(conv.kernel[(size_t)column * conv.taps + s], kept[s], y);
-                        }
-                    y = fmaf(conv.kernel[(size_t)column * conv.taps + conv.taps - 1], now, y);
+                        if (s < conv.taps - 1) y = fmaf(conv_weight[s], conv_kept[s], y);
+                    float last_weight = conv_weight[0];
+#pragma unroll
+                    for (int s = 1; s < 4; ++s)
+                        if (s == conv.taps - 1) last_weight = conv_weight[s];
+                    y = fmaf(last_weight, now, y);
                     reinterpret_cast<bf16*>(out)[(size_t)token * ldo + column] =
                         __float2bfloat16_rn(held_c * y);
                     if (conv.write_state) {
 #pragma unroll
                         for (int s = 0; s < 2; ++s)
                             if (s + 1 < conv.taps - 1)
-                                rows[(size_t)s * columns + column] = __float2bfloat16_rn(kept[s + 1]);
+                                conv_rows[(size_t)s * columns + column] = __float2bfloat16_rn(conv_kept[s + 1]);
                         if (conv.taps > 1)
-                            rows[(size_t)(conv.taps - 2) * columns + column] = __float2bfloat16_rn(now);
+                            conv_rows[(size_t)(conv.taps - 2) * columns + column] = __float2bfloat16_rn(now);
                     }
                 }
             } else if (EPILOGUE == SWIGLU) {
-                float up = 0.f;
-#pragma unroll
-                for (int wi = 0; wi < WARPS_K; ++wi)
-                    up += sums[((size_t)(WARPS_K + wi) * ROWS + r) * TOKENS + token];
                 if (bias != nullptr) up += bias[up_offset + column];
                 reinterpret_cast<bf16*>(out)[(size_t)token * ldo + column] =
                     __float2bfloat16_rn(value / (1.f + expf(-value)) * up);
@@ -435,7 +539,9 @@ skinny_gemm_kernel(const bf16* a, int lda, const bf16* __restrict__ w,
                 reinterpret_cast<bf16*>(out)[(size_t)token * ldo + column] =
                     __float2bfloat16_rn(value);
             } else if (EPILOGUE == ADD_RESIDUAL) {
-                reinterpret_cast<float*>(out)[(size_t)token * ldo + column] += value;
+                // added where the value lives (one addition per address, so the result is the
+                // same): the thread does not wait for the old value to come and go
+                atomicAdd(reinterpret_cast<float*>(out) + (size_t)token * ldo + column, value);
             } else {
                 reinterpret_cast<float*>(out)[(size_t)token * ldo + column] = value;
             }
