@@ -249,7 +249,7 @@ def fill_requests(engine, prompts, ids):
 
 def time_decode(engine, batch, context, warmup, steps, seed, sampler=None):
     """Device-timed decode: ``steps`` graph replays after ``warmup``; contexts end at
-    ``context``. Returns (seconds, launches per step, mean context)."""
+    ``context``. Returns (seconds, clock record, mean context, kernels launched per step)."""
     import torch
 
     from mlx_one_b200.engine.runner import StepEntry
@@ -258,17 +258,21 @@ def time_decode(engine, batch, context, warmup, steps, seed, sampler=None):
     load_steps = 0
     if sampler:
         load_steps = max(min(2048, context - warmup - steps - 65), 0) // 64 * 64
-    prompt_length = context - max(warmup, 3) - load_steps - steps - 1
+    prompt_length = context - max(warmup, 3) - load_steps - steps - 2
     ids = [f"decode{batch}_{i}" for i in range(batch)]
     prompts = random_prompts(vocab, batch, prompt_length, seed)
     firsts = fill_requests(engine, prompts, ids)
     runner = engine.runner
     entries = [StepEntry(i, [t]) for i, t in zip(ids, firsts)]
+    # the kernels of one decode step at this batch and context, counted where they are launched
+    # (or captured): the first step, alone
     before = engine.model.ops.launches
+    last = runner.decode_steps(entries, 1)[-1].tolist()
+    launches_per_step = engine.model.ops.launches - before
+    entries = [StepEntry(i, [t]) for i, t in zip(ids, last)]
     chosen = runner.decode_steps(entries, max(warmup, 3))
     torch.cuda.synchronize()
     last = chosen[-1].tolist()
-    # launches of one eager step = what the first call launched before it captured
     entries = [StepEntry(i, [t]) for i, t in zip(ids, last)]
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     load_began = None
@@ -296,30 +300,7 @@ def time_decode(engine, batch, context, warmup, steps, seed, sampler=None):
     mean_context = context - 1 - steps / 2
     for request_id in ids:
         engine.cache.close(request_id)
-    return seconds, clocks, mean_context, engine.model.ops.launches - before
-
-
-def count_step_launches(engine, batch):
-    """Kernels that one decode step launches (counted on an eager step of a fresh shape)."""
-    import torch
-
-    from mlx_one_b200.engine.runner import StepEntry
-
-    runner, cache, ops = engine.runner, engine.cache, engine.model.ops
-    ids = [f"count{i}" for i in range(batch)]
-    for request_id in ids:
-        cache.open(request_id)
-    runner.step([StepEntry(i, [1, 2, 3]) for i in ids])
-    graphs, runner.use_graphs = runner.use_graphs, False
-    before = ops.launches
-    logits = runner.step([StepEntry(i, [4], (0,)) for i in ids])
-    ops.argmax(logits)
-    launched = ops.launches - before
-    runner.use_graphs = graphs
-    torch.cuda.synchronize()
-    for request_id in ids:
-        cache.close(request_id)
-    return launched
+    return seconds, clocks, mean_context, launches_per_step
 
 
 def time_e2e(engine, batch, context, warmup, steps, seed):
@@ -922,10 +903,9 @@ def main() -> int:
     state_bytes = sum(g.storage[:, 0].numel() * g.storage.element_size()
                       for g in engine.cache.states)
 
-    launches_per_step = count_step_launches(engine, args.batch)
     sampler = ClockSampler()
-    seconds, clocks, mean_context, _ = time_decode(engine, args.batch, args.context, warmup,
-                                                   args.steps, seed=1, sampler=sampler)
+    seconds, clocks, mean_context, launches_per_step = time_decode(
+        engine, args.batch, args.context, warmup, args.steps, seed=1, sampler=sampler)
     value = args.batch * args.steps / seconds
     step_bytes = weight_bytes + args.batch * (mean_context * kv_per_token + 2 * state_bytes)
     achieved = step_bytes / (seconds / args.steps) / 1e9

@@ -472,6 +472,46 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kv,
     // tile is put into shared memory below, over whatever the copy brought)
     for (; ahead < DECODE_STAGES - 1 && (PREP || tile + ahead * DECODE_WARPS != newest); ++ahead)
         fetch(ahead);
+    // PREP: what the preparation needs beside the projection's row depends on the step's
+    // positions and on constants only, so it is worked out while the projection still runs:
+    // this lane's norm weights and the sines and cosines of its rotation pairs (query layout:
+    // dims 16 kk + 2t, +1, +8 + 2t, +9 + 2t; key layout: dims lane + 32 i and that + HD / 2).
+    float q_scale[PREP ? HD / 16 : 1][4], q_sine[PREP ? HD / 32 : 1][4], q_cosine[PREP ? HD / 32 : 1][4];
+    constexpr int KEY_PAIRS = (HD / 2 + 31) / 32;
+    float k_scale_lo[KEY_PAIRS], k_scale_hi[KEY_PAIRS], k_sine[KEY_PAIRS], k_cosine[KEY_PAIRS];
+    // the warp that will meet the tile with the token's own position prepares its key
+    const bool meets_newest = PREP && prep.write_kv && newest >= tile && newest <= my_last &&
+                              (newest - tile) % DECODE_WARPS == 0;
+    if (PREP) {
+#pragma unroll
+        for (int kk = 0; kk < HD / 16; ++kk)
+#pragma unroll
+            for (int c = 0; c < 4; ++c)
+                q_scale[kk][c] = prep.q_weight != nullptr
+                                     ? prep.q_weight[kk * 16 + (c >> 1) * 8 + 2 * t + (c & 1)] : 1.f;
+#pragma unroll
+        for (int kk = 0; kk < HD / 32; ++kk)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                q_sine[kk][c] = 0.f; q_cosine[kk][c] = 1.f;
+                if (prep.inv_freq != nullptr)
+                    sincosf((float)position * prep.inv_freq[kk * 16 + (c >> 1) * 8 + 2 * t + (c & 1)],
+                            &q_sine[kk][c], &q_cosine[kk][c]);
+            }
+#pragma unroll
+        for (int i = 0; i < KEY_PAIRS; ++i) {
+            const int j = lane + 32 * i;
+            k_scale_lo[i] = k_scale_hi[i] = 1.f; k_sine[i] = 0.f; k_cosine[i] = 1.f;
+            if (meets_newest && j < HD / 2) {
+                if (prep.k_weight != nullptr) {
+                    k_scale_lo[i] = prep.k_weight[j];
+                    k_scale_hi[i] = prep.k_weight[j + HD / 2];
+                }
+                if (prep.inv_freq != nullptr)
+                    sincosf((float)position * prep.inv_freq[j], &k_sine[i], &k_cosine[i]);
+            }
+        }
+    }
     griddep_wait();
     for (; ahead < DECODE_STAGES - 1; ++ahead) fetch(ahead);
 
@@ -507,9 +547,7 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kv,
 #pragma unroll
                 for (int kk = 0; kk < HD / 16; ++kk)
 #pragma unroll
-                    for (int c = 0; c < 4; ++c)
-                        v[kk][c] = v[kk][c] * inv *
-                                   prep.q_weight[kk * 16 + (c >> 1) * 8 + 2 * t + (c & 1)];
+                    for (int c = 0; c < 4; ++c) v[kk][c] = v[kk][c] * inv * q_scale[kk][c];
             }
             if (prep.inv_freq != nullptr) {
                 // dimension j of the first half pairs with j + HD / 2: piece kk with piece kk + HD / 32
@@ -517,18 +555,53 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kv,
                 for (int kk = 0; kk < HD / 32; ++kk)
 #pragma unroll
                     for (int c = 0; c < 4; ++c) {
-                        const int j = kk * 16 + (c >> 1) * 8 + 2 * t + (c & 1);
-                        float sine, cosine;
-                        sincosf((float)position * prep.inv_freq[j], &sine, &cosine);
                         const float a = v[kk][c], b = v[kk + HD / 32][c];
-                        v[kk][c] = a * cosine - b * sine;
-                        v[kk + HD / 32][c] = b * cosine + a * sine;
+                        v[kk][c] = a * q_cosine[kk][c] - b * q_sine[kk][c];
+                        v[kk + HD / 32][c] = b * q_cosine[kk][c] + a * q_sine[kk][c];
                     }
             }
 #pragma unroll
             for (int kk = 0; kk < HD / 16; ++kk) {
                 qb[kk][0] = live ? pack_bf16(v[kk][0], v[kk][1]) : 0u;
                 qb[kk][1] = live ? pack_bf16(v[kk][2], v[kk][3]) : 0u;
+            }
+        }
+    }
+    // The token's own key and value (the warp that will meet their tile): normed and rotated
+    // here from the projection's row, while the first tiles are on their way. Lane e takes dims
+    // e, e + 32, ...: a rotation pair (j, j + HD / 2) lies in one lane.
+    float k_lo[KEY_PAIRS], k_hi[KEY_PAIRS], v_lo[KEY_PAIRS], v_hi[KEY_PAIRS];
+    if (PREP && meets_newest) {
+        constexpr int HALF = HD / 2;
+        const bf16* row = q + (size_t)request * (heads + 2 * kv_heads) * HD;
+        const bf16* k_src = row + (size_t)(heads + kv_head) * HD;
+        const bf16* v_src = row + (size_t)(heads + kv_heads + kv_head) * HD;
+        float sum = 0.f;
+#pragma unroll
+        for (int i = 0; i < KEY_PAIRS; ++i) {
+            const int j = lane + 32 * i;
+            const bool mine = j < HALF;
+            k_lo[i] = mine ? __bfloat162float(k_src[j]) : 0.f;
+            k_hi[i] = mine ? __bfloat162float(k_src[j + HALF]) : 0.f;
+            v_lo[i] = mine ? __bfloat162float(v_src[j]) : 0.f;
+            v_hi[i] = mine ? __bfloat162float(v_src[j + HALF]) : 0.f;
+            sum += k_lo[i] * k_lo[i] + k_hi[i] * k_hi[i];
+        }
+        if (prep.k_weight != nullptr) {
+            sum = warp_sum(sum);
+            const float inv = rsqrtf(sum / (float)HD + prep.eps);
+#pragma unroll
+            for (int i = 0; i < KEY_PAIRS; ++i) {
+                k_lo[i] = k_lo[i] * inv * k_scale_lo[i];
+                k_hi[i] = k_hi[i] * inv * k_scale_hi[i];
+            }
+        }
+        if (prep.inv_freq != nullptr) {
+#pragma unroll
+            for (int i = 0; i < KEY_PAIRS; ++i) {
+                const float a = k_lo[i], b = k_hi[i];
+                k_lo[i] = a * k_cosine[i] - b * k_sine[i];
+                k_hi[i] = b * k_cosine[i] + a * k_sine[i];
             }
         }
     }
@@ -556,52 +629,10 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kv,
         const bf16* v_tile = k_tile + KEYS * T::STRIDE;
         const int first = tile * KEYS;
         if (PREP && tile == newest && prep.write_kv) {
-            // The token's own key and value: normed and rotated here from the projection's row,
-            // put into the tile over what the copy brought, and written to the request's page by
-            // the first block of this key head. Lane e takes dims e, e + 32, ...: a rotation
-            // pair (j, j + HD / 2) lies in one lane.
+            // The token's own key and value, prepared before the loop: put into the tile over
+            // what the copy brought, and written to the request's page by the first block of
+            // this key head.
             constexpr int HALF = HD / 2;
-            constexpr int PAIRS = (HALF + 31) / 32;      // pairs (j, j + HALF) of a lane: j = lane + 32 i
-            const bf16* row = q + (size_t)request * (heads + 2 * kv_heads) * HD;
-            const bf16* k_src = row + (size_t)(heads + kv_head) * HD;
-            const bf16* v_src = row + (size_t)(heads + kv_heads + kv_head) * HD;
-            float k_lo[PAIRS], k_hi[PAIRS], v_lo[PAIRS], v_hi[PAIRS];
-            float sum = 0.f;
-#pragma unroll
-            for (int i = 0; i < PAIRS; ++i) {
-                const int j = lane + 32 * i;
-                const bool mine = j < HALF;
-                k_lo[i] = mine ? __bfloat162float(k_src[j]) : 0.f;
-                k_hi[i] = mine ? __bfloat162float(k_src[j + HALF]) : 0.f;
-                v_lo[i] = mine ? __bfloat162float(v_src[j]) : 0.f;
-                v_hi[i] = mine ? __bfloat162float(v_src[j + HALF]) : 0.f;
-                sum += k_lo[i] * k_lo[i] + k_hi[i] * k_hi[i];
-            }
-            if (prep.k_weight != nullptr) {
-                sum = warp_sum(sum);
-                const float inv = rsqrtf(sum / (float)HD + prep.eps);
-#pragma unroll
-                for (int i = 0; i < PAIRS; ++i) {
-                    const int j = lane + 32 * i;
-                    if (j < HALF) {
-                        k_lo[i] = k_lo[i] * inv * prep.k_weight[j];
-                        k_hi[i] = k_hi[i] * inv * prep.k_weight[j + HALF];
-                    }
-                }
-            }
-            if (prep.inv_freq != nullptr) {
-#pragma unroll
-                for (int i = 0; i < PAIRS; ++i) {
-                    const int j = lane + 32 * i;
-                    if (j < HALF) {
-                        float sine, cosine;
-                        sincosf((float)position * prep.inv_freq[j], &sine, &cosine);
-                        const float a = k_lo[i], b = k_hi[i];
-                        k_lo[i] = a * cosine - b * sine;
-                        k_hi[i] = b * cosine + a * sine;
-                    }
-                }
-            }
             bf16* k_row = const_cast<bf16*>(k_tile) + (size_t)(position - first) * T::STRIDE;
             bf16* v_row = const_cast<bf16*>(v_tile) + (size_t)(position - first) * T::STRIDE;
             const int block = pages.page_shift >= 0 ? position >> pages.page_shift
@@ -612,7 +643,7 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kv,
             const size_t at = (((size_t)(page < 0 ? 0 : page) * kv_heads + kv_head) * page_size +
                                (position - block * page_size)) * HD;
 #pragma unroll
-            for (int i = 0; i < PAIRS; ++i) {
+            for (int i = 0; i < KEY_PAIRS; ++i) {
                 const int j = lane + 32 * i;
                 if (j >= HALF) continue;
                 const bf16 ka = __float2bfloat16_rn(k_lo[i]), kb = __float2bfloat16_rn(k_hi[i]);

@@ -98,6 +98,16 @@ __global__ void add_rmsnorm_rows_kernel(float* __restrict__ residual, const T* _
                                         int hidden, float eps) {
     __shared__ float scratch[33];
     griddep_launch();
+    // the norm's weights do not depend on the kernel before this one: they are on their way
+    // while it finishes, and the row's values are the only round trip after it
+    float scale[PASSES][4];
+#pragma unroll
+    for (int pass = 0; pass < PASSES; ++pass) {
+        const int c = (pass * blockDim.x + threadIdx.x) * 4;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) scale[pass][i] = 0.f;
+        if (c < hidden) Vec4<float>::load(weight + c, scale[pass]);
+    }
     griddep_wait();
     const size_t base = (size_t)blockIdx.x * hidden;
     float values[PASSES][4];
@@ -126,10 +136,9 @@ __global__ void add_rmsnorm_rows_kernel(float* __restrict__ residual, const T* _
     for (int pass = 0; pass < PASSES; ++pass) {
         const int c = (pass * blockDim.x + threadIdx.x) * 4;
         if (c < hidden) {
-            float scale[4], result[4];
-            Vec4<float>::load(weight + c, scale);
+            float result[4];
 #pragma unroll
-            for (int i = 0; i < 4; ++i) result[i] = values[pass][i] * inv * scale[i];
+            for (int i = 0; i < 4; ++i) result[i] = values[pass][i] * inv * scale[pass][i];
             Vec4<T>::store(out + base + c, result);
         }
     }

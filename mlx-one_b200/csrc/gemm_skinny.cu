@@ -92,7 +92,8 @@ __global__ void __launch_bounds__(WARPS * 32)
 skinny_gemm_kernel(const bf16* a, int lda, const bf16* __restrict__ w,
                    const float* __restrict__ bias, void* out, int ldo, int m, int n, int k,
                    int up_offset, const float* source, int source_ld,
-                   const float* __restrict__ norm_weight, float eps, ConvUpdate conv) {
+                   const float* __restrict__ norm_weight, float eps, ConvUpdate conv,
+                   int share_base, int share_extra) {
     // A SwiGLU block splits its warps in two halves: the first on 16 gate rows, the second on
     // the 16 matching up rows (measured faster than tiles of 8 + 8 rows, which balance better
     // but pay the per-tile reduction twice as often).
@@ -120,13 +121,15 @@ skinny_gemm_kernel(const bf16* a, int lda, const bf16* __restrict__ w,
     // With at least a tile for every block, blocks take whole tiles (some one more than others:
     // a tile's fixed cost weighs more than the imbalance); with fewer, the rows are spread to
     // within one row, so that every SM streams.
+    // (The shares come from the host as quotient and remainder of tiles, or rows, by blocks: the
+    // first `share_extra` blocks take one more. A division here would stand between the
+    // kernel's start and its first copy, in every one of a step's products.)
     const int whole_tiles = (columns + ROWS - 1) / ROWS;
     const bool by_tiles = whole_tiles >= (int)gridDim.x;
-    const int row_begin = by_tiles ? ROWS * (int)((long long)whole_tiles * blockIdx.x / gridDim.x)
-                                   : (int)((long long)columns * blockIdx.x / gridDim.x);
-    const int row_end = by_tiles
-        ? min(columns, ROWS * (int)((long long)whole_tiles * (blockIdx.x + 1) / gridDim.x))
-        : (int)((long long)columns * (blockIdx.x + 1) / gridDim.x);
+    const int share_begin = (int)blockIdx.x * share_base + min((int)blockIdx.x, share_extra);
+    const int share_end = share_begin + share_base + ((int)blockIdx.x < share_extra ? 1 : 0);
+    const int row_begin = by_tiles ? ROWS * share_begin : share_begin;
+    const int row_end = by_tiles ? min(columns, ROWS * share_end) : share_end;
     const int tile_count = PARTS * ((row_end - row_begin + ROWS - 1) / ROWS);
     const int slices = (k + SLICE - 1) / SLICE;
     const int mine = slices > wk ? (slices - wk + WARPS_K - 1) / WARPS_K : 0;   // per tile
@@ -213,89 +216,109 @@ skinny_gemm_kernel(const bf16* a, int lda, const bf16* __restrict__ w,
         if (p < total) fetch();
         copy_commit();
     }
+    // NORM: the norm's weights do not depend on the kernel before this one either. They wait in
+    // the space of the partial sums (unused until the first tile ends), behind the few floats
+    // through which the warps of a token exchange their sums of squares.
+    float* norm_exchange = sums_base;
+    float* norm_scale = sums_base + 64;
+    if (RESIDENT && NORM) {
+        for (int c = threadIdx.x; c * 4 < k; c += WARPS * 32)
+            copy16(shared_address(norm_scale + c * 4), norm_weight + c * 4, true);
+        copy_commit();
+    }
     griddep_launch();
     griddep_wait();            // from here on the predecessor's results may be read
 
     // resident activations: [token][K] with 16-byte pieces swizzled by the token's parity
     const int resident_stride = ((k + 63) / 64) * 64 * 2;        // bytes per token
     if (RESIDENT && NORM) {
-        // One warp per token. A lane holds its pieces of the row in registers between the sum
-        // of squares and the scaling, so the row crosses from L2 once; all its loads are in
-        // flight together.
-        constexpr int HELD = 8;                       // pieces of 8 values per lane: K <= 2048
+        // All warps: SHARERS warps a token, each a contiguous share of the row. A lane keeps
+        // its first HELD pieces (of 8 values) in registers between the sum of squares and the
+        // scaling, so that a row of up to SHARERS * 32 * HELD * 8 values crosses from L2 once
+        // (longer rows are read again for the scaling); all of a lane's loads are in flight
+        // together. The block reads TOKENS rows of 32-bit values where the plain kernel reads
+        // 16-bit ones, which is what the norm costs here: no kernel of its own, no pass over
+        // memory for its result.
+        constexpr int HELD = 4;
+        constexpr int SHARERS = WARPS / TOKENS > 0 ? WARPS / TOKENS : 1;
+        static_assert(!NORM || TOKENS <= WARPS, "a warp per token at least");
         const int pieces = resident_stride / 16;
-        for (int token = warp; token < TOKENS; token += WARPS) {
-            unsigned char* row_out = resident + token * resident_stride;
-            const float* row = source + (size_t)token * source_ld;
-            uint4 lo[HELD], hi[HELD];
+        const int share = (pieces + SHARERS - 1) / SHARERS;          // pieces of a warp
+        const int token = warp / SHARERS, sharer = warp % SHARERS;
+        const int first_piece = sharer * share;
+        const int end_piece = min(first_piece + share, pieces);
+        unsigned char* row_out = resident + token * resident_stride;
+        const float* row = source + (size_t)token * source_ld;
+        auto squares = [](const uint4& a0, const uint4& a1) {
+            const float v[8] = {__uint_as_float(a0.x), __uint_as_float(a0.y), __uint_as_float(a0.z),
+                                __uint_as_float(a0.w), __uint_as_float(a1.x), __uint_as_float(a1.y),
+                                __uint_as_float(a1.z), __uint_as_float(a1.w)};
             float sum = 0.f;
-            if (token < m) {
 #pragma unroll
-                for (int j = 0; j < HELD; ++j) {
-                    const int c = lane + 32 * j;
-                    if (c * 8 < k) {
-                        lo[j] = load_l2(row + c * 8);
-                        hi[j] = load_l2(row + c * 8 + 4);
-                    } else {
-                        lo[j] = hi[j] = make_uint4(0u, 0u, 0u, 0u);
-                    }
-                }
-#pragma unroll
-                for (int j = 0; j < HELD; ++j) {
-                    const float v[8] = {__uint_as_float(lo[j].x), __uint_as_float(lo[j].y),
-                                        __uint_as_float(lo[j].z), __uint_as_float(lo[j].w),
-                                        __uint_as_float(hi[j].x), __uint_as_float(hi[j].y),
-                                        __uint_as_float(hi[j].z), __uint_as_float(hi[j].w)};
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) sum += v[i] * v[i];
-                }
-                for (int c = lane + 32 * HELD; c * 8 < k; c += 32) {     // longer rows: the rest
-                    const uint4 a0 = load_l2(row + c * 8), a1 = load_l2(row + c * 8 + 4);
-                    const float v[8] = {__uint_as_float(a0.x), __uint_as_float(a0.y),
-                                        __uint_as_float(a0.z), __uint_as_float(a0.w),
-                                        __uint_as_float(a1.x), __uint_as_float(a1.y),
-                                        __uint_as_float(a1.z), __uint_as_float(a1.w)};
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) sum += v[i] * v[i];
-                }
-            }
-            sum = warp_sum(sum);
-            const float inv = rsqrtf(sum / (float)k + eps);
-            auto scaled = [&](const uint4& a0, const uint4& a1, int c) {
-                const float4 w0 = *reinterpret_cast<const float4*>(norm_weight + c * 8);
-                const float4 w1 = *reinterpret_cast<const float4*>(norm_weight + c * 8 + 4);
-                __nv_bfloat162 p0 = __floats2bfloat162_rn(__uint_as_float(a0.x) * inv * w0.x,
-                                                          __uint_as_float(a0.y) * inv * w0.y);
-                __nv_bfloat162 p1 = __floats2bfloat162_rn(__uint_as_float(a0.z) * inv * w0.z,
-                                                          __uint_as_float(a0.w) * inv * w0.w);
-                __nv_bfloat162 p2 = __floats2bfloat162_rn(__uint_as_float(a1.x) * inv * w1.x,
-                                                          __uint_as_float(a1.y) * inv * w1.y);
-                __nv_bfloat162 p3 = __floats2bfloat162_rn(__uint_as_float(a1.z) * inv * w1.z,
-                                                          __uint_as_float(a1.w) * inv * w1.w);
-                uint4 packed;
-                packed.x = *reinterpret_cast<uint32_t*>(&p0);
-                packed.y = *reinterpret_cast<uint32_t*>(&p1);
-                packed.z = *reinterpret_cast<uint32_t*>(&p2);
-                packed.w = *reinterpret_cast<uint32_t*>(&p3);
-                return packed;
-            };
+            for (int i = 0; i < 8; ++i) sum += v[i] * v[i];
+            return sum;
+        };
+        uint4 lo[HELD], hi[HELD];
+        float sum = 0.f;
+        if (token < m) {
 #pragma unroll
             for (int j = 0; j < HELD; ++j) {
-                const int c = lane + 32 * j;
-                if (c < pieces) {
+                const int c = first_piece + lane + 32 * j;
+                if (c < end_piece && c * 8 < k) {
+                    lo[j] = load_l2(row + c * 8);
+                    hi[j] = load_l2(row + c * 8 + 4);
+                } else {
+                    lo[j] = hi[j] = make_uint4(0u, 0u, 0u, 0u);
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < HELD; ++j) sum += squares(lo[j], hi[j]);
+            for (int c = first_piece + lane + 32 * HELD; c < end_piece && c * 8 < k; c += 32)
+                sum += squares(load_l2(row + c * 8), load_l2(row + c * 8 + 4));
+        }
+        sum = warp_sum(sum);
+        if (lane == 0) norm_exchange[token * SHARERS + sharer] = sum;
+        copy_wait<0>();        // the norm's weights (and the ring's first slices) have landed
+        __syncthreads();
+        float total = 0.f;
+#pragma unroll
+        for (int i = 0; i < SHARERS; ++i) total += norm_exchange[token * SHARERS + i];
+        const float inv = rsqrtf(total / (float)k + eps);
+        auto scaled = [&](const uint4& a0, const uint4& a1, int c) {
+            const float4 w0 = *reinterpret_cast<const float4*>(norm_scale + c * 8);
+            const float4 w1 = *reinterpret_cast<const float4*>(norm_scale + c * 8 + 4);
+            __nv_bfloat162 p0 = __floats2bfloat162_rn(__uint_as_float(a0.x) * inv * w0.x,
+                                                      __uint_as_float(a0.y) * inv * w0.y);
+            __nv_bfloat162 p1 = __floats2bfloat162_rn(__uint_as_float(a0.z) * inv * w0.z,
+                                                      __uint_as_float(a0.w) * inv * w0.w);
+            __nv_bfloat162 p2 = __floats2bfloat162_rn(__uint_as_float(a1.x) * inv * w1.x,
+                                                      __uint_as_float(a1.y) * inv * w1.y);
+            __nv_bfloat162 p3 = __floats2bfloat162_rn(__uint_as_float(a1.z) * inv * w1.z,
+                                                      __uint_as_float(a1.w) * inv * w1.w);
+            uint4 packed;
+            packed.x = *reinterpret_cast<uint32_t*>(&p0);
+            packed.y = *reinterpret_cast<uint32_t*>(&p1);
+            packed.z = *reinterpret_cast<uint32_t*>(&p2);
+            packed.w = *reinterpret_cast<uint32_t*>(&p3);
+            return packed;
+        };
+        if (token < TOKENS) {
+#pragma unroll
+            for (int j = 0; j < HELD; ++j) {
+                const int c = first_piece + lane + 32 * j;
+                if (c < end_piece) {
                     const uint4 packed = (token < m && c * 8 < k) ? scaled(lo[j], hi[j], c)
                                                                   : make_uint4(0u, 0u, 0u, 0u);
                     *reinterpret_cast<uint4*>(row_out + ((c ^ ((token & 1) << 2)) << 4)) = packed;
                 }
             }
-            for (int c = lane + 32 * HELD; c < pieces; c += 32) {
+            for (int c = first_piece + lane + 32 * HELD; c < end_piece; c += 32) {
                 uint4 packed = make_uint4(0u, 0u, 0u, 0u);
                 if (token < m && c * 8 < k)
                     packed = scaled(load_l2(row + c * 8), load_l2(row + c * 8 + 4), c);
                 *reinterpret_cast<uint4*>(row_out + ((c ^ ((token & 1) << 2)) << 4)) = packed;
             }
         }
-        copy_wait<0>();
         __syncthreads();
     } else if (RESIDENT) {
         const int pieces = resident_stride / 16;
@@ -576,6 +599,9 @@ cudaError_t launch(const void* a, int lda, const void* w, const float* bias, voi
     const int grid = columns < g_sm_count ? columns : g_sm_count;
     const int whole_tiles = (columns + ROWS - 1) / ROWS;
     const int tiles_a_block = PARTS * (whole_tiles >= grid ? (whole_tiles + grid - 1) / grid : 1);
+    // what the blocks share out: whole tiles when there is one for every block, else rows
+    const int units = whole_tiles >= grid ? whole_tiles : columns;
+    const int share_base = units / grid, share_extra = units % grid;
     const size_t rings = (size_t)WARPS * STAGES * SLICE_BYTES;
     const size_t sums = (size_t)2 * WARPS * ROWS * 8 * NT * sizeof(float);
     const size_t resident = (size_t)8 * NT * ((k + 63) / 64) * 64 * 2;
@@ -585,15 +611,17 @@ cudaError_t launch(const void* a, int lda, const void* w, const float* bias, voi
     const size_t token_ring = !use_resident && NT == 1 ? (size_t)WARPS * STAGES * 8 * SLICE * 2 : 0;
     const size_t shared = rings + token_ring + sums + (use_resident ? resident : 0);
     cudaError_t err;
-    if (EPILOGUE != GATED_CONV && norm.source != nullptr) {
-        if (!fits) return cudaErrorInvalidValue;
-        constexpr bool WITH_NORM = NT <= 2 && EPILOGUE != GATED_CONV;
+    if (norm.source != nullptr) {
+        // (the norm's weights wait in the space of the partial sums, behind 64 floats)
+        if (!fits || NT > 2 || (size_t)(64 + k) * sizeof(float) > sums) return cudaErrorInvalidValue;
+        constexpr bool WITH_NORM = NT <= 2;
         auto kernel = skinny_gemm_kernel<NT, EPILOGUE, WITH_NORM, WITH_NORM>;
         err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
         if (err != cudaSuccess) return err;
         return launch_kernel(kernel, dim3(grid), dim3(WARPS * 32), shared, stream, true,
                              (const bf16*)nullptr, 0, (const bf16*)w, bias, out, ldo, m, n, k,
-                             up_offset, norm.source, norm.ld, norm.weight, norm.eps, conv);
+                             up_offset, norm.source, norm.ld, norm.weight, norm.eps, conv,
+                             share_base, share_extra);
     }
     if (use_resident) {
         auto kernel = skinny_gemm_kernel<NT, EPILOGUE, (NT <= 2), false>;
@@ -601,14 +629,16 @@ cudaError_t launch(const void* a, int lda, const void* w, const float* bias, voi
         if (err != cudaSuccess) return err;
         return launch_kernel(kernel, dim3(grid), dim3(WARPS * 32), shared, stream, true,
                              (const bf16*)a, lda, (const bf16*)w, bias, out, ldo, m, n, k,
-                             up_offset, (const float*)nullptr, 0, (const float*)nullptr, 0.f, conv);
+                             up_offset, (const float*)nullptr, 0, (const float*)nullptr, 0.f, conv,
+                             share_base, share_extra);
     }
     auto kernel = skinny_gemm_kernel<NT, EPILOGUE, false, false>;
     err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
     if (err != cudaSuccess) return err;
     return launch_kernel(kernel, dim3(grid), dim3(WARPS * 32), shared, stream, true, (const bf16*)a,
                          lda, (const bf16*)w, bias, out, ldo, m, n, k, up_offset,
-                         (const float*)nullptr, 0, (const float*)nullptr, 0.f, conv);
+                         (const float*)nullptr, 0, (const float*)nullptr, 0.f, conv,
+                             share_base, share_extra);
 }
 
 template <int EPILOGUE>
@@ -697,7 +727,38 @@ MLXONE_API int mlxone_gemm_skinny_norm_fits(int m, int k) {
     const int nt = m <= 8 ? 1 : 2;
     const size_t sums = (size_t)2 * WARPS * ROWS * 8 * nt * sizeof(float);
     const size_t resident = (size_t)8 * nt * ((k + 63) / 64) * 64 * 2;
-    return rings + sums + resident <= SHARED_LIMIT ? 1 : 0;
+    return rings + sums + resident <= SHARED_LIMIT && (size_t)(64 + k) * sizeof(float) <= sums ? 1 : 0;
+}
+
+// As mlxone_gemm_skinny_conv with a = RMSNorm(source; norm_weight, eps) in bfloat16, the norm
+// applied while the rows are brought in (sizes as for mlxone_gemm_skinny_norm_fits).
+MLXONE_API int mlxone_gemm_skinny_conv_norm(const float* source, int source_ld,
+                                            const float* norm_weight, float eps, const void* w,
+                                            const float* bias, void* out, int m, int channels, int k,
+                                            const float* conv_kernel, const float* conv_bias,
+                                            void* state, const int* slots, const int* history,
+                                            int taps, int write_state, cudaStream_t stream) {
+    if (m == 0 || channels == 0) return 0;
+    MLXONE_REQUIRE(mlxone_gemm_skinny_norm_fits(m, k), "gemm_skinny_conv_norm: %d rows of %d do not fit", m, k);
+    MLXONE_REQUIRE(channels > 0 && source_ld % 4 == 0 &&
+                       (reinterpret_cast<uintptr_t>(source) & 15) == 0 &&
+                       (reinterpret_cast<uintptr_t>(norm_weight) & 15) == 0 &&
+                       (reinterpret_cast<uintptr_t>(w) & 15) == 0,
+                   "gemm_skinny_conv_norm: operands must be 16-byte aligned");
+    MLXONE_REQUIRE(taps >= 1 && taps <= 4, "gemm_skinny_conv_norm: kernel width %d is not in 1..4", taps);
+    ConvUpdate conv;
+    conv.kernel = conv_kernel; conv.bias = conv_bias; conv.state = static_cast<bf16*>(state);
+    conv.slots = slots; conv.history = history; conv.taps = taps; conv.write_state = write_state;
+    NormInput norm;
+    norm.source = source; norm.ld = source_ld; norm.weight = norm_weight; norm.eps = eps;
+    const cudaError_t err = launch_for_rows<GATED_CONV>(nullptr, 0, w, bias, out, channels, m,
+                                                        3 * channels, k, 0, stream, norm, conv);
+    if (err != cudaSuccess) {
+        mlxone_set_error("gemm_skinny_conv_norm: launch failed: %s", cudaGetErrorString(err));
+        return 2;
+    }
+    MLXONE_LAUNCH_CHECK("gemm_skinny_conv_norm");
+    return 0;
 }
 
 // As mlxone_gemm_skinny with a = RMSNorm(source; norm_weight, eps) in bfloat16, the norm applied

@@ -61,18 +61,27 @@ class CudaOps:
         self.launches = 0
         self.tensor_core_attention = True
         self.skinny_products = True
-        # applying a norm inside the product that consumes it saves a launch but delays the
-        # product's start; with dependent launches the separate norm kernel is hidden behind
-        # the next product's weight prefetch and is faster, so this is off by default
-        self.fused_norms = False
+        # A norm applied inside the product that consumes it (the skinny product reads the 32-bit
+        # rows, all warps sharing the sums of squares, the norm's weights staged before the wait
+        # for the kernel before it): no norm kernel, but every block reads rows of twice the size.
+        # Decode steps of the 1.2B shape at 4096 keys: batch 1 / 2 / 4 / 6 0.578 / 0.588 / 0.615 /
+        # 0.644 ms against 0.597 / 0.610 / 0.642 / 0.660 ms with the norm kernel; batch 8 0.68
+        # against 0.67 ms, batch 16 0.95 against 0.89 ms. So up to `fused_norm_max_rows` rows.
+        self.fused_norms = True
+        self.fused_norm_max_rows = 6
         self.tcgen05_min_rows = 128
         self.tcgen05_attention = True     # prefill attention with tcgen05 where it takes the geometry
-        # decode attention: up to 8 key splits merged by a thread-block cluster through distributed
-        # shared memory instead of a scratch buffer and a merge kernel (one launch fewer a layer).
-        # Decode steps of the 1.2B shape: batch 8 at 512 / 2048 / 4096 keys 0.634 / 0.677 / 0.691 ms
-        # against 0.645 / 0.684 / 0.702 ms with the merge kernel; batch 8 at 8192 keys, batch 1
-        # and batch 2 at 32768 keys the same either way (more than 12 splits keep the merge kernel)
+        # decode attention: key splits merged by a thread-block cluster through distributed shared
+        # memory instead of a scratch buffer and a merge kernel (one launch fewer a layer), for up
+        # to `cluster_merge_max_splits` splits. Measured inside the decode step of the 1.2B shape at
+        # 4096 keys (the kernel before attention is the qkv product, whose blocks still hold their
+        # SMs' shared memory when the clusters are placed): clusters of 2 and 3 (batch 20 to 32)
+        # 1.004 against 1.036 ms and 1.08 against 1.12 ms; clusters of 8 at batch 8 take either
+        # 19.5 or 31 us a launch where nine splits and the merge kernel take 17.5 + 3 us
+        # (0.686 against 0.667 ms a step); clusters of 4 at batch 12 (16 rows, four of them
+        # fillers) 37 against 23.6 us a launch, at batch 16 29 against 30 us.
         self.cluster_merge = True
+        self.cluster_merge_max_splits = 3
         # a step of single tokens: q/k norm, rotation and the page write inside the decode
         # attention kernel instead of a kernel of their own before it
         self.fused_decode_attention = True
@@ -274,6 +283,7 @@ class CudaOps:
         """Whether RMSNorm(residual) can be applied by the skinny product while it loads its
         input (bfloat16, up to 16 rows, the rows fit into shared memory)."""
         return (self.fused_norms and self.skinny_products and dtype == torch.bfloat16
+                and residual.shape[0] <= self.fused_norm_max_rows
                 and residual.dtype == torch.float32 and residual.is_contiguous()
                 and bool(self.lib.mlxone_gemm_skinny_norm_fits(residual.shape[0], residual.shape[1])))
 
@@ -407,9 +417,25 @@ class CudaOps:
     def linear_short_conv(self, a, w, w_bias, *, kernel, bias, taps, ctx, view, write):
         """short_conv(linear(a, w, w_bias)): for a decode step of few rows one kernel, the
         convolution's update being the product's epilogue; else the two operations."""
-        if (not isinstance(a, NormedInput) and ctx.max_portion == 1
-                and a.shape[0] == ctx.requests and taps <= 4 and w.shape[0] % 3 == 0
-                and view.state.dtype == torch.bfloat16 and self._skinny(a, w, fused=True)):
+        fits = (ctx.max_portion == 1 and a.shape[0] == ctx.requests and taps <= 4
+                and w.shape[0] % 3 == 0 and view.state.dtype == torch.bfloat16)
+        if isinstance(a, NormedInput) and fits:
+            # the norm while the rows are loaded, the product, the convolution's update: one kernel
+            self._need(w, torch.bfloat16, "w")
+            self._need(kernel, torch.float32, "conv kernel")
+            if w.shape[1] != a.residual.shape[1]:
+                raise KernelError(f"matrix product of {tuple(a.shape)} with {tuple(w.shape)}^T")
+            hidden = w.shape[0] // 3
+            out = torch.empty((a.shape[0], hidden), dtype=a.dtype, device=self.device)
+            self._call("mlxone_gemm_skinny_conv_norm", _c_void_p(_ptr(a.residual)),
+                       _c_int(a.residual.stride(0)), _c_void_p(_ptr(a.weight)), _c_float(a.eps),
+                       _c_void_p(_ptr(w)), _c_void_p(_ptr(w_bias)), _c_void_p(_ptr(out)),
+                       _c_int(a.shape[0]), _c_int(hidden), _c_int(a.shape[1]),
+                       _c_void_p(_ptr(kernel)), _c_void_p(_ptr(bias)), _c_void_p(_ptr(view.state)),
+                       _c_void_p(_ptr(view.slots)), _c_void_p(_ptr(ctx.history)), _c_int(taps),
+                       _c_int(1 if write else 0))
+            return out
+        if not isinstance(a, NormedInput) and fits and self._skinny(a, w, fused=True):
             self._check_product(a, w)
             self._need(kernel, torch.float32, "conv kernel")
             hidden = w.shape[0] // 3
@@ -561,10 +587,9 @@ class CudaOps:
         (None when a thread-block cluster merges them, or there is one split)."""
         splits = self.decode_splits(requests, heads, kv_heads, head_dim, width * view.page_size,
                                     window)
-        if self.cluster_merge and 8 < splits <= 12 and width * view.page_size <= 8192:
-            splits = 8          # with more keys a ninth split is worth more than the merge kernel
+        clustered = self.cluster_merge and splits <= min(self.cluster_merge_max_splits, 8)
         partial = None
-        if splits > 8 or (splits > 1 and not self.cluster_merge):
+        if splits > 1 and not clustered:
             partial = torch.empty(requests * heads * splits * (head_dim + 2),
                                   dtype=torch.float32, device=self.device)
         return splits, partial

@@ -164,10 +164,11 @@ def _skinny_product_case(ops, m, n, k):
     # the same product with the RMSNorm of 32-bit rows applied while they are loaded
     from mlx_one_b200.parts import NormedInput
     rows = torch.randn(m, k).to(DEVICE)
-    ops.fused_norms = True
+    kept = (ops.fused_norms, ops.fused_norm_max_rows)
+    ops.fused_norms, ops.fused_norm_max_rows = True, 16       # as many rows as the kernel takes
     fits = ops.can_fuse_norm(rows, torch.bfloat16)
-    ops.fused_norms = False
-    assert fits or m > 8 or k > 4096
+    ops.fused_norms, ops.fused_norm_max_rows = kept
+    assert fits or m > 16 or k > 4000
     if fits:
         scale = (1 + 0.1 * torch.randn(k)).to(DEVICE)
         lazy = NormedInput(rows, scale, 1e-5, torch.bfloat16, ops)
@@ -339,6 +340,26 @@ def _linear_short_conv_case(ops, plain, rows, hidden, k, taps, bias):
                                        state_cpu[slots[r], valid].float(), **tolerance(dtype))
     untouched = [s for s in range(rows + 2) if s not in slots.tolist()]
     assert torch.equal(state_gpu.cpu()[untouched], state[untouched])
+    # the same with the RMSNorm of 32-bit rows applied while they are loaded: still one kernel
+    from mlx_one_b200.parts import NormedInput
+    source = torch.randn(rows, k).to(DEVICE)
+    kept = (ops.fused_norms, ops.fused_norm_max_rows)
+    ops.fused_norms, ops.fused_norm_max_rows = True, 16       # as many rows as the kernel takes
+    fits = ops.can_fuse_norm(source, dtype)
+    ops.fused_norms, ops.fused_norm_max_rows = kept
+    assert fits or rows > 16
+    if fits and taps <= 4:
+        lazy = NormedInput(source, (1 + 0.1 * torch.randn(k)).to(DEVICE), 1e-5, dtype, ops)
+        states = [state.clone().to(DEVICE) for _ in range(2)]
+        results = []
+        for given, held in zip((lazy, lazy.materialize()), states):
+            before = ops.launches
+            results.append(ops.linear_short_conv(given, to(w), to(w_bias), kernel=to(kernel),
+                                                 bias=to(conv_bias), taps=taps, ctx=ctx,
+                                                 view=StateView(held, to(slots), need), write=True))
+            assert ops.launches - before == 1
+        torch.testing.assert_close(results[0].float(), results[1].float(), **tolerance(dtype))
+        torch.testing.assert_close(states[0].float(), states[1].float(), **tolerance(dtype))
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
@@ -452,13 +473,14 @@ def test_attention_decode_tensor_cores(ops, plain, heads, kv_heads, head_dim, pa
     """One token per request: contexts at the edges of tiles, split over several blocks, which
     are merged by a kernel of its own or, as a thread-block cluster, among themselves."""
     far = (0, 5) if histories[0] > 100 and window is None else None
-    ops.cluster_merge = cluster
+    kept = (ops.cluster_merge, ops.cluster_merge_max_splits)
+    ops.cluster_merge, ops.cluster_merge_max_splits = cluster, 8       # clusters of every size
     try:
         attention_case(ops, plain, torch.bfloat16, heads, kv_heads, head_dim, page_size,
                        portions=[1] * 5, histories=histories, window=window, tensor_cores=True,
                        spike=far)
     finally:
-        ops.cluster_merge = False
+        ops.cluster_merge, ops.cluster_merge_max_splits = kept
 
 
 @pytest.mark.parametrize("heads,kv_heads,page_size", [
@@ -542,14 +564,15 @@ def test_decode_attention_from_the_fused_projection(ops, plain, heads, kv_heads,
                      scale=head_dim ** -0.5, window=window, write=True)
     kv_gpu = kv.clone().to(DEVICE)
     on_gpu = lambda v: None if v is None else v.to(DEVICE)
-    ops.cluster_merge = cluster
+    kept = (ops.cluster_merge, ops.cluster_merge_max_splits)
+    ops.cluster_merge, ops.cluster_merge_max_splits = cluster, 8       # clusters of every size
     before = ops.launches
     try:
         got = ops.qkv_attention(qkv.to(DEVICE), q_weight=on_gpu(q_weight), k_weight=on_gpu(k_weight),
                                 rotary=None if rotary is None else (rotary[0].to(DEVICE), head_dim),
                                 ctx=ctx, view=PagedView(kv_gpu, table, page_size, need), **arguments)
     finally:
-        ops.cluster_merge = True
+        ops.cluster_merge, ops.cluster_merge_max_splits = kept
     assert ops.launches - before <= 2                   # one kernel, or one and the merge kernel
     kv_cpu = kv.clone()
     want = plain.qkv_attention(qkv, q_weight=q_weight, k_weight=k_weight, rotary=rotary,
