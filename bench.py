@@ -657,6 +657,66 @@ def decode_step_case(batch: int, context: int) -> int:
     return 0
 
 
+def decode_timeline_case(batch: int, context: int) -> int:
+    """Where a decode step's time goes, kernel by kernel, as the step really runs (CUDA-graph
+    replays with dependent launches): the device's own activity records, taken through
+    torch.profiler, give every kernel's begin and end. A kernel's "exposed" time is the part of
+    it after every earlier kernel of the step has ended, which is what it adds to the step (a
+    kernel that starts early and waits for its predecessor shows a long duration and a short
+    exposed time). Prints one JSON line; times under the profiler are for shares, the step's
+    own time is the benchmark's."""
+    import collections
+
+    import torch
+    from torch.profiler import ProfilerActivity, profile
+
+    from mlx_one_b200.engine.runner import StepEntry
+
+    engine = build_engine(LFM2_1_2B, LFM2_1_2B["num_hidden_layers"], batch, context, 64)
+    engine.model.ops.set_dependent_launches(True)
+    runner = engine.runner
+    ids = [f"step{i}" for i in range(batch)]
+    prompts = random_prompts(engine.model.spec.vocab_size, batch, context - 40, seed=3)
+    firsts = fill_requests(engine, prompts, ids)
+    last = runner.decode_steps([StepEntry(i, [t]) for i, t in zip(ids, firsts)], 16)[-1].tolist()
+    torch.cuda.synchronize()
+    with profile(activities=[ProfilerActivity.CUDA]) as record:
+        runner.decode_steps([StepEntry(i, [t]) for i, t in zip(ids, last)], 8)
+        torch.cuda.synchronize()
+    engine.model.ops.check_errors()
+    kernels = sorted(((e.name, e.time_range.start, e.time_range.end) for e in record.events()
+                      if e.device_type.name == "CUDA" and "Memcpy" not in e.name
+                      and "Memset" not in e.name), key=lambda k: k[1])
+    # a step ends with the kernel that moves the chosen tokens on
+    ends = [i for i, k in enumerate(kernels) if "decode_advance" in k[0]]
+    if len(ends) < 6:
+        print(json.dumps({"kernel": "decode_timeline", "error": "no steps in the record"}))
+        return 1
+    steps = [(ends[i] + 1, ends[i + 1] + 1) for i in range(2, len(ends) - 1)]
+    calls, duration, exposed = collections.Counter(), collections.Counter(), collections.Counter()
+    total = 0.0
+    for begin, end in steps:
+        horizon = kernels[begin][1]
+        total += kernels[end - 1][2] - horizon
+        for name, start, stop in kernels[begin:end]:
+            short = name.replace("void (anonymous namespace)::", "").replace("void ", "")
+            short = short.split("(")[0]
+            calls[short] += 1
+            duration[short] += stop - start
+            exposed[short] += max(stop - max(horizon, start), 0.0) + max(start - horizon, 0.0)
+            horizon = max(horizon, stop)
+    count = len(steps)
+    table = [{"kernel": name, "calls_per_step": calls[name] // count,
+              "us_each": round(duration[name] / calls[name], 2),
+              "exposed_us_each": round(exposed[name] / calls[name], 2),
+              "exposed_us_per_step": round(exposed[name] / count, 1)}
+             for name in sorted(exposed, key=exposed.get, reverse=True)]
+    print(json.dumps({"kernel": "decode_timeline", "batch": batch, "context": context,
+                      "steps_averaged": count, "us_per_step": round(total / count, 1),
+                      "kernels": table}))
+    return 0
+
+
 def kernel_case(name: str, batch: int, context: int) -> int:
     """Runs one kernel of the step alone a few times at the benchmark's sizes and prints its
     time: the case that the ncu summaries under profiles/ were captured on."""
@@ -666,6 +726,8 @@ def kernel_case(name: str, batch: int, context: int) -> int:
 
     if name == "decode_step":
         return decode_step_case(batch, context)
+    if name == "decode_timeline":
+        return decode_timeline_case(batch, context)
 
     from mlx_one_b200.kernels import default_ops
     from mlx_one_b200.parts.base import PagedKeyValues, PagedView, StepContext
@@ -872,7 +934,8 @@ def main() -> int:
                         help="run one kernel alone instead of the benchmark: skinny_swiglu, "
                              "skinny_in_proj, skinny_down, decode_attention, prefill_attention, tcgen05_swiglu, "
                              "swapped_swiglu, mixed_attention, sampling, decode_step (the "
-                             "whole step, eager, for a launch list)")
+                             "whole step, eager, for a launch list), decode_timeline (where "
+                             "the graph-replayed step's time goes, kernel by kernel)")
     parser.add_argument("--dependent-launches", type=int, default=1,
                         help="1: kernels of a decode step may start while the one before ends")
     args = parser.parse_args()
