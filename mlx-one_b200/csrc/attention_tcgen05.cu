@@ -46,13 +46,12 @@ using bf16 = __nv_bfloat16;
 constexpr int HD = 64;
 constexpr int ROWS = 128;              // query rows per block
 constexpr int STAGES = 3;              // ring of key/value tiles
-// Threads that share a query row. One: a thread owns its row's scores of a tile and all of its
-// output, and the softmax warps exchange nothing. (Two threads per row, each with half of the keys
-// and of the output, were faster while the output was kept in registers; with the output in
-// tensor memory one is: 8192 tokens 556 -> 603 TFLOP/s.)
-constexpr int PARTS = 1;
-constexpr int COPY_WARP = 4 * PARTS, MMA_WARP = 4 * PARTS + 1;
-constexpr int THREADS = (4 * PARTS + 2) * 32;     // softmax warps, the copy warp, the product warp
+// PARTS (a parameter of the kernel): threads that share a query row, each for its share of a
+// tile's keys and of the output dimensions. One: a thread owns its row's scores of a tile and
+// all of its output, and the softmax warps exchange nothing, which is the faster form when an SM
+// has several items to overlap (8192 tokens: 603 against 556 TFLOP/s). Two: a tile's softmax
+// takes half as long, which is what counts when a block has one item and nothing beside it, the
+// portion of a prompt in a step of decodes (see the launch).
 constexpr int WAIT_LIMIT = 1 << 24;
 constexpr int ERROR_WAIT = 9;
 constexpr int Q_BYTES = ROWS * HD * 2;
@@ -257,8 +256,8 @@ struct Item {
     int tile_count;
 };
 
-template <int KEYS>
-__global__ void __launch_bounds__(THREADS, Shape<KEYS>::BLOCKS_PER_SM)
+template <int KEYS, int PARTS>
+__global__ void __launch_bounds__((4 * PARTS + 2) * 32, Shape<KEYS>::BLOCKS_PER_SM)
 attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q,
                          const __grid_constant__ CUtensorMap map_kv, long long value_rows,
                          const int* __restrict__ block_table, int table_width, int page_size,
@@ -267,6 +266,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q,
                          int heads, int kv_heads, float scale_log2, int window, int token_tiles,
                          int* __restrict__ error_flag) {
     using S = Shape<KEYS>;
+    constexpr int COPY_WARP = 4 * PARTS, MMA_WARP = 4 * PARTS + 1;
+    constexpr int THREADS = (4 * PARTS + 2) * 32;     // softmax warps, the copy warp, the product warp
     constexpr int Q_BUFFERS = S::Q_BUFFERS, K_BYTES = S::K_BYTES, STAGE_BYTES = S::STAGE_BYTES;
     constexpr int P_BYTES = S::P_BYTES, TMEM_COLUMNS = S::TMEM_COLUMNS;
     extern __shared__ unsigned char shared_raw[];
@@ -386,9 +387,9 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q,
             const int* table = block_table + (size_t)item.request * table_width;
             const int last_position = item.first_position + item.tokens_here - 1;
             const int lowest = window > 0 ? max(item.first_position - window + 1, 0) : 0;
-            for (int j = 0; j < item.tile_count && ok; ++j, ++t) {
-                const int s = t % STAGES;
-                // this box's rows in the cache, if some query row may see its keys
+            // this lane's box of the item's tile j: its rows in the cache, if some query row
+            // may see its keys
+            auto box_row = [&](int j) {
                 long long row = -1;
                 const int key = (item.tile_first + j) * KEYS + lane * box_keys;
                 if (lane < boxes && key <= last_position && key + box_keys - 1 >= lowest) {
@@ -397,6 +398,11 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q,
                     if (page >= 0)
                         row = ((long long)page * kv_heads + item.kv_head) * page_size + key % page_size;
                 }
+                return row;
+            };
+            for (int j = 0; j < item.tile_count && ok; ++j, ++t) {
+                const int s = t % STAGES;
+                const long long row = box_row(j);
                 const int live = __popc(__ballot_sync(0xffffffffu, row >= 0));
                 if (lane == 0) {
                     ok = barrier_wait(kv_empty(s), ((t / STAGES) & 1) ^ 1, error_flag);
@@ -750,13 +756,19 @@ MLXONE_API int mlxone_attention_prefill_tcgen05(const void* q, const void* kv, c
     long long blocks = all_items < resident ? all_items : resident;
     if ((all_items + blocks - 1) / blocks > MAX_ITEMS) blocks = (all_items + MAX_ITEMS - 1) / MAX_ITEMS;
     const int shared = small_tiles ? Shape<64>::SHARED_BYTES : Shape<128>::SHARED_BYTES;
-    auto kernel = small_tiles ? attention_tcgen05_kernel<64> : attention_tcgen05_kernel<128>;
+    // fewer items than SMs (a prompt's portion beside a step's decodes): every block has one
+    // item and walks its key tiles one after the other, so two threads share a row's softmax
+    const bool shared_rows = all_items < g_sm_count;
+    const int threads = ((shared_rows ? 2 : 1) * 4 + 2) * 32;
+    auto kernel = small_tiles ? attention_tcgen05_kernel<64, 1>
+                              : shared_rows ? attention_tcgen05_kernel<128, 2>
+                                            : attention_tcgen05_kernel<128, 1>;
     const cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, shared);
     if (err != cudaSuccess) {
         mlxone_set_error("attention_prefill_tcgen05: %s", cudaGetErrorString(err));
         return 2;
     }
-    kernel<<<dim3((unsigned)blocks), THREADS, shared, stream>>>(
+    kernel<<<dim3((unsigned)blocks), threads, shared, stream>>>(
         map_q, map_kv, value_rows, block_table, table_width, page_size, box_keys, request_start,
         history, static_cast<bf16*>(out), requests, heads, kv_heads, scale * 1.4426950408889634f,
         window, token_tiles, error_flag);
