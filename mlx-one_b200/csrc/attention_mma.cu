@@ -1024,6 +1024,21 @@ MLXONE_API int mlxone_attention_decode(const void* q, const void* kv, const int*
     return 0;
 }
 
+// The merge of key splits alone: partial [items, splits, head_dim + 2] (unnormalised output,
+// maximum, sum) -> out [items, head_dim] bfloat16. For kernels that leave their splits to it.
+MLXONE_API int mlxone_attention_merge(const float* partial, void* out, int items, int splits,
+                                      int head_dim, cudaStream_t stream) {
+    if (items == 0) return 0;
+    MLXONE_REQUIRE(items > 0 && splits >= 1 && partial != nullptr, "attention_merge: bad sizes");
+#define CALL(HD)                                                                                  \
+    launch_kernel(attention_merge_kernel<HD>, dim3((items + 3) / 4), dim3(128), 0, stream, true, \
+                  partial, (bf16*)out, items, splits)
+    MLXONE_HEAD_DIMS(CALL)
+#undef CALL
+    MLXONE_LAUNCH_CHECK("attention_merge");
+    return 0;
+}
+
 // 1 if mlxone_attention_decode_fused takes this head size: a multiple of 32 up to 128.
 MLXONE_API int mlxone_attention_decode_fused_supports(int head_dim) {
     return head_dim % 32 == 0 && head_dim >= 32 && head_dim <= 128 ? 1 : 0;

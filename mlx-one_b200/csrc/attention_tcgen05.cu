@@ -252,8 +252,9 @@ struct Item {
     int q_token;            // first token of the tile among all tokens of the step
     int tokens_here;        // tokens of the tile that belong to the portion
     int first_position;     // position of the first token in its request
-    int tile_first;         // first key tile
-    int tile_count;
+    int tile_first;         // first key tile (of this item's split)
+    int tile_count;         // 0: a split without keys (it only reports that it saw none)
+    int split;
 };
 
 template <int KEYS, int PARTS>
@@ -264,7 +265,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q,
                          int box_keys, const int* __restrict__ request_start,
                          const int* __restrict__ history, bf16* __restrict__ out, int requests,
                          int heads, int kv_heads, float scale_log2, int window, int token_tiles,
-                         int* __restrict__ error_flag) {
+                         int splits, float* __restrict__ partial, int* __restrict__ error_flag) {
     using S = Shape<KEYS>;
     constexpr int COPY_WARP = 4 * PARTS, MMA_WARP = 4 * PARTS + 1;
     constexpr int THREADS = (4 * PARTS + 2) * 32;     // softmax warps, the copy warp, the product warp
@@ -285,7 +286,11 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q,
     // the end (the last tiles of a causal prompt walk the most keys). They are dealt out in
     // rounds of gridDim.x, every other round in reverse, so that the block with the heaviest
     // item of one round gets the lightest of the next and all blocks walk about as many keys.
-    const int all_items = token_tiles * kv_heads;
+    // (With `splits` > 1 an item is cut further, by key tiles: split s of an item walks its share
+    // of the item's key tiles and leaves an unnormalised output with its maximum and sum in
+    // `partial`, [token, head, split][HD + 2], which a merge kernel adds up. That is for launches
+    // with fewer items than SMs, whose blocks would otherwise walk long rows of tiles alone.)
+    const int all_items = token_tiles * kv_heads * splits;
     const int rounds = all_items / (int)gridDim.x, rest = all_items % (int)gridDim.x;
     const int last_place = (rounds & 1) ? (int)gridDim.x - 1 - (int)blockIdx.x : (int)blockIdx.x;
     const int mine = rounds + (last_place < rest ? 1 : 0);
@@ -294,8 +299,9 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q,
         const int index = k * gridDim.x + ((k & 1) ? gridDim.x - 1 - blockIdx.x : blockIdx.x);
         Item item;
         item.request = -1;
-        item.kv_head = index % kv_heads;
-        int left = index / kv_heads;
+        item.split = index % splits;
+        item.kv_head = (index / splits) % kv_heads;
+        int left = index / splits / kv_heads;
         for (int r = 0; r < requests; ++r) {
             const int first = request_start[r], count = request_start[r + 1] - first;
             const int tiles = (count + tile_tokens - 1) / tile_tokens;
@@ -309,6 +315,12 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q,
                 const int lowest = window > 0 ? max(item.first_position - window + 1, 0) : 0;
                 item.tile_first = lowest / KEYS;
                 item.tile_count = last_position / KEYS - item.tile_first + 1;
+                if (splits > 1) {
+                    const int share = (item.tile_count + splits - 1) / splits;
+                    const int end = item.tile_first + item.tile_count;
+                    item.tile_first += item.split * share;
+                    item.tile_count = max(min(share, end - item.tile_first), 0);
+                }
                 break;
             }
             left -= tiles;
@@ -370,7 +382,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q,
         int taken = 0, t = 0;
         for (int n = 0; n < mine && ok; ++n) {
             const Item item = items[n];
-            if (item.request < 0) continue;
+            if (item.request < 0 || item.tile_count <= 0) continue;
             if (lane == 0) {
                 const int qb = taken % Q_BUFFERS;
                 ok = barrier_wait(q_empty(qb), ((taken / Q_BUFFERS) & 1) ^ 1, error_flag);
@@ -423,7 +435,8 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q,
             // a place in the walk: item n, its tile j; `taken` and `t` as above
             struct Place { int n, j, taken, t; };
             auto settle = [&](Place& place) {          // skips items without work
-                while (place.n < mine && items[place.n].request < 0) ++place.n;
+                while (place.n < mine &&
+                       (items[place.n].request < 0 || items[place.n].tile_count <= 0)) ++place.n;
             };
             auto step = [&](Place place) {
                 if (place.j + 1 < items[place.n].tile_count) {
@@ -505,6 +518,20 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q,
             const Item item = items[n];
             if (item.request < 0) continue;
             const bool valid = token < item.tokens_here;
+            // where this row's part of the split's result goes (splits > 1)
+            float* split_row = partial == nullptr ? nullptr
+                : partial + (((size_t)(item.q_token + token) * heads + item.kv_head * group +
+                              row % group) * splits + item.split) * (HD + 2);
+            if (item.tile_count <= 0) {
+                // a split without keys: nothing was loaded or multiplied, the row reports zeros
+                // with a maximum of minus infinity, which the merge gives no weight
+                if (valid && split_row != nullptr) {
+#pragma unroll
+                    for (int d = 0; d < MY_DIMS; ++d) split_row[part * MY_DIMS + d] = 0.f;
+                    if (part == 0) { split_row[HD] = -INFINITY; split_row[HD + 1] = 0.f; }
+                }
+                continue;
+            }
             const int position = item.first_position + token;
             const int last_position = item.first_position + item.tokens_here - 1;
             const int limit_hi = valid ? position : -1;
@@ -626,7 +653,13 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q,
 #pragma unroll
                 for (int other = 0; other < PARTS; ++other) l += sums[other * ROWS + row];
             }
-            if (ok && valid) {
+            if (ok && valid && split_row != nullptr) {
+                // unnormalised, against m: the merge scales the splits to their common maximum
+#pragma unroll
+                for (int d = 0; d < MY_DIMS; d += 2)       // (a row of HD + 2 floats is 8-byte aligned)
+                    *reinterpret_cast<float2*>(split_row + part * MY_DIMS + d) = make_float2(o[d], o[d + 1]);
+                if (part == 0) { split_row[HD] = m; split_row[HD + 1] = l; }
+            } else if (ok && valid) {
                 const float inv = l > 0.f ? 1.f / l : 0.f;
                 const int head = item.kv_head * group + row % group;
                 bf16* dst = out + ((size_t)(item.q_token + token) * heads + head) * HD + part * MY_DIMS;
@@ -691,13 +724,41 @@ MLXONE_API int mlxone_attention_tcgen05_supports(int head_dim, int heads, int kv
     return supported(head_dim, heads, kv_heads, page_size) && find_encoder() ? 1 : 0;
 }
 
+// Into how many parts, by keys, a launch should cut its items: more than one when there are
+// fewer items (tiles of 128 query rows x key heads) than SMs and the contexts (up to
+// `max_context` keys) are long enough for at least six tiles of 64 keys a part. The caller then
+// gives `partial`, tokens x heads x splits x (64 + 2) floats, and merges it afterwards
+// (mlxone_attention_merge).
+MLXONE_API int mlxone_attention_tcgen05_splits(int tokens, int requests, int heads, int kv_heads,
+                                               int max_context) {
+    if (tokens <= 0 || requests <= 0 || kv_heads <= 0 || heads % kv_heads != 0) return 1;
+    if (g_sm_count == 0) {
+        int device = 0;
+        cudaGetDevice(&device);
+        cudaDeviceGetAttribute(&g_sm_count, cudaDevAttrMultiProcessorCount, device);
+        if (g_sm_count <= 0) g_sm_count = 148;
+    }
+    const int tile_tokens = ROWS / (heads / kv_heads);
+    if (tile_tokens < 1) return 1;
+    const long long items = (long long)((tokens + tile_tokens - 1) / tile_tokens + requests) * kv_heads;
+    if (items >= g_sm_count) return 1;
+    long long splits = 2LL * g_sm_count / items;
+    const long long by_keys = max_context / 64 / 6;
+    if (splits > by_keys) splits = by_keys;
+    if (splits > 8) splits = 8;
+    return splits < 1 ? 1 : (int)splits;
+}
+
 // q: [tokens, heads, 64] bfloat16; kv: [2, pages, kv_heads, page_size, 64]; out: [tokens, heads * 64].
+// splits > 1 (with partial, see mlxone_attention_tcgen05_splits): the items are cut by keys and
+// `out` is left for the merge to write.
 MLXONE_API int mlxone_attention_prefill_tcgen05(const void* q, const void* kv, const int* block_table,
                                                 int table_width, int page_size, int pages,
                                                 const int* request_start, const int* history,
                                                 void* out, int tokens, int requests, int heads,
                                                 int kv_heads, int head_dim, float scale, int window,
-                                                int* error_flag, cudaStream_t stream) {
+                                                int splits, float* partial, int* error_flag,
+                                                cudaStream_t stream) {
     if (tokens == 0) return 0;
     MLXONE_REQUIRE(tokens > 0 && requests > 0, "attention_prefill_tcgen05: bad sizes");
     MLXONE_REQUIRE(supported(head_dim, heads, kv_heads, page_size),
@@ -719,10 +780,14 @@ MLXONE_API int mlxone_attention_prefill_tcgen05(const void* q, const void* kv, c
         cudaDeviceGetAttribute(&g_sm_count, cudaDevAttrMultiProcessorCount, device);
         if (g_sm_count <= 0) g_sm_count = 148;
     }
+    MLXONE_REQUIRE(splits >= 1 && splits <= 64 && (splits == 1 || partial != nullptr),
+                   "attention_prefill_tcgen05: %d splits need a scratch buffer", splits);
+    if (splits == 1) partial = nullptr;
     const int token_tiles = (tokens + tile_tokens - 1) / tile_tokens + requests;     // an upper bound
-    const long long all_items = (long long)token_tiles * kv_heads;
-    // tiles of 64 keys and two blocks an SM when there are items for all of those blocks
-    const bool small_tiles = all_items >= 2LL * g_sm_count;
+    const long long all_items = (long long)token_tiles * kv_heads * splits;
+    // tiles of 64 keys and two blocks an SM when there are items for all of those blocks, or
+    // when the items are cut by keys (their parts then run side by side)
+    const bool small_tiles = all_items >= 2LL * g_sm_count || splits > 1;
     const int keys = small_tiles ? 64 : 128;
     const int box_keys = page_size < keys ? page_size : keys;
     CUtensorMap map_q, map_kv;
@@ -758,7 +823,7 @@ MLXONE_API int mlxone_attention_prefill_tcgen05(const void* q, const void* kv, c
     const int shared = small_tiles ? Shape<64>::SHARED_BYTES : Shape<128>::SHARED_BYTES;
     // fewer items than SMs (a prompt's portion beside a step's decodes): every block has one
     // item and walks its key tiles one after the other, so two threads share a row's softmax
-    const bool shared_rows = all_items < g_sm_count;
+    const bool shared_rows = !small_tiles && all_items < g_sm_count;
     const int threads = ((shared_rows ? 2 : 1) * 4 + 2) * 32;
     auto kernel = small_tiles ? attention_tcgen05_kernel<64, 1>
                               : shared_rows ? attention_tcgen05_kernel<128, 2>
@@ -771,7 +836,7 @@ MLXONE_API int mlxone_attention_prefill_tcgen05(const void* q, const void* kv, c
     kernel<<<dim3((unsigned)blocks), threads, shared, stream>>>(
         map_q, map_kv, value_rows, block_table, table_width, page_size, box_keys, request_start,
         history, static_cast<bf16*>(out), requests, heads, kv_heads, scale * 1.4426950408889634f,
-        window, token_tiles, error_flag);
+        window, token_tiles, splits, partial, error_flag);
     MLXONE_LAUNCH_CHECK("attention_prefill_tcgen05");
     return 0;
 }

@@ -71,6 +71,8 @@ class CudaOps:
         self.fused_norm_max_rows = 6
         self.tcgen05_min_rows = 128
         self.tcgen05_attention = True     # prefill attention with tcgen05 where it takes the geometry
+        # ... and with the keys of its few items cut into parts when a launch has fewer items than SMs
+        self.prefill_key_splits = True
         # decode attention: key splits merged by a thread-block cluster through distributed shared
         # memory instead of a scratch buffer and a merge kernel (one launch fewer a layer), for up
         # to `cluster_merge_max_splits` splits. Measured inside the decode step of the 1.2B shape at
@@ -542,13 +544,34 @@ class CudaOps:
             if (self.tcgen05_attention and q.dtype == torch.bfloat16
                     and self.lib.mlxone_attention_tcgen05_supports(
                         _c_int(head_dim), _c_int(heads), _c_int(kv_heads), _c_int(view.page_size))):
+                # few query tiles (a prompt's portion beside a step's decodes): their keys are
+                # cut into parts that run side by side, and a merge follows
+                bound = min(ctx.max_context, width * view.page_size)
+                if window:
+                    bound = min(bound, window + ctx.max_portion)
+                splits = 1
+                if self.prefill_key_splits:
+                    splits = self.lib.mlxone_attention_tcgen05_splits(
+                        _c_int(tokens - singles), _c_int(rest), _c_int(heads), _c_int(kv_heads),
+                        _c_int(bound))
+                partial = None
+                if splits > 1:
+                    partial = torch.empty(tokens * heads * splits * (head_dim + 2),
+                                          dtype=torch.float32, device=self.device)
                 self._call("mlxone_attention_prefill_tcgen05", _c_void_p(_ptr(q)),
                            _c_void_p(_ptr(view.kv)), _c_void_p(_ptr(table)),
                            _c_int(width), _c_int(view.page_size), _c_int(pages),
                            _c_void_p(_ptr(starts)), _c_void_p(_ptr(history)),
                            _c_void_p(_ptr(out)), _c_int(tokens), _c_int(rest),
                            _c_int(heads), _c_int(kv_heads), _c_int(head_dim), _c_float(scale),
-                           _c_int(window or 0), _c_void_p(_ptr(self.error_flag)))
+                           _c_int(window or 0), _c_int(splits), _c_void_p(_ptr(partial)),
+                           _c_void_p(_ptr(self.error_flag)))
+                if partial is not None:
+                    # (the leading single tokens are the decode kernel's: their rows stay)
+                    skip = singles * heads * splits * (head_dim + 2)
+                    self._call("mlxone_attention_merge", _c_void_p(_ptr(partial[skip:])),
+                               _c_void_p(_ptr(out[singles:])), _c_int((tokens - singles) * heads),
+                               _c_int(splits), _c_int(head_dim))
             else:
                 self._call("mlxone_attention_prefill", _c_void_p(_ptr(q)),
                            _c_void_p(_ptr(view.kv)), _c_void_p(_ptr(table)),

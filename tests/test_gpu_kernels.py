@@ -497,7 +497,36 @@ def test_attention_prefill_tcgen05(ops, plain, heads, kv_heads, page_size, windo
                    portions=[7, 1, 300, 2, 128, 33], histories=[0, 200, 500, 64, 128, 1000],
                    window=window, tensor_cores=True, tcgen05=True,
                    spike=(2, 5 if window is None else 700))
-    assert ops.launches - before == 1
+    assert ops.launches - before <= 2           # with few key heads: cut by keys, and a merge
+
+
+@pytest.mark.parametrize("heads,kv_heads,page_size", [(24, 8, 16), (32, 8, 16), (4, 2, 8), (5, 1, 64)])
+@pytest.mark.parametrize("window", [None, 300, 1000])
+@pytest.mark.parametrize("portions,histories", [([512], [1100]), ([3, 200, 1], [5000, 0, 77]),
+                                                 ([130], [0])])
+def test_attention_prefill_tcgen05_key_splits(ops, plain, heads, kv_heads, page_size, window,
+                                              portions, histories):
+    """Fewer items than SMs (a prompt's portion beside a step's decodes): the items' keys are cut
+    into parts that run side by side and a merge kernel adds them up. Parts without keys (rows
+    early in a prompt, a window that ends before the part), one far key that must show, and the
+    same launch uncut."""
+    far = (0, 5) if window is None and histories[0] > 64 else None
+    before = ops.launches
+    attention_case(ops, plain, torch.bfloat16, heads, kv_heads, 64, page_size, portions=portions,
+                   histories=histories, window=window, tensor_cores=True, tcgen05=True, spike=far)
+    cut = ops.launches - before
+    kept, ops.prefill_key_splits = ops.prefill_key_splits, False
+    try:
+        before = ops.launches
+        attention_case(ops, plain, torch.bfloat16, heads, kv_heads, 64, page_size,
+                       portions=portions, histories=histories, window=window, tensor_cores=True,
+                       tcgen05=True, spike=far)
+        assert ops.launches - before == 1
+    finally:
+        ops.prefill_key_splits = kept
+    assert cut in (1, 2)
+    if portions == [512] and window is None:
+        assert cut == 2                 # this one is cut: the kernel and the merge
 
 
 @pytest.mark.parametrize("heads,kv_heads,page_size", [(32, 8, 16), (8, 4, 8), (6, 6, 64),
