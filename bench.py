@@ -994,7 +994,7 @@ def main() -> int:
     products = None if args.skip_points else product_fractions(model, args.batch, peak)
 
     line = {
-        "metric": "decode tok/s at batch 8 (LFM2-1.2B shape, bf16, context 4096)",
+        "metric": f"decode tok/s at batch {args.batch} (LFM2-1.2B shape, bf16, context {args.context})",
         "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps,
         "warmup": warmup, "ms_per_step": round(seconds / args.steps * 1e3, 4),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",

@@ -361,7 +361,7 @@ skinny_gemm_kernel(const bf16* a, int lda, const bf16* __restrict__ w,
     };
 
     float acc[NT][4];
-    uint4 tokens_now[2][NT], tokens_next[2][NT];
+    uint4 tokens_now[2][NT], tokens_next[2][NT], tokens_after[2][NT];
     if (TOKEN_RING) {
         // the activations of the slices whose weights are already on their way, then all of it
         // has to land once; from here on a slice's weights and activations travel together
@@ -372,9 +372,11 @@ skinny_gemm_kernel(const bf16* a, int lda, const bf16* __restrict__ w,
         copy_wait<0>();
         __syncwarp();
     } else if (!RESIDENT && total > 0) {
+        // the activations come from L2 two slices ahead (see the slice loop)
         load_tokens(wk * SLICE, tokens_now);
+        if (total > 1) load_tokens((wk + (mine > 1 ? 1 : 0) * WARPS_K) * SLICE, tokens_next);
     }
-    int next_slice = mine > 1 ? 1 : 0;       // the slice (within a tile) whose tokens are fetched next
+    int next_slice = 2 % max(mine, 1);       // the slice (within a tile) whose tokens are fetched next
 
     // The sum that this thread finishes after every tile (see below): row `r` of the tile for
     // token `token`, a share of it.
@@ -433,7 +435,7 @@ skinny_gemm_kernel(const bf16* a, int lda, const bf16* __restrict__ w,
                 for (int q = 0; q < 2; ++q)
                     now[q][0] = *reinterpret_cast<const uint4*>(
                         slice + SLICE_BYTES + g * 128 + (((q * 4 + t) ^ ((g & 1) << 2)) << 4));
-            } else if (index + 1 < total) {
+            } else if (index + 2 < total) {
                 load_tokens((wk + next_slice * WARPS_K) * SLICE, next);
                 if (++next_slice == mine) next_slice = 0;
             }
@@ -455,21 +457,34 @@ skinny_gemm_kernel(const bf16* a, int lda, const bf16* __restrict__ w,
         if (RESIDENT || TOKEN_RING) {
             for (int i = 0; i < mine; ++i) consume(i, tokens_now, tokens_next);
         } else {
-            // The activations come from L2 one slice ahead. Two slices a turn, the two sets of
-            // registers changing roles: a set is first read a whole slice after its loads were
-            // issued. (Moving `next` into `now` at the end of every slice made each slice wait
-            // for its successor's loads.) An odd slice at a tile's end pays that move once.
-            int i = 0;
-            for (; i + 1 < mine; i += 2) {
-                consume(i, tokens_now, tokens_next);
-                consume(i + 1, tokens_next, tokens_now);
-            }
-            if (i < mine) {
-                consume(i, tokens_now, tokens_next);
+            // The activations come from L2 two slices ahead, through three sets of registers
+            // that change roles: a set is first read two slices after its loads were issued, which
+            // is longer than a trip to L2 takes while the weights stream. Three slices a turn;
+            // what is left of a tile pays one or two moves between the sets (a move waits for
+            // its loads, so it is kept out of the turns).
+            auto move = [&](uint4 (&to)[2][NT], const uint4 (&from)[2][NT]) {
 #pragma unroll
                 for (int q = 0; q < 2; ++q)
 #pragma unroll
-                    for (int nt = 0; nt < NT; ++nt) tokens_now[q][nt] = tokens_next[q][nt];
+                    for (int nt = 0; nt < NT; ++nt) to[q][nt] = from[q][nt];
+            };
+            int i = 0;
+            for (; i + 2 < mine; i += 3) {
+                consume(i, tokens_now, tokens_after);
+                consume(i + 1, tokens_next, tokens_now);
+                consume(i + 2, tokens_after, tokens_next);
+            }
+            if (mine - i == 1) {
+                // used now, loaded after: next and after hold the two slices to come
+                consume(i, tokens_now, tokens_after);
+                move(tokens_now, tokens_next);
+                move(tokens_next, tokens_after);
+            } else if (mine - i == 2) {
+                // used now and next, loaded after and now: after and now hold the slices to come
+                consume(i, tokens_now, tokens_after);
+                consume(i + 1, tokens_next, tokens_now);
+                move(tokens_next, tokens_now);
+                move(tokens_now, tokens_after);
             }
         }
 
