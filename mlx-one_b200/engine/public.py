@@ -60,6 +60,7 @@ class _InFlight:
     ahead: bool = False
     prompt_tokens: int = 0
     flag_at: int = 0                  # where in ``host`` the kernels' error flag lies
+    report: Any = None                # the device tensor being copied, kept until the copy is read
 
 
 class EngineRequestHandle:
@@ -159,6 +160,7 @@ class Engine:
         self._trace_sink = trace_sink          # called with every step's record, if given
         self._pinned: list[torch.Tensor | None] = [None, None]
         self._copy_turn = 0
+        self._copy_stream: Any = None
         self._inflight: _InFlight | None = None
         self._turn = threading.RLock()       # one thread at a time plans, launches and commits
         self._stepped = threading.Condition()   # notified after every turn
@@ -394,7 +396,7 @@ class Engine:
                             if item.request.phase is Phase.PREFILL)
         return _InFlight(list(planned), host, event, len(drawing), bool(drawing),
                          launched_at=started, ahead=ahead, prompt_tokens=prompt_tokens,
-                         flag_at=flag_at)
+                         flag_at=flag_at, report=report if drawing else None)
 
     def _finish(self, inflight: "_InFlight") -> list[Request]:
         sampled: list[int] = []
@@ -510,9 +512,20 @@ class Engine:
         if buffer is None or buffer.numel() < count:
             buffer = torch.zeros(max(count, 256), dtype=torch.int32, pin_memory=True)
             self._pinned[self._copy_turn] = buffer
-        buffer[:count].copy_(report, non_blocking=True)
-        event = torch.cuda.Event()
-        event.record()
+        # On a stream of its own, behind the step: the next step's metadata copy (host to device)
+        # then does not queue behind this one (device to host), and its kernels, which will
+        # overwrite the report at their end, wait for this copy only after their own copy.
+        if self._copy_stream is None:
+            self._copy_stream = torch.cuda.Stream(device=report.device)
+        main = torch.cuda.current_stream(report.device)
+        stepped = torch.cuda.Event()
+        stepped.record(main)
+        self._copy_stream.wait_event(stepped)
+        with torch.cuda.stream(self._copy_stream):
+            buffer[:count].copy_(report, non_blocking=True)
+            event = torch.cuda.Event()
+            event.record(self._copy_stream)
+        self._runner.wait_before_kernels = event
         return buffer, event
 
     def run(self) -> None:

@@ -78,6 +78,9 @@ class Runner:
         # what the host reads back after a step that chose tokens: int32, the tokens of the
         # wanted rows (``last_greedy``, then any filler rows'), then the kernels' error flag
         self.last_report: torch.Tensor | None = None
+        # an event that the next step's kernels (not its metadata copy) wait for: the caller's
+        # copy of ``last_report`` to the host on a stream of its own
+        self.wait_before_kernels: Any = None
         # tokens chosen on the device, by request number (see StepEntry.from_device)
         # (one entry more than there are requests: where filler rows publish theirs)
         self.published = torch.zeros(cache.max_requests + 1, dtype=torch.int32,
@@ -348,6 +351,11 @@ class Runner:
             event = torch.cuda.Event()
             event.record()
             self._events[self._turn] = event
+            if self.wait_before_kernels is not None:
+                # (a copy on another stream that reads what this step's kernels will overwrite:
+                # it has had this step's metadata copy to finish in, so the wait costs nothing)
+                torch.cuda.current_stream(self.device).wait_event(self.wait_before_kernels)
+                self.wait_before_kernels = None
 
         def on_device(name: str) -> torch.Tensor:
             start, size = offsets[name]
