@@ -313,6 +313,8 @@ class Runner:
             history.append(length)
         # filler rows of logits: any valid token row; their tokens are published to the spare entry
         rows.extend([0] * fill_wanted)
+        # every token's row wanted, in order: the logits need no picking of rows
+        every_row = wanted == tokens and rows == list(range(tokens))
         want_index.extend([self.cache.max_requests] * fill_wanted)
         if draw is not None:
             draw = list(draw) + [(1.0, 0, 1.0, 0, 0)] * fill_wanted
@@ -335,7 +337,7 @@ class Runner:
         captured = None
         if decode_only or portions:
             key = (requests, singles, tokens, tuple(widths), wanted, loop is not None, greedy,
-                   draw is not None, any(e.from_device for e in entries))
+                   draw is not None, any(e.from_device for e in entries), every_row)
             captured = self._graphs.get(key)
             if captured is None:
                 captured = _DecodeGraph(torch.empty(cursor, dtype=torch.int32,
@@ -390,7 +392,8 @@ class Runner:
             residual, delta = self.model.forward(ctx)
             if not wanted:
                 return None
-            logits = self.model.logits(residual, delta, on_device("rows")[:wanted])
+            logits = self.model.logits(residual, delta,
+                                       None if every_row else on_device("rows")[:wanted])
             if (greedy or draw is not None) and loop is None:
                 if draw is not None:
                     chosen, _ = self.ops.sample(

@@ -118,9 +118,13 @@ class Model:
                 self.observer(place, residual, delta)
         return residual, delta
 
-    def logits(self, residual, delta, rows: torch.Tensor) -> torch.Tensor:
-        """32-bit logits [len(rows), vocab] at the token rows ``rows`` (int32, device)."""
-        picked, picked_delta = self.ops.gather_rows(residual, delta, rows)
+    def logits(self, residual, delta, rows: torch.Tensor | None) -> torch.Tensor:
+        """32-bit logits [len(rows), vocab] at the token rows ``rows`` (int32, device); None:
+        at every row, in order (a step of single tokens that all want theirs: nothing to pick)."""
+        if rows is None:
+            picked, picked_delta = residual, delta
+        else:
+            picked, picked_delta = self.ops.gather_rows(residual, delta, rows)
         # the output product may apply the norm itself where the kernels can do that
         if self.final_norm.supports_lazy:
             normed = self.final_norm.forward(picked, picked_delta, lazy=True)
