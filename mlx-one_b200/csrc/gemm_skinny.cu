@@ -110,13 +110,21 @@ skinny_gemm_kernel(const bf16* a, int lda, const bf16* __restrict__ w,
     const int g = lane >> 2, t = lane & 3;
     unsigned char* ring = shared_bytes + (size_t)warp * STAGES * SLOT_BYTES;
     const uint32_t ring_address = shared_address(ring);
+    // (gated convolution: every group of 16 channels is three tiles: B, C, x)
+    constexpr int PARTS = EPILOGUE == GATED_CONV ? 3 : 1;
+    // Gated convolution with up to 8 tokens: the three tiles of a group of channels (B, C, x)
+    // leave their partial sums in sections of their own and are added up together after the
+    // third, one barrier a group instead of one a tile. (With 16 tokens the sections do not
+    // fit beside the activations; each tile is then added up by itself.)
+    constexpr bool GROUPED = EPILOGUE == GATED_CONV && NT == 1;
+    constexpr int SECTIONS = GROUPED ? PARTS : 1;
     // two sets of partial sums, used in turn, so that one block-wide barrier per tile is enough
     float* sums_base = reinterpret_cast<float*>(shared_bytes + (size_t)WARPS * STAGES * SLOT_BYTES);
-    unsigned char* resident = reinterpret_cast<unsigned char*>(sums_base + 2 * WARPS * ROWS * TOKENS);
+    unsigned char* resident =
+        reinterpret_cast<unsigned char*>(sums_base + 2 * SECTIONS * WARPS * ROWS * TOKENS);
 
     // this block's rows (of the gate half for SwiGLU) and the tiles that cover them
     // (gated convolution: channels; every group of 16 channels is three tiles: B, C, x)
-    constexpr int PARTS = EPILOGUE == GATED_CONV ? 3 : 1;
     const int columns = EPILOGUE == SWIGLU ? up_offset : n / PARTS;
     // With at least a tile for every block, blocks take whole tiles (some one more than others:
     // a tile's fixed cost weighs more than the imbalance); with fewer, the rows are spread to
@@ -497,8 +505,11 @@ skinny_gemm_kernel(const bf16* a, int lda, const bf16* __restrict__ w,
         constexpr int TURN = SPLIT == 4 ? 8 : 16;
         static_assert(SPLIT >= 1 && SHARE >= 1 && SPLIT * ROWS * TOKENS == WARPS * 32,
                       "one share of one sum for every thread");
-        float* sums = sums_base + (size_t)(tile & 1) * WARPS * ROWS * TOKENS;
-        float* mine_sums = sums + (size_t)warp * ROWS * TOKENS;
+        // (GROUPED: the group's set, this tile's section of it)
+        const int set = GROUPED ? (tile / PARTS) & 1 : tile & 1;
+        const int section = GROUPED ? tile % PARTS : 0;
+        float* sums = sums_base + (size_t)set * SECTIONS * WARPS * ROWS * TOKENS;
+        float* mine_sums = sums + (size_t)(section * WARPS + warp) * ROWS * TOKENS;
         auto place = [](int token, int r) { return token * ROWS + (r ^ (((token >> 1) & 1) << 3)); };
         const int my_turn = (wk / SHARE) * TURN;
 #pragma unroll
@@ -508,6 +519,7 @@ skinny_gemm_kernel(const bf16* a, int lda, const bf16* __restrict__ w,
             mine_sums[place(nt * 8 + 2 * t, g + 8) ^ my_turn] = acc[nt][2];
             mine_sums[place(nt * 8 + 2 * t + 1, g + 8) ^ my_turn] = acc[nt][3];
         }
+        if (GROUPED && section != PARTS - 1) continue;       // the group's last tile adds all three up
         __syncthreads();
         const int column = row_begin + (tile / PARTS) * ROWS + r;
         const float* my_share = sums + (size_t)share * SHARE * ROWS * TOKENS + (place(token, r) ^ (share * TURN));
@@ -529,15 +541,30 @@ skinny_gemm_kernel(const bf16* a, int lda, const bf16* __restrict__ w,
             if (GROUPS == 2) return group[0] + group[GROUPS - 1];
             return group[0];
         };
-        float value = shares_sum(my_share), up = 0.f;
+        float value = shares_sum(my_share + (size_t)(GROUPED ? PARTS - 1 : 0) * WARPS * ROWS * TOKENS);
+        float up = 0.f, first = 0.f, second = 0.f;          // SwiGLU's up; GROUPED: B and C
         if (EPILOGUE == SWIGLU) up = shares_sum(my_share + (size_t)WARPS_K * ROWS * TOKENS);
+        if (GROUPED) {
+            first = shares_sum(my_share);
+            second = shares_sum(my_share + (size_t)WARPS * ROWS * TOKENS);
+        }
 #pragma unroll
         for (int across = 1; across < SPLIT; across <<= 1) {
             value += __shfl_xor_sync(0xffffffffu, value, across);
             if (EPILOGUE == SWIGLU) up += __shfl_xor_sync(0xffffffffu, up, across);
+            if (GROUPED) {
+                first += __shfl_xor_sync(0xffffffffu, first, across);
+                second += __shfl_xor_sync(0xffffffffu, second, across);
+            }
         }
         if (owner && column < row_end) {
             if (bias != nullptr) value += bias[(tile % PARTS) * columns + column];
+            if (GROUPED) {
+                // the three projections are rounded as if they had been stored
+                if (bias != nullptr) { first += bias[column]; second += bias[columns + column]; }
+                held_b = __bfloat162float(__float2bfloat16_rn(first));
+                held_c = __bfloat162float(__float2bfloat16_rn(second));
+            }
             if (EPILOGUE == GATED_CONV) {
                 // the three projections are rounded as if they had been stored; a block has one
                 // item per thread at most, so B and C wait in registers for x
@@ -618,7 +645,9 @@ cudaError_t launch(const void* a, int lda, const void* w, const float* bias, voi
     const int units = whole_tiles >= grid ? whole_tiles : columns;
     const int share_base = units / grid, share_extra = units % grid;
     const size_t rings = (size_t)WARPS * STAGES * SLICE_BYTES;
-    const size_t sums = (size_t)2 * WARPS * ROWS * 8 * NT * sizeof(float);
+    // (the gated convolution with up to 8 tokens keeps a section of sums for each of its three tiles)
+    const size_t sections = EPILOGUE == GATED_CONV && NT == 1 ? 3 : 1;
+    const size_t sums = (size_t)2 * sections * WARPS * ROWS * 8 * NT * sizeof(float);
     const size_t resident = (size_t)8 * NT * ((k + 63) / 64) * 64 * 2;
     // activations in shared memory pay off when a block reuses them for several tiles
     const bool fits = NT <= 2 && rings + sums + resident <= SHARED_LIMIT;
@@ -745,6 +774,17 @@ MLXONE_API int mlxone_gemm_skinny_norm_fits(int m, int k) {
     return rings + sums + resident <= SHARED_LIMIT && (size_t)(64 + k) * sizeof(float) <= sums ? 1 : 0;
 }
 
+// Rows and K up to which mlxone_gemm_skinny_conv_norm applies the norm itself (its partial sums
+// take more room than the plain product's).
+MLXONE_API int mlxone_gemm_skinny_conv_norm_fits(int m, int k) {
+    if (!mlxone_gemm_skinny_norm_fits(m, k)) return 0;
+    const int nt = m <= 8 ? 1 : 2;
+    const size_t rings = (size_t)WARPS * STAGES * SLICE_BYTES;
+    const size_t sums = (size_t)2 * (nt == 1 ? 3 : 1) * WARPS * ROWS * 8 * nt * sizeof(float);
+    const size_t resident = (size_t)8 * nt * ((k + 63) / 64) * 64 * 2;
+    return rings + sums + resident <= SHARED_LIMIT ? 1 : 0;
+}
+
 // As mlxone_gemm_skinny_conv with a = RMSNorm(source; norm_weight, eps) in bfloat16, the norm
 // applied while the rows are brought in (sizes as for mlxone_gemm_skinny_norm_fits).
 MLXONE_API int mlxone_gemm_skinny_conv_norm(const float* source, int source_ld,
@@ -754,7 +794,7 @@ MLXONE_API int mlxone_gemm_skinny_conv_norm(const float* source, int source_ld,
                                             void* state, const int* slots, const int* history,
                                             int taps, int write_state, cudaStream_t stream) {
     if (m == 0 || channels == 0) return 0;
-    MLXONE_REQUIRE(mlxone_gemm_skinny_norm_fits(m, k), "gemm_skinny_conv_norm: %d rows of %d do not fit", m, k);
+    MLXONE_REQUIRE(mlxone_gemm_skinny_conv_norm_fits(m, k), "gemm_skinny_conv_norm: %d rows of %d do not fit", m, k);
     MLXONE_REQUIRE(channels > 0 && source_ld % 4 == 0 &&
                        (reinterpret_cast<uintptr_t>(source) & 15) == 0 &&
                        (reinterpret_cast<uintptr_t>(norm_weight) & 15) == 0 &&

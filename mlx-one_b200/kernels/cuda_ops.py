@@ -421,7 +421,8 @@ class CudaOps:
         convolution's update being the product's epilogue; else the two operations."""
         fits = (ctx.max_portion == 1 and a.shape[0] == ctx.requests and taps <= 4
                 and w.shape[0] % 3 == 0 and view.state.dtype == torch.bfloat16)
-        if isinstance(a, NormedInput) and fits:
+        if (isinstance(a, NormedInput) and fits and self.lib.mlxone_gemm_skinny_conv_norm_fits(
+                _c_int(a.shape[0]), _c_int(a.shape[1]))):
             # the norm while the rows are loaded, the product, the convolution's update: one kernel
             self._need(w, torch.bfloat16, "w")
             self._need(kernel, torch.float32, "conv kernel")
