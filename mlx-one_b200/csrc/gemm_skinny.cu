@@ -112,11 +112,14 @@ skinny_gemm_kernel(const bf16* a, int lda, const bf16* __restrict__ w,
     const uint32_t ring_address = shared_address(ring);
     // (gated convolution: every group of 16 channels is three tiles: B, C, x)
     constexpr int PARTS = EPILOGUE == GATED_CONV ? 3 : 1;
-    // Gated convolution with up to 8 tokens: the three tiles of a group of channels (B, C, x)
-    // leave their partial sums in sections of their own and are added up together after the
-    // third, one barrier a group instead of one a tile. (With 16 tokens the sections do not
-    // fit beside the activations; each tile is then added up by itself.)
-    constexpr bool GROUPED = EPILOGUE == GATED_CONV && NT == 1;
+    // Gated convolution with up to 8 tokens and the activations in shared memory: the three
+    // tiles of a group of channels (B, C, x) leave their partial sums in sections of their own
+    // and are added up together after the third, one barrier a group instead of one a tile.
+    // (With 16 tokens, or rows too long for shared memory, the sections do not fit; each tile is
+    // then added up by itself. Three tiles of output rows a barrier, for the other epilogues,
+    // was measured too: slower, 0.6546 against 0.6460 ms a decode step; the last run's three
+    // reductions and stores stand at the kernel's end.)
+    constexpr bool GROUPED = EPILOGUE == GATED_CONV && NT == 1 && RESIDENT;
     constexpr int SECTIONS = GROUPED ? PARTS : 1;
     // two sets of partial sums, used in turn, so that one block-wide barrier per tile is enough
     float* sums_base = reinterpret_cast<float*>(shared_bytes + (size_t)WARPS * STAGES * SLOT_BYTES);
@@ -645,13 +648,17 @@ cudaError_t launch(const void* a, int lda, const void* w, const float* bias, voi
     const int units = whole_tiles >= grid ? whole_tiles : columns;
     const int share_base = units / grid, share_extra = units % grid;
     const size_t rings = (size_t)WARPS * STAGES * SLICE_BYTES;
-    // (the gated convolution with up to 8 tokens keeps a section of sums for each of its three tiles)
-    const size_t sections = EPILOGUE == GATED_CONV && NT == 1 ? 3 : 1;
-    const size_t sums = (size_t)2 * sections * WARPS * ROWS * 8 * NT * sizeof(float);
+    // (the gated convolution with up to 8 tokens and resident activations keeps a section of
+    // sums for each of its three tiles)
+    auto sums_for = [](bool with_resident) {
+        const size_t sections = EPILOGUE == GATED_CONV && NT == 1 && with_resident ? 3 : 1;
+        return (size_t)2 * sections * WARPS * ROWS * 8 * NT * sizeof(float);
+    };
     const size_t resident = (size_t)8 * NT * ((k + 63) / 64) * 64 * 2;
     // activations in shared memory pay off when a block reuses them for several tiles
-    const bool fits = NT <= 2 && rings + sums + resident <= SHARED_LIMIT;
+    const bool fits = NT <= 2 && rings + sums_for(true) + resident <= SHARED_LIMIT;
     const bool use_resident = fits && (norm.source != nullptr || tiles_a_block >= 2);
+    const size_t sums = sums_for(use_resident);
     const size_t token_ring = !use_resident && NT == 1 ? (size_t)WARPS * STAGES * 8 * SLICE * 2 : 0;
     const size_t shared = rings + token_ring + sums + (use_resident ? resident : 0);
     cudaError_t err;
