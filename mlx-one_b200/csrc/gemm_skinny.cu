@@ -11,19 +11,22 @@
 //     copies its slices of w asynchronously through a ring of its own in shared memory, and the
 //     ring runs on into the next tile, so the stream never drains inside the kernel;
 //   * slices are multiplied on tensor cores (mma m16n8k16: w is the 16-row operand, eight
-//     tokens the 8-column one); per tile the warps' partial sums are added in shared memory in
-//     a fixed order;
+//     tokens the 8-column one); per tile the warps' partial sums are added in shared memory by
+//     all threads, in a fixed tree that is the same for every number of tokens;
 //   * the copies of the first slices are issued before the kernel waits for its predecessor
 //     (griddep_wait), so weights already stream while the previous kernel finishes;
 //   * the activations are read after that wait: into shared memory once per block when the
-//     block has several tiles and they fit, else from L2 slice by slice, one slice ahead.
+//     block has several tiles and they fit (as they are, or as the RMSNorm of 32-bit rows, which
+//     the kernel then computes itself); else, up to 8 tokens, through the rings beside the
+//     weights; else from L2 slice by slice, two slices ahead.
 //
 // Within a 32-wide piece of K, thread t of a quad reads elements 8t..8t+7 of both operands
 // with one 16-byte load and feeds them to two mma instructions; the sum over K does not care
 // in which order the products are taken.
 //
 // Epilogues: store bfloat16 (+ bias); SwiGLU (the block also owns the 16 matching rows of the
-// "up" half and writes silu(gate) * up); add into the 32-bit residual stream; store float32;
+// "up" half and writes silu(gate) * up); add into the 32-bit residual stream (red.global.add, one
+// addition per address); store float32;
 // gated short convolution of a decode step (w = [B rows; C rows; x rows], the block owns the same
 // channels of all three and applies the convolution's single-token update, so that neither the
 // three projections nor a second kernel touch memory).
