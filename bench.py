@@ -10,7 +10,8 @@ chosen token fed to the next step on the device). ``e2e`` is the same through th
 entry point (``Engine.step``), token ids crossing the host in both directions every step.
 ``prefill`` is one 2,048-token prompt through the step function. ``roofline`` relates the
 decode step to the bytes it has to read: every weight once and the cache of the live
-requests. ``points`` holds decode at batch 1, 16, 32 and 64 and at contexts of 512 and 32,768.
+requests. ``points`` holds decode at batch 1, 16, 32 and 64, at contexts of 512 and 32,768, and
+for the LFM2-700M and LFM2-350M shapes.
 
 Two more workloads, each printing one JSON line of its own (the default line is unchanged):
 
@@ -992,6 +993,22 @@ def main() -> int:
     prefill_seconds = time_prefill(engine, PREFILL_TOKENS, 2, 3, seed=11)
     flops = model_flops(spec, PREFILL_TOKENS)
     products = None if args.skip_points else product_fractions(model, args.batch, peak)
+
+    if not args.skip_points:
+        # the two smaller shapes of the family at the default batch and context
+        import gc
+        del engine, model
+        gc.collect()
+        torch.cuda.empty_cache()
+        for label, shape in (("lfm2_700m", LFM2_700M), ("lfm2_350m", LFM2_350M)):
+            small = build_engine(shape, shape["num_hidden_layers"], args.batch, args.context,
+                                 warmup + args.steps, name=f"random-{label}")
+            small.model.ops.set_dependent_launches(bool(args.dependent_launches))
+            s, _, _, _ = time_decode(small, args.batch, args.context, warmup, args.steps, seed=21)
+            points[f"decode_b{args.batch}_{label}"] = round(args.batch * args.steps / s, 1)
+            del small
+            gc.collect()
+            torch.cuda.empty_cache()
 
     line = {
         "metric": f"decode tok/s at batch {args.batch} (LFM2-1.2B shape, bf16, context {args.context})",
