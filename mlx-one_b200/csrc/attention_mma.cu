@@ -826,8 +826,24 @@ __global__ void attention_merge_kernel(const float* __restrict__ partial, bf16* 
     const int lane = threadIdx.x & 31;
     if (item >= items) return;
     const float* base = partial + (size_t)item * splits * ROW_FLOATS;
-    float top = -INFINITY;
-    for (int s = lane; s < splits; s += 32) top = fmaxf(top, base[(size_t)s * ROW_FLOATS + HD]);
+    // the first HELD splits' values are asked for together with the maxima and sums, before
+    // anything is computed from them: one trip to L2 for all of it, not one after the other
+    constexpr int HELD = 16;
+    float held[HELD][MINE];
+#pragma unroll
+    for (int j = 0; j < HELD; ++j)
+#pragma unroll
+        for (int i = 0; i < MINE; ++i) {
+            const int d = lane + 32 * i;
+            held[j][i] = (j < splits && d < HD) ? base[(size_t)j * ROW_FLOATS + d] : 0.f;
+        }
+    float its_top = -INFINITY, its_sum = 0.f;          // of split `lane`
+    if (lane < splits) {
+        its_top = base[(size_t)lane * ROW_FLOATS + HD];
+        its_sum = base[(size_t)lane * ROW_FLOATS + HD + 1];
+    }
+    float top = its_top;
+    for (int s = lane + 32; s < splits; s += 32) top = fmaxf(top, base[(size_t)s * ROW_FLOATS + HD]);
     top = warp_max(top);
     float sum = 0.f;
     float value[MINE];
@@ -838,12 +854,22 @@ __global__ void attention_merge_kernel(const float* __restrict__ partial, bf16* 
         float weight = 0.f;
         if (s0 + lane < splits) {
             const float* src = base + (size_t)(s0 + lane) * ROW_FLOATS;
-            weight = src[HD] == -INFINITY ? 0.f : fast_exp2(src[HD] - top);
-            sum += src[HD + 1] * weight;
+            const float t = s0 == 0 ? its_top : src[HD];
+            weight = t == -INFINITY ? 0.f : fast_exp2(t - top);
+            sum += (s0 == 0 ? its_sum : src[HD + 1]) * weight;
         }
         const int count = min(32, splits - s0);
+        if (s0 == 0) {
+#pragma unroll
+            for (int j = 0; j < HELD; ++j) {
+                if (j >= count) break;
+                const float w = __shfl_sync(0xffffffffu, weight, j);
+#pragma unroll
+                for (int i = 0; i < MINE; ++i) value[i] = fmaf(held[j][i], w, value[i]);
+            }
+        }
 #pragma unroll 8
-        for (int j = 0; j < count; ++j) {
+        for (int j = s0 == 0 ? HELD : 0; j < count; ++j) {
             const float w = __shfl_sync(0xffffffffu, weight, j);
             const float* src = base + (size_t)(s0 + j) * ROW_FLOATS;
 #pragma unroll
