@@ -17,6 +17,23 @@ __global__ void embedding_kernel(const int* __restrict__ ids, const T* __restric
     }
     const T* row = table + (size_t)id * hidden;
     float* dst = out + (size_t)t * hidden;
+    if (sizeof(T) == 2 && hidden % 8 == 0 && (reinterpret_cast<uintptr_t>(table) & 15) == 0 &&
+        (reinterpret_cast<uintptr_t>(out) & 15) == 0) {
+        // eight values a load: the whole row is asked for at once (it comes from DRAM, and a
+        // decode step begins with this kernel)
+        for (int c = threadIdx.x * 8; c < hidden; c += blockDim.x * 8) {
+            const uint4 raw = *reinterpret_cast<const uint4*>(row + c);
+            const __nv_bfloat162* pairs = reinterpret_cast<const __nv_bfloat162*>(&raw);
+            float4 lo, hi;
+            lo.x = __low2float(pairs[0]); lo.y = __high2float(pairs[0]);
+            lo.z = __low2float(pairs[1]); lo.w = __high2float(pairs[1]);
+            hi.x = __low2float(pairs[2]); hi.y = __high2float(pairs[2]);
+            hi.z = __low2float(pairs[3]); hi.w = __high2float(pairs[3]);
+            *reinterpret_cast<float4*>(dst + c) = lo;
+            *reinterpret_cast<float4*>(dst + c + 4) = hi;
+        }
+        return;
+    }
     for (int c = threadIdx.x; c < hidden; c += blockDim.x) dst[c] = to_float<T>(row[c]);
 }
 
