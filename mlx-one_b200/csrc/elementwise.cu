@@ -274,11 +274,19 @@ __global__ void gather_rows_kernel(const float* __restrict__ residual, const T* 
     griddep_wait();
     int src = rows[blockIdx.x];
     src = min(max(src, 0), tokens - 1);
-    for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
-        picked[(size_t)blockIdx.x * hidden + c] = residual[(size_t)src * hidden + c];
-        if (delta != nullptr)
-            picked_delta[(size_t)blockIdx.x * hidden + c] = delta[(size_t)src * hidden + c];
+    const float* from = residual + (size_t)src * hidden;
+    float* to = picked + (size_t)blockIdx.x * hidden;
+    if (hidden % 4 == 0 && (reinterpret_cast<uintptr_t>(residual) & 15) == 0 &&
+        (reinterpret_cast<uintptr_t>(picked) & 15) == 0) {
+        // 16 bytes a load, so that a row's loads are on their way together
+        for (int c = threadIdx.x * 4; c < hidden; c += blockDim.x * 4)
+            *reinterpret_cast<float4*>(to + c) = *reinterpret_cast<const float4*>(from + c);
+    } else {
+        for (int c = threadIdx.x; c < hidden; c += blockDim.x) to[c] = from[c];
     }
+    if (delta != nullptr)
+        for (int c = threadIdx.x; c < hidden; c += blockDim.x)
+            picked_delta[(size_t)blockIdx.x * hidden + c] = delta[(size_t)src * hidden + c];
 }
 
 MLXONE_API int mlxone_gather_rows(const float* residual, const void* delta, const int* rows,
@@ -302,6 +310,8 @@ MLXONE_API int mlxone_gather_rows(const float* residual, const void* delta, cons
 template <typename T>
 __global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int width,
                               long long total) {
+    griddep_launch();
+    griddep_wait();
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= total) return;
     const long long t = i / width;
@@ -311,18 +321,47 @@ __global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out
     out[i] = from_float<T>(gate / (1.f + expf(-gate)) * up);
 }
 
+// The same for bfloat16 with width % 8 == 0: eight neighbouring values a thread, 16-byte loads.
+__global__ void swiglu_wide_kernel(const __nv_bfloat16* __restrict__ gate_up,
+                                   __nv_bfloat16* __restrict__ out, int width, long long groups) {
+    griddep_launch();
+    griddep_wait();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= groups) return;
+    const int per_row = width / 8;
+    const long long t = i / per_row;
+    const int f = (int)(i - t * per_row) * 8;
+    const uint4 g = *reinterpret_cast<const uint4*>(gate_up + t * 2 * width + f);
+    const uint4 u = *reinterpret_cast<const uint4*>(gate_up + t * 2 * width + width + f);
+    const __nv_bfloat162* gp = reinterpret_cast<const __nv_bfloat162*>(&g);
+    const __nv_bfloat162* up = reinterpret_cast<const __nv_bfloat162*>(&u);
+    uint4 packed;
+    __nv_bfloat162* q = reinterpret_cast<__nv_bfloat162*>(&packed);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const float g0 = __low2float(gp[k]), g1 = __high2float(gp[k]);
+        q[k] = __floats2bfloat162_rn(g0 / (1.f + expf(-g0)) * __low2float(up[k]),
+                                     g1 / (1.f + expf(-g1)) * __high2float(up[k]));
+    }
+    *reinterpret_cast<uint4*>(out + t * width + f) = packed;
+}
+
 MLXONE_API int mlxone_swiglu(const void* gate_up, void* out, int rows, int width, int dtype,
                              cudaStream_t stream) {
     if (rows == 0) return 0;
     MLXONE_REQUIRE(rows > 0 && width > 0, "swiglu: bad sizes");
     const long long total = (long long)rows * width;
     const int blocks = ceil_div_host(total, 256);
-    if (dtype == MLXONE_BF16)
-        swiglu_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(
-            (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, width, total);
+    if (dtype == MLXONE_BF16 && width % 8 == 0 && (reinterpret_cast<uintptr_t>(gate_up) & 15) == 0 &&
+        (reinterpret_cast<uintptr_t>(out) & 15) == 0)
+        launch_kernel(swiglu_wide_kernel, dim3(ceil_div_host(total / 8, 256)), dim3(256), 0, stream,
+                      true, (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, width, total / 8);
+    else if (dtype == MLXONE_BF16)
+        launch_kernel(swiglu_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, true,
+                      (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, width, total);
     else
-        swiglu_kernel<float><<<blocks, 256, 0, stream>>>((const float*)gate_up, (float*)out,
-                                                        width, total);
+        launch_kernel(swiglu_kernel<float>, dim3(blocks), dim3(256), 0, stream, true,
+                      (const float*)gate_up, (float*)out, width, total);
     MLXONE_LAUNCH_CHECK("swiglu");
     return 0;
 }
