@@ -828,7 +828,7 @@ __global__ void attention_merge_kernel(const float* __restrict__ partial, bf16* 
     const float* base = partial + (size_t)item * splits * ROW_FLOATS;
     // the first HELD splits' values are asked for together with the maxima and sums, before
     // anything is computed from them: one trip to L2 for all of it, not one after the other
-    constexpr int HELD = 16;
+    constexpr int HELD = 32;
     float held[HELD][MINE];
 #pragma unroll
     for (int j = 0; j < HELD; ++j)
