@@ -51,6 +51,30 @@ def test_whole_decode_and_portions(models, name):
         assert_close(replay(runner, cache, steps)["p"], want, torch.float32, f"portions {sizes}")
 
 
+def test_a_step_that_wants_every_row_in_order_picks_none(models):
+    """Single tokens that all want their logits (a decode step): the step function hands the
+    output product every row as it is, without the row gather, and each request gets the logits
+    of its whole sequence's last position."""
+    folder, loaded, plain = models["A"]
+    config, _, page = CONFIGS["A"]
+    runner, cache = runner_for(loaded, page, 256)
+    requests = prompts(config["vocab_size"], (9, 14, 5), seed=12)
+    for i, tokens in enumerate(requests):
+        cache.open(i)
+        runner.step([StepEntry(i, tokens[:-1])])
+    picked = []
+    gather = loaded.model.ops.gather_rows
+    loaded.model.ops.gather_rows = lambda *a, **k: (picked.append(1), gather(*a, **k))[1]
+    try:
+        every = runner.step([StepEntry(i, [tokens[-1]], (0,)) for i, tokens in enumerate(requests)])
+        assert not picked
+    finally:
+        loaded.model.ops.gather_rows = gather
+    for i, tokens in enumerate(requests):
+        assert_close(every[i:i + 1], plain.logits(tokens)[-1:], torch.float32, f"request {i}")
+        cache.close(i)
+
+
 @pytest.mark.parametrize("name", list(CONFIGS))
 def test_mixed_batches_reuse_pages(models, name):
     folder, loaded, plain = models[name]
